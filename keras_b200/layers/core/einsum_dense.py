@@ -1,0 +1,339 @@
+"""``EinsumDense``: a dense layer over an einsum equation.
+
+Behaviour of keras/src/layers/core/einsum_dense.py: kernel/bias shapes are derived from the
+equation (:1700-1900), VarianceScaling initialisers receive explicit input/output axes
+(:165-199), LoRA, int8 and float8 modes.  Equations that are a plain contraction of trailing
+input axes with leading kernel axes lower to one GEMM without permute copies.
+"""
+
+import re
+import string
+
+import torch
+
+from keras_b200 import activations, constraints, initializers, ops, quantizers, regularizers
+from keras_b200.core.export_registry import keras_export
+from keras_b200.kernels import dispatch
+from keras_b200.layers.layer import Layer
+
+
+def analyze_einsum(equation, bias_axes, input_shape, output_shape):
+    """→ (kernel_shape, bias_shape, full_output_shape, kernel_input_axes, kernel_output_axes)."""
+    eq = equation.replace("...", "0")
+    left_elided = False
+    m = re.fullmatch(r"([a-zA-Z]+),([a-zA-Z]+)->([a-zA-Z]+)", eq)
+    if not m:
+        m = re.fullmatch(r"0([a-zA-Z]+),([a-zA-Z]+)->0([a-zA-Z]+)", eq)
+        left_elided = bool(m)
+    if not m:
+        m = re.fullmatch(r"([a-zA-Z]{2,})0,([a-zA-Z]+)->([a-zA-Z]+)0", eq)
+    if not m:
+        raise ValueError(
+            f"Invalid einsum equation '{equation}'. Equations must be in the form [X],[Y]->[Z], "
+            "...[X],[Y]->...[Z], or [X]...,[Y]->[Z]...."
+        )
+    in_spec, w_spec, out_spec = m.group(1), m.group(2), m.group(3)
+    elided = len(input_shape) - len(in_spec)
+    full_out = [input_shape[0]] + ([output_shape] if isinstance(output_shape, int) else list(output_shape))
+    if elided > 0 and left_elided:
+        for i in range(1, elided):
+            full_out.insert(1, input_shape[i])
+    elif elided > 0:
+        full_out.extend(input_shape[len(input_shape) - elided:])
+    if left_elided:
+        in_pos = {c: (i + elided) - len(input_shape) for i, c in enumerate(in_spec)}
+        out_pos = {c: i + elided for i, c in enumerate(out_spec)}
+    else:
+        in_pos = {c: i for i, c in enumerate(in_spec)}
+        out_pos = {c: i for i, c in enumerate(out_spec)}
+    for c in in_spec:
+        if c in out_pos:
+            o = full_out[out_pos[c]]
+            if o is not None and o != input_shape[in_pos[c]]:
+                raise ValueError(
+                    f"Input shape and output shape do not match at shared dimension '{c}'. Input shape is "
+                    f"{input_shape[in_pos[c]]}, and output shape is {o}."
+                )
+    for c in out_spec:
+        if c not in in_spec and c not in w_spec:
+            raise ValueError(
+                f"Dimension '{c}' was specified in the output '{out_spec}' but has no corresponding dim in the "
+                f"input spec '{in_spec}' or weight spec '{out_spec}'"
+            )
+    kernel_shape, in_axes, out_axes = [], [], []
+    for i, c in enumerate(w_spec):
+        if c in out_pos:
+            kernel_shape.append(full_out[out_pos[c]])
+            out_axes.append(i)
+        elif c in in_pos:
+            kernel_shape.append(input_shape[in_pos[c]])
+            in_axes.append(i)
+        else:
+            raise ValueError(
+                f"Weight dimension '{c}' did not have a match in either the input spec '{in_spec}' or the output "
+                f"spec '{out_spec}'. For this layer, the weight must be fully specified."
+            )
+    bias_shape = None
+    if bias_axes is not None:
+        shift = elided if left_elided else 0
+        sizes = {c: full_out[i + shift] for i, c in enumerate(out_spec)}
+        for c in bias_axes:
+            if c not in out_spec:
+                raise ValueError(f"Bias dimension '{c}' was requested, but is not part of the output spec '{out_spec}'")
+        first = min(out_spec.find(c) for c in bias_axes)
+        bias_shape = [sizes[c] if c in bias_axes else 1 for c in out_spec[first:]]
+        if not left_elided:
+            bias_shape.extend([1] * elided)
+    return kernel_shape, bias_shape, full_out, in_axes, out_axes
+
+
+def _gemm_plan(equation):
+    """Detect ``<batch...><k...>,<k...><n...>-><batch...><n...>``: one GEMM, no permutes."""
+    eq = equation.replace("...", "")
+    m = re.fullmatch(r"([a-zA-Z]+),([a-zA-Z]+)->([a-zA-Z]+)", eq)
+    if not m:
+        return None
+    a, w, o = m.groups()
+    k = [c for c in w if c in a and c not in o]
+    n = [c for c in w if c not in a]
+    if not k or not n or w != "".join(k) + "".join(n):
+        return None
+    if not a.endswith("".join(k)):
+        return None
+    batch = a[: len(a) - len(k)]
+    if o != batch + "".join(n):
+        return None
+    if any(c in w for c in batch):
+        return None
+    return len(k), len(n)
+
+
+@keras_export("keras.layers.EinsumDense")
+class EinsumDense(Layer):
+    def __init__(self, equation, output_shape, activation=None, bias_axes=None, kernel_initializer="glorot_uniform",
+                 bias_initializer="zeros", kernel_regularizer=None, bias_regularizer=None, kernel_constraint=None,
+                 bias_constraint=None, lora_rank=None, lora_alpha=None, gptq_unpacked_column_size=None,
+                 quantization_config=None, **kwargs):
+        super().__init__(**kwargs)
+        self.equation = equation
+        self.partial_output_shape = (output_shape,) if isinstance(output_shape, int) else tuple(output_shape)
+        self.bias_axes = bias_axes
+        self.activation = activations.get(activation)
+        self.kernel_initializer = initializers.get(kernel_initializer)
+        self.bias_initializer = initializers.get(bias_initializer)
+        self.kernel_regularizer = regularizers.get(kernel_regularizer)
+        self.bias_regularizer = regularizers.get(bias_regularizer)
+        self.kernel_constraint = constraints.get(kernel_constraint)
+        self.bias_constraint = constraints.get(bias_constraint)
+        self.lora_rank = lora_rank
+        self.lora_alpha = lora_alpha if lora_alpha is not None else lora_rank
+        self.lora_enabled = False
+        self.quantization_config = quantization_config
+        self._is_quantized = False
+        self._gemm = _gemm_plan(equation)
+
+    def build(self, input_shape):
+        kshape, bshape, full_out, in_axes, out_axes = analyze_einsum(self.equation, self.bias_axes, input_shape, self.partial_output_shape)
+        self._kernel_shape = tuple(kshape)
+        self.full_output_shape = tuple(full_out)
+        self._kernel_in_axes, self._kernel_out_axes = in_axes, out_axes
+        if self.quantization_mode:
+            self.quantized_build(self._kernel_shape, mode=self.quantization_mode)
+        if self.quantization_mode != "int8":
+            init = self.kernel_initializer
+            if isinstance(init, initializers.VarianceScaling):
+                base = init
+
+                def init(shape, dtype=None, _b=base):
+                    return _b(shape, dtype=dtype, input_axes=in_axes, output_axes=out_axes)
+
+            self._kernel = self.add_weight(name="kernel", shape=self._kernel_shape, initializer=init, regularizer=self.kernel_regularizer,
+                                           constraint=self.kernel_constraint, dtype=self.dtype, trainable=True)
+        if bshape is not None:
+            self.bias = self.add_weight(name="bias", shape=tuple(bshape), initializer=self.bias_initializer, regularizer=self.bias_regularizer,
+                                        constraint=self.bias_constraint, dtype=self.dtype, trainable=True)
+        else:
+            self.bias = None
+        self.built = True
+        if self.lora_rank:
+            self.enable_lora(self.lora_rank, lora_alpha=self.lora_alpha)
+
+    @property
+    def kernel(self):
+        if not self.built:
+            raise AttributeError("You must build the layer before accessing `kernel`.")
+        if self.lora_enabled:
+            return ops.add(self._kernel.value, (self.lora_alpha / self.lora_rank) * ops.matmul(self.lora_kernel_a.value, self.lora_kernel_b.value))
+        return self._kernel
+
+    def compute_output_shape(self, _):
+        return self.full_output_shape
+
+    def _contract(self, inputs, kernel):
+        """einsum(equation, inputs, kernel) lowered to a single GEMM when the equation allows."""
+        plan = self._gemm
+        if plan is not None and isinstance(inputs, torch.Tensor):
+            nk, nn = plan
+            kv = kernel.value if hasattr(kernel, "value") else kernel
+            kdim = 1
+            for d in kv.shape[:nk]:
+                kdim *= d
+            lead = inputs.shape[: inputs.ndim - nk]
+            x2 = inputs.reshape(tuple(lead) + (kdim,))
+            w2 = kv.reshape(kdim, -1)
+            out = ops.matmul(x2, w2)
+            return out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+        return ops.einsum(self.equation, inputs, kernel)
+
+    def call(self, inputs, training=None):
+        x = self._contract(inputs, self.kernel)
+        if self.bias is not None:
+            x = ops.add(x, self.bias)
+        if self.activation is not None and self.activation is not activations.linear:
+            x = self.activation(x)
+        return x
+
+    def enable_lora(self, rank, lora_alpha=None, a_initializer="he_uniform", b_initializer="zeros"):
+        if self.kernel_constraint:
+            raise ValueError("Lora is incompatible with kernel constraints. In order to enable lora on this layer, remove the `kernel_constraint` argument.")
+        if not self.built:
+            raise ValueError("Cannot enable lora on a layer that isn't yet built.")
+        if self.lora_enabled:
+            raise ValueError("lora is already enabled. This can only be done once per layer.")
+        self._tracker_unlock()
+        self.lora_kernel_a = self.add_weight(name="lora_kernel_a", shape=self._kernel_shape[:-1] + (rank,), initializer=initializers.get(a_initializer), regularizer=self.kernel_regularizer)
+        self.lora_kernel_b = self.add_weight(name="lora_kernel_b", shape=(rank, self._kernel_shape[-1]), initializer=initializers.get(b_initializer), regularizer=self.kernel_regularizer)
+        self._kernel.trainable = False
+        self._lock_state()
+        self._invalidate()
+        self.lora_enabled = True
+        self.lora_rank = rank
+        self.lora_alpha = lora_alpha if lora_alpha is not None else rank
+
+    # -- persistence ---------------------------------------------------------------------
+    @property
+    def variable_serialization_spec(self):
+        return {
+            None: ["kernel", "bias"],
+            "int8": ["kernel", "bias", "kernel_scale"],
+            "float8": ["kernel", "bias", "inputs_scale", "inputs_amax_history", "kernel_scale", "kernel_amax_history",
+                       "outputs_grad_scale", "outputs_grad_amax_history"],
+        }
+
+    def _saved_names(self):
+        mode = self.quantization_mode if self._is_quantized else None
+        if mode not in self.variable_serialization_spec:
+            raise self._quantization_mode_error(mode)
+        return [n for n in self.variable_serialization_spec[mode] if not (n == "bias" and self.bias is None)]
+
+    def save_own_variables(self, store):
+        if not self.built:
+            return
+        mode = self.quantization_mode if self._is_quantized else None
+        kernel, scale = self._kernel, getattr(self, "kernel_scale", None)
+        if self.lora_enabled:
+            delta = (self.lora_alpha / self.lora_rank) * torch.matmul(self.lora_kernel_a._value, self.lora_kernel_b._value)
+            if mode == "int8":
+                full = self._kernel._value.to(torch.float32) / self.kernel_scale._value + delta
+                kernel, scale = quantizers.abs_max_quantize(full, axis=self._kernel_in_axes, to_numpy=False)
+            else:
+                kernel = self._kernel._value + delta.to(self._kernel._value.dtype)
+        for i, name in enumerate(self._saved_names()):
+            if name == "kernel":
+                store[str(i)] = kernel
+            elif name == "kernel_scale" and mode == "int8":
+                store[str(i)] = scale
+            else:
+                store[str(i)] = getattr(self, name)
+
+    def load_own_variables(self, store):
+        if not self.built:
+            return
+        names = self._saved_names()
+        if len(store.keys()) != len(names):
+            raise ValueError(f"Layer '{self.name}' expected {len(names)} variables, but received {len(store.keys())} variables during loading. Expected: {names}")
+        for i, name in enumerate(names):
+            target = self._kernel if name == "kernel" else getattr(self, name)
+            value = store[str(i)]
+            if name == "kernel_scale" and tuple(value.shape) != tuple(target.shape):
+                value = torch.as_tensor(value).reshape(tuple(target.shape))
+            target.assign(value)
+        if self.lora_enabled:
+            self.lora_kernel_a.assign(torch.zeros_like(self.lora_kernel_a._value))
+            self.lora_kernel_b.assign(torch.zeros_like(self.lora_kernel_b._value))
+
+    def get_config(self):
+        cfg = {
+            "output_shape": self.partial_output_shape, "equation": self.equation, "activation": activations.serialize(self.activation),
+            "bias_axes": self.bias_axes, "kernel_initializer": initializers.serialize(self.kernel_initializer),
+            "bias_initializer": initializers.serialize(self.bias_initializer), "kernel_regularizer": regularizers.serialize(self.kernel_regularizer),
+            "bias_regularizer": regularizers.serialize(self.bias_regularizer), "activity_regularizer": regularizers.serialize(self.activity_regularizer),
+            "kernel_constraint": constraints.serialize(self.kernel_constraint), "bias_constraint": constraints.serialize(self.bias_constraint),
+        }
+        if self.lora_rank:
+            cfg["lora_rank"] = self.lora_rank
+            cfg["lora_alpha"] = self.lora_alpha
+        return {**super().get_config(), **cfg}
+
+    # -- quantization --------------------------------------------------------------------
+    def quantized_build(self, kernel_shape, mode, config=None):
+        if mode == "int8":
+            self._kernel = self.add_weight(name="kernel", shape=kernel_shape, initializer="zeros", dtype="int8", trainable=False)
+            scale_shape = tuple(1 if i in self._kernel_in_axes else d for i, d in enumerate(kernel_shape))
+            self.kernel_scale = self.add_weight(name="kernel_scale", shape=scale_shape, initializer="ones", trainable=False)
+        elif mode == "float8":
+            quantizers.float8_build(self)
+        else:
+            raise self._quantization_mode_error(mode)
+        self._is_quantized = True
+
+    def _finish(self, x, inputs):
+        if self.lora_enabled:
+            lora = ops.einsum(self.equation, inputs, ops.matmul(self.lora_kernel_a, self.lora_kernel_b))
+            x = ops.add(x, (self.lora_alpha / self.lora_rank) * lora)
+        if self.bias is not None:
+            x = ops.add(x, ops.cast(self.bias, x.dtype))
+        if self.activation is not None:
+            x = self.activation(x)
+        return x
+
+    def _int8_call(self, inputs, training=None):
+        # Weight-only path: de-quantise the kernel, contract in the compute dtype (the reference's
+        # torch backend does the same, keras/src/layers/core/einsum_dense.py:1086-1098).
+        kernel = self._kernel.value.to(inputs.dtype) / self.kernel_scale.value.to(inputs.dtype)
+        return self._finish(self._contract(inputs, kernel.detach()), inputs)
+
+    def _float8_call(self, inputs, training=None):
+        if self.lora_enabled:
+            raise NotImplementedError("Currently, `_float8_call` doesn't support LoRA")
+        plan = self._gemm
+        kv = self._kernel.value
+        if plan is not None:
+            nk = plan[0]
+            kdim = 1
+            for d in kv.shape[:nk]:
+                kdim *= d
+            lead = inputs.shape[: inputs.ndim - nk]
+            out = quantizers.float8_matmul(self, inputs.reshape(tuple(lead) + (kdim,)), kv.reshape(kdim, -1), None, training)
+            out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+        else:
+            out = quantizers.float8_matmul(self, inputs, kv, self.equation, training)
+        return self._finish(out, inputs)
+
+    def quantize(self, mode=None, type_check=True, config=None):
+        if type_check and type(self) is not EinsumDense:
+            raise self._not_implemented_error(self.quantize)
+        self.quantization_config = config
+        kernel_shape = tuple(self._kernel.shape)
+        if mode == "int8":
+            q, scale = quantizers.abs_max_quantize(self._kernel._value, axis=tuple(self._kernel_in_axes), to_numpy=False)
+            self._untrack_variable(self._kernel)
+            del self._kernel
+            self.quantized_build(kernel_shape, mode)
+            self._kernel.assign(q)
+            self.kernel_scale.assign(scale)
+        elif mode == "float8":
+            self.quantized_build(kernel_shape, mode)
+        else:
+            raise self._quantization_mode_error(mode)
+        quantizers.set_quantized_policy(self, mode)

@@ -1,0 +1,531 @@
+"""``Functional``: a ``Model`` defined by a DAG of layers between ``Input`` tensors and outputs.
+
+Behaviour of keras/src/models/functional.py:27-940: input standardisation (:256-373), config
+schema with ``inbound_nodes`` as serialised ``args``/``kwargs`` (:430-504), two-pass node replay
+on load (:507-687).
+"""
+
+import copy
+import inspect
+import warnings
+
+import torch
+
+from keras_b200 import ops, tree
+from keras_b200.core.dtypes import standardize_dtype
+from keras_b200.core.keras_tensor import KerasTensor
+from keras_b200.layers.core.input_layer import Input, InputLayer
+from keras_b200.layers.input_spec import InputSpec
+from keras_b200.layers.layer import Layer
+from keras_b200.models.model import Model
+from keras_b200.ops.function import Function, make_node_key
+from keras_b200.ops.node import KerasHistory, Node
+from keras_b200.ops.operation import Operation
+
+
+class Functional(Function, Model):
+    def __new__(cls, *args, **kwargs):
+        return Model.__new__(cls)
+
+    def __init__(self, inputs, outputs, name=None, **kwargs):
+        if isinstance(inputs, dict):
+            for k, v in inputs.items():
+                if isinstance(v, KerasTensor) and k != v.name:
+                    warnings.warn(
+                        "When providing `inputs` as a dict, all keys in the dict must match the names of the "
+                        f"corresponding tensors. Received key '{k}' mapping to value {v} which has name '{v.name}'. "
+                        "Change the tensor name to '{k}' (via `Input(..., name='{k}')`)"
+                    )
+        trainable = kwargs.pop("trainable", None)
+        flat_inputs = tree.flatten(inputs)
+        flat_outputs = tree.flatten(outputs)
+        for x in flat_inputs:
+            if not isinstance(x, KerasTensor):
+                raise ValueError(f"All `inputs` values must be KerasTensors. Received: inputs={inputs} including invalid value {x} of type {type(x)}")
+        for x in flat_outputs:
+            if not isinstance(x, KerasTensor):
+                raise ValueError(f"All `outputs` values must be KerasTensors. Received: outputs={outputs} including invalid value {x} of type {type(x)}")
+        if not all(is_input_keras_tensor(t) for t in flat_inputs):
+            inputs, outputs = clone_graph_nodes(inputs, outputs)
+        Layer.__init__(self, name=name, **kwargs)
+        Function.__init__(self, inputs, outputs, name=self.name)
+        if trainable is not None:
+            self.trainable = trainable
+        self._layers = self.layers
+        self.build(None)
+        self._convert_input_args = False
+        self._allow_non_tensor_positional_args = True
+        output_layers = [x._keras_history[0] for x in self.outputs]
+        self.output_names = [x.name for x in output_layers]
+        self._init_trainer_state()
+
+    def _lock_state(self):
+        pass
+
+    def _obj_type(self):
+        return "Functional"
+
+    @property
+    def layers(self):
+        return [op for op in self._operations if isinstance(op, Layer)]
+
+    @layers.setter
+    def layers(self, _):
+        raise AttributeError("`Model.layers` attribute is reserved and should not be used. Please use another name.")
+
+    def call(self, inputs, training=None, mask=None, **kwargs):
+        inputs = self._standardize_inputs(inputs)
+        if mask is None:
+            masks = [None] * len(inputs)
+        else:
+            masks = tree.flatten(mask)
+            for x, m in zip(inputs, masks):
+                if m is not None:
+                    try:
+                        x._keras_mask = m
+                    except AttributeError:
+                        pass
+        outputs = self._run_through_graph(inputs, operation_fn=lambda op: operation_fn(op, training=training, **kwargs))
+        return unpack_singleton(outputs)
+
+    def compute_output_spec(self, inputs, training=None, mask=None):
+        return Function.compute_output_spec(self, inputs)
+
+    def compute_output_shape(self, input_shape):
+        return Function.compute_output_shape(self, input_shape)
+
+    def build(self, input_shape):
+        self.built = True
+
+    @property
+    def input_shape(self):
+        shapes = tree.map_structure(lambda x: x.shape, self.inputs)
+        if isinstance(shapes, list) and len(shapes) == 1:
+            return shapes[0]
+        return shapes
+
+    @property
+    def output_shape(self):
+        shapes = tree.map_structure(lambda x: x.shape, self.outputs)
+        if isinstance(shapes, list) and len(shapes) == 1:
+            return shapes[0]
+        return shapes
+
+    def _assert_input_compatibility(self, *args):
+        return Function._assert_input_compatibility(self, *args)
+
+    def _maybe_warn_inputs_struct_mismatch(self, inputs, raise_exception=False):
+        try:
+            tree.assert_same_structure(tree.lists_to_tuples(inputs), tree.lists_to_tuples(self._inputs_struct))
+        except Exception:
+            model_struct = tree.map_structure(lambda x: x.name, self._inputs_struct)
+            in_struct = tree.map_structure(lambda x: f"Tensor(shape={tuple(x.shape)})" if hasattr(x, "shape") else str(x), inputs)
+            msg = f"The structure of `inputs` doesn't match the expected structure.\nExpected: {model_struct}\nReceived: inputs={in_struct}"
+            if raise_exception:
+                raise ValueError(msg)
+            warnings.warn(msg)
+
+    def _convert_inputs_to_tensors(self, flat_inputs):
+        out = []
+        for x, ref in zip(flat_inputs, self._inputs):
+            if x is None:
+                out.append(None)
+            else:
+                out.append(ops.convert_to_tensor(x, dtype=ref.dtype) if not isinstance(x, KerasTensor) else x)
+        return out
+
+    def _adjust_input_rank(self, flat_inputs):
+        adjusted = []
+        for x, ref in zip(flat_inputs, self._inputs):
+            if x is None:
+                adjusted.append(x)
+                continue
+            x_rank, ref_rank = len(x.shape), len(ref.shape)
+            if x_rank == ref_rank:
+                adjusted.append(x)
+            elif x_rank == ref_rank + 1 and x.shape[-1] == 1:
+                adjusted.append(ops.squeeze(x, axis=-1))
+            elif x_rank == ref_rank - 1 and ref.shape[-1] == 1:
+                adjusted.append(ops.expand_dims(x, axis=-1))
+            else:
+                raise ValueError(f"Invalid input shape for input {x}. Expected shape {ref.shape}, but input has incompatible shape {tuple(x.shape)}")
+        for i, x in enumerate(flat_inputs):
+            m = getattr(x, "_keras_mask", None)
+            if m is not None and adjusted[i] is not x:
+                try:
+                    adjusted[i]._keras_mask = m
+                except AttributeError:
+                    pass
+        return adjusted
+
+    def _standardize_inputs(self, inputs):
+        raise_exception = False
+        if isinstance(self._inputs_struct, list) and len(self._inputs_struct) == 1 and isinstance(inputs, (torch.Tensor, KerasTensor)):
+            inputs = [inputs]
+        elif isinstance(inputs, dict) and not isinstance(self._inputs_struct, dict):
+            if hasattr(self._inputs_struct, "__len__") and all(isinstance(i, KerasTensor) for i in self._inputs_struct):
+                expected = set(i.name for i in self._inputs_struct)
+                if expected.issubset(inputs.keys()):
+                    inputs = [inputs[i.name] for i in self._inputs_struct]
+                else:
+                    raise_exception = True
+            elif isinstance(self._inputs_struct, KerasTensor):
+                if self._inputs_struct.name in inputs:
+                    inputs = [inputs[self._inputs_struct.name]]
+                else:
+                    raise_exception = True
+            else:
+                raise_exception = True
+        if isinstance(self._inputs_struct, dict) and not isinstance(inputs, dict) and list(self._inputs_struct.keys()) != sorted(self._inputs_struct.keys()):
+            raise_exception = True
+        if isinstance(inputs, dict) and isinstance(self._inputs_struct, dict):
+            flat = [inputs[k] for k in sorted(self._inputs_struct.keys())] if set(self._inputs_struct).issubset(inputs) else tree.flatten(inputs)
+            if len(flat) != len(self._inputs):
+                self._maybe_warn_inputs_struct_mismatch(inputs, raise_exception=True)
+        else:
+            flat = tree.flatten(inputs)
+            if len(flat) != len(self._inputs) or raise_exception:
+                self._maybe_warn_inputs_struct_mismatch(inputs, raise_exception=True)
+        flat = self._convert_inputs_to_tensors(flat)
+        return self._adjust_input_rank(flat)
+
+    @property
+    def input(self):
+        return self._inputs_struct
+
+    @property
+    def output(self):
+        return self._outputs_struct
+
+    def add_loss(self, loss):
+        raise NotImplementedError
+
+    @property
+    def input_spec(self):
+        if hasattr(self, "_manual_input_spec"):
+            return self._manual_input_spec
+
+        def shape_with_no_batch_size(x):
+            x = list(x)
+            if x:
+                x[0] = None
+            return tuple(x)
+
+        def make_spec_for_tensor(x, name=None):
+            optional = False
+            hist = x._keras_history
+            if isinstance(hist[0], InputLayer):
+                if hist[0].optional:
+                    optional = True
+            return InputSpec(shape=shape_with_no_batch_size(x.shape), allow_last_axis_squeeze=True, name=x._keras_history[0].name if name is None else name, optional=optional)
+
+        if isinstance(self._inputs_struct, dict):
+            if all(isinstance(x, KerasTensor) for x in self._inputs_struct.values()):
+                names = sorted(self._inputs_struct.keys())
+                return [make_spec_for_tensor(self._inputs_struct[n], name=n) for n in names]
+            return None
+        return [make_spec_for_tensor(x) for x in self.inputs]
+
+    @input_spec.setter
+    def input_spec(self, value):
+        self._manual_input_spec = value
+
+    # -- config --------------------------------------------------------------------------
+    def get_config(self):
+        from keras_b200.saving import serialization_lib
+
+        if not functional_like_constructor(self.__class__):
+            return Model.get_config(self)
+        config = {"name": self.name, "trainable": self.trainable}
+        node_reindexing = {}
+        for operation in self.operations:
+            kept = 0
+            for i, node in enumerate(operation._inbound_nodes):
+                key = make_node_key(operation, i)
+                if key in self._nodes:
+                    node_reindexing[key] = kept
+                    kept += 1
+        layer_configs = []
+        for operation in self.operations:
+            filtered = []
+            for i, node in enumerate(operation._inbound_nodes):
+                key = make_node_key(operation, i)
+                if key in self._nodes:
+                    node_data = serialize_node(node, own_nodes=self._nodes)
+                    if node_data is not None:
+                        filtered.append(node_data)
+            layer_config = serialization_lib.serialize_keras_object(operation)
+            layer_config["name"] = operation.name
+            layer_config["inbound_nodes"] = filtered
+            layer_configs.append(layer_config)
+        config["layers"] = layer_configs
+
+        def get_tensor_config(tensor):
+            operation, node_index, tensor_index = tensor._keras_history
+            key = make_node_key(operation, node_index)
+            assert key in self._nodes
+            return [operation.name, node_reindexing[key], tensor_index]
+
+        def map_tensors(tensors):
+            if isinstance(tensors, KerasTensor):
+                return [get_tensor_config(tensors)]
+            return tree.map_structure(lambda t: get_tensor_config(t) if isinstance(t, KerasTensor) else t, tensors)
+
+        config["input_layers"] = map_tensors(self._inputs_struct)
+        config["output_layers"] = map_tensors(self._outputs_struct)
+        return copy.deepcopy(config)
+
+
+def functional_from_config(cls, config, custom_objects=None):
+    from keras_b200.saving import serialization_lib
+
+    created_layers = {}
+    unprocessed_nodes = {}
+
+    def add_unprocessed_node(layer, node_data):
+        unprocessed_nodes.setdefault(layer, []).append(node_data)
+
+    def process_node(layer, node_data):
+        args, kwargs = deserialize_node(node_data, created_layers)
+        layer(*args, **kwargs)
+
+    def process_layer(layer_data):
+        layer_name = layer_data["name"]
+        if "module" not in layer_data:
+            layer = serialization_lib.deserialize_keras_object(layer_data, custom_objects=custom_objects) if False else _legacy_layer(layer_data, custom_objects)
+        else:
+            layer = serialization_lib.deserialize_keras_object(layer_data, custom_objects=custom_objects)
+        if not isinstance(layer, Operation):
+            raise ValueError(f"Unexpected object from deserialization, expected a layer or operation, got a {type(layer)}")
+        created_layers[layer_name] = layer
+        for node_data in layer_data["inbound_nodes"]:
+            add_unprocessed_node(layer, node_data)
+
+    functional_config = {}
+    for key in ["layers", "input_layers", "output_layers"]:
+        functional_config[key] = config.pop(key)
+    for key in ["name", "trainable"]:
+        if key in config:
+            functional_config[key] = config.pop(key)
+        else:
+            functional_config[key] = None
+
+    for layer_data in functional_config["layers"]:
+        process_layer(layer_data)
+
+    while unprocessed_nodes:
+        progressed = False
+        for layer_data in functional_config["layers"]:
+            layer = created_layers[layer_data["name"]]
+            if layer in unprocessed_nodes:
+                node_data_list = unprocessed_nodes[layer]
+                node_index = 0
+                while node_index < len(node_data_list):
+                    node_data = node_data_list[node_index]
+                    try:
+                        process_node(layer, node_data)
+                        progressed = True
+                    except IndexError:
+                        break
+                    node_index += 1
+                if node_index < len(node_data_list):
+                    unprocessed_nodes[layer] = node_data_list[node_index:]
+                else:
+                    del unprocessed_nodes[layer]
+        if not progressed and unprocessed_nodes:
+            raise ValueError("Could not rebuild the model graph from its config: some nodes depend on tensors that are never produced.")
+
+    name = functional_config["name"]
+    trainable = functional_config["trainable"]
+
+    def get_tensor(layer_name, node_index, tensor_index):
+        assert layer_name in created_layers
+        layer = created_layers[layer_name]
+        if isinstance(layer, Functional):
+            node_index -= 1
+        layer_output_tensors = layer._inbound_nodes[node_index].output_tensors
+        return layer_output_tensors[tensor_index]
+
+    def map_tensors(tensors):
+        if isinstance(tensors, list) and len(tensors) == 3 and isinstance(tensors[0], str):
+            return get_tensor(*tensors)
+        if isinstance(tensors, dict):
+            return {k: map_tensors(v) for k, v in tensors.items()}
+        if isinstance(tensors, tuple):
+            return tuple(map_tensors(v) for v in tensors)
+        return [map_tensors(v) for v in tensors]
+
+    input_tensors = map_tensors(functional_config["input_layers"])
+    output_tensors = map_tensors(functional_config["output_layers"])
+    if isinstance(input_tensors, list) and len(input_tensors) == 1:
+        input_tensors = input_tensors[0]
+    if isinstance(output_tensors, list) and len(output_tensors) == 1:
+        output_tensors = output_tensors[0]
+    return cls(inputs=input_tensors, outputs=output_tensors, name=name, trainable=trainable, **config)
+
+
+def _legacy_layer(layer_data, custom_objects):
+    from keras_b200.legacy.saving import legacy_serialization
+
+    return legacy_serialization.deserialize_layer(layer_data, custom_objects=custom_objects)
+
+
+def operation_fn(operation, **call_context_args):
+    """Bind call-context args (``training`` …) the operation accepts."""
+
+    def call(*args, **kwargs):
+        if isinstance(operation, Layer):
+            plan = operation._plan
+            for name, value in call_context_args.items():
+                if value is not None and (name in plan.arg_names or plan.has_var_kw) and name not in kwargs:
+                    kwargs[name] = value
+        return operation(*args, **kwargs)
+
+    return call
+
+
+def functional_like_constructor(cls):
+    init_args = inspect.getfullargspec(cls.__init__).args[1:]
+    functional_init_args = inspect.getfullargspec(Functional.__init__).args[1:]
+    return init_args == functional_init_args
+
+
+def unpack_singleton(x):
+    if isinstance(x, (list, tuple)) and len(x) == 1:
+        return x[0]
+    return x
+
+
+def serialize_node(node, own_nodes=()):
+    from keras_b200.saving import serialization_lib
+
+    if not node.input_tensors:
+        return
+    def serialize_keras_tensor(x):
+        if isinstance(x, KerasTensor):
+            operation, node_index, tensor_index = x._keras_history
+            irrelevant = 0
+            for i, n in enumerate(operation._inbound_nodes[:node_index]):
+                if make_node_key(operation, i) not in own_nodes:
+                    irrelevant += 1
+            x._keras_history = KerasHistory(operation, node_index - irrelevant, tensor_index)
+            serialized = serialization_lib.serialize_keras_object(x)
+            x._keras_history = KerasHistory(operation, node_index, tensor_index)
+            return serialized
+        return x
+
+    args = tree.map_structure(serialize_keras_tensor, node.arguments.args)
+    kwargs = tree.map_structure(serialize_keras_tensor, node.arguments.kwargs)
+    return {"args": serialization_lib.serialize_keras_object(args), "kwargs": serialization_lib.serialize_keras_object(kwargs)}
+
+
+def deserialize_node(node_data, created_layers):
+    from keras_b200.saving import serialization_lib
+
+    if not node_data:
+        return [], {}
+    if isinstance(node_data, list):
+        # Keras 2 format: [[layer_name, node_index, tensor_index, kwargs], ...]
+        input_tensors = []
+        for input_data in node_data:
+            inbound_layer_name, inbound_node_index, inbound_tensor_index = input_data[0], input_data[1], input_data[2]
+            kwargs = input_data[3] if len(input_data) == 4 else {}
+            inbound_layer = created_layers[inbound_layer_name]
+            if len(inbound_layer._inbound_nodes) <= inbound_node_index:
+                raise IndexError("Layer node index out of bounds.")
+            inbound_node = inbound_layer._inbound_nodes[inbound_node_index]
+            input_tensors.append(inbound_node.output_tensors[inbound_tensor_index])
+        return [unpack_singleton(input_tensors)], kwargs
+
+    args = serialization_lib.deserialize_keras_object(node_data["args"])
+    kwargs = serialization_lib.deserialize_keras_object(node_data["kwargs"])
+
+    def convert_revived_tensor(x):
+        if isinstance(x, KerasTensor):
+            history = x._pre_serialization_keras_history
+            if history is None:
+                return x
+            layer = created_layers.get(history[0], None)
+            if layer is None:
+                raise ValueError(f"Unknown layer: {history[0]}")
+            inbound_node_index = history[1]
+            inbound_tensor_index = history[2]
+            if len(layer._inbound_nodes) <= inbound_node_index:
+                raise IndexError(f"Layer node index out of bounds.\ninbound_layer = {layer}\ninbound_layer._inbound_nodes = {layer._inbound_nodes}\ninbound_node_index = {inbound_node_index}")
+            inbound_node = layer._inbound_nodes[inbound_node_index]
+            return inbound_node.output_tensors[inbound_tensor_index]
+        return x
+
+    args = tree.map_structure(convert_revived_tensor, args)
+    kwargs = tree.map_structure(convert_revived_tensor, kwargs)
+    return args, kwargs
+
+
+def is_input_keras_tensor(x):
+    op, node_index, _ = x._keras_history
+    node = op._inbound_nodes[node_index]
+    return node.is_input
+
+
+def clone_single_keras_tensor(x):
+    return KerasTensor(shape=x.shape, dtype=x.dtype, sparse=x.sparse, name=f"{x.name}_clone")
+
+
+def clone_keras_tensors(tensors, kt_id_mapping):
+    def swap(x):
+        if not isinstance(x, KerasTensor):
+            return x
+        if id(x) in kt_id_mapping:
+            return kt_id_mapping[id(x)]
+        new_x = clone_single_keras_tensor(x)
+        kt_id_mapping[id(x)] = new_x
+        return new_x
+
+    return tree.map_structure(swap, tensors)
+
+
+def find_nodes_by_inputs_and_outputs(inputs, outputs):
+    from keras_b200.ops.function import _find_between
+
+    return _find_between(inputs, outputs)
+
+
+def clone_graph_nodes(inputs, outputs):
+    """Make a sub-graph defined by intermediate tensors self-contained by cloning its inputs."""
+    from keras_b200.ops.function import nodes_between
+
+    nodes_to_clone = nodes_between(inputs, outputs)
+    cloned_inputs = []
+    cloned_outputs = []
+    kt_id_mapping = {}
+    op_id_mapping = {}
+    for kt_input in tree.flatten(inputs):
+        if is_input_keras_tensor(kt_input):
+            cloned_inputs.append(kt_input)
+            kt_id_mapping[id(kt_input)] = kt_input
+        else:
+            cloned_input = Input(batch_shape=kt_input.shape, dtype=kt_input.dtype, sparse=kt_input.sparse, name=f"{kt_input.name}CLONE")
+            cloned_inputs.append(cloned_input)
+            kt_id_mapping[id(kt_input)] = cloned_input
+            op_id_mapping[id(kt_input._keras_history[0])] = cloned_input._keras_history[0]
+    cloned_inputs = tree.pack_sequence_as(inputs, cloned_inputs)
+    for kt_output in tree.flatten(outputs):
+        cpy = clone_single_keras_tensor(kt_output)
+        cpy._keras_history = kt_output._keras_history
+        cloned_outputs.append(cpy)
+        kt_id_mapping[id(kt_output)] = cpy
+    cloned_outputs = tree.pack_sequence_as(outputs, cloned_outputs)
+    for node in nodes_to_clone:
+        if id(node.operation) in op_id_mapping:
+            operation = op_id_mapping[id(node.operation)]
+        else:
+            operation = node.operation
+        output_copy = clone_keras_tensors(node.output_tensors, kt_id_mapping)
+        if not isinstance(operation, InputLayer):
+            call_args_copy = clone_keras_tensors(node.arguments.args, kt_id_mapping)
+            call_kwargs_copy = clone_keras_tensors(node.arguments.kwargs, kt_id_mapping)
+        else:
+            call_args_copy = ()
+            call_kwargs_copy = {}
+        Node(operation, call_args=call_args_copy, call_kwargs=call_kwargs_copy, outputs=output_copy)
+    return cloned_inputs, cloned_outputs
