@@ -1,0 +1,290 @@
+"""Headline benchmark: ResNet-50 v1 training throughput (images/sec), mixed_bfloat16, SGD momentum.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--config resnet50]
+
+For N>1 launch one rank per GPU with ``python -m torch.distributed.run``.  Rank 0 prints one JSON
+line.  ``value`` is the job-wide images/sec timed on the device (CUDA events, max over ranks) with
+device-resident synthetic inputs; ``e2e`` repeats the measurement through the public
+``train_on_batch`` API with a host→device copy of every batch from pinned memory and a
+device→host read of the loss every step.  ``--impl reference`` runs unmodified reference Keras
+(torch backend) from ``baseline/_ref`` on the same config.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+CONFIGS = {
+    "resnet50": {"model": "ResNet-50 v1", "per_gpu_batch": 256, "image": 224, "classes": 1000},
+    "resnet50_small": {"model": "ResNet-50 v1 (smoke size)", "per_gpu_batch": 16, "image": 64, "classes": 1000},
+}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while timing runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([p.strip() for p in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=6)
+        clocks, reasons, maxc = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                maxc = float(s[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": maxc, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def _dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def _timed(torch, dist, world, steps, step_fn):
+    """Barrier + sync, K steps between CUDA events, sync; returns max-over-ranks milliseconds."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step_fn(i)
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def run_ours(args, cfg):
+    import numpy as np
+    import torch
+
+    rank, world, local = _dist_env()
+    torch.cuda.set_device(local)
+    sys.path.insert(0, ROOT)
+    import keras_b200 as keras
+    from keras_b200.kernels import ops as kops
+
+    dist = None
+    if world > 1:
+        keras.distribution.initialize()
+        import torch.distributed as dist
+
+        keras.distribution.set_distribution(keras.distribution.DataParallel())
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    bs, img, classes = cfg["per_gpu_batch"], cfg["image"], cfg["classes"]
+    model = keras.applications.ResNet50(weights=None, input_shape=(img, img, 3), classes=classes)
+    model.compile(optimizer=keras.optimizers.SGD(learning_rate=0.1, momentum=0.9), loss="sparse_categorical_crossentropy")
+
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_buf = 3
+    host_x = [torch.randn((bs, img, img, 3), generator=gen, dtype=torch.float32).pin_memory() for _ in range(n_buf)]
+    host_y = [torch.randint(0, classes, (bs,), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_buf)]
+    dev_x = [t.cuda() for t in host_x]
+    dev_y = [t.cuda() for t in host_y]
+
+    model.train_on_batch(host_x[0], host_y[0])  # builds model, optimizer, kernels
+    train_fn = model.make_train_function()
+
+    def dev_step(i):
+        train_fn([(dev_x[i % n_buf], dev_y[i % n_buf])])
+
+    for i in range(args.warmup):
+        dev_step(i)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = kops.launch_count()
+    ms = _timed(torch, dist, world, args.steps, dev_step)
+    launches = kops.launch_count() - launches0
+    clocks = sampler.stop()
+
+    last = {}
+
+    def e2e_step(i):
+        last["loss"] = model.train_on_batch(host_x[i % n_buf], host_y[i % n_buf])
+
+    for i in range(min(args.warmup, 3)):
+        e2e_step(i)
+    ms_e2e = _timed(torch, dist, world, args.steps, e2e_step)
+
+    if rank == 0:
+        total = bs * world * args.steps
+        value = total / (ms / 1e3)
+        e2e_value = total / (ms_e2e / 1e3)
+        baseline = _published_baseline()
+        out = {
+            "metric": "ResNet-50 training throughput", "value": value, "unit": "images/sec", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / baseline) if baseline else None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "image_size": img, "seq_len": None,
+                       "parallelism": f"dp{world}", "optimizer": "SGD(momentum=0.9, lr=0.1)", "policy": "mixed_bfloat16",
+                       "l2_hygiene": "inputs_larger_than_L2 (per-step batch and activations exceed 126 MB)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "images/sec", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(host_x[0].numel() * 4 + host_y[0].numel() * 8), "d2h_bytes_per_step": 4,
+                    "api": "Model.train_on_batch(pinned host tensors) -> float loss"},
+            "gpu_launches": int(launches),
+            "final_loss": float(last["loss"]) if not isinstance(last["loss"], (list, tuple)) else float(last["loss"][0]),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference(args, cfg):
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "keras")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref of the reference did not run)"}))
+        return
+    os.environ["KERAS_BACKEND"] = "torch"
+    os.environ.setdefault("KERAS_HOME", "/tmp/keras_ref_home")
+    sys.path.insert(0, ref)
+    import torch
+
+    rank, world, local = _dist_env()
+    torch.cuda.set_device(local)
+    try:
+        import keras
+    except Exception as e:  # pragma: no cover
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"reference import failed: {type(e).__name__}: {str(e)[:200]}"}))
+        return
+    dist = None
+    if world > 1:
+        keras.distribution.initialize()
+        import torch.distributed as dist
+
+        keras.distribution.set_distribution(keras.distribution.DataParallel())
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    bs, img, classes = cfg["per_gpu_batch"], cfg["image"], cfg["classes"]
+    model = keras.applications.ResNet50(weights=None, input_shape=(img, img, 3), classes=classes)
+    model.compile(optimizer=keras.optimizers.SGD(learning_rate=0.1, momentum=0.9), loss="sparse_categorical_crossentropy")
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_buf = 3
+    host_x = [torch.randn((bs, img, img, 3), generator=gen, dtype=torch.float32).pin_memory() for _ in range(n_buf)]
+    host_y = [torch.randint(0, classes, (bs,), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_buf)]
+    dev_x = [t.cuda() for t in host_x]
+    dev_y = [t.cuda() for t in host_y]
+    last = {}
+
+    def dev_step(i):
+        last["loss"] = model.train_on_batch(dev_x[i % n_buf], dev_y[i % n_buf])
+
+    def e2e_step(i):
+        last["loss"] = model.train_on_batch(host_x[i % n_buf], host_y[i % n_buf])
+
+    for i in range(max(args.warmup, 1)):
+        dev_step(i)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = _timed(torch, dist, world, args.steps, dev_step)
+    clocks = sampler.stop()
+    for i in range(min(args.warmup, 3)):
+        e2e_step(i)
+    ms_e2e = _timed(torch, dist, world, args.steps, e2e_step)
+    if rank == 0:
+        total = bs * world * args.steps
+        loss = last["loss"]
+        out = {
+            "metric": "ResNet-50 training throughput", "value": total / (ms / 1e3), "unit": "images/sec", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "image_size": img, "seq_len": None,
+                       "parallelism": f"dp{world}", "optimizer": "SGD(momentum=0.9, lr=0.1)", "policy": "mixed_bfloat16",
+                       "framework": f"keras {keras.__version__} (torch backend, stock code path)",
+                       "l2_hygiene": "inputs_larger_than_L2"},
+            "clocks": clocks,
+            "e2e": {"value": total / (ms_e2e / 1e3), "unit": "images/sec", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(host_x[0].numel() * 4 + host_y[0].numel() * 8), "d2h_bytes_per_step": 4,
+                    "api": "Model.train_on_batch(pinned host tensors) -> float loss"},
+            "gpu_launches": 0,
+            "final_loss": float(loss if not isinstance(loss, (list, tuple)) else loss[0]),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _published_baseline():
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            pub = json.load(f).get("published") or {}
+        for v in pub.values():
+            if isinstance(v, (int, float)):
+                return float(v)
+    except Exception:
+        pass
+    return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="resnet50", choices=sorted(CONFIGS))
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    cfg = CONFIGS[args.config]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        # convenience: re-launch under torchrun when asked for N>1 from a plain python call
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+               "--master-port", os.environ.get("MASTER_PORT", "29533"), os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,50 +1,43 @@
 """Routing of hot ops to the sm_100a kernels.
 
-Each function returns ``None`` when the call does not qualify (CPU tensor, unsupported dtype or
-shape, kernels disabled by ``KERAS_B200_DISABLE_FUSED_KERNELS=1``); the caller then uses its
-library path.  On a CUDA device the extension must be loadable: a missing build raises instead
-of silently falling back.
+Each function returns ``None`` (or ``False``) when the call does not qualify (CPU tensor,
+unsupported dtype or shape, kernels disabled by ``KERAS_B200_DISABLE_FUSED_KERNELS=1``, symbolic
+tracing on the meta device); the caller then uses its library path.  On a CUDA device the kernel
+library must be loadable: a missing build raises instead of silently falling back.
 """
+
+import torch
 
 from keras_b200.core import config
 
-
-def _ext():
-    from keras_b200.kernels import loader
-
-    return loader.get()
+_FLOAT_IO = (torch.float32, torch.bfloat16)
 
 
 def enabled(t):
-    return t.is_cuda and config.fused_kernels_enabled()
+    return isinstance(t, torch.Tensor) and t.is_cuda and config.fused_kernels_enabled()
 
 
+def _ops():
+    from keras_b200.kernels import ops
+
+    return ops
+
+
+# ------------------------------------------------------------------------------------ GEMM
 def matmul(a, b):
-    return None
+    if not (enabled(a) and enabled(b)):
+        return None
+    from keras_b200.kernels import gemm
 
-
-def conv(x, kernel, strides, padding, data_format, dilation):
-    return None
-
-
-def softmax_cross_entropy(logits, labels):
-    return None
-
-
-def layer_norm(x, gamma, beta, eps):
-    return None
-
-
-def rms_norm(x, scale, eps):
-    return None
-
-
-def flash_attention(q, k, v, mask, scale, is_causal):
-    return None
+    return gemm.matmul(a, b)
 
 
 def dense(x, kernel, bias, activation_name):
-    return None
+    if not enabled(x):
+        return None
+    from keras_b200.kernels import gemm
+
+    return gemm.dense(x, kernel, bias, activation_name)
 
 
 def int8_matmul(q_inputs, kernel, out_scale):
@@ -55,13 +48,141 @@ def fp8_matmul(layer, inputs, kernel, equation, training):
     return None
 
 
-def batch_norm(layer, inputs, training):
-    return None
+def conv(x, kernel, strides, padding, data_format, dilation):
+    if not (enabled(x) and enabled(kernel)):
+        return None
+    from keras_b200.kernels import conv as conv_mod
+
+    return conv_mod.conv(x, kernel, strides, padding, data_format, dilation)
+
+
+# ------------------------------------------------------------------------- normalisation
+def layer_norm(x, gamma, beta, eps):
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.shape[-1] > 8192 or x.numel() == 0:
+        return None
+    return _ops().FusedNorm.apply(x, gamma, beta, float(eps), False)
+
+
+def rms_norm(x, scale, eps):
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.shape[-1] > 8192 or x.numel() == 0:
+        return None
+    return _ops().FusedNorm.apply(x, scale, None, float(eps), True)
+
+
+def batch_norm(layer, inputs, training, residual=None, relu=False):
+    """Fused channels-last BatchNorm (+residual)(+ReLU).  Returns ``None`` when not applicable."""
+    x = inputs
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim < 2:
+        return None
+    axis = layer.axis % x.ndim
+    if axis != x.ndim - 1:
+        return None
+    C = x.shape[-1]
+    vec = 8 if x.dtype == torch.bfloat16 else 4
+    if C % vec != 0 or x.numel() == 0:
+        return None
+    gamma = layer.gamma._value if layer.scale else None
+    beta = layer.beta._value if layer.center else None
+    if (gamma is not None and gamma.dtype != torch.float32) or (beta is not None and beta.dtype != torch.float32):
+        return None
+    mm, mv = layer.moving_mean._value, layer.moving_variance._value
+    if mm.dtype != torch.float32:
+        return None
+    ops = _ops()
+    if training:
+        if beta is None:
+            beta = torch.zeros(C, dtype=torch.float32, device=x.device)
+        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu))
+    if torch.is_grad_enabled() and (x.requires_grad or (gamma is not None and gamma.requires_grad and layer.trainable)):
+        return None
+    with torch.no_grad():
+        inv = torch.rsqrt(mv + layer.epsilon)
+        scale = inv * gamma if gamma is not None else inv
+        shift = -mm * scale
+        if beta is not None:
+            shift = shift + beta
+    return ops.bn_inference(x, scale.contiguous(), shift.contiguous(), residual, relu)
+
+
+def softmax_cross_entropy(logits, labels):
+    if not enabled(logits) or logits.dtype not in _FLOAT_IO or logits.numel() == 0:
+        return None
+    if logits.shape[-1] < 64:
+        return None
+    return _ops().FusedSoftmaxXent.apply(logits, labels)
+
+
+def flash_attention(q, k, v, mask, scale, is_causal):
+    if not enabled(q):
+        return None
+    from keras_b200.kernels import attention
+
+    return attention.flash_attention(q, k, v, mask, scale, is_causal)
+
+
+# ---------------------------------------------------------------------------- optimizers
+def _plan_for(opt, grads, variables, slot_lists):
+    if not variables:
+        return None
+    p0 = variables[0]._value
+    if not enabled(p0):
+        return None
+    params = [v._value for v in variables]
+    for p, g in zip(params, grads):
+        if p.dtype != torch.float32 or g.dtype != torch.float32 or not g.is_contiguous() or not p.is_contiguous() or not p.is_cuda:
+            return None
+    key = (tuple(id(v) for v in variables), tuple(g.data_ptr() for g in grads), tuple(p.data_ptr() for p in params))
+    cache = getattr(opt, "_fused_plan", None)
+    if cache is not None and cache[0] == key:
+        return cache[1]
+    slots = []
+    for lst in slot_lists:
+        if lst is None:
+            slots.append(None)
+        else:
+            slots.append([lst[opt._get_variable_index(v)]._value for v in variables])
+    shadows = None
+    from keras_b200.kernels import shadow
+
+    shadows = shadow.shadows_for(variables)
+    plan = _ops().OptimizerPlan(params, list(grads), slots[0], slots[1] if len(slots) > 1 else None, shadows, [1.0] * len(params))
+    opt._fused_plan = (key, plan)
+    return plan
+
+
+def _decays(opt, variables, lr):
+    wd = opt.weight_decay
+    if wd is None:
+        return None
+    return [(1.0 - wd * lr) if opt._use_weight_decay(v) else 1.0 for v in variables]
 
 
 def fused_sgd(opt, grads, variables, lr):
-    return False
+    if opt.gradient_accumulation_steps:
+        return False
+    slot0 = opt.momentums if opt.momentum != 0 else None
+    plan = _plan_for(opt, grads, variables, [slot0])
+    if plan is None:
+        return False
+    d = _decays(opt, variables, lr)
+    if d is not None:
+        plan.set_decays(d)
+    scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
+    plan.sgd(lr, opt.momentum, opt.nesterov, grad_scale=scale, zero_grad=True)
+    opt._fused_zeroed_grads = True
+    return True
 
 
 def fused_adam(opt, grads, variables, lr):
-    return False
+    if opt.gradient_accumulation_steps:
+        return False
+    plan = _plan_for(opt, grads, variables, [opt._momentums, opt._velocities])
+    if plan is None:
+        return False
+    d = _decays(opt, variables, lr)
+    if d is not None:
+        plan.set_decays(d)
+    scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
+    plan.adam(opt._alpha(lr), opt.beta_1, opt.beta_2, opt.epsilon, grad_scale=scale, zero_grad=True)
+    opt._fused_zeroed_grads = True
+    return True

@@ -1,0 +1,259 @@
+"""Python side of the sm_100a kernels: ``ctypes`` launch wrappers and autograd functions."""
+
+import ctypes
+
+import torch
+
+from keras_b200.kernels import loader
+
+_vp = ctypes.c_void_p
+_ll = ctypes.c_longlong
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+
+def _p(t):
+    return _vp(t.data_ptr()) if t is not None else _vp(0)
+
+
+def _dt(t):
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _lib():
+    lib = loader.get()
+    if lib is None:
+        raise RuntimeError("The sm_100a kernel library needs a CUDA device.")
+    return lib
+
+
+_LAUNCHES = [0]
+
+
+def launch_count():
+    """Number of kernel-launcher calls made by this process so far."""
+    return _LAUNCHES[0]
+
+
+def _check(code, what):
+    _LAUNCHES[0] += 1
+    if code != 0:
+        msg = ctypes.c_char_p(_lib().kb200_last_error()).value if False else b""
+        try:
+            fn = _lib().kb200_last_error
+            fn.restype = ctypes.c_char_p
+            msg = fn() or b""
+        except Exception:
+            pass
+        raise RuntimeError(f"{what} failed with code {code}: {msg.decode(errors='ignore')}")
+
+
+# ------------------------------------------------------------------------------ batch norm
+class _BNState:
+    """Per-layer scratch reused across steps (sums / mean / invstd / scale / shift), keyed by C."""
+
+    def __init__(self, C, device):
+        self.sums = torch.empty(2 * C, dtype=torch.float32, device=device)
+        self.bsums = torch.empty(2 * C, dtype=torch.float32, device=device)
+
+
+class FusedBatchNormAct(torch.autograd.Function):
+    """y = relu?(batchnorm_train(x) (+ residual)) for channels-last x, with moving-stat update."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu):
+        lib = _lib()
+        C = x.shape[-1]
+        M = x.numel() // C
+        x = x.contiguous()
+        dev = x.device
+        sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
+        stats = torch.empty(4 * C, dtype=torch.float32, device=dev)
+        mean, invstd, scale, shift = stats[:C], stats[C:2 * C], stats[2 * C:3 * C], stats[3 * C:]
+        y = torch.empty_like(x)
+        st = _stream()
+        dt = _dt(x)
+        _check(lib.kb200_bn_stats(_p(x), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_stats")
+        _check(lib.kb200_bn_finalize(_p(sums), _p(gamma), _p(beta), _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C),
+                                     _p(mean), _p(invstd), _p(scale), _p(shift), st), "bn_finalize")
+        res = residual.contiguous() if residual is not None else None
+        _check(lib.kb200_bn_apply(_p(x), _p(res), _p(y), _p(scale), _p(shift), _ll(M), _i(C), _i(1 if relu else 0), _i(dt), st), "bn_apply")
+        ctx.save_for_backward(x, y if relu else None, gamma, stats)
+        ctx.relu = relu
+        ctx.has_res = residual is not None
+        ctx.dims = (M, C)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        x, y, gamma, stats = ctx.saved_tensors
+        M, C = ctx.dims
+        mean, invstd = stats[:C], stats[C:2 * C]
+        dy = dy.contiguous()
+        dev = x.device
+        sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
+        dx = torch.empty_like(x)
+        dres = torch.empty_like(x) if ctx.has_res else None
+        st = _stream()
+        dt = _dt(x)
+        _check(lib.kb200_bn_bwd_reduce(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_bwd_reduce")
+        _check(lib.kb200_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
+        dgamma = sums[C:].clone() if gamma is not None else None
+        dbeta = sums[:C].clone()
+        return dx, dgamma, dbeta, dres, None, None, None, None, None
+
+
+def bn_inference(x, scale, shift, residual, relu):
+    """y = relu?(x*scale + shift (+ residual)) with per-channel fp32 scale/shift (no autograd)."""
+    lib = _lib()
+    C = x.shape[-1]
+    M = x.numel() // C
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    res = residual.contiguous() if residual is not None else None
+    _check(lib.kb200_bn_apply(_p(x), _p(res), _p(y), _p(scale), _p(shift), _ll(M), _i(C), _i(1 if relu else 0), _i(_dt(x)), _stream()), "bn_apply")
+    return y
+
+
+# ------------------------------------------------------------------- layer norm / rms norm
+class FusedNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, rms):
+        lib = _lib()
+        D = x.shape[-1]
+        rows = x.numel() // D
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        stats = torch.empty(2 * rows, dtype=torch.float32, device=x.device)
+        mean, rstd = stats[:rows], stats[rows:]
+        g = gamma.float().contiguous() if gamma is not None else None
+        b = beta.float().contiguous() if beta is not None else None
+        _check(lib.kb200_norm_fwd(_p(x), _p(g), _p(b), _p(y), _p(mean), _p(rstd), _ll(rows), _i(D), _f(eps), _i(1 if rms else 0), _i(_dt(x)), _stream()), "norm_fwd")
+        ctx.save_for_backward(x, g, stats)
+        ctx.rms = rms
+        ctx.has_beta = beta is not None
+        ctx.gamma_dtype = gamma.dtype if gamma is not None else None
+        ctx.beta_dtype = beta.dtype if beta is not None else None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        x, g, stats = ctx.saved_tensors
+        D = x.shape[-1]
+        rows = x.numel() // D
+        mean, rstd = stats[:rows], stats[rows:]
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        lib.kb200_norm_bwd_blocks.restype = ctypes.c_int
+        nb = lib.kb200_norm_bwd_blocks(_ll(rows))
+        pdg = torch.empty((nb, D), dtype=torch.float32, device=x.device)
+        pdb = torch.empty((nb, D), dtype=torch.float32, device=x.device) if ctx.has_beta else None
+        dgamma = torch.empty(D, dtype=torch.float32, device=x.device) if g is not None else None
+        dbeta = torch.empty(D, dtype=torch.float32, device=x.device) if ctx.has_beta else None
+        _check(lib.kb200_norm_bwd(_p(dy), _p(x), _p(g), _p(mean), _p(rstd), _p(dx), _p(pdg), _p(pdb), _p(dgamma), _p(dbeta), _ll(rows), _i(D),
+                                  _i(1 if ctx.rms else 0), _i(_dt(x)), _stream()), "norm_bwd")
+        if dgamma is not None and ctx.gamma_dtype != torch.float32:
+            dgamma = dgamma.to(ctx.gamma_dtype)
+        if dbeta is not None and ctx.beta_dtype != torch.float32:
+            dbeta = dbeta.to(ctx.beta_dtype)
+        return dx, dgamma, dbeta, None, None
+
+
+# ----------------------------------------------------------------- softmax cross-entropy
+class FusedSoftmaxXent(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels):
+        lib = _lib()
+        V = logits.shape[-1]
+        rows = logits.numel() // V
+        logits = logits.contiguous()
+        labels64 = labels.reshape(-1).to(torch.int64).contiguous()
+        out = torch.empty(2 * rows, dtype=torch.float32, device=logits.device)
+        loss, lse = out[:rows], out[rows:]
+        _check(lib.kb200_xent_fwd(_p(logits), _p(labels64), _p(loss), _p(lse), _ll(rows), _i(V), _i(_dt(logits)), _stream()), "xent_fwd")
+        ctx.save_for_backward(logits, labels64, lse)
+        ctx.out_shape = labels.shape
+        return loss.reshape(labels.shape).to(logits.dtype) if logits.dtype != torch.float32 else loss.reshape(labels.shape)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        lib = _lib()
+        logits, labels64, lse = ctx.saved_tensors
+        V = logits.shape[-1]
+        rows = logits.numel() // V
+        dl = dloss.reshape(-1).float().contiguous()
+        dlogits = torch.empty_like(logits)
+        _check(lib.kb200_xent_bwd(_p(logits), _p(labels64), _p(lse), _p(dl), _p(dlogits), _ll(rows), _i(V), _i(_dt(logits)), _stream()), "xent_bwd")
+        return dlogits, None
+
+
+# ------------------------------------------------------------------------ fused optimizers
+class OptimizerPlan:
+    """Device-resident descriptor + chunk tables for one (optimizer, variable list) pair."""
+
+    def __init__(self, params, grads, slot0, slot1, shadows, decays):
+        lib = _lib()
+        lib.kb200_opt_chunk_elems.restype = ctypes.c_int
+        lib.kb200_opt_desc_bytes.restype = ctypes.c_int
+        chunk = lib.kb200_opt_chunk_elems()
+        assert lib.kb200_opt_desc_bytes() == 56
+        import numpy as np
+
+        n = len(params)
+        desc = np.zeros(n, dtype=[("param", "<u8"), ("grad", "<u8"), ("slot0", "<u8"), ("slot1", "<u8"), ("shadow", "<u8"), ("numel", "<i8"), ("decay", "<f4"), ("pad", "<i4")])
+        chunks = []
+        for i, p in enumerate(params):
+            desc[i]["param"] = p.data_ptr()
+            desc[i]["grad"] = grads[i].data_ptr()
+            desc[i]["slot0"] = slot0[i].data_ptr() if slot0 is not None and slot0[i] is not None else 0
+            desc[i]["slot1"] = slot1[i].data_ptr() if slot1 is not None and slot1[i] is not None else 0
+            desc[i]["shadow"] = shadows[i].data_ptr() if shadows is not None and shadows[i] is not None else 0
+            desc[i]["numel"] = p.numel()
+            desc[i]["decay"] = decays[i]
+            for start in range(0, p.numel(), chunk):
+                chunks.append((i, 0, start))
+        ch = np.array(chunks, dtype=[("tensor", "<i4"), ("pad", "<i4"), ("start", "<i8")]) if chunks else np.zeros(0, dtype=[("tensor", "<i4"), ("pad", "<i4"), ("start", "<i8")])
+        dev = params[0].device
+        self.desc_host = desc
+        self.desc = torch.from_numpy(desc.view(np.uint8).copy()).to(dev)
+        self.chunks = torch.from_numpy(ch.view(np.uint8).copy()).to(dev)
+        self.n_chunks = len(chunks)
+        self.found_inf = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.keep = (params, grads, slot0, slot1, shadows)
+
+    def set_decays(self, decays):
+        """Refresh per-tensor decay factors (they depend on the learning rate)."""
+        import numpy as np
+
+        changed = False
+        for i, d in enumerate(decays):
+            if self.desc_host[i]["decay"] != np.float32(d):
+                self.desc_host[i]["decay"] = d
+                changed = True
+        if changed:
+            self.desc.copy_(torch.from_numpy(self.desc_host.view(np.uint8).copy()), non_blocking=True)
+
+    def adam(self, alpha, beta1, beta2, eps, grad_scale=1.0, zero_grad=True, check_inf=False):
+        lib = _lib()
+        _check(lib.kb200_fused_adam(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _f(alpha), _f(beta1), _f(beta2), _f(eps), _f(grad_scale),
+                                    _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _stream()), "fused_adam")
+
+    def sgd(self, lr, momentum, nesterov, grad_scale=1.0, zero_grad=True, check_inf=False):
+        lib = _lib()
+        _check(lib.kb200_fused_sgd(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _f(lr), _f(momentum), _i(1 if nesterov else 0), _f(grad_scale),
+                                   _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _stream()), "fused_sgd")
+
+
+def cast_f32_to_bf16(src, dst):
+    lib = _lib()
+    _check(lib.kb200_cast_f32_bf16(_p(src), _p(dst), _ll(src.numel()), _stream()), "cast_f32_bf16")

@@ -1,0 +1,65 @@
+"""bf16 shadow copies of fp32 variables.
+
+Under ``mixed_bfloat16`` every layer reads its fp32 variables in bf16.  Instead of one cast kernel
+per variable per step, the fused optimizer writes a bf16 copy of each parameter as part of its
+update; reads return that copy through an autograd function whose backward hands the gradient to
+the fp32 parameter.
+"""
+
+import torch
+
+_ENABLED = False
+
+
+def shadows_for(variables):
+    """List of bf16 shadow tensors (or ``None``) aligned with ``variables``."""
+    out = []
+    any_shadow = False
+    for v in variables:
+        sh = getattr(v, "_shadow_tensor", None)
+        out.append(sh)
+        any_shadow = any_shadow or sh is not None
+    return out if any_shadow else None
+
+
+class _ShadowRead(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, param, shadow):
+        return shadow.view_as(shadow)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad.float(), None
+
+
+def attach(variables):
+    """Create shadows for fp32 CUDA variables that are read with autocast."""
+    from keras_b200.kernels import ops
+
+    for v in variables:
+        p = v._value
+        if p is None or not p.is_cuda or p.dtype != torch.float32 or not v._autocast or getattr(v, "_shadow_tensor", None) is not None:
+            continue
+        sh = torch.empty_like(p, dtype=torch.bfloat16)
+        ops.cast_f32_to_bf16(p.detach().reshape(-1), sh.reshape(-1))
+        v._shadow_tensor = sh
+        state = {"dirty": False}
+
+        def read(value, _v=v, _sh=sh, _state=state):
+            if _state["dirty"]:
+                ops.cast_f32_to_bf16(_v._value.detach().reshape(-1), _sh.reshape(-1))
+                _state["dirty"] = False
+            if value.requires_grad and torch.is_grad_enabled():
+                return _ShadowRead.apply(value, _sh)
+            return _sh
+
+        def invalidate(_state=state):
+            _state["dirty"] = True
+
+        v._shadow = (torch.bfloat16, read, invalidate)
+
+
+def detach(variables):
+    for v in variables:
+        v._shadow = None
+        v._shadow_tensor = None

@@ -288,7 +288,7 @@ class Layer(Operation):
         elif isinstance(value, SeedGenerator):
             if not any(value is s for s in self._seed_generators):
                 self._seed_generators.append(value)
-                self._track_variable(value.state)
+                self._invalidate()
 
     def _track_variable(self, variable):
         if variable.trainable:
@@ -319,6 +319,9 @@ class Layer(Operation):
         object.__setattr__(self, "_cached_vars", None)
 
     def __setattr__(self, name, value):
+        if name in _UNTRACKED_ATTRS:
+            object.__setattr__(self, name, value)
+            return
         if name[0] != "_" or not isinstance(value, (bool, int, float, str, type(None))):
             try:
                 value = self._track_value(value)
@@ -451,6 +454,12 @@ class Layer(Operation):
                     seen.add(id(v))
                     all_vars.append(v)
                     non_trainable.append(v)
+            for sg in layer._seed_generators:
+                v = sg.state
+                if id(v) not in seen:
+                    seen.add(id(v))
+                    all_vars.append(v)
+                    non_trainable.append(v)
 
         # own variables first, then metrics, then sub-layers depth-first (reference order)
         def walk(layer, anc):
@@ -475,7 +484,7 @@ class Layer(Operation):
         stack = [self]
         while stack:
             l = stack.pop()
-            total += len(l._trainable_variables) * 1000003 + len(l._non_trainable_variables) * 10007 + len(l._layers) * 101 + (7 if l._trainable else 0) + len(l._metrics)
+            total += len(l._trainable_variables) * 1000003 + len(l._non_trainable_variables) * 10007 + len(l._layers) * 101 + (7 if l._trainable else 0) + len(l._metrics) + len(l._seed_generators) * 13
             stack.extend(l._layers)
         return total
 
@@ -1156,6 +1165,8 @@ class _NoAutocast:
 
 
 _NO_AUTOCAST = None
+# Trainer-owned objects that are reported through `Model.metrics` explicitly.
+_UNTRACKED_ATTRS = frozenset({"_loss_tracker", "_compile_metrics", "_compile_loss", "_parallel_engine", "_grad_arena", "history"})
 _TRACK_EXTRA = ()
 
 

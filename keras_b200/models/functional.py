@@ -47,6 +47,10 @@ class Functional(Function, Model):
                 raise ValueError(f"All `outputs` values must be KerasTensors. Received: outputs={outputs} including invalid value {x} of type {type(x)}")
         if not all(is_input_keras_tensor(t) for t in flat_inputs):
             inputs, outputs = clone_graph_nodes(inputs, outputs)
+        if "_compute_loss_has_training_arg" not in self.__dict__:
+            from keras_b200.trainers.trainer import Trainer
+
+            Trainer.__init__(self)
         Layer.__init__(self, name=name, **kwargs)
         Function.__init__(self, inputs, outputs, name=self.name)
         if trainable is not None:
@@ -85,7 +89,15 @@ class Functional(Function, Model):
                         x._keras_mask = m
                     except AttributeError:
                         pass
-        outputs = self._run_through_graph(inputs, operation_fn=lambda op: operation_fn(op, training=training, **kwargs))
+        fusion = None
+        if inputs and isinstance(inputs[0], torch.Tensor) and inputs[0].is_cuda:
+            from keras_b200.core import config as _config
+
+            if _config.fused_kernels_enabled():
+                from keras_b200.models import fusion as fusion_mod
+
+                fusion = _FusionCtx(fusion_mod, training)
+        outputs = self._run_through_graph(inputs, operation_fn=lambda op: operation_fn(op, training=training, **kwargs), fusion=fusion)
         return unpack_singleton(outputs)
 
     def compute_output_spec(self, inputs, training=None, mask=None):
@@ -274,6 +286,14 @@ class Functional(Function, Model):
         config["input_layers"] = map_tensors(self._inputs_struct)
         config["output_layers"] = map_tensors(self._outputs_struct)
         return copy.deepcopy(config)
+
+
+class _FusionCtx:
+    __slots__ = ("mod", "training", "Deferred", "run_bn", "build_plan", "applicable")
+
+    def __init__(self, mod, training):
+        self.mod, self.training = mod, training
+        self.Deferred, self.run_bn, self.build_plan, self.applicable = mod.Deferred, mod.run_bn, mod.build_plan, mod.applicable
 
 
 def functional_from_config(cls, config, custom_objects=None):

@@ -1,0 +1,93 @@
+"""Graph-level fusion for ``Functional`` models.
+
+The executor of a ``Functional`` walks its nodes in order; this module finds, once per model,
+the node patterns that a single sm_100a kernel can execute:
+
+* ``BatchNormalization → ReLU``                         → BN apply with fused ReLU
+* ``BatchNormalization → Add(other) [→ ReLU]``          → BN apply with fused residual add (and ReLU)
+
+(the residual bottleneck of keras/src/applications/resnet.py:219-273 is conv→BN→ReLU ×2, conv→BN,
+Add, ReLU).  A fused BN is *deferred*: its node records the input, and the kernel runs when the
+consumer node is reached so the residual operand is available.  Patterns only fire on CUDA tensors
+with a channels-last BN; otherwise execution is node by node as written.
+"""
+
+import torch
+
+from keras_b200.layers.activations.activation_layers import Activation, ReLU
+from keras_b200.layers.merging.merging_layers import Add
+from keras_b200.layers.normalization.normalization_layers import BatchNormalization
+
+
+class Deferred:
+    __slots__ = ("layer", "x", "shape", "dtype", "device", "ndim")
+
+    def __init__(self, layer, x):
+        self.layer, self.x = layer, x
+        self.shape, self.dtype, self.device, self.ndim = x.shape, x.dtype, x.device, x.ndim
+
+
+def _is_relu(op):
+    if isinstance(op, ReLU):
+        return op.max_value is None and op.negative_slope == 0.0 and op.threshold == 0.0
+    if isinstance(op, Activation):
+        return getattr(op.activation, "__name__", "") == "relu"
+    return False
+
+
+def build_plan(function):
+    """Return {id(node): role} with roles 'defer_bn', 'consume_add', 'consume_relu', 'maybe_identity'."""
+    nodes = function._ordered_nodes()
+    in_graph = set(id(n) for n in nodes)
+    consumers = {}
+    for n in nodes:
+        for t in n.input_tensors:
+            consumers.setdefault(id(t), []).append(n)
+    output_ids = {id(t) for t in function._outputs}
+    plan = {}
+    for n in nodes:
+        op = n.operation
+        if not isinstance(op, BatchNormalization) or op.renorm or op.synchronized or len(n.outputs) != 1:
+            continue
+        out = n.outputs[0]
+        if id(out) in output_ids:
+            continue
+        cons = consumers.get(id(out), [])
+        if len(cons) != 1 or id(cons[0]) in plan:
+            continue
+        c = cons[0]
+        if _is_relu(c.operation) and len(c.input_tensors) == 1:
+            plan[id(n)] = "defer_bn"
+            plan[id(c)] = "consume_relu"
+        elif isinstance(c.operation, Add) and len(c.input_tensors) == 2 and len(c.outputs) == 1:
+            other = [t for t in c.input_tensors if t is not out]
+            if len(other) != 1 or tuple(other[0].shape) != tuple(out.shape):
+                continue
+            plan[id(n)] = "defer_bn"
+            plan[id(c)] = "consume_add"
+            add_out = c.outputs[0]
+            cc = consumers.get(id(add_out), [])
+            if id(add_out) not in output_ids and len(cc) == 1 and _is_relu(cc[0].operation) and id(cc[0]) not in plan:
+                plan[id(c)] = "consume_add_relu"
+                plan[id(cc[0])] = "identity"
+    return plan
+
+
+def applicable(x):
+    return isinstance(x, torch.Tensor) and x.is_cuda
+
+
+def run_bn(layer, x, training, residual=None, relu=False):
+    """Execute a (possibly fused) BatchNormalization outside of ``Layer.__call__``."""
+    from keras_b200.kernels import dispatch
+
+    train = bool(training) and layer.trainable
+    out = dispatch.batch_norm(layer, x, train, residual=residual, relu=relu)
+    if out is not None:
+        return out
+    out = layer(x, training=training)
+    if residual is not None:
+        out = out + residual
+    if relu:
+        out = torch.relu(out)
+    return out

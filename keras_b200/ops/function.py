@@ -15,6 +15,12 @@ from keras_b200.core.keras_tensor import KerasTensor
 from keras_b200.ops.operation import Operation
 
 
+def torch_relu(x):
+    import torch
+
+    return torch.relu(x)
+
+
 @keras_export("keras.Function")
 class Function(Operation):
     def __init__(self, inputs, outputs, name=None):
@@ -44,7 +50,8 @@ class Function(Operation):
         self._nodes_by_depth = nodes_by_depth
         self._operations = operations
         self._operations_by_depth = operations_by_depth
-        self._plan = None
+        self._node_order = None
+        self._fusion_plan = None
         for inp in self._inputs:
             if inp._keras_history.operation and not inp._keras_history.operation._outbound_nodes:
                 raise ValueError("`inputs` not connected to `outputs`")
@@ -81,10 +88,15 @@ class Function(Operation):
         self._assert_input_compatibility(inputs)
         return self._run_through_graph(inputs)
 
-    def _run_through_graph(self, inputs, operation_fn=None, call_fn=None):
+    def _run_through_graph(self, inputs, operation_fn=None, call_fn=None, fusion=None):
         flat_in = tree.flatten(inputs)
         env = {id(ref): val for ref, val in zip(self._inputs, flat_in)}
-        for node in self._ordered_nodes():
+        nodes = self._node_order
+        if nodes is None:
+            nodes = self._node_order = self._ordered_nodes()
+        if fusion is not None and flat_in and fusion.applicable(flat_in[0]):
+            return self._run_fused(env, nodes, operation_fn, fusion)
+        for node in nodes:
             if any(id(t) not in env for t in node.input_tensors):
                 continue
             args, kwargs = node.arguments.fill_in(env)
@@ -102,6 +114,59 @@ class Function(Operation):
                 path = tree.flatten_with_path(self._outputs_struct)[i][0]
                 raise ValueError(f"Output with path `{'.'.join(map(str, path))}` is not connected to `inputs`")
             flat_out.append(env[id(ref)])
+        return tree.pack_sequence_as(self._outputs_struct, flat_out)
+
+    def _run_fused(self, env, nodes, operation_fn, fusion):
+        """Executor used on CUDA: like the plain loop, with the fusion plan's deferred BN nodes."""
+        plan = self._fusion_plan
+        if plan is None:
+            plan = self._fusion_plan = fusion.build_plan(self)
+        training = fusion.training
+        for node in nodes:
+            ins = node.input_tensors
+            if any(id(t) not in env for t in ins):
+                continue
+            role = plan.get(id(node))
+            outs = node.outputs
+            if role == "defer_bn":
+                x = env[id(ins[0])]
+                if isinstance(x, fusion.Deferred):
+                    x = fusion.run_bn(x.layer, x.x, training)
+                env[id(outs[0])] = fusion.Deferred(node.operation, x)
+                continue
+            if role == "consume_relu":
+                d = env[id(ins[0])]
+                env[id(outs[0])] = fusion.run_bn(d.layer, d.x, training, relu=True) if isinstance(d, fusion.Deferred) else node.operation(d)
+                continue
+            if role in ("consume_add", "consume_add_relu"):
+                a, b = env[id(ins[0])], env[id(ins[1])]
+                if isinstance(a, fusion.Deferred) and isinstance(b, fusion.Deferred):
+                    b = fusion.run_bn(b.layer, b.x, training)
+                if isinstance(b, fusion.Deferred):
+                    a, b = b, a
+                if isinstance(a, fusion.Deferred):
+                    env[id(outs[0])] = fusion.run_bn(a.layer, a.x, training, residual=b, relu=role == "consume_add_relu")
+                else:
+                    r = node.operation([a, b])
+                    env[id(outs[0])] = torch_relu(r) if role == "consume_add_relu" else r
+                continue
+            if role == "identity":
+                env[id(outs[0])] = env[id(ins[0])]
+                continue
+            args, kwargs = node.arguments.fill_in(env)
+            op = node.operation if operation_fn is None else operation_fn(node.operation)
+            result = op(*args, **kwargs)
+            if len(outs) == 1 and not isinstance(result, (list, tuple, dict)):
+                env[id(outs[0])] = result
+            else:
+                for ref, val in zip(outs, tree.flatten(result)):
+                    env[id(ref)] = val
+        flat_out = []
+        for ref in self._outputs:
+            v = env[id(ref)]
+            if isinstance(v, fusion.Deferred):
+                v = fusion.run_bn(v.layer, v.x, training)
+            flat_out.append(v)
         return tree.pack_sequence_as(self._outputs_struct, flat_out)
 
     def _assert_input_compatibility(self, inputs):

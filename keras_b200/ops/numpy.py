@@ -34,7 +34,9 @@ def _t(x, dtype=None):
 
 def _dt(x):
     """dtype spelling usable by ``result_type``: tensor dtype, or Python type for scalars."""
-    if isinstance(x, (_T, Variable)):
+    if isinstance(x, Variable):
+        return x.value.dtype
+    if isinstance(x, _T):
         return x.dtype
     if isinstance(x, bool):
         return "bool"
@@ -51,6 +53,12 @@ def _pair(x1, x2):
     """Promote two operands to their common Keras dtype."""
     if type(x1) is _T and type(x2) is _T and x1.dtype == x2.dtype:
         return x1, x2
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
+    if type(x1) is _T and type(x2) is _T and x1.dtype == x2.dtype:
+        return x1, x2
     d = to_torch_dtype(result_type(_dt(x1), _dt(x2)))
     return convert_to_tensor(x1, d), convert_to_tensor(x2, d)
 
@@ -64,6 +72,10 @@ def _floatize(x):
 
 
 def _pair_float(x1, x2):
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
     d = to_torch_dtype(result_type(_dt(x1), _dt(x2), float))
     return convert_to_tensor(x1, d), convert_to_tensor(x2, d)
 
@@ -472,11 +484,11 @@ def _promote_sum_dtype(x):
 def sum(x, axis=None, keepdims=False):
     x = _promote_sum_dtype(_t(x))
     if axis is None:
-        r = torch.sum(x)
+        r = torch.sum(x, dtype=x.dtype)
         return r.reshape((1,) * x.ndim) if keepdims else r
     if axis == ():
         return x
-    return torch.sum(x, dim=_axis(axis), keepdim=keepdims)
+    return torch.sum(x, dim=_axis(axis), keepdim=keepdims, dtype=x.dtype)
 
 
 @op("numpy")
@@ -485,12 +497,12 @@ def prod(x, axis=None, keepdims=False, dtype=None):
     if dtype is not None:
         x = x.to(to_torch_dtype(dtype))
     if axis is None:
-        r = torch.prod(x)
+        r = torch.prod(x, dtype=x.dtype)
         return r.reshape((1,) * x.ndim) if keepdims else r
     if not isinstance(axis, (list, tuple)):
         axis = (axis,)
     for a in sorted([a % x.ndim for a in axis], reverse=True):
-        x = torch.prod(x, dim=a, keepdim=keepdims)
+        x = torch.prod(x, dim=a, keepdim=keepdims, dtype=x.dtype)
     return x
 
 
@@ -717,9 +729,9 @@ def _nan_reduce(name, body):
 def nansum(x, axis=None, keepdims=False):
     x = _promote_sum_dtype(_t(x))
     if axis is None:
-        r = torch.nansum(x)
+        r = torch.nansum(x, dtype=x.dtype)
         return r.reshape((1,) * x.ndim) if keepdims else r
-    return torch.nansum(x, dim=_axis(axis), keepdim=keepdims)
+    return torch.nansum(x, dim=_axis(axis), keepdim=keepdims, dtype=x.dtype)
 
 
 @op("numpy")
@@ -950,7 +962,7 @@ def trace(x, offset=0, axis1=0, axis2=1):
     x = _t(x)
     if x.dtype in (torch.int8, torch.int16, torch.uint8, torch.bool):
         x = x.to(torch.int32)
-    return torch.sum(torch.diagonal(x, offset, axis1, axis2), dim=-1)
+    return torch.sum(torch.diagonal(x, offset, axis1, axis2), dim=-1, dtype=x.dtype)
 
 
 @op("numpy")

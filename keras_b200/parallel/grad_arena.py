@@ -1,0 +1,44 @@
+"""Flat gradient storage shared by the optimizer and the data-parallel reducer.
+
+Gradients of all trainable variables live in one buffer per dtype, in reverse creation order (the
+order in which backward produces them), each padded to 128 bytes.  ``param.grad`` is a view into
+the buffer, so autograd accumulates in place and every pointer is stable across steps.
+"""
+
+import torch
+
+
+class GradArena:
+    ALIGN = 32  # elements (128 bytes for fp32)
+
+    def __init__(self, variables):
+        self.signature = tuple(id(v) for v in variables)
+        self.variables = list(variables)
+        params = [v._value for v in variables]
+        dev = params[0].device
+        self.offsets = {}
+        total = 0
+        # reverse order: the last layers' gradients are ready first and sit at the front
+        for idx in range(len(params) - 1, -1, -1):
+            p = params[idx]
+            self.offsets[idx] = total
+            n = p.numel()
+            total += (n + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.total = total
+        self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.views = []
+        for idx, p in enumerate(params):
+            off = self.offsets[idx]
+            if p.dtype == torch.float32:
+                self.views.append(self.flat[off:off + p.numel()].view(p.shape))
+            else:
+                self.views.append(None)
+
+    def bind(self):
+        for v, view in zip(self.variables, self.views):
+            p = v._value
+            if view is not None and p.grad is not view:
+                p.grad = view
+
+    def zero(self):
+        self.flat.zero_()

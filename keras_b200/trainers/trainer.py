@@ -271,17 +271,42 @@ class Trainer:
             if engine is not None:
                 engine.backward_and_apply(self, loss, trainable_weights)
             else:
+                arena = self._gradient_arena(trainable_weights)
                 params = [v._value for v in trainable_weights]
-                for p in params:
-                    p.grad = None
+                if arena is None:
+                    for p in params:
+                        p.grad = None
                 loss.backward()
                 grads = [p.grad for p in params]
-                self.optimizer.apply(grads, trainable_weights)
-                for p in params:
-                    p.grad = None
+                opt = self.optimizer
+                opt._fused_zeroed_grads = False
+                opt.apply(grads, trainable_weights)
+                if arena is None:
+                    for p in params:
+                        p.grad = None
+                elif not opt._fused_zeroed_grads:
+                    arena.zero()
         else:
             warnings.warn("The model does not have any trainable weights.")
         return self.compute_metrics(x, y, y_pred, sample_weight=sample_weight)
+
+    def _gradient_arena(self, trainable_weights):
+        """Persistent flat gradient storage: ``.grad`` of every trainable parameter is a view into
+        one buffer, so pointers are stable across steps (fused optimizer tables are built once, the
+        step is CUDA-graph friendly) and the optimizer kernel zeroes gradients as it consumes them."""
+        from keras_b200.kernels import dispatch
+
+        if not trainable_weights or not dispatch.enabled(trainable_weights[0]._value):
+            return None
+        arena = getattr(self, "_grad_arena", None)
+        sig = tuple(id(v) for v in trainable_weights)
+        if arena is None or arena.signature != sig:
+            from keras_b200.parallel.grad_arena import GradArena
+
+            arena = GradArena(trainable_weights)
+            self._grad_arena = arena
+        arena.bind()
+        return arena
 
     def test_step(self, data):
         x, y, sample_weight = data_adapter_utils.unpack_x_y_sample_weight(data)

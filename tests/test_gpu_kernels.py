@@ -1,0 +1,166 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references (needs a B200)."""
+
+import numpy as np
+import pytest
+import torch
+
+import keras_b200 as keras
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from keras_b200.kernels import ops
+
+    return ops
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("relu,res", [(False, False), (True, False), (True, True)])
+def test_fused_batchnorm_forward_backward(dtype, tol, relu, res):
+    torch.manual_seed(0)
+    N, H, W, C = 6, 9, 7, 64
+    x = (torch.randn(N, H, W, C, device="cuda") * 2 + 0.5).to(dtype).requires_grad_(True)
+    r = torch.randn(N, H, W, C, device="cuda").to(dtype).requires_grad_(True) if res else None
+    gamma = (torch.rand(C, device="cuda") + 0.5).requires_grad_(True)
+    beta = torch.randn(C, device="cuda").requires_grad_(True)
+    mm, mv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    y = _ops().FusedBatchNormAct.apply(x, gamma, beta, r, mm, mv, 0.9, 1e-3, relu)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    # fp32 reference
+    xf = x.detach().float().requires_grad_(True)
+    rf = r.detach().float().requires_grad_(True) if res else None
+    gf, bf = gamma.detach().clone().requires_grad_(True), beta.detach().clone().requires_grad_(True)
+    mean = xf.mean((0, 1, 2))
+    var = (xf * xf).mean((0, 1, 2)) - mean * mean
+    ref = (xf - mean) * torch.rsqrt(var + 1e-3) * gf + bf
+    if res:
+        ref = ref + rf
+    if relu:
+        ref = torch.relu(ref)
+    ref.backward(dy.float())
+    assert torch.allclose(y.float(), ref, atol=tol * 4, rtol=tol)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=tol * 4, rtol=tol * 4)
+    assert torch.allclose(gamma.grad, gf.grad, atol=tol * 40, rtol=tol * 4)
+    assert torch.allclose(beta.grad, bf.grad, atol=tol * 40, rtol=tol * 4)
+    if res:
+        assert torch.allclose(r.grad.float(), rf.grad, atol=tol * 4, rtol=tol)
+    assert torch.allclose(mm, 0.1 * mean.detach(), atol=1e-2, rtol=1e-2)
+    assert torch.allclose(mv, 0.9 + 0.1 * var.detach(), atol=1e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("D", [768, 1000, 4096])
+def test_fused_norm(dtype, tol, rms, D):
+    torch.manual_seed(1)
+    x = torch.randn(37, D, device="cuda").to(dtype).requires_grad_(True)
+    g = (torch.rand(D, device="cuda") + 0.5).requires_grad_(True)
+    b = None if rms else torch.randn(D, device="cuda").requires_grad_(True)
+    y = _ops().FusedNorm.apply(x, g, b, 1e-5, rms)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_(True)
+    gf = g.detach().clone().requires_grad_(True)
+    if rms:
+        ref = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-5) * gf
+    else:
+        bf = b.detach().clone().requires_grad_(True)
+        ref = torch.nn.functional.layer_norm(xf, (D,), gf, bf, 1e-5)
+    ref.backward(dy.float())
+    assert torch.allclose(y.float(), ref, atol=tol * 4, rtol=tol)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=tol * 4, rtol=tol * 4)
+    assert torch.allclose(g.grad, gf.grad, atol=tol * 40, rtol=tol * 4)
+    if not rms:
+        assert torch.allclose(b.grad, bf.grad, atol=tol * 40, rtol=tol * 4)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("V", [1000, 50257])
+def test_fused_softmax_cross_entropy(dtype, tol, V):
+    torch.manual_seed(2)
+    logits = (torch.randn(19, V, device="cuda") * 3).to(dtype).requires_grad_(True)
+    labels = torch.randint(0, V, (19,), device="cuda")
+    loss = _ops().FusedSoftmaxXent.apply(logits, labels)
+    w = torch.rand(19, device="cuda")
+    (loss.float() * w).sum().backward()
+    lf = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, labels, reduction="none")
+    (ref * w).sum().backward()
+    assert torch.allclose(loss.float(), ref, atol=tol * 4, rtol=tol)
+    assert torch.allclose(logits.grad.float(), lf.grad, atol=tol, rtol=tol * 4)
+
+
+def test_fused_optimizers_match_eager_rules():
+    torch.manual_seed(3)
+    shapes = [(64, 33), (7,), (3, 3, 16, 32), (1000,)]
+    for kind in ("adam", "sgd"):
+        vs = [keras.Variable(torch.randn(s).numpy()) for s in shapes]
+        ref = [v.numpy().astype("float64") for v in vs]
+        if kind == "adam":
+            opt = keras.optimizers.AdamW(1e-2, weight_decay=0.1)
+        else:
+            opt = keras.optimizers.SGD(1e-2, momentum=0.9, nesterov=True)
+        m = [np.zeros_like(r) for r in ref]
+        vv = [np.zeros_like(r) for r in ref]
+        grads = [torch.zeros(s, device="cuda") for s in shapes]
+        for t in range(1, 4):
+            gs = [torch.randn(s, device="cuda") for s in shapes]
+            for dst, src in zip(grads, gs):
+                dst.copy_(src)
+            opt.apply(grads, vs)
+            assert opt._fused_zeroed_grads and all(float(g.abs().sum()) == 0.0 for g in grads)
+            for i, g in enumerate(gs):
+                g = g.cpu().numpy().astype("float64")
+                if kind == "adam":
+                    ref[i] *= 1 - 0.1 * 1e-2
+                    m[i] += (g - m[i]) * 0.1
+                    vv[i] += (g * g - vv[i]) * 0.001
+                    alpha = 1e-2 * np.sqrt(1 - 0.999 ** t) / (1 - 0.9 ** t)
+                    ref[i] -= alpha * m[i] / (np.sqrt(vv[i]) + 1e-7)
+                else:
+                    m[i] = 0.9 * m[i] - 1e-2 * g
+                    ref[i] += 0.9 * m[i] - 1e-2 * g
+        for v, r in zip(vs, ref):
+            np.testing.assert_allclose(v.numpy(), r, rtol=2e-4, atol=2e-5)
+
+
+def test_resnet_step_fused_matches_unfused(monkeypatch):
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(8, 64, 64, 3)).astype("float32")
+    y = rng.integers(0, 10, size=(8,))
+
+    def run(disable):
+        keras.backend.clear_session(free_memory=False)
+        keras.config.set_dtype_policy("mixed_bfloat16")
+        keras.utils.set_random_seed(7)
+        monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "1" if disable else "0")
+        model = keras.applications.ResNet50(weights=None, input_shape=(64, 64, 3), classes=10)
+        model.compile(optimizer=keras.optimizers.SGD(0.01, momentum=0.9), loss="sparse_categorical_crossentropy")
+        return [model.train_on_batch(x, y) for _ in range(3)], model
+
+    fused, mf = run(False)
+    plain, mp = run(True)
+    assert all(np.isfinite(fused)) and all(np.isfinite(plain))
+    assert abs(fused[0] - plain[0]) < 0.05 * abs(plain[0]) + 0.05
+    from keras_b200.kernels import ops
+
+    assert ops.launch_count() > 0
+
+
+def test_training_on_gpu_transformer_block():
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    inp = keras.Input((64,), dtype="int32")
+    h = keras.layers.Embedding(1000, 128)(inp)
+    h = keras.layers.LayerNormalization()(h)
+    h = keras.layers.Dense(256, activation="gelu")(h)
+    out = keras.layers.Dense(1000)(h)
+    model = keras.Model(inp, out)
+    model.compile(optimizer=keras.optimizers.AdamW(1e-3, weight_decay=0.01), loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
+    rng = np.random.default_rng(0)
+    x = rng.integers(0, 1000, size=(16, 64))
+    y = rng.integers(0, 1000, size=(16, 64))
+    losses = [model.train_on_batch(x, y) for _ in range(8)]
+    assert np.isfinite(losses).all() and losses[-1] < losses[0]
