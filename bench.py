@@ -135,6 +135,14 @@ def run_ours(args, cfg):
 
     for i in range(args.warmup):
         dev_step(i)
+    if args.profile_range:
+        # one step between cudaProfilerStart/Stop for `ncu --profile-from-start off`
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        dev_step(0)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return
     sampler = ClockSampler(local)
     sampler.start()
     launches0 = kops.launch_count()
@@ -270,6 +278,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="resnet50", choices=sorted(CONFIGS))
+    ap.add_argument("--profile-range", action="store_true", help="run warm-up, then one step inside cudaProfilerStart/Stop, and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -5,7 +5,11 @@
 // by: one statistics pass (per-channel sum / sum of squares, fp32 accumulation, E[x^2]-E[x]^2
 // variance as the reference), a C-sized finalize (scale/shift, moving statistics update) and one
 // apply pass y = relu(x*scale + shift + residual) with bf16 or fp32 I/O.  Backward is one
-// reduction pass plus one apply pass.
+// reduction pass, a C-sized coefficient kernel and one apply pass dx = A*dy' + B*x + C.
+//
+// All passes are HBM-bound.  Work split: a thread owns one 16-byte channel vector for the whole
+// kernel (its per-channel coefficients live in registers, no index arithmetic per element) and
+// walks rows with four independent 16-byte loads in flight per tensor.
 #include "common.cuh"
 
 template <typename T>
@@ -13,34 +17,55 @@ struct Vec;
 template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
-  using Raw = bf16x8;
-  __device__ static void load(const __nv_bfloat16* p, float* f) { unpack8(*reinterpret_cast<const bf16x8*>(p), f); }
+  using Raw = uint4;
+  __device__ static Raw load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static void unpack(const Raw& r, float* f) { unpack8(reinterpret_cast<const bf16x8&>(r), f); }
   __device__ static void store(__nv_bfloat16* p, const float* f) { *reinterpret_cast<bf16x8*>(p) = pack8(f); }
 };
 template <>
 struct Vec<float> {
   static constexpr int N = 4;
-  __device__ static void load(const float* p, float* f) {
-    float4 v = *reinterpret_cast<const float4*>(p);
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-  }
+  using Raw = float4;
+  __device__ static Raw load_raw(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  __device__ static void unpack(const Raw& v, float* f) { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
   __device__ static void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
 };
 
-constexpr int BN_CX = 32;  // channel vectors per block (one warp wide)
-constexpr int BN_RY = 8;   // row lanes per block
+constexpr int BN_THREADS = 256;
+constexpr int BN_U = 4;  // rows in flight per thread
+
+struct BnGeom {
+  int cx;       // channel vectors per block (power of two <= 32)
+  int ry;       // row lanes per block = 256 / cx
+  int gy;       // blocks along channels
+  int gx;       // blocks along rows
+};
+
+static BnGeom bn_geom(long long M, int cvecs, int blocks_per_sm) {
+  BnGeom g;
+  g.cx = 1;
+  while (g.cx < 32 && g.cx < cvecs) g.cx <<= 1;
+  g.ry = BN_THREADS / g.cx;
+  g.gy = (cvecs + g.cx - 1) / g.cx;
+  long long want = (148ll * blocks_per_sm + g.gy - 1) / g.gy;
+  long long maxb = (M + (long long)g.ry * BN_U - 1) / ((long long)g.ry * BN_U);
+  long long gx = want < maxb ? want : maxb;
+  g.gx = (int)(gx < 1 ? 1 : gx);
+  return g;
+}
 
 // sums[0:C] += sum_rows a(row, c);  sums[C:2C] += sum_rows b(row, c)
 // MODE 0 (forward stats): a = x, b = x*x
 // MODE 1 (backward):      a = dy', b = dy' * xhat, dy' = dy * (y > 0 if relu)
 template <typename T, int MODE>
-__global__ void __launch_bounds__(BN_CX* BN_RY) bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ y,
-                                                                const float* __restrict__ mean, const float* __restrict__ invstd,
-                                                                long long M, int C, float* __restrict__ sums) {
+__global__ void __launch_bounds__(BN_THREADS, 2) bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ y,
+                                                              const float* __restrict__ mean, const float* __restrict__ invstd, long long M,
+                                                              int C, int cx_log2, float* __restrict__ sums) {
   constexpr int V = Vec<T>::N;
-  const int cv = blockIdx.y * BN_CX + threadIdx.x;  // channel-vector index
-  const int cvecs = C / V;
-  const bool active = cv < cvecs;
+  const int cx = 1 << cx_log2, ry = BN_THREADS >> cx_log2;
+  const int tx = threadIdx.x & (cx - 1), ty = threadIdx.x >> cx_log2;
+  const int cv = blockIdx.y * cx + tx;
+  const bool active = cv < C / V;
   const int c0 = cv * V;
   float sa[V], sb[V], mu[V], is[V];
 #pragma unroll
@@ -50,46 +75,64 @@ __global__ void __launch_bounds__(BN_CX* BN_RY) bn_reduce_kernel(const T* __rest
     for (int k = 0; k < V; ++k) { mu[k] = mean[c0 + k]; is[k] = invstd[c0 + k]; }
   }
   if (active) {
-    for (long long r = (long long)blockIdx.x * BN_RY + threadIdx.y; r < M; r += (long long)gridDim.x * BN_RY) {
-      float xv[V];
-      Vec<T>::load(x + r * C + c0, xv);
-      if (MODE == 0) {
+    const long long step = (long long)gridDim.x * ry * BN_U;
+    for (long long r0 = (long long)blockIdx.x * ry * BN_U + ty; r0 < M; r0 += step) {
+      typename Vec<T>::Raw rx[BN_U], rd[BN_U], rm[BN_U];
 #pragma unroll
-        for (int k = 0; k < V; ++k) { sa[k] += xv[k]; sb[k] += xv[k] * xv[k]; }
-      } else {
-        float dv[V];
-        Vec<T>::load(dy + r * C + c0, dv);
-        if (y != nullptr) {
-          float yv[V];
-          Vec<T>::load(y + r * C + c0, yv);
-#pragma unroll
-          for (int k = 0; k < V; ++k) dv[k] = yv[k] > 0.f ? dv[k] : 0.f;
+      for (int u = 0; u < BN_U; ++u) {
+        const long long r = r0 + (long long)u * ry;
+        if (r < M) {
+          rx[u] = Vec<T>::load_raw(x + r * C + c0);
+          if (MODE == 1) {
+            rd[u] = Vec<T>::load_raw(dy + r * C + c0);
+            if (y != nullptr) rm[u] = Vec<T>::load_raw(y + r * C + c0);
+          }
         }
+      }
 #pragma unroll
-        for (int k = 0; k < V; ++k) { sa[k] += dv[k]; sb[k] += dv[k] * (xv[k] - mu[k]) * is[k]; }
+      for (int u = 0; u < BN_U; ++u) {
+        if (r0 + (long long)u * ry >= M) continue;
+        float xv[V];
+        Vec<T>::unpack(rx[u], xv);
+        if (MODE == 0) {
+#pragma unroll
+          for (int k = 0; k < V; ++k) { sa[k] += xv[k]; sb[k] += xv[k] * xv[k]; }
+        } else {
+          float dv[V], yv[V];
+          Vec<T>::unpack(rd[u], dv);
+          if (y != nullptr) Vec<T>::unpack(rm[u], yv);
+#pragma unroll
+          for (int k = 0; k < V; ++k) {
+            const float d = (y != nullptr && !(yv[k] > 0.f)) ? 0.f : dv[k];
+            sa[k] += d;
+            sb[k] += d * (xv[k] - mu[k]) * is[k];
+          }
+        }
       }
     }
   }
-  __shared__ float red[2][BN_RY][BN_CX][Vec<T>::N + 1];
+  // reduce over the row lanes of the block, then one atomic per channel per block
+  __shared__ float red[2][BN_THREADS][Vec<T>::N + 1];
 #pragma unroll
-  for (int k = 0; k < V; ++k) { red[0][threadIdx.y][threadIdx.x][k] = sa[k]; red[1][threadIdx.y][threadIdx.x][k] = sb[k]; }
+  for (int k = 0; k < V; ++k) { red[0][threadIdx.x][k] = sa[k]; red[1][threadIdx.x][k] = sb[k]; }
   __syncthreads();
-  if (threadIdx.y == 0 && active) {
+  if (ty == 0 && active) {
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       float a = 0.f, b = 0.f;
-#pragma unroll
-      for (int j = 0; j < BN_RY; ++j) { a += red[0][j][threadIdx.x][k]; b += red[1][j][threadIdx.x][k]; }
+      for (int j = 0; j < ry; ++j) { a += red[0][j * cx + tx][k]; b += red[1][j * cx + tx][k]; }
       atomicAdd(&sums[c0 + k], a);
       atomicAdd(&sums[C + c0 + k], b);
     }
   }
 }
 
+// pre_bias: bias of the producing convolution that was folded away (the normalised output does not
+// depend on it; only the moving mean does).
 __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                   float* __restrict__ moving_mean, float* __restrict__ moving_var, float momentum, float eps, float inv_m,
-                                   int C, float* __restrict__ mean_out, float* __restrict__ invstd_out, float* __restrict__ scale_out,
-                                   float* __restrict__ shift_out) {
+                                   const float* __restrict__ pre_bias, float* __restrict__ moving_mean, float* __restrict__ moving_var,
+                                   float momentum, float eps, float inv_m, int C, float* __restrict__ mean_out, float* __restrict__ invstd_out,
+                                   float* __restrict__ scale_out, float* __restrict__ shift_out) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const float mean = sums[c] * inv_m;
@@ -100,73 +143,93 @@ __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* 
   invstd_out[c] = invstd;
   scale_out[c] = g * invstd;
   shift_out[c] = b - mean * g * invstd;
-  if (moving_mean) moving_mean[c] = moving_mean[c] * momentum + mean * (1.f - momentum);
+  const float full_mean = mean + (pre_bias ? pre_bias[c] : 0.f);
+  if (moving_mean) moving_mean[c] = moving_mean[c] * momentum + full_mean * (1.f - momentum);
   if (moving_var) moving_var[c] = moving_var[c] * momentum + var * (1.f - momentum);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, T* __restrict__ y,
-                                                       const float* __restrict__ scale, const float* __restrict__ shift, long long nvec, int C,
-                                                       int relu) {
+// Backward coefficients: dx = A*dy' + B*x + Cc
+__global__ void bn_bwd_coeff_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
+                                    const float* __restrict__ invstd, float inv_m, int C, float* __restrict__ coef) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float g = gamma ? gamma[c] : 1.f, is = invstd[c], mu = mean[c];
+  const float s1 = sums[c] * inv_m, s2 = sums[C + c] * inv_m;
+  const float a = g * is;
+  coef[c] = a;
+  coef[C + c] = -a * is * s2;
+  coef[2 * C + c] = a * (mu * is * s2 - s1);
+}
+
+// MODE 0: y  = relu?(x*p0 + p1 (+ res))                      (p0 = scale, p1 = shift)
+// MODE 1: dx = p0*dy' + p1*x + p2, dres = dy'                 (in0 = dy, in1 = x, mask from y)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __restrict__ in0, const T* __restrict__ in1, const T* __restrict__ ymask,
+                                                             T* __restrict__ out0, T* __restrict__ out1, const float* __restrict__ p0,
+                                                             const float* __restrict__ p1, const float* __restrict__ p2, long long M, int C,
+                                                             int cx_log2, int relu) {
   constexpr int V = Vec<T>::N;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    const long long e = i * V;
-    const int c0 = (int)(e % C);
-    float xv[V];
-    Vec<T>::load(x + e, xv);
+  const int cx = 1 << cx_log2, ry = BN_THREADS >> cx_log2;
+  const int tx = threadIdx.x & (cx - 1), ty = threadIdx.x >> cx_log2;
+  const int cv = blockIdx.y * cx + tx;
+  if (cv >= C / V) return;
+  const int c0 = cv * V;
+  float a[V], b[V], cc[V];
 #pragma unroll
-    for (int k = 0; k < V; ++k) xv[k] = xv[k] * scale[c0 + k] + shift[c0 + k];
-    if (res != nullptr) {
-      float rv[V];
-      Vec<T>::load(res + e, rv);
+  for (int k = 0; k < V; ++k) {
+    a[k] = p0[c0 + k];
+    b[k] = p1[c0 + k];
+    cc[k] = (MODE == 1) ? p2[c0 + k] : 0.f;
+  }
+  const long long step = (long long)gridDim.x * ry * BN_U;
+  for (long long r0 = (long long)blockIdx.x * ry * BN_U + ty; r0 < M; r0 += step) {
+    typename Vec<T>::Raw q0[BN_U], q1[BN_U], qm[BN_U];
 #pragma unroll
-      for (int k = 0; k < V; ++k) xv[k] += rv[k];
+    for (int u = 0; u < BN_U; ++u) {
+      const long long r = r0 + (long long)u * ry;
+      if (r < M) {
+        const long long e = r * C + c0;
+        q0[u] = Vec<T>::load_raw(in0 + e);
+        if (in1 != nullptr) q1[u] = Vec<T>::load_raw(in1 + e);
+        if (MODE == 1 && ymask != nullptr) qm[u] = Vec<T>::load_raw(ymask + e);
+      }
     }
-    if (relu) {
 #pragma unroll
-      for (int k = 0; k < V; ++k) xv[k] = fmaxf(xv[k], 0.f);
+    for (int u = 0; u < BN_U; ++u) {
+      const long long r = r0 + (long long)u * ry;
+      if (r >= M) continue;
+      const long long e = r * C + c0;
+      float o[V], v0[V], v1[V];
+      Vec<T>::unpack(q0[u], v0);
+      if (in1 != nullptr) Vec<T>::unpack(q1[u], v1);
+      if (MODE == 0) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          float t = v0[k] * a[k] + b[k];
+          if (in1 != nullptr) t += v1[k];
+          o[k] = relu ? fmaxf(t, 0.f) : t;
+        }
+        Vec<T>::store(out0 + e, o);
+      } else {
+        float vm[V];
+        if (ymask != nullptr) Vec<T>::unpack(qm[u], vm);
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          const float d = (ymask != nullptr && !(vm[k] > 0.f)) ? 0.f : v0[k];
+          v0[k] = d;
+          o[k] = a[k] * d + b[k] * v1[k] + cc[k];
+        }
+        Vec<T>::store(out0 + e, o);
+        if (out1 != nullptr) Vec<T>::store(out1 + e, v0);
+      }
     }
-    Vec<T>::store(y + e, xv);
   }
 }
 
-// dx = scale * (dy' - sum_dy/M - xhat * sum_dy_xhat/M);  dres = dy'
-template <typename T>
-__global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y,
-                                                           const float* __restrict__ mean, const float* __restrict__ invstd,
-                                                           const float* __restrict__ gamma, const float* __restrict__ sums, T* __restrict__ dx,
-                                                           T* __restrict__ dres, long long nvec, int C, float inv_m) {
-  constexpr int V = Vec<T>::N;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    const long long e = i * V;
-    const int c0 = (int)(e % C);
-    float dv[V], xv[V], out[V];
-    Vec<T>::load(dy + e, dv);
-    Vec<T>::load(x + e, xv);
-    if (y != nullptr) {
-      float yv[V];
-      Vec<T>::load(y + e, yv);
-#pragma unroll
-      for (int k = 0; k < V; ++k) dv[k] = yv[k] > 0.f ? dv[k] : 0.f;
-    }
-#pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const int c = c0 + k;
-      const float is = invstd[c];
-      const float xhat = (xv[k] - mean[c]) * is;
-      const float g = gamma ? gamma[c] : 1.f;
-      out[k] = g * is * (dv[k] - sums[c] * inv_m - xhat * sums[C + c] * inv_m);
-    }
-    Vec<T>::store(dx + e, out);
-    if (dres != nullptr) Vec<T>::store(dres + e, dv);
-  }
-}
-
-static inline int bn_grid_rows(long long M, int col_tiles) {
-  long long want = (148ll * 8 + col_tiles - 1) / col_tiles;
-  long long maxb = (M + BN_RY - 1) / BN_RY;
-  long long g = want < maxb ? want : maxb;
-  return (int)(g < 1 ? 1 : g);
+static inline int ilog2(int v) {
+  int l = 0;
+  while ((1 << l) < v) ++l;
+  return l;
 }
 
 template <typename T>
@@ -175,12 +238,12 @@ static int bn_reduce_launch(int mode, const void* x, const void* dy, const void*
   constexpr int V = Vec<T>::N;
   if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
   cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, stream);
-  const int col_tiles = (C / V + BN_CX - 1) / BN_CX;
-  dim3 grid(bn_grid_rows(M, col_tiles), col_tiles), block(BN_CX, BN_RY);
+  const BnGeom g = bn_geom(M, C / V, 4);
+  dim3 grid(g.gx, g.gy);
   if (mode == 0)
-    bn_reduce_kernel<T, 0><<<grid, block, 0, stream>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, M, C, sums);
+    bn_reduce_kernel<T, 0><<<grid, BN_THREADS, 0, stream>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, M, C, ilog2(g.cx), sums);
   else
-    bn_reduce_kernel<T, 1><<<grid, block, 0, stream>>>((const T*)x, (const T*)dy, (const T*)y, mean, invstd, M, C, sums);
+    bn_reduce_kernel<T, 1><<<grid, BN_THREADS, 0, stream>>>((const T*)x, (const T*)dy, (const T*)y, mean, invstd, M, C, ilog2(g.cx), sums);
   KB_CHECK_LAUNCH("bn_reduce");
   return 0;
 }
@@ -191,28 +254,32 @@ KB_API int kb200_bn_stats(const void* x, long long M, int C, int dtype, float* s
                     : bn_reduce_launch<float>(0, x, nullptr, nullptr, nullptr, nullptr, M, C, sums, stream);
 }
 
-KB_API int kb200_bn_finalize(const float* sums, const float* gamma, const float* beta, float* moving_mean, float* moving_var, float momentum,
-                             float eps, long long M, int C, float* mean_out, float* invstd_out, float* scale_out, float* shift_out,
-                             cudaStream_t stream) {
-  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, beta, moving_mean, moving_var, momentum, eps, 1.f / (float)M, C, mean_out,
-                                                          invstd_out, scale_out, shift_out);
+KB_API int kb200_bn_finalize(const float* sums, const float* gamma, const float* beta, const float* pre_bias, float* moving_mean,
+                             float* moving_var, float momentum, float eps, long long M, int C, float* mean_out, float* invstd_out,
+                             float* scale_out, float* shift_out, cudaStream_t stream) {
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, beta, pre_bias, moving_mean, moving_var, momentum, eps, 1.f / (float)M, C,
+                                                          mean_out, invstd_out, scale_out, shift_out);
   KB_CHECK_LAUNCH("bn_finalize");
+  return 0;
+}
+
+template <typename T>
+static int bn_apply_launch(const void* x, const void* res, void* y, const float* scale, const float* shift, long long M, int C, int relu,
+                           cudaStream_t stream) {
+  constexpr int V = Vec<T>::N;
+  if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
+  const BnGeom g = bn_geom(M, C / V, 6);
+  dim3 grid(g.gx, g.gy);
+  bn_apply_kernel<T, 0><<<grid, BN_THREADS, 0, stream>>>((const T*)x, (const T*)res, nullptr, (T*)y, nullptr, scale, shift, nullptr, M, C,
+                                                        ilog2(g.cx), relu);
+  KB_CHECK_LAUNCH("bn_apply");
   return 0;
 }
 
 KB_API int kb200_bn_apply(const void* x, const void* res, void* y, const float* scale, const float* shift, long long M, int C, int relu, int dtype,
                           cudaStream_t stream) {
-  const int V = dtype == 1 ? 8 : 4;
-  if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
-  const long long nvec = M * C / V;
-  int blocks = (int)((nvec + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  if (dtype == 1)
-    bn_apply_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (__nv_bfloat16*)y, scale, shift, nvec, C, relu);
-  else
-    bn_apply_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, (const float*)res, (float*)y, scale, shift, nvec, C, relu);
-  KB_CHECK_LAUNCH("bn_apply");
-  return 0;
+  return dtype == 1 ? bn_apply_launch<__nv_bfloat16>(x, res, y, scale, shift, M, C, relu, stream)
+                    : bn_apply_launch<float>(x, res, y, scale, shift, M, C, relu, stream);
 }
 
 KB_API int kb200_bn_bwd_reduce(const void* dy, const void* x, const void* y, const float* mean, const float* invstd, long long M, int C, int dtype,
@@ -221,20 +288,25 @@ KB_API int kb200_bn_bwd_reduce(const void* dy, const void* x, const void* y, con
                     : bn_reduce_launch<float>(1, x, dy, y, mean, invstd, M, C, sums, stream);
 }
 
-KB_API int kb200_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean, const float* invstd, const float* gamma,
-                              const float* sums, void* dx, void* dres, long long M, int C, int dtype, cudaStream_t stream) {
-  const int V = dtype == 1 ? 8 : 4;
-  if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
-  const long long nvec = M * C / V;
-  int blocks = (int)((nvec + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  const float inv_m = 1.f / (float)M;
-  if (dtype == 1)
-    bn_bwd_apply_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, mean, invstd, gamma, sums,
-                                                                  (__nv_bfloat16*)dx, (__nv_bfloat16*)dres, nvec, C, inv_m);
-  else
-    bn_bwd_apply_kernel<float><<<blocks, 256, 0, stream>>>((const float*)dy, (const float*)x, (const float*)y, mean, invstd, gamma, sums, (float*)dx, (float*)dres, nvec,
-                                                          C, inv_m);
+template <typename T>
+static int bn_bwd_apply_launch(const void* dy, const void* x, const void* y, const float* coef, void* dx, void* dres, long long M, int C,
+                               cudaStream_t stream) {
+  constexpr int V = Vec<T>::N;
+  const BnGeom g = bn_geom(M, C / V, 4);
+  dim3 grid(g.gx, g.gy);
+  bn_apply_kernel<T, 1><<<grid, BN_THREADS, 0, stream>>>((const T*)dy, (const T*)x, (const T*)y, (T*)dx, (T*)dres, coef, coef + C, coef + 2 * C, M,
+                                                        C, ilog2(g.cx), 0);
   KB_CHECK_LAUNCH("bn_bwd_apply");
   return 0;
+}
+
+// coef: scratch of 3*C floats (written here)
+KB_API int kb200_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean, const float* invstd, const float* gamma,
+                              const float* sums, float* coef, void* dx, void* dres, long long M, int C, int dtype, cudaStream_t stream) {
+  const int V = dtype == 1 ? 8 : 4;
+  if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
+  bn_bwd_coeff_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, mean, invstd, 1.f / (float)M, C, coef);
+  KB_CHECK_LAUNCH("bn_bwd_coeff");
+  return dtype == 1 ? bn_bwd_apply_launch<__nv_bfloat16>(dy, x, y, coef, dx, dres, M, C, stream)
+                    : bn_bwd_apply_launch<float>(dy, x, y, coef, dx, dres, M, C, stream);
 }

@@ -12,3 +12,16 @@ void kb200_set_error(const char* msg) {
 KB_API const char* kb200_last_error() { return g_last_error; }
 
 KB_API int kb200_abi_version() { return 1; }
+
+// Make `device`'s primary context current on the calling thread.  Launchers are reached through
+// ctypes from arbitrary Python threads (e.g. the autograd engine's), which may not have touched
+// the CUDA runtime yet; driver-API helpers such as tensor-map encoding need a current context.
+KB_API int kb200_bind_device(int device) {
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) {
+    kb200_set_error(cudaGetErrorString(e));
+    return -1;
+  }
+  cudaFree(0);
+  return 0;
+}

@@ -69,7 +69,7 @@ def rms_norm(x, scale, eps):
     return _ops().FusedNorm.apply(x, scale, None, float(eps), True)
 
 
-def batch_norm(layer, inputs, training, residual=None, relu=False):
+def batch_norm(layer, inputs, training, residual=None, relu=False, pre_bias=None):
     """Fused channels-last BatchNorm (+residual)(+ReLU).  Returns ``None`` when not applicable."""
     x = inputs
     if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim < 2:
@@ -92,13 +92,13 @@ def batch_norm(layer, inputs, training, residual=None, relu=False):
     if training:
         if beta is None:
             beta = torch.zeros(C, dtype=torch.float32, device=x.device)
-        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu))
+        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu), pre_bias)
     if torch.is_grad_enabled() and (x.requires_grad or (gamma is not None and gamma.requires_grad and layer.trainable)):
         return None
     with torch.no_grad():
         inv = torch.rsqrt(mv + layer.epsilon)
         scale = inv * gamma if gamma is not None else inv
-        shift = -mm * scale
+        shift = -mm * scale if pre_bias is None else (pre_bias.float() - mm) * scale
         if beta is not None:
             shift = shift + beta
     return ops.bn_inference(x, scale.contiguous(), shift.contiguous(), residual, relu)

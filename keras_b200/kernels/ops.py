@@ -24,7 +24,17 @@ def _dt(t):
     raise TypeError(f"unsupported dtype {t.dtype}")
 
 
+import threading
+
+_TL = threading.local()
+
+
 def _stream():
+    """Current stream handle; also binds this thread to the current device on first use."""
+    dev = torch.cuda.current_device()
+    if getattr(_TL, "dev", None) != dev:
+        loader.get().kb200_bind_device(_i(dev))
+        _TL.dev = dev
     return _vp(torch.cuda.current_stream().cuda_stream)
 
 
@@ -69,7 +79,7 @@ class FusedBatchNormAct(torch.autograd.Function):
     """y = relu?(batchnorm_train(x) (+ residual)) for channels-last x, with moving-stat update."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu):
+    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu, pre_bias=None):
         lib = _lib()
         C = x.shape[-1]
         M = x.numel() // C
@@ -82,7 +92,7 @@ class FusedBatchNormAct(torch.autograd.Function):
         st = _stream()
         dt = _dt(x)
         _check(lib.kb200_bn_stats(_p(x), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_stats")
-        _check(lib.kb200_bn_finalize(_p(sums), _p(gamma), _p(beta), _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C),
+        _check(lib.kb200_bn_finalize(_p(sums), _p(gamma), _p(beta), _p(pre_bias), _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C),
                                      _p(mean), _p(invstd), _p(scale), _p(shift), st), "bn_finalize")
         res = residual.contiguous() if residual is not None else None
         _check(lib.kb200_bn_apply(_p(x), _p(res), _p(y), _p(scale), _p(shift), _ll(M), _i(C), _i(1 if relu else 0), _i(dt), st), "bn_apply")
@@ -100,16 +110,17 @@ class FusedBatchNormAct(torch.autograd.Function):
         mean, invstd = stats[:C], stats[C:2 * C]
         dy = dy.contiguous()
         dev = x.device
-        sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
+        sums = torch.empty(5 * C, dtype=torch.float32, device=dev)
+        coef = sums[2 * C:]
         dx = torch.empty_like(x)
         dres = torch.empty_like(x) if ctx.has_res else None
         st = _stream()
         dt = _dt(x)
         _check(lib.kb200_bn_bwd_reduce(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_bwd_reduce")
-        _check(lib.kb200_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
-        dgamma = sums[C:].clone() if gamma is not None else None
-        dbeta = sums[:C].clone()
-        return dx, dgamma, dbeta, dres, None, None, None, None, None
+        _check(lib.kb200_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(coef), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
+        dgamma = sums[C:2 * C] if gamma is not None else None
+        dbeta = sums[:C]
+        return dx, dgamma, dbeta, dres, None, None, None, None, None, None
 
 
 def bn_inference(x, scale, shift, residual, relu):

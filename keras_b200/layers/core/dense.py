@@ -76,7 +76,10 @@ class Dense(Layer):
         act = self.activation
         fused = dispatch.dense(inputs, kernel, self.bias, getattr(act, "__name__", None))
         if fused is not None:
-            return fused
+            out, act_done = fused
+            if not act_done and act is not None and act is not activations.linear:
+                out = act(out)
+            return out
         x = ops.matmul(inputs, kernel)
         if self.bias is not None:
             x = ops.add(x, self.bias)

@@ -20,11 +20,20 @@ from keras_b200.layers.normalization.normalization_layers import BatchNormalizat
 
 
 class Deferred:
-    __slots__ = ("layer", "x", "shape", "dtype", "device", "ndim")
+    __slots__ = ("layer", "x", "pre_bias", "shape", "dtype", "device", "ndim")
 
-    def __init__(self, layer, x):
-        self.layer, self.x = layer, x
+    def __init__(self, layer, x, pre_bias=None):
+        self.layer, self.x, self.pre_bias = layer, x, pre_bias
         self.shape, self.dtype, self.device, self.ndim = x.shape, x.dtype, x.device, x.ndim
+
+
+class NoBias:
+    """Output of a convolution whose bias add was folded into the following BatchNormalization."""
+
+    __slots__ = ("x", "bias")
+
+    def __init__(self, x, bias):
+        self.x, self.bias = x, bias
 
 
 def _is_relu(op):
@@ -70,21 +79,61 @@ def build_plan(function):
             if id(add_out) not in output_ids and len(cc) == 1 and _is_relu(cc[0].operation) and id(cc[0]) not in plan:
                 plan[id(c)] = "consume_add_relu"
                 plan[id(cc[0])] = "identity"
+    # Convolution bias feeding a fused BN: the normalised output does not depend on it (training
+    # mode) and its gradient is exactly zero, so the add and the bias-gradient reduction are dropped;
+    # the bias only enters the moving-mean update (and the shift in inference mode).
+    from keras_b200.layers.convolutional.base_conv import BaseConv
+
+    producers = {}
+    for n in nodes:
+        for t in n.outputs:
+            producers[id(t)] = n
+    for n in nodes:
+        if plan.get(id(n)) != "defer_bn":
+            continue
+        src = producers.get(id(n.input_tensors[0]))
+        if src is None or id(src) in plan:
+            continue
+        op = src.operation
+        if not isinstance(op, BaseConv) or not op.use_bias or op.lora_enabled or op.data_format != "channels_last":
+            continue
+        if getattr(op.activation, "__name__", "linear") != "linear" or op.activity_regularizer is not None:
+            continue
+        out = src.outputs[0]
+        if id(out) in output_ids or len(consumers.get(id(out), [])) != 1 or len(src.input_tensors) != 1:
+            continue
+        if n.operation.axis % len(out.shape) != len(out.shape) - 1:
+            continue
+        plan[id(src)] = "conv_fold_bias"
     return plan
+
+
+def run_conv_nobias(layer, x):
+    """The convolution of ``layer`` without its bias add (autocast applied as ``Layer.__call__`` would)."""
+    from keras_b200.core.variables import AutocastScope
+
+    td = layer._compute_torch_dtype()
+    if x.dtype != td and x.dtype.is_floating_point:
+        x = x.to(td)
+    with AutocastScope(layer.compute_dtype):
+        return layer.convolution_op(x, layer.kernel)
 
 
 def applicable(x):
     return isinstance(x, torch.Tensor) and x.is_cuda
 
 
-def run_bn(layer, x, training, residual=None, relu=False):
+def run_bn(layer, x, training, residual=None, relu=False, pre_bias=None):
     """Execute a (possibly fused) BatchNormalization outside of ``Layer.__call__``."""
     from keras_b200.kernels import dispatch
 
     train = bool(training) and layer.trainable
-    out = dispatch.batch_norm(layer, x, train, residual=residual, relu=relu)
+    bias_value = pre_bias._value if pre_bias is not None else None
+    out = dispatch.batch_norm(layer, x, train, residual=residual, relu=relu, pre_bias=bias_value)
     if out is not None:
         return out
+    if pre_bias is not None:
+        x = x + pre_bias.value.to(x.dtype)
     out = layer(x, training=training)
     if residual is not None:
         out = out + residual

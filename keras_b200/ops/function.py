@@ -128,24 +128,33 @@ class Function(Operation):
                 continue
             role = plan.get(id(node))
             outs = node.outputs
-            if role == "defer_bn":
+            if role == "conv_fold_bias":
                 x = env[id(ins[0])]
                 if isinstance(x, fusion.Deferred):
-                    x = fusion.run_bn(x.layer, x.x, training)
-                env[id(outs[0])] = fusion.Deferred(node.operation, x)
+                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
+                env[id(outs[0])] = fusion.NoBias(fusion.run_conv_nobias(node.operation, x), node.operation.bias)
+                continue
+            if role == "defer_bn":
+                x = env[id(ins[0])]
+                pre_bias = None
+                if isinstance(x, fusion.NoBias):
+                    x, pre_bias = x.x, x.bias
+                elif isinstance(x, fusion.Deferred):
+                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
+                env[id(outs[0])] = fusion.Deferred(node.operation, x, pre_bias)
                 continue
             if role == "consume_relu":
                 d = env[id(ins[0])]
-                env[id(outs[0])] = fusion.run_bn(d.layer, d.x, training, relu=True) if isinstance(d, fusion.Deferred) else node.operation(d)
+                env[id(outs[0])] = fusion.run_bn(d.layer, d.x, training, relu=True, pre_bias=d.pre_bias) if isinstance(d, fusion.Deferred) else node.operation(d)
                 continue
             if role in ("consume_add", "consume_add_relu"):
                 a, b = env[id(ins[0])], env[id(ins[1])]
                 if isinstance(a, fusion.Deferred) and isinstance(b, fusion.Deferred):
-                    b = fusion.run_bn(b.layer, b.x, training)
+                    b = fusion.run_bn(b.layer, b.x, training, pre_bias=b.pre_bias)
                 if isinstance(b, fusion.Deferred):
                     a, b = b, a
                 if isinstance(a, fusion.Deferred):
-                    env[id(outs[0])] = fusion.run_bn(a.layer, a.x, training, residual=b, relu=role == "consume_add_relu")
+                    env[id(outs[0])] = fusion.run_bn(a.layer, a.x, training, residual=b, relu=role == "consume_add_relu", pre_bias=a.pre_bias)
                 else:
                     r = node.operation([a, b])
                     env[id(outs[0])] = torch_relu(r) if role == "consume_add_relu" else r
@@ -165,7 +174,7 @@ class Function(Operation):
         for ref in self._outputs:
             v = env[id(ref)]
             if isinstance(v, fusion.Deferred):
-                v = fusion.run_bn(v.layer, v.x, training)
+                v = fusion.run_bn(v.layer, v.x, training, pre_bias=v.pre_bias)
             flat_out.append(v)
         return tree.pack_sequence_as(self._outputs_struct, flat_out)
 

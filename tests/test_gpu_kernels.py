@@ -164,3 +164,43 @@ def test_training_on_gpu_transformer_block():
     y = rng.integers(0, 1000, size=(16, 64))
     losses = [model.train_on_batch(x, y) for _ in range(8)]
     assert np.isfinite(losses).all() and losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 192), (1000, 264, 520), (4096, 1024, 768), (136, 8, 8)])
+def test_tcgen05_gemm_all_operand_majors(M, N, K):
+    from keras_b200.kernels import gemm
+
+    torch.manual_seed(0)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(K, N, device="cuda") * 0.5).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    ref = a.float() @ b.float()
+    out = gemm.gemm(a, b, 0, 1, M, N, K)                       # A K-major, B MN-major
+    gemm.check_errors()
+    assert torch.allclose(out.float(), ref, atol=0.06 * K ** 0.5, rtol=2e-2)
+    out = gemm.gemm(a, b.t().contiguous(), 0, 0, M, N, K, bias=bias, act=1, out_dtype=torch.float32)   # B K-major, fused bias+relu
+    gemm.check_errors()
+    assert torch.allclose(out, torch.relu(ref + bias), atol=0.06 * K ** 0.5, rtol=2e-2)
+    out = gemm.gemm(a.t().contiguous(), b, 1, 1, M, N, K)       # A MN-major, B MN-major
+    gemm.check_errors()
+    assert torch.allclose(out.float(), ref, atol=0.06 * K ** 0.5, rtol=2e-2)
+
+
+def test_tcgen05_gemm_autograd_matches_torch():
+    from keras_b200.kernels import gemm
+
+    torch.manual_seed(1)
+    x = torch.randn(512, 256, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(256, 384, device="cuda") * 0.1).bfloat16().requires_grad_(True)
+    b = torch.randn(384, device="cuda").requires_grad_(True)
+    y = gemm.GemmFn.apply(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gemm.check_errors()
+    xf, wf, bf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    ref = xf @ wf + bf
+    ref.backward(dy.float())
+    assert torch.allclose(y.float(), ref, atol=0.3, rtol=2e-2)
+    assert torch.allclose(x.grad.float(), xf.grad, atol=0.3, rtol=3e-2)
+    assert torch.allclose(w.grad.float(), wf.grad, atol=1.0, rtol=3e-2)
+    assert torch.allclose(b.grad, bf.grad, atol=0.5, rtol=2e-2)
