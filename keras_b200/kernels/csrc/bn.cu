@@ -32,7 +32,7 @@ struct Vec<float> {
 };
 
 constexpr int BN_THREADS = 256;
-constexpr int BN_U = 4;  // rows in flight per thread
+constexpr int BN_U = 4;  // rows in flight per thread (apply and backward-reduce kernels)
 
 struct BnGeom {
   int cx;       // channel vectors per block (power of two <= 32)
@@ -41,31 +41,67 @@ struct BnGeom {
   int gx;       // blocks along rows
 };
 
-static BnGeom bn_geom(long long M, int cvecs, int blocks_per_sm) {
+static int bn_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    sms = v;
+  }
+  return sms;
+}
+
+// Grid = one resident wave: `resident` blocks per SM (from the occupancy calculator), capped by the rows available.
+static BnGeom bn_geom(long long M, int cvecs, int resident, int rows_per_iter) {
   BnGeom g;
   g.cx = 1;
   while (g.cx < 32 && g.cx < cvecs) g.cx <<= 1;
   g.ry = BN_THREADS / g.cx;
   g.gy = (cvecs + g.cx - 1) / g.cx;
-  long long want = (148ll * blocks_per_sm + g.gy - 1) / g.gy;
-  long long maxb = (M + (long long)g.ry * BN_U - 1) / ((long long)g.ry * BN_U);
+  long long want = ((long long)bn_sm_count() * resident) / g.gy;
+  if (want < 1) want = 1;
+  long long maxb = (M + (long long)g.ry * rows_per_iter - 1) / ((long long)g.ry * rows_per_iter);
   long long gx = want < maxb ? want : maxb;
   g.gx = (int)(gx < 1 ? 1 : gx);
   return g;
 }
 
+template <typename K>
+static int bn_resident_blocks(K kernel) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, BN_THREADS, 0) != cudaSuccess || n < 1) n = 2;
+  return n;
+}
+
+// ReLU mask of a row vector: from the saved bit mask (one byte per thread vector), else from y > 0, else all ones.
+template <typename T>
+__device__ __forceinline__ unsigned bn_mask_bits(const typename Vec<T>::Raw& ry, bool have_y, const unsigned char* bits, long long vec_index) {
+  constexpr int V = Vec<T>::N;
+  if (bits != nullptr) return bits[vec_index];
+  if (!have_y) return 0xffu;
+  float yv[V];
+  Vec<T>::unpack(ry, yv);
+  unsigned m = 0;
+#pragma unroll
+  for (int k = 0; k < V; ++k) m |= (yv[k] > 0.f ? 1u : 0u) << k;
+  return m;
+}
+
 // sums[0:C] += sum_rows a(row, c);  sums[C:2C] += sum_rows b(row, c)
 // MODE 0 (forward stats): a = x, b = x*x
-// MODE 1 (backward):      a = dy', b = dy' * xhat, dy' = dy * (y > 0 if relu)
-template <typename T, int MODE>
+// MODE 1 (backward):      a = dy', b = dy' * xhat, dy' = dy * relu_mask
+template <typename T, int MODE, int U>
 __global__ void __launch_bounds__(BN_THREADS, 2) bn_reduce_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ y,
-                                                              const float* __restrict__ mean, const float* __restrict__ invstd, long long M,
-                                                              int C, int cx_log2, float* __restrict__ sums) {
+                                                              const unsigned char* __restrict__ bits, const float* __restrict__ mean,
+                                                              const float* __restrict__ invstd, long long M, int C, int cx_log2,
+                                                              float* __restrict__ sums) {
   constexpr int V = Vec<T>::N;
   const int cx = 1 << cx_log2, ry = BN_THREADS >> cx_log2;
   const int tx = threadIdx.x & (cx - 1), ty = threadIdx.x >> cx_log2;
+  const int cvecs = C / V;
   const int cv = blockIdx.y * cx + tx;
-  const bool active = cv < C / V;
+  const bool active = cv < cvecs;
   const int c0 = cv * V;
   float sa[V], sb[V], mu[V], is[V];
 #pragma unroll
@@ -75,22 +111,24 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_reduce_kernel(const T* __res
     for (int k = 0; k < V; ++k) { mu[k] = mean[c0 + k]; is[k] = invstd[c0 + k]; }
   }
   if (active) {
-    const long long step = (long long)gridDim.x * ry * BN_U;
-    for (long long r0 = (long long)blockIdx.x * ry * BN_U + ty; r0 < M; r0 += step) {
-      typename Vec<T>::Raw rx[BN_U], rd[BN_U], rm[BN_U];
+    const long long step = (long long)gridDim.x * ry * U;
+    for (long long r0 = (long long)blockIdx.x * ry * U + ty; r0 < M; r0 += step) {
+      typename Vec<T>::Raw rx[U], rd[U], rm[U];
+      unsigned mb[U];
 #pragma unroll
-      for (int u = 0; u < BN_U; ++u) {
+      for (int u = 0; u < U; ++u) {
         const long long r = r0 + (long long)u * ry;
         if (r < M) {
           rx[u] = Vec<T>::load_raw(x + r * C + c0);
           if (MODE == 1) {
             rd[u] = Vec<T>::load_raw(dy + r * C + c0);
-            if (y != nullptr) rm[u] = Vec<T>::load_raw(y + r * C + c0);
+            if (bits != nullptr) mb[u] = bits[r * cvecs + cv];
+            else if (y != nullptr) rm[u] = Vec<T>::load_raw(y + r * C + c0);
           }
         }
       }
 #pragma unroll
-      for (int u = 0; u < BN_U; ++u) {
+      for (int u = 0; u < U; ++u) {
         if (r0 + (long long)u * ry >= M) continue;
         float xv[V];
         Vec<T>::unpack(rx[u], xv);
@@ -98,12 +136,12 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_reduce_kernel(const T* __res
 #pragma unroll
           for (int k = 0; k < V; ++k) { sa[k] += xv[k]; sb[k] += xv[k] * xv[k]; }
         } else {
-          float dv[V], yv[V];
+          float dv[V];
           Vec<T>::unpack(rd[u], dv);
-          if (y != nullptr) Vec<T>::unpack(rm[u], yv);
+          const unsigned m = bits != nullptr ? mb[u] : bn_mask_bits<T>(rm[u], y != nullptr, nullptr, 0);
 #pragma unroll
           for (int k = 0; k < V; ++k) {
-            const float d = (y != nullptr && !(yv[k] > 0.f)) ? 0.f : dv[k];
+            const float d = ((m >> k) & 1u) ? dv[k] : 0.f;
             sa[k] += d;
             sb[k] += d * (xv[k] - mu[k]) * is[k];
           }
@@ -111,18 +149,30 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_reduce_kernel(const T* __res
       }
     }
   }
-  // reduce over the row lanes of the block, then one atomic per channel per block
-  __shared__ float red[2][BN_THREADS][Vec<T>::N + 1];
+  // lanes of a warp that own the same channel vector differ by multiples of cx
 #pragma unroll
-  for (int k = 0; k < V; ++k) { red[0][threadIdx.x][k] = sa[k]; red[1][threadIdx.x][k] = sb[k]; }
+  for (int k = 0; k < V; ++k) {
+    for (int o = 16; o >= cx; o >>= 1) {
+      sa[k] += __shfl_xor_sync(0xffffffffu, sa[k], o);
+      sb[k] += __shfl_xor_sync(0xffffffffu, sb[k], o);
+    }
+  }
+  __shared__ float red[BN_THREADS / 32][2][32 * V];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane < cx) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) { red[warp][0][lane * V + k] = sa[k]; red[warp][1][lane * V + k] = sb[k]; }
+  }
   __syncthreads();
-  if (ty == 0 && active) {
+  // warps whose lanes all map to tx = lane & (cx-1); every warp holds a partial for each of the cx vectors
+  for (int i = threadIdx.x; i < 2 * cx * V; i += BN_THREADS) {
+    const int which = i / (cx * V), j = i % (cx * V);
+    const int c = (blockIdx.y * cx) * V + j;
+    if (c < C) {
+      float a = 0.f;
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      float a = 0.f, b = 0.f;
-      for (int j = 0; j < ry; ++j) { a += red[0][j * cx + tx][k]; b += red[1][j * cx + tx][k]; }
-      atomicAdd(&sums[c0 + k], a);
-      atomicAdd(&sums[C + c0 + k], b);
+      for (int w = 0; w < BN_THREADS / 32; ++w) a += red[w][which][j];
+      atomicAdd(&sums[which * C + c], a);
     }
   }
 }
@@ -161,14 +211,15 @@ __global__ void bn_bwd_coeff_kernel(const float* __restrict__ sums, const float*
   coef[2 * C + c] = a * (mu * is * s2 - s1);
 }
 
-// MODE 0: y  = relu?(x*p0 + p1 (+ res))                      (p0 = scale, p1 = shift)
-// MODE 1: dx = p0*dy' + p1*x + p2, dres = dy'                 (in0 = dy, in1 = x, mask from y)
+// MODE 0: y  = relu?(x*p0 + p1 (+ res)), bits = (y > 0)      (p0 = scale, p1 = shift)
+// MODE 1: dx = p0*dy' + p1*x + p2, dres = dy'                 (in0 = dy, in1 = x, mask from bits or y)
 template <typename T, int MODE>
 __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __restrict__ in0, const T* __restrict__ in1, const T* __restrict__ ymask,
-                                                             T* __restrict__ out0, T* __restrict__ out1, const float* __restrict__ p0,
-                                                             const float* __restrict__ p1, const float* __restrict__ p2, long long M, int C,
-                                                             int cx_log2, int relu) {
+                                                             unsigned char* __restrict__ bits, T* __restrict__ out0, T* __restrict__ out1,
+                                                             const float* __restrict__ p0, const float* __restrict__ p1,
+                                                             const float* __restrict__ p2, long long M, int C, int cx_log2, int relu) {
   constexpr int V = Vec<T>::N;
+  const int cvecs = C / V;
   const int cx = 1 << cx_log2, ry = BN_THREADS >> cx_log2;
   const int tx = threadIdx.x & (cx - 1), ty = threadIdx.x >> cx_log2;
   const int cv = blockIdx.y * cx + tx;
@@ -184,6 +235,7 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __rest
   const long long step = (long long)gridDim.x * ry * BN_U;
   for (long long r0 = (long long)blockIdx.x * ry * BN_U + ty; r0 < M; r0 += step) {
     typename Vec<T>::Raw q0[BN_U], q1[BN_U], qm[BN_U];
+    unsigned mb[BN_U];
 #pragma unroll
     for (int u = 0; u < BN_U; ++u) {
       const long long r = r0 + (long long)u * ry;
@@ -191,7 +243,10 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __rest
         const long long e = r * C + c0;
         q0[u] = Vec<T>::load_raw(in0 + e);
         if (in1 != nullptr) q1[u] = Vec<T>::load_raw(in1 + e);
-        if (MODE == 1 && ymask != nullptr) qm[u] = Vec<T>::load_raw(ymask + e);
+        if (MODE == 1) {
+          if (bits != nullptr) mb[u] = bits[r * cvecs + cv];
+          else if (ymask != nullptr) qm[u] = Vec<T>::load_raw(ymask + e);
+        }
       }
     }
 #pragma unroll
@@ -203,19 +258,21 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __rest
       Vec<T>::unpack(q0[u], v0);
       if (in1 != nullptr) Vec<T>::unpack(q1[u], v1);
       if (MODE == 0) {
+        unsigned m = 0;
 #pragma unroll
         for (int k = 0; k < V; ++k) {
           float t = v0[k] * a[k] + b[k];
           if (in1 != nullptr) t += v1[k];
+          m |= (t > 0.f ? 1u : 0u) << k;
           o[k] = relu ? fmaxf(t, 0.f) : t;
         }
         Vec<T>::store(out0 + e, o);
+        if (bits != nullptr) bits[r * cvecs + cv] = (unsigned char)m;
       } else {
-        float vm[V];
-        if (ymask != nullptr) Vec<T>::unpack(qm[u], vm);
+        const unsigned m = bits != nullptr ? mb[u] : bn_mask_bits<T>(qm[u], ymask != nullptr, nullptr, 0);
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-          const float d = (ymask != nullptr && !(vm[k] > 0.f)) ? 0.f : v0[k];
+          const float d = ((m >> k) & 1u) ? v0[k] : 0.f;
           v0[k] = d;
           o[k] = a[k] * d + b[k] * v1[k] + cc[k];
         }
@@ -233,25 +290,31 @@ static inline int ilog2(int v) {
 }
 
 template <typename T>
-static int bn_reduce_launch(int mode, const void* x, const void* dy, const void* y, const float* mean, const float* invstd, long long M, int C,
-                            float* sums, cudaStream_t stream) {
+static int bn_reduce_launch(int mode, const void* x, const void* dy, const void* y, const unsigned char* bits, const float* mean,
+                            const float* invstd, long long M, int C, float* sums, cudaStream_t stream) {
   constexpr int V = Vec<T>::N;
+  constexpr int U0 = 8;
   if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
   cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, stream);
-  const BnGeom g = bn_geom(M, C / V, 4);
-  dim3 grid(g.gx, g.gy);
-  if (mode == 0)
-    bn_reduce_kernel<T, 0><<<grid, BN_THREADS, 0, stream>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, M, C, ilog2(g.cx), sums);
-  else
-    bn_reduce_kernel<T, 1><<<grid, BN_THREADS, 0, stream>>>((const T*)x, (const T*)dy, (const T*)y, mean, invstd, M, C, ilog2(g.cx), sums);
+  if (mode == 0) {
+    static const int resident = bn_resident_blocks(bn_reduce_kernel<T, 0, U0>);
+    const BnGeom g = bn_geom(M, C / V, resident, U0);
+    bn_reduce_kernel<T, 0, U0><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, M, C,
+                                                                           ilog2(g.cx), sums);
+  } else {
+    static const int resident = bn_resident_blocks(bn_reduce_kernel<T, 1, BN_U>);
+    const BnGeom g = bn_geom(M, C / V, resident, BN_U);
+    bn_reduce_kernel<T, 1, BN_U><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, (const T*)dy, (const T*)y, bits, mean, invstd, M, C,
+                                                                             ilog2(g.cx), sums);
+  }
   KB_CHECK_LAUNCH("bn_reduce");
   return 0;
 }
 
 // dtype: 0 = float32, 1 = bfloat16
 KB_API int kb200_bn_stats(const void* x, long long M, int C, int dtype, float* sums, cudaStream_t stream) {
-  return dtype == 1 ? bn_reduce_launch<__nv_bfloat16>(0, x, nullptr, nullptr, nullptr, nullptr, M, C, sums, stream)
-                    : bn_reduce_launch<float>(0, x, nullptr, nullptr, nullptr, nullptr, M, C, sums, stream);
+  return dtype == 1 ? bn_reduce_launch<__nv_bfloat16>(0, x, nullptr, nullptr, nullptr, nullptr, nullptr, M, C, sums, stream)
+                    : bn_reduce_launch<float>(0, x, nullptr, nullptr, nullptr, nullptr, nullptr, M, C, sums, stream);
 }
 
 KB_API int kb200_bn_finalize(const float* sums, const float* gamma, const float* beta, const float* pre_bias, float* moving_mean,
@@ -264,49 +327,76 @@ KB_API int kb200_bn_finalize(const float* sums, const float* gamma, const float*
 }
 
 template <typename T>
-static int bn_apply_launch(const void* x, const void* res, void* y, const float* scale, const float* shift, long long M, int C, int relu,
-                           cudaStream_t stream) {
+static int bn_apply_launch(const void* x, const void* res, void* y, unsigned char* bits, const float* scale, const float* shift, long long M,
+                           int C, int relu, cudaStream_t stream) {
   constexpr int V = Vec<T>::N;
   if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
-  const BnGeom g = bn_geom(M, C / V, 6);
-  dim3 grid(g.gx, g.gy);
-  bn_apply_kernel<T, 0><<<grid, BN_THREADS, 0, stream>>>((const T*)x, (const T*)res, nullptr, (T*)y, nullptr, scale, shift, nullptr, M, C,
-                                                        ilog2(g.cx), relu);
+  static const int resident = bn_resident_blocks(bn_apply_kernel<T, 0>);
+  const BnGeom g = bn_geom(M, C / V, resident, BN_U);
+  bn_apply_kernel<T, 0><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, (const T*)res, nullptr, bits, (T*)y, nullptr, scale, shift,
+                                                                    nullptr, M, C, ilog2(g.cx), relu);
   KB_CHECK_LAUNCH("bn_apply");
   return 0;
 }
 
 KB_API int kb200_bn_apply(const void* x, const void* res, void* y, const float* scale, const float* shift, long long M, int C, int relu, int dtype,
                           cudaStream_t stream) {
-  return dtype == 1 ? bn_apply_launch<__nv_bfloat16>(x, res, y, scale, shift, M, C, relu, stream)
-                    : bn_apply_launch<float>(x, res, y, scale, shift, M, C, relu, stream);
+  return dtype == 1 ? bn_apply_launch<__nv_bfloat16>(x, res, y, nullptr, scale, shift, M, C, relu, stream)
+                    : bn_apply_launch<float>(x, res, y, nullptr, scale, shift, M, C, relu, stream);
+}
+
+// As kb200_bn_apply, and also writes the ReLU mask: one byte per 16-byte vector of y (bit k = element k > 0),
+// M * C / V bytes with V = 8 (bf16) or 4 (fp32).  The backward entry points read it instead of y.
+KB_API int kb200_bn_apply_mask(const void* x, const void* res, void* y, unsigned char* bits, const float* scale, const float* shift, long long M,
+                               int C, int relu, int dtype, cudaStream_t stream) {
+  return dtype == 1 ? bn_apply_launch<__nv_bfloat16>(x, res, y, bits, scale, shift, M, C, relu, stream)
+                    : bn_apply_launch<float>(x, res, y, bits, scale, shift, M, C, relu, stream);
 }
 
 KB_API int kb200_bn_bwd_reduce(const void* dy, const void* x, const void* y, const float* mean, const float* invstd, long long M, int C, int dtype,
                                float* sums, cudaStream_t stream) {
-  return dtype == 1 ? bn_reduce_launch<__nv_bfloat16>(1, x, dy, y, mean, invstd, M, C, sums, stream)
-                    : bn_reduce_launch<float>(1, x, dy, y, mean, invstd, M, C, sums, stream);
+  return dtype == 1 ? bn_reduce_launch<__nv_bfloat16>(1, x, dy, y, nullptr, mean, invstd, M, C, sums, stream)
+                    : bn_reduce_launch<float>(1, x, dy, y, nullptr, mean, invstd, M, C, sums, stream);
 }
 
 template <typename T>
-static int bn_bwd_apply_launch(const void* dy, const void* x, const void* y, const float* coef, void* dx, void* dres, long long M, int C,
-                               cudaStream_t stream) {
+static int bn_bwd_apply_launch(const void* dy, const void* x, const void* y, const unsigned char* bits, const float* coef, void* dx, void* dres,
+                               long long M, int C, cudaStream_t stream) {
   constexpr int V = Vec<T>::N;
-  const BnGeom g = bn_geom(M, C / V, 4);
-  dim3 grid(g.gx, g.gy);
-  bn_apply_kernel<T, 1><<<grid, BN_THREADS, 0, stream>>>((const T*)dy, (const T*)x, (const T*)y, (T*)dx, (T*)dres, coef, coef + C, coef + 2 * C, M,
-                                                        C, ilog2(g.cx), 0);
+  static const int resident = bn_resident_blocks(bn_apply_kernel<T, 1>);
+  const BnGeom g = bn_geom(M, C / V, resident, BN_U);
+  bn_apply_kernel<T, 1><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)dy, (const T*)x, (const T*)y, const_cast<unsigned char*>(bits),
+                                                                    (T*)dx, (T*)dres, coef, coef + C, coef + 2 * C, M, C, ilog2(g.cx), 0);
   KB_CHECK_LAUNCH("bn_bwd_apply");
   return 0;
+}
+
+static int bn_bwd_apply_any(const void* dy, const void* x, const void* y, const unsigned char* bits, const float* mean, const float* invstd,
+                            const float* gamma, const float* sums, float* coef, void* dx, void* dres, long long M, int C, int dtype,
+                            cudaStream_t stream) {
+  const int V = dtype == 1 ? 8 : 4;
+  if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
+  bn_bwd_coeff_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, mean, invstd, 1.f / (float)M, C, coef);
+  KB_CHECK_LAUNCH("bn_bwd_coeff");
+  return dtype == 1 ? bn_bwd_apply_launch<__nv_bfloat16>(dy, x, y, bits, coef, dx, dres, M, C, stream)
+                    : bn_bwd_apply_launch<float>(dy, x, y, bits, coef, dx, dres, M, C, stream);
 }
 
 // coef: scratch of 3*C floats (written here)
 KB_API int kb200_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean, const float* invstd, const float* gamma,
                               const float* sums, float* coef, void* dx, void* dres, long long M, int C, int dtype, cudaStream_t stream) {
-  const int V = dtype == 1 ? 8 : 4;
-  if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
-  bn_bwd_coeff_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, mean, invstd, 1.f / (float)M, C, coef);
-  KB_CHECK_LAUNCH("bn_bwd_coeff");
-  return dtype == 1 ? bn_bwd_apply_launch<__nv_bfloat16>(dy, x, y, coef, dx, dres, M, C, stream)
-                    : bn_bwd_apply_launch<float>(dy, x, y, coef, dx, dres, M, C, stream);
+  return bn_bwd_apply_any(dy, x, y, nullptr, mean, invstd, gamma, sums, coef, dx, dres, M, C, dtype, stream);
+}
+
+// Backward with the ReLU mask taken from the bit mask of kb200_bn_apply_mask (bits may be null: no ReLU).
+KB_API int kb200_bn_bwd_reduce_mask(const void* dy, const void* x, const unsigned char* bits, const float* mean, const float* invstd, long long M,
+                                    int C, int dtype, float* sums, cudaStream_t stream) {
+  return dtype == 1 ? bn_reduce_launch<__nv_bfloat16>(1, x, dy, nullptr, bits, mean, invstd, M, C, sums, stream)
+                    : bn_reduce_launch<float>(1, x, dy, nullptr, bits, mean, invstd, M, C, sums, stream);
+}
+
+KB_API int kb200_bn_bwd_apply_mask(const void* dy, const void* x, const unsigned char* bits, const float* mean, const float* invstd,
+                                   const float* gamma, const float* sums, float* coef, void* dx, void* dres, long long M, int C, int dtype,
+                                   cudaStream_t stream) {
+  return bn_bwd_apply_any(dy, x, nullptr, bits, mean, invstd, gamma, sums, coef, dx, dres, M, C, dtype, stream);
 }

@@ -104,6 +104,37 @@ def batch_norm(layer, inputs, training, residual=None, relu=False, pre_bias=None
     return ops.bn_inference(x, scale.contiguous(), shift.contiguous(), residual, relu)
 
 
+def max_pool2d(x, pool_size, strides, padding, zero_pad=None):
+    """Channels-last 2-D max pooling; ``zero_pad=((top, bottom), (left, right))`` folds a preceding ZeroPadding2D.
+
+    Returns ``None`` when not applicable."""
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim != 4 or x.numel() == 0:
+        return None
+    N, H, W, C = x.shape
+    if C % (8 if x.dtype == torch.bfloat16 else 4) != 0 or pool_size[0] * pool_size[1] > 255:
+        return None
+    if zero_pad is not None:
+        if padding != "valid":
+            return None
+        (pt, pb), (pl, pr) = zero_pad
+        OH = (H + pt + pb - pool_size[0]) // strides[0] + 1
+        OW = (W + pl + pr - pool_size[1]) // strides[1] + 1
+        mode = 1
+    elif padding == "same":
+        OH, OW = -(-H // strides[0]), -(-W // strides[1])
+        pt = max((OH - 1) * strides[0] + pool_size[0] - H, 0) // 2
+        pl = max((OW - 1) * strides[1] + pool_size[1] - W, 0) // 2
+        mode = 0
+    else:
+        OH = (H - pool_size[0]) // strides[0] + 1
+        OW = (W - pool_size[1]) // strides[1] + 1
+        pt = pl = 0
+        mode = 0
+    if OH <= 0 or OW <= 0:
+        return None
+    return _ops().FusedMaxPool2D.apply(x, tuple(pool_size), tuple(strides), (pt, pl), (OH, OW), mode)
+
+
 def softmax_cross_entropy(logits, labels):
     if not enabled(logits) or logits.dtype not in _FLOAT_IO or logits.numel() == 0:
         return None

@@ -56,7 +56,7 @@ def launch_count():
 def _check(code, what):
     _LAUNCHES[0] += 1
     if code != 0:
-        msg = ctypes.c_char_p(_lib().kb200_last_error()).value if False else b""
+        msg = b""
         try:
             fn = _lib().kb200_last_error
             fn.restype = ctypes.c_char_p
@@ -66,15 +66,37 @@ def _check(code, what):
         raise RuntimeError(f"{what} failed with code {code}: {msg.decode(errors='ignore')}")
 
 
+# ------------------------------------------------------------------------------ max pooling
+class FusedMaxPool2D(torch.autograd.Function):
+    """Channels-last 2-D max pooling with the padding folded in (``pad_mode`` 1: zeros, 0: ignored)."""
+
+    @staticmethod
+    def forward(ctx, x, pool, strides, pads, out_hw, pad_mode):
+        lib = _lib()
+        x = x.contiguous()
+        N, H, W, C = x.shape
+        OH, OW = out_hw
+        y = torch.empty((N, OH, OW, C), dtype=x.dtype, device=x.device)
+        idx = torch.empty((N, OH, OW, C), dtype=torch.uint8, device=x.device)
+        _check(lib.kb200_maxpool2d_fwd(_p(x), _p(y), _p(idx), _i(N), _i(H), _i(W), _i(C), _i(OH), _i(OW), _i(pool[0]), _i(pool[1]), _i(strides[0]),
+                                       _i(strides[1]), _i(pads[0]), _i(pads[1]), _i(pad_mode), _i(_dt(x)), _stream()), "maxpool_fwd")
+        ctx.save_for_backward(idx)
+        ctx.geom = (N, H, W, C, OH, OW, pool, strides, pads, _dt(x))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        (idx,) = ctx.saved_tensors
+        N, H, W, C, OH, OW, pool, strides, pads, dt = ctx.geom
+        dy = dy.contiguous()
+        dx = torch.empty((N, H, W, C), dtype=dy.dtype, device=dy.device)
+        _check(lib.kb200_maxpool2d_bwd(_p(dy), _p(idx), _p(dx), _i(N), _i(H), _i(W), _i(C), _i(OH), _i(OW), _i(pool[0]), _i(pool[1]), _i(strides[0]),
+                                       _i(strides[1]), _i(pads[0]), _i(pads[1]), _i(dt), _stream()), "maxpool_bwd")
+        return dx, None, None, None, None, None
+
+
 # ------------------------------------------------------------------------------ batch norm
-class _BNState:
-    """Per-layer scratch reused across steps (sums / mean / invstd / scale / shift), keyed by C."""
-
-    def __init__(self, C, device):
-        self.sums = torch.empty(2 * C, dtype=torch.float32, device=device)
-        self.bsums = torch.empty(2 * C, dtype=torch.float32, device=device)
-
-
 class FusedBatchNormAct(torch.autograd.Function):
     """y = relu?(batchnorm_train(x) (+ residual)) for channels-last x, with moving-stat update."""
 
@@ -95,8 +117,13 @@ class FusedBatchNormAct(torch.autograd.Function):
         _check(lib.kb200_bn_finalize(_p(sums), _p(gamma), _p(beta), _p(pre_bias), _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C),
                                      _p(mean), _p(invstd), _p(scale), _p(shift), st), "bn_finalize")
         res = residual.contiguous() if residual is not None else None
-        _check(lib.kb200_bn_apply(_p(x), _p(res), _p(y), _p(scale), _p(shift), _ll(M), _i(C), _i(1 if relu else 0), _i(dt), st), "bn_apply")
-        ctx.save_for_backward(x, y if relu else None, gamma, stats)
+        bits = None
+        if relu:
+            bits = torch.empty(M * (C // (8 if dt == 1 else 4)), dtype=torch.uint8, device=dev)
+            _check(lib.kb200_bn_apply_mask(_p(x), _p(res), _p(y), _p(bits), _p(scale), _p(shift), _ll(M), _i(C), _i(1), _i(dt), st), "bn_apply")
+        else:
+            _check(lib.kb200_bn_apply(_p(x), _p(res), _p(y), _p(scale), _p(shift), _ll(M), _i(C), _i(0), _i(dt), st), "bn_apply")
+        ctx.save_for_backward(x, bits, gamma, stats)
         ctx.relu = relu
         ctx.has_res = residual is not None
         ctx.dims = (M, C)
@@ -105,7 +132,7 @@ class FusedBatchNormAct(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         lib = _lib()
-        x, y, gamma, stats = ctx.saved_tensors
+        x, bits, gamma, stats = ctx.saved_tensors
         M, C = ctx.dims
         mean, invstd = stats[:C], stats[C:2 * C]
         dy = dy.contiguous()
@@ -116,8 +143,8 @@ class FusedBatchNormAct(torch.autograd.Function):
         dres = torch.empty_like(x) if ctx.has_res else None
         st = _stream()
         dt = _dt(x)
-        _check(lib.kb200_bn_bwd_reduce(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_bwd_reduce")
-        _check(lib.kb200_bn_bwd_apply(_p(dy), _p(x), _p(y), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(coef), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
+        _check(lib.kb200_bn_bwd_reduce_mask(_p(dy), _p(x), _p(bits), _p(mean), _p(invstd), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_bwd_reduce")
+        _check(lib.kb200_bn_bwd_apply_mask(_p(dy), _p(x), _p(bits), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(coef), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
         dgamma = sums[C:2 * C] if gamma is not None else None
         dbeta = sums[:C]
         return dx, dgamma, dbeta, dres, None, None, None, None, None, None

@@ -289,12 +289,12 @@ class Functional(Function, Model):
 
 
 class _FusionCtx:
-    __slots__ = ("mod", "training", "Deferred", "NoBias", "run_bn", "run_conv_nobias", "build_plan", "applicable")
+    __slots__ = ("mod", "training", "Deferred", "NoBias", "run_bn", "run_conv_nobias", "run_pool_padded", "Padded", "build_plan", "applicable")
 
     def __init__(self, mod, training):
         self.mod, self.training = mod, training
         self.Deferred, self.NoBias, self.run_bn, self.build_plan, self.applicable = mod.Deferred, mod.NoBias, mod.run_bn, mod.build_plan, mod.applicable
-        self.run_conv_nobias = mod.run_conv_nobias
+        self.run_conv_nobias, self.run_pool_padded, self.Padded = mod.run_conv_nobias, mod.run_pool_padded, mod.Padded
 
 
 def functional_from_config(cls, config, custom_objects=None):

@@ -27,6 +27,15 @@ class Deferred:
         self.shape, self.dtype, self.device, self.ndim = x.shape, x.dtype, x.device, x.ndim
 
 
+class Padded:
+    """Input of a folded ZeroPadding2D: the consumer applies ``pairs`` itself."""
+
+    __slots__ = ("x", "pairs")
+
+    def __init__(self, x, pairs):
+        self.x, self.pairs = x, pairs
+
+
 class NoBias:
     """Output of a convolution whose bias add was folded into the following BatchNormalization."""
 
@@ -62,9 +71,16 @@ def build_plan(function):
         if id(out) in output_ids:
             continue
         cons = consumers.get(id(out), [])
-        if len(cons) != 1 or id(cons[0]) in plan:
+        if len(cons) != 1:
             continue
         c = cons[0]
+        if plan.get(id(c)) in ("consume_add", "consume_add_relu"):
+            # second BN operand of an already planned Add: deferred too, so that its producing convolution can
+            # drop its bias; the executor materialises it before the fused BN+Add of the first operand
+            plan[id(n)] = "defer_bn"
+            continue
+        if id(c) in plan:
+            continue
         if _is_relu(c.operation) and len(c.input_tensors) == 1:
             plan[id(n)] = "defer_bn"
             plan[id(c)] = "consume_relu"
@@ -105,18 +121,55 @@ def build_plan(function):
         if n.operation.axis % len(out.shape) != len(out.shape) - 1:
             continue
         plan[id(src)] = "conv_fold_bias"
+    # ZeroPadding2D in front of a max pooling or of a bias-folded convolution ("valid" padding): the padded copy
+    # is never made; the pooling kernel and the convolution take the padding as a parameter.
+    from keras_b200.layers.pooling.pooling import MaxPooling2D
+    from keras_b200.layers.reshaping.reshaping_layers import ZeroPadding2D
+
+    for n in nodes:
+        op = n.operation
+        if not isinstance(op, ZeroPadding2D) or op.data_format != "channels_last" or id(n) in plan or len(n.input_tensors) != 1:
+            continue
+        out = n.outputs[0]
+        cons = consumers.get(id(out), [])
+        if id(out) in output_ids or len(cons) != 1:
+            continue
+        c = cons[0]
+        cop = c.operation
+        if isinstance(cop, MaxPooling2D) and cop.padding == "valid" and cop.data_format == "channels_last" and id(c) not in plan:
+            plan[id(n)] = "pad_fold"
+            plan[id(c)] = "pool_padded"
+        elif plan.get(id(c)) == "conv_fold_bias" and cop.rank == 2 and cop.padding == "valid" and all(lo == hi for lo, hi in op.padding):
+            plan[id(n)] = "pad_fold"
     return plan
 
 
-def run_conv_nobias(layer, x):
-    """The convolution of ``layer`` without its bias add (autocast applied as ``Layer.__call__`` would)."""
+def run_pool_padded(layer, x, pairs):
+    from keras_b200 import ops
+    from keras_b200.kernels import dispatch
+
+    out = dispatch.max_pool2d(x, layer.pool_size, layer.strides, "valid", zero_pad=pairs)
+    if out is not None:
+        return out
+    pads = [(0, 0), tuple(pairs[0]), tuple(pairs[1]), (0, 0)]
+    return layer(ops.pad(x, pads))
+
+
+def run_conv_nobias(layer, x, pairs=None):
+    """The convolution of ``layer`` without its bias add (autocast applied as ``Layer.__call__`` would).
+
+    ``pairs``: symmetric zero padding of a folded ZeroPadding2D, applied by the convolution itself."""
+    from keras_b200 import ops
     from keras_b200.core.variables import AutocastScope
 
     td = layer._compute_torch_dtype()
     if x.dtype != td and x.dtype.is_floating_point:
         x = x.to(td)
     with AutocastScope(layer.compute_dtype):
-        return layer.convolution_op(x, layer.kernel)
+        if pairs is None:
+            return layer.convolution_op(x, layer.kernel)
+        return ops.conv(x, layer.kernel, strides=list(layer.strides), padding=tuple(lo for lo, _ in pairs),
+                        dilation_rate=layer.dilation_rate, data_format=layer.data_format)
 
 
 def applicable(x):

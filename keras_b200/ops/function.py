@@ -128,11 +128,24 @@ class Function(Operation):
                 continue
             role = plan.get(id(node))
             outs = node.outputs
-            if role == "conv_fold_bias":
+            if role == "pad_fold":
                 x = env[id(ins[0])]
                 if isinstance(x, fusion.Deferred):
                     x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
-                env[id(outs[0])] = fusion.NoBias(fusion.run_conv_nobias(node.operation, x), node.operation.bias)
+                env[id(outs[0])] = fusion.Padded(x, node.operation.padding)
+                continue
+            if role == "pool_padded":
+                x = env[id(ins[0])]
+                env[id(outs[0])] = fusion.run_pool_padded(node.operation, x.x, x.pairs)
+                continue
+            if role == "conv_fold_bias":
+                x = env[id(ins[0])]
+                pairs = None
+                if isinstance(x, fusion.Padded):
+                    x, pairs = x.x, x.pairs
+                elif isinstance(x, fusion.Deferred):
+                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
+                env[id(outs[0])] = fusion.NoBias(fusion.run_conv_nobias(node.operation, x, pairs), node.operation.bias)
                 continue
             if role == "defer_bn":
                 x = env[id(ins[0])]

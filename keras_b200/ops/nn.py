@@ -236,6 +236,12 @@ def _pool(x, pool_size, strides, padding, data_format, kind):
     pool_size = _tuple(pool_size, nsp)
     strides = pool_size if strides is None else _tuple(strides, nsp)
     padding = padding.lower()
+    if kind == "max" and nsp == 2 and data_format == "channels_last" and x.is_cuda:
+        from keras_b200.kernels import dispatch
+
+        out = dispatch.max_pool2d(x, pool_size, strides, padding)
+        if out is not None:
+            return out
     xc = _to_cf(x, data_format)
     fn_max = {1: F.max_pool1d, 2: F.max_pool2d, 3: F.max_pool3d}[nsp]
     fn_avg = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nsp]
@@ -331,7 +337,9 @@ def conv(inputs, kernel, strides=1, padding="valid", data_format=None, dilation_
     groups = in_ch // kin
     kt = _conv_kernel_to_torch(k)
     pad = 0
-    if padding.lower() == "same":
+    if not isinstance(padding, str):
+        pad = _tuple(padding, nsp)  # explicit symmetric zero padding per spatial dimension
+    elif padding.lower() == "same":
         xc, pad = _explicit_same(xc, tuple(k.shape[:nsp]), strides, dilation)
     elif padding.lower() == "causal":
         left = (k.shape[0] - 1) * dilation[0]

@@ -204,3 +204,31 @@ def test_tcgen05_gemm_autograd_matches_torch():
     assert torch.allclose(x.grad.float(), xf.grad, atol=0.3, rtol=3e-2)
     assert torch.allclose(w.grad.float(), wf.grad, atol=1.0, rtol=3e-2)
     assert torch.allclose(b.grad, bf.grad, atol=0.5, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ["zero_pad", "same", "valid"])
+def test_fused_max_pool_matches_torch(dtype, case):
+    import torch.nn.functional as F
+
+    from keras_b200.kernels import dispatch
+
+    torch.manual_seed(0)
+    x = torch.randn(3, 13, 17, 16, device="cuda").to(dtype).requires_grad_(True)
+    xr = x.detach().float().requires_grad_(True)
+    if case == "zero_pad":
+        y = dispatch.max_pool2d(x, (3, 3), (2, 2), "valid", zero_pad=((1, 1), (1, 1)))
+        ref = F.max_pool2d(F.pad(xr.permute(0, 3, 1, 2), (1, 1, 1, 1)), 3, 2).permute(0, 2, 3, 1)
+    elif case == "same":
+        y = dispatch.max_pool2d(x, (3, 3), (2, 2), "same")
+        ref = F.max_pool2d(F.pad(xr.permute(0, 3, 1, 2), (1, 1, 1, 1), value=-float("inf")), 3, 2).permute(0, 2, 3, 1)
+    else:
+        y = dispatch.max_pool2d(x, (2, 3), (2, 1), "valid")
+        ref = F.max_pool2d(xr.permute(0, 3, 1, 2), (2, 3), (2, 1)).permute(0, 2, 3, 1)
+    assert y is not None and y.shape == ref.shape
+    torch.testing.assert_close(y.float(), ref, rtol=0, atol=0)
+    g = torch.randn_like(ref)
+    y.backward(g.to(dtype))
+    ref.backward(g.to(dtype).float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=1e-2 if dtype == torch.bfloat16 else 1e-6, atol=1e-2 if dtype == torch.bfloat16 else 1e-6)

@@ -164,4 +164,5 @@ def test_fusion_plan_on_resnet_block():
     assert model.count_params() == 23597957 or model.count_params() > 2e7
     plan = fusion.build_plan(model)
     roles = list(plan.values())
-    assert roles.count("defer_bn") == 49 and roles.count("consume_add_relu") == 16 and roles.count("consume_relu") == 33
+    assert roles.count("defer_bn") == 53 and roles.count("consume_add_relu") == 16 and roles.count("consume_relu") == 33
+    assert roles.count("conv_fold_bias") == 53 and roles.count("pad_fold") == 2 and roles.count("pool_padded") == 1
