@@ -180,6 +180,11 @@ def run_ours(args, cfg):
         }
         print(json.dumps(out))
     if world > 1:
+        torch.cuda.synchronize()
+        engine = getattr(model, "_parallel_engine", None)
+        if engine is not None:
+            engine.check(wait=True)
+            engine.close()
         dist.barrier()
         dist.destroy_process_group()
 

@@ -71,6 +71,7 @@ class Variable:
         self._overwrite_with_gradient = False
         self._layout = layout
         self._global_shape = None
+        self._shard_slices = None
         self._shard_spec = None
         self._value = None
         self._shadow = None
@@ -193,6 +194,11 @@ class Variable:
             # Uninitialized (created in a stateless scope): produce a throw-away value.
             v = self._initializer(self._shape, dtype=self._dtype)
             return self._maybe_autocast(convert_to_tensor(v, dtype=self._torch_dtype))
+        if self._shard_slices is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            if not tensor_parallel.in_local_shards():
+                return self._maybe_autocast(tensor_parallel.gather_variable(self))
         return self._maybe_autocast(self._value)
 
     def _maybe_autocast(self, value):
@@ -207,6 +213,8 @@ class Variable:
 
     def _direct_assign(self, value):
         with torch.no_grad():
+            if self._shard_slices is not None and tuple(value.shape) != tuple(self._value.shape):
+                value = value[self._shard_slices]
             self._value.copy_(value)
         if self._shadow is not None:
             self._shadow[2]()
@@ -241,6 +249,11 @@ class Variable:
                 return v
         if self._value is None:
             return convert_to_tensor(self._initializer(self._shape, dtype=self._dtype), dtype=self._torch_dtype)
+        if self._shard_slices is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            if not tensor_parallel.in_local_shards():
+                return tensor_parallel.gather_variable(self)
         return self._value
 
     @property

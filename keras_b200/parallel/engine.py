@@ -1,0 +1,168 @@
+"""Execution engines behind ``keras.distribution``: what runs when ``fit`` is called under a distribution.
+
+``DataParallelEngine`` is the counterpart of wrapping the model in DistributedDataParallel
+(keras/src/backend/torch/trainer.py:45-92) plus the per-variable metric all-reduce (:207-244):
+
+* at creation every variable (model and optimizer) is broadcast from the first rank of the replica group;
+* gradients of all trainable variables live in one flat arena (reverse creation order).  On CUDA the arena is
+  a symmetric buffer and one kernel pair per step all-reduces it in place over NVLink peer memory (mean over
+  replicas); the fused optimizer kernel then consumes and zeroes it.  With ``KERAS_B200_COMM=nccl`` or on CPU the
+  arena is reduced with one library all-reduce;
+* metric state is reduced as ONE packed buffer when results are read, and never written back.
+
+``ModelParallelEngine`` adds tensor-parallel variable shards on a second mesh axis (see ``tensor_parallel``).
+"""
+
+import torch
+import torch.distributed as dist
+
+from keras_b200.parallel import collectives, process_groups
+from keras_b200.parallel.grad_arena import GradArena
+
+
+def make_engine(distribution, model):
+    from keras_b200.distribution import distribution_lib
+
+    if isinstance(distribution, distribution_lib.ModelParallel):
+        return ModelParallelEngine(distribution, model)
+    return DataParallelEngine(distribution, model)
+
+
+class DataParallelEngine:
+    def __init__(self, distribution, model):
+        self.distribution = distribution
+        mesh = distribution.device_mesh
+        self.groups = mesh.backend_mesh
+        self.axis = distribution.batch_dim_name or mesh.axis_names[0]
+        self.group = self.groups.get_group(self.axis)
+        self.members = self.groups.members(self.axis)
+        self.world = len(self.members) if process_groups.is_initialized() else 1
+        self._arena = None
+        self._reducer = None
+        self._steps = 0
+        self._synced_ids = set()
+        self.sync_variables(model)
+
+    # -- variables -----------------------------------------------------------------------
+    def _replicated_variables(self, model):
+        vs = list(model.variables)
+        opt = getattr(model, "optimizer", None)
+        if opt is not None and getattr(opt, "built", False):
+            vs += list(opt.variables)
+        return vs
+
+    def sync_variables(self, model):
+        """Broadcast every not-yet-synchronised replicated variable from the first rank of the replica group."""
+        if self.world <= 1:
+            return
+        todo = [v for v in self._replicated_variables(model) if id(v) not in self._synced_ids and getattr(v, "_value", None) is not None]
+        if not todo:
+            return
+        src = self.members[0]
+        by_dtype = {}
+        for v in todo:
+            by_dtype.setdefault(v._value.dtype, []).append(v)
+        with torch.no_grad():
+            for dtype, vs in by_dtype.items():
+                flat = torch.cat([v._value.detach().reshape(-1) for v in vs]) if vs else None
+                if flat.dtype == torch.bool:
+                    flat = flat.to(torch.uint8)
+                collectives.broadcast(flat, src=src, group=self.group)
+                off = 0
+                for v in vs:
+                    n = v._value.numel()
+                    v._value.detach().copy_(flat[off:off + n].view(v._value.shape).to(v._value.dtype))
+                    off += n
+        for v in todo:
+            self._synced_ids.add(id(v))
+
+    # -- gradients -----------------------------------------------------------------------
+    def _gradient_arena(self, trainable_weights):
+        sig = tuple(id(v) for v in trainable_weights)
+        if self._arena is not None and self._arena.signature == sig:
+            return self._arena
+        params = [v._value for v in trainable_weights]
+        dev = params[0].device
+        if self._reducer is not None:
+            self._reducer.close()
+            self._reducer = None
+        flat = None
+        if self.world > 1 and collectives.use_p2p(dev) and all(p.dtype == torch.float32 for p in params):
+            numel = GradArena.required_numel(trainable_weights)
+            self._reducer = collectives.P2PAllReducer(numel, self.group, self.members)
+            flat = self._reducer.flat
+        self._arena = GradArena(trainable_weights, flat=flat)
+        return self._arena
+
+    def backward_and_apply(self, model, loss, trainable_weights):
+        opt = model.optimizer
+        first = self._steps == 0
+        if first:
+            if not opt.built:
+                opt.build(trainable_weights)
+            self.sync_variables(model)
+        arena = self._gradient_arena(trainable_weights)
+        arena.bind()
+        loss.backward()
+        if self.world > 1:
+            if self._reducer is not None:
+                if first:
+                    collectives.barrier()  # absorb start-up skew (lazy initialisation, autotuning) on the host
+                self._reducer.all_reduce(scale=1.0 / self.world)
+            else:
+                collectives.all_reduce(arena.flat, group=self.group)
+                arena.flat.div_(self.world)
+        params = [v._value for v in trainable_weights]
+        grads = [p.grad for p in params]
+        opt._fused_zeroed_grads = False
+        opt.apply(grads, trainable_weights)
+        if not opt._fused_zeroed_grads:
+            arena.zero()
+        self._steps += 1
+
+    # -- metrics -------------------------------------------------------------------------
+    def reduced_metric_state(self, model):
+        """[(variable, value summed over replicas)] with one packed all-reduce; variables are left untouched."""
+        vs = [v for v in model.metrics_variables if getattr(v, "_value", None) is not None]
+        if self.world <= 1 or not vs:
+            return []
+        with torch.no_grad():
+            flat = torch.cat([v._value.detach().reshape(-1).to(torch.float64) for v in vs])
+            collectives.all_reduce(flat, group=self.group)
+            out, off = [], 0
+            for v in vs:
+                n = v._value.numel()
+                out.append((v, flat[off:off + n].view(v._value.shape).to(v._value.dtype)))
+                off += n
+        return out
+
+    def sync_metrics(self, model):
+        return self.reduced_metric_state(model)
+
+    def check(self, wait=False):
+        if self._reducer is not None:
+            self._reducer.check(wait=wait)
+
+    def close(self):
+        if self._reducer is not None:
+            self._reducer.close()
+            self._reducer = None
+            self._arena = None
+
+
+class ModelParallelEngine(DataParallelEngine):
+    """Data parallel over ``batch_dim_name`` plus sharded variables on the remaining mesh axes.
+
+    Gradients of a sharded variable are reduced over the batch axis only (its shard differs between model-axis
+    peers); replicated variables receive partial gradients on every model-axis peer, which the tensor-parallel
+    layers already reduce through their backward collectives, so the same batch-axis reduction applies.
+    """
+
+    def __init__(self, distribution, model):
+        super().__init__(distribution, model)
+        from keras_b200.parallel import tensor_parallel
+
+        self.plan = tensor_parallel.plan_for_model(distribution, model)
+
+    def _replicated_variables(self, model):
+        return [v for v in super()._replicated_variables(model) if getattr(v, "_layout", None) is None or all(a is None for a in v._layout)]

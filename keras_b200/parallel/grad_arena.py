@@ -11,7 +11,11 @@ import torch
 class GradArena:
     ALIGN = 32  # elements (128 bytes for fp32)
 
-    def __init__(self, variables):
+    @classmethod
+    def required_numel(cls, variables):
+        return sum((v._value.numel() + cls.ALIGN - 1) // cls.ALIGN * cls.ALIGN for v in variables)
+
+    def __init__(self, variables, flat=None):
         self.signature = tuple(id(v) for v in variables)
         self.variables = list(variables)
         params = [v._value for v in variables]
@@ -25,7 +29,13 @@ class GradArena:
             n = p.numel()
             total += (n + self.ALIGN - 1) // self.ALIGN * self.ALIGN
         self.total = total
-        self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        if flat is not None:
+            if flat.numel() < total or flat.dtype != torch.float32:
+                raise ValueError("external gradient storage is too small")
+            flat.zero_()
+            self.flat = flat
+        else:
+            self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
         self.views = []
         for idx, p in enumerate(params):
             off = self.offsets[idx]

@@ -238,7 +238,17 @@ class Trainer:
         return self.get_metrics_result()
 
     def get_metrics_result(self):
-        self._sync_metrics()
+        engine = getattr(self, "_parallel_engine", None)
+        mapping = engine.reduced_metric_state(self) if engine is not None else []
+        if mapping:
+            from keras_b200.core.scopes import StatelessScope
+
+            # distributed: results come from the state summed over replicas; local state is left as it is
+            with StatelessScope(state_mapping=mapping):
+                return self._local_metrics_result()
+        return self._local_metrics_result()
+
+    def _local_metrics_result(self):
         return_metrics = LazyLogs()
         for metric in self.metrics:
             result = metric.result()
@@ -247,12 +257,6 @@ class Trainer:
             else:
                 return_metrics[metric.name] = result
         return return_metrics
-
-    def _sync_metrics(self):
-        """Hook for distributed runs: the parallel engine reduces packed metric state here."""
-        engine = getattr(self, "_parallel_engine", None)
-        if engine is not None:
-            engine.sync_metrics(self)
 
     # -- step functions ------------------------------------------------------------------
     def train_step(self, data):

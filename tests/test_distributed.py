@@ -1,0 +1,140 @@
+"""Multi-process paths on CPU (gloo, world size 2): data-parallel training equals large-batch training,
+packed metric reduction, sharded variables, host-side failure detection."""
+
+import os
+import socket
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _run(fn, world, *args, timeout=240):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    with tempfile.TemporaryDirectory() as tmp:
+        procs = [ctx.Process(target=_entry, args=(fn.__name__, r, world, port, tmp) + args) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout)
+        codes = [p.exitcode for p in procs]
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+        out = {}
+        for r in range(world):
+            f = os.path.join(tmp, f"out{r}.npz")
+            if os.path.exists(f):
+                out[r] = dict(np.load(f, allow_pickle=True))
+        return codes, out
+
+
+def _entry(fn_name, rank, world, port, tmp, *args):
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                       "KERAS_TORCH_DEVICE": "cpu", "CUDA_VISIBLE_DEVICES": ""})
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    torch.set_num_threads(1)
+    result = globals()[fn_name](rank, world, *args)
+    if result is not None:
+        np.savez(os.path.join(tmp, f"out{rank}.npz"), **result)
+
+
+def _make_model(keras):
+    keras.utils.set_random_seed(7)
+    inp = keras.Input((6,))
+    x = keras.layers.Dense(8, activation="relu")(inp)
+    out = keras.layers.Dense(3)(x)
+    m = keras.Model(inp, out)
+    m.compile(optimizer=keras.optimizers.SGD(0.1, momentum=0.9), loss=keras.losses.MeanSquaredError(), metrics=[keras.metrics.MeanAbsoluteError()])
+    return m
+
+
+def _data():
+    rng = np.random.RandomState(0)
+    return rng.randn(32, 6).astype("float32"), rng.randn(32, 3).astype("float32")
+
+
+def _dp_worker(rank, world):
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    dist = keras.distribution.DataParallel()
+    keras.distribution.set_distribution(dist)
+    m = _make_model(keras)
+    x, y = _data()
+    hist = m.fit(x, y, batch_size=4, epochs=2, shuffle=False, verbose=0)
+    w = {f"w{i}": v for i, v in enumerate(m.get_weights())}
+    w["loss"] = np.array(hist.history["loss"])
+    w["mae"] = np.array(hist.history["mean_absolute_error"])
+    return w
+
+
+def test_data_parallel_matches_large_batch():
+    codes, out = _run(_dp_worker, 2)
+    assert codes == [0, 0], codes
+    import keras_b200 as keras
+
+    m = _make_model(keras)
+    x, y = _data()
+    hist = m.fit(x, y, batch_size=8, epochs=2, shuffle=False, verbose=0)
+    ref = m.get_weights()
+    for r in (0, 1):
+        for i, w in enumerate(ref):
+            np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=1e-5, atol=1e-6)
+        # metrics and loss are reduced over replicas: both ranks report the global values
+        np.testing.assert_allclose(out[r]["mae"], hist.history["mean_absolute_error"], rtol=1e-5)
+        np.testing.assert_allclose(out[r]["loss"], hist.history["loss"], rtol=1e-5)
+
+
+def _tp_worker(rank, world):
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    mesh = keras.distribution.DeviceMesh((1, 2), ["batch", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["dense.*kernel"] = (None, "model")
+    lm["dense.*bias"] = ("model",)
+    keras.distribution.set_distribution(keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="batch"))
+    keras.utils.set_random_seed(3)
+    inp = keras.Input((6,))
+    out = keras.layers.Dense(8, name="dense")(inp)
+    m = keras.Model(inp, out)
+    m.compile(optimizer=keras.optimizers.SGD(0.05), loss="mse")
+    x, y = np.ones((4, 6), "float32"), np.zeros((4, 8), "float32")
+    k = m.layers[-1].kernel
+    local_shape = tuple(k._value.shape)
+    before = np.array(k.numpy(), copy=True)
+    m.train_on_batch(x, y)
+    after = k.numpy()
+    return {"local": np.array(local_shape), "global": np.array(tuple(k.shape)), "before": before, "after": after, "pred": m.predict(x, verbose=0)}
+
+
+def test_model_parallel_sharded_variables_match_unsharded():
+    codes, out = _run(_tp_worker, 2)
+    assert codes == [0, 0], codes
+    import keras_b200 as keras
+
+    keras.utils.set_random_seed(3)
+    inp = keras.Input((6,))
+    m = keras.Model(inp, keras.layers.Dense(8, name="dense")(inp))
+    m.compile(optimizer=keras.optimizers.SGD(0.05), loss="mse")
+    x, y = np.ones((4, 6), "float32"), np.zeros((4, 8), "float32")
+    before = np.array(m.layers[-1].kernel.numpy(), copy=True)
+    m.train_on_batch(x, y)
+    for r in (0, 1):
+        assert tuple(out[r]["local"]) == (6, 4) and tuple(out[r]["global"]) == (6, 8)
+        np.testing.assert_allclose(out[r]["before"], before, rtol=1e-6)
+        np.testing.assert_allclose(out[r]["after"], m.layers[-1].kernel.numpy(), rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(out[r]["pred"], m.predict(x, verbose=0), rtol=1e-5, atol=1e-6)
