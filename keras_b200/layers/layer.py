@@ -33,6 +33,8 @@ _TENSOR_TYPES = (torch.Tensor, KerasTensor)
 class _TrackedList(list):
     """List that reports inserted values to its owner layer (so appended sub-layers are tracked)."""
 
+    _tree_rebuild_as_list = True
+
     def __init__(self, owner, values=()):
         self._owner = owner
         super().__init__(owner._track_value(v) for v in values)
@@ -910,6 +912,14 @@ class Layer(Operation):
     # -- masks ---------------------------------------------------------------------------
     def compute_mask(self, inputs, previous_mask):
         return previous_mask
+
+    @property
+    def _call_has_training_arg(self):
+        return self._plan.has_training
+
+    @property
+    def _call_has_mask_arg(self):
+        return self._plan.has_mask
 
     def _set_output_mask(self, inputs, outputs, previous_mask):
         flat_out = tree.flatten(outputs)

@@ -79,6 +79,10 @@ def _children(x):
         tx = type(x)
 
         def rebuild(vals, _tx=tx):
+            if _tx is list or _tx is tuple:
+                return _tx(vals)
+            if getattr(_tx, "_tree_rebuild_as_list", False):
+                return list(vals)
             try:
                 return _tx(vals)
             except TypeError:
