@@ -60,4 +60,10 @@ _optional("keras_b200.layers.core.torch_module_wrapper", ["TorchModuleWrapper"])
 _optional("keras_b200.layers.core.ternary_dense", ["TernaryDense"])
 _optional("keras_b200.layers.preprocessing", ["DataLayer", "CategoryEncoding", "Discretization", "HashedCrossing", "Hashing", "MelSpectrogram",
                                                "Normalization", "Pipeline", "Rescaling", "STFTSpectrogram", "IndexLookup", "IntegerLookup",
-                                               "StringLookup", "TextVectorization"])
+                                               "StringLookup", "TextVectorization", "AugMix", "AutoContrast", "CenterCrop",
+                                               "ContrastLimitedAdaptiveHistogramEqualization", "CutMix", "Equalization", "MaxNumBoundingBoxes",
+                                               "MixUp", "RandAugment", "RandomBrightness", "RandomColorDegeneration", "RandomColorJitter",
+                                               "RandomContrast", "RandomCrop", "RandomElasticTransform", "RandomErasing", "RandomFlip",
+                                               "RandomGaussianBlur", "RandomGrayscale", "RandomHue", "RandomInvert", "RandomPerspective",
+                                               "RandomPosterization", "RandomRotation", "RandomSaturation", "RandomSharpness", "RandomShear",
+                                               "RandomTranslation", "RandomZoom", "Resizing", "Solarization"])
