@@ -17,3 +17,25 @@ from keras_b200.core.variables import Variable  # noqa: F401
 @keras_export(["keras.backend.clear_session", "keras.utils.clear_session"])
 def clear_session(free_memory=True):
     _clear_session(free_memory)
+
+
+@keras_export("keras.backend.is_float_dtype")
+def is_float_dtype(dtype):
+    dtype = standardize_dtype(dtype)
+    return dtype.startswith("float") or dtype.startswith("bfloat")
+
+
+@keras_export("keras.backend.is_int_dtype")
+def is_int_dtype(dtype):
+    dtype = standardize_dtype(dtype)
+    return dtype.startswith("int") or dtype.startswith("uint")
+
+
+def backend_name():
+    return backend()
+
+
+def rnn(*args, **kwargs):
+    from keras_b200.layers.rnn.rnn_loop import rnn as _rnn
+
+    return _rnn(*args, **kwargs)

@@ -54,7 +54,7 @@ _TORCH_TO_NAME = {
 _PY_TYPES = {bool: "bool", int: "int32", float: "float32", str: "string", complex: "complex64"}
 
 
-@keras_export("keras.backend.standardize_dtype")
+@keras_export(["keras.backend.standardize_dtype", "keras.utils.standardize_dtype"])
 def standardize_dtype(dtype):
     """Any dtype spelling (str, torch/numpy dtype, Python type, None) → canonical name."""
     if dtype is None:

@@ -1,5 +1,7 @@
 """Automatic object names: ``dense``, ``dense_1`` … (keras/src/utils/naming.py)."""
 
+from keras_b200.core.export_registry import keras_export
+
 import collections
 import re
 
@@ -26,6 +28,7 @@ def auto_name(prefix):
     return uniquify(to_snake_case(prefix))
 
 
+@keras_export("keras.backend.get_uid")
 def get_uid(prefix=""):
     counts = global_state.get_global_attribute(
         "object_uids", default=collections.defaultdict(int), set_to_default=True

@@ -86,7 +86,8 @@ class Variable:
                     f"specified. Received: initializer={initializer} and shape={shape}"
                 )
         else:
-            initializer = _as_init_value(initializer, dtype)
+            if not isinstance(initializer, torch.nn.Parameter):  # a Parameter is adopted as the storage itself
+                initializer = _as_init_value(initializer, dtype)
             if dtype is None:
                 dtype = initializer.dtype
         self._dtype = standardize_dtype(dtype)

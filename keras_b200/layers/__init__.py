@@ -1,3 +1,4 @@
+from keras_b200.core.export_registry import keras_export
 from keras_b200.layers.input_spec import InputSpec  # noqa: F401
 from keras_b200.layers.layer import Layer, _late_bind  # noqa: F401
 
@@ -67,3 +68,21 @@ _optional("keras_b200.layers.preprocessing", ["DataLayer", "CategoryEncoding", "
                                                "RandomGaussianBlur", "RandomGrayscale", "RandomHue", "RandomInvert", "RandomPerspective",
                                                "RandomPosterization", "RandomRotation", "RandomSaturation", "RandomSharpness", "RandomShear",
                                                "RandomTranslation", "RandomZoom", "Resizing", "Solarization"])
+
+
+@keras_export("keras.layers.serialize")
+def serialize(layer):
+    """Config dict of a layer (keras/src/layers/__init__.py)."""
+    from keras_b200.saving import serialization_lib
+
+    return serialization_lib.serialize_keras_object(layer)
+
+
+@keras_export("keras.layers.deserialize")
+def deserialize(config, custom_objects=None):
+    from keras_b200.saving import serialization_lib
+
+    obj = serialization_lib.deserialize_keras_object(config, custom_objects=custom_objects)
+    if not isinstance(obj, Layer):
+        raise ValueError(f"`keras.layers.deserialize` was passed a `config` object that is not a `keras.layers.Layer`. Received: {config}")
+    return obj

@@ -992,7 +992,10 @@ class Layer(Operation):
 
             return compute_output_spec(run, *args, **call_kwargs)
         plan = self._plan
-        bound = dict(zip(plan.arg_names, args))
+        pos_names = plan.arg_names[: plan.n_positional] if plan.n_positional < len(args) else plan.arg_names
+        bound = dict(zip(pos_names, args))
+        for i in range(len(pos_names), len(args)):
+            bound[f"arg{i}"] = args[i]  # call(*args): positional inputs beyond the named parameters
         bound.update(kwargs)
         shape_params = list(inspect.signature(self.compute_output_shape).parameters)
         shapes = {f"{k}_shape": _shape_structure(v) for k, v in bound.items() if _shape_structure(v) is not None and k not in ("training", "mask")}

@@ -213,6 +213,7 @@ class F1Score(FBetaScore):
         return cfg
 
 
+@keras_export("keras.metrics.pearson_correlation")
 def pearson_correlation(y_true, y_pred, axis=-1):
     y_pred = convert_to_tensor(y_pred)
     y_true = convert_to_tensor(y_true).to(y_pred.dtype)
@@ -224,6 +225,7 @@ def pearson_correlation(y_true, y_pred, axis=-1):
     return torch.sum(yt * yp, dim=axis)
 
 
+@keras_export("keras.metrics.concordance_correlation")
 def concordance_correlation(y_true, y_pred, axis=-1):
     y_pred = convert_to_tensor(y_pred)
     y_true = convert_to_tensor(y_true).to(y_pred.dtype)

@@ -6,7 +6,10 @@ from keras_b200.optimizers.optimizers import (  # noqa: F401
     SGD, Adadelta, Adafactor, Adagrad, Adam, Adamax, AdamW, Ftrl, Lamb, Lion, Muon, Nadam, Optimizer, RMSprop, ScheduleFreeAdamW,
 )
 
-ALL_OBJECTS = {Optimizer, Adam, SGD, RMSprop, Adadelta, AdamW, Adagrad, Adamax, Adafactor, Nadam, Ftrl, Lion, Lamb, Muon, ScheduleFreeAdamW, LossScaleOptimizer}
+from keras_b200.optimizers.multi_optimizer import MultiOptimizer, OptimizerMap  # noqa: F401,E402
+from keras_b200.optimizers import legacy  # noqa: F401,E402
+
+ALL_OBJECTS = {MultiOptimizer, Optimizer, Adam, SGD, RMSprop, Adadelta, AdamW, Adagrad, Adamax, Adafactor, Nadam, Ftrl, Lion, Lamb, Muon, ScheduleFreeAdamW, LossScaleOptimizer}
 ALL_OBJECTS_DICT = {cls.__name__.lower(): cls for cls in ALL_OBJECTS}
 
 

@@ -212,14 +212,33 @@ def unpack_int2(packed, orig_len, axis=0, dtype="int8"):
 
 @keras_export("keras.quantizers.pack_ternary")
 def pack_ternary(arr, axis=0):
-    """{-1, 0, 1} → two bits each (stored as value + 1), four per byte."""
-    a = convert_to_tensor(arr).to(torch.int8) + 1
-    return pack_int2(a.to(torch.int8).cpu(), axis=axis, dtype="int8")
+    """Pack values in {-1, 0, +1} at five per ``uint8`` byte (base 3: ``d0 + 3 d1 + 9 d2 + 27 d3 + 81 d4`` with
+    ``d = t + 1``), the layout of keras/src/quantizers/quantizers.py:1179-1260.  Returns ``(packed, packed_shape, orig_len)``."""
+    a = convert_to_numpy(convert_to_tensor(arr))
+    axis = axis % a.ndim
+    a = np.moveaxis(a, axis, 0)
+    n = a.shape[0]
+    pad = (-n) % 5
+    if pad:
+        a = np.concatenate([a, np.zeros((pad,) + a.shape[1:], dtype=a.dtype)], axis=0)
+    d = (np.clip(np.rint(a), -1, 1) + 1).astype(np.uint8).reshape((-1, 5) + a.shape[1:])
+    weights = np.array([1, 3, 9, 27, 81], dtype=np.uint8).reshape((1, 5) + (1,) * (a.ndim - 1))
+    packed = (d * weights).sum(axis=1).astype(np.uint8)
+    packed = np.moveaxis(packed, 0, axis)
+    return convert_to_tensor(packed), tuple(packed.shape), n
 
 
 @keras_export("keras.quantizers.unpack_ternary")
 def unpack_ternary(packed, orig_len, axis=0):
-    return (unpack_int2(packed, orig_len, axis=axis, dtype="uint8").to(torch.int8) - 1)
+    p = convert_to_tensor(packed)
+    axis = axis % p.ndim
+    p = torch.movedim(p, axis, 0).to(torch.int16)
+    digits = []
+    for _ in range(5):
+        digits.append(p % 3)
+        p = p // 3
+    out = torch.stack(digits, dim=1).reshape((-1,) + tuple(digits[0].shape[1:]))[:orig_len]
+    return torch.movedim((out - 1).to(torch.int8), 0, axis)
 
 
 # --- layer-level helpers shared by Dense / EinsumDense / Embedding ---------------------------

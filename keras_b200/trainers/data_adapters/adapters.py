@@ -196,6 +196,41 @@ class GeneratorDataAdapter(DataAdapter):
     partial_batch_size = property(lambda self: None)
 
 
+class IterableDatasetAdapter(DataAdapter):
+    """Re-iterable pipelines of batches (``keras_b200.utils.dataset_utils.Dataset`` and other objects whose ``__iter__``
+    starts a fresh pass).  Under a distribution each process takes batches ``p, p+N, ...``."""
+
+    def __init__(self, dataset, class_weight=None):
+        self._dataset = dataset
+        self._class_weight = class_weight
+        from keras_b200.distribution import distribution_lib
+
+        dist = distribution_lib.distribution()
+        self._num_shards = getattr(dist, "num_data_shards", 1) if dist is not None and getattr(dist, "auto_shard_dataset", True) else 1
+        self._shard_id = getattr(dist, "data_shard_id", 0) if self._num_shards > 1 else 0
+
+    def get_numpy_iterator(self):
+        it = iter(self._dataset)
+        if self._num_shards > 1:
+            it = itertools.islice(it, self._shard_id, None, self._num_shards)
+        for batch in it:
+            if not isinstance(batch, tuple):
+                batch = (batch,)
+            yield batch
+
+    @property
+    def num_batches(self):
+        try:
+            n = len(self._dataset)
+        except TypeError:
+            return None
+        return len(range(self._shard_id, n, self._num_shards)) if self._num_shards > 1 else n
+
+    batch_size = property(lambda self: None)
+    has_partial_batch = property(lambda self: None)
+    partial_batch_size = property(lambda self: None)
+
+
 def peek_and_restore(generator):
     batches = list(itertools.islice(generator, data_adapter_utils.NUM_BATCHES_FOR_TENSOR_SPEC))
     return batches, lambda: itertools.chain(batches, generator)
@@ -391,6 +426,10 @@ def get_data_adapter(x, y=None, sample_weight=None, batch_size=None, steps_per_e
         if class_weight is not None:
             raise ValueError("Argument `class_weight` is not supported for torch DataLoader inputs. You can modify your `__getitem__ ` method to return input tensor, label and class_weight. ")
         return TorchDataLoaderAdapter(x)
+    if hasattr(x, "__iter__") and not hasattr(x, "__next__") and not _is_generator(x) and not isinstance(x, (list, tuple, dict, str, bytes)):
+        if y is not None or sample_weight is not None:
+            raise ValueError("When providing `x` as a dataset, `y` and `sample_weight` should not be passed. Instead, they should be included as part of the dataset.")
+        return IterableDatasetAdapter(x, class_weight=class_weight)
     if _is_generator(x) or hasattr(x, "__next__"):
         if y is not None:
             raise ValueError("When providing `x` as a generator, `y` should not be passed. Instead, the targets should be included as part of the generator.")

@@ -16,7 +16,24 @@ Sequence = PyDataset
 def __getattr__(name):
     import importlib
 
-    for mod in ("keras_b200.utils.misc_utils", "keras_b200.utils.summary_utils", "keras_b200.utils.dataset_utils", "keras_b200.utils.image_utils"):
+    if name == "FeatureSpace":
+        from keras_b200.layers.preprocessing.feature_space import FeatureSpace
+
+        return FeatureSpace
+    if name == "bounding_boxes":
+        return importlib.import_module("keras_b200.utils.bounding_boxes")
+    if name == "legacy":
+        return importlib.import_module("keras_b200.legacy.saving.legacy_serialization_api")
+    if name == "get_source_inputs":
+        from keras_b200.ops.operation_utils import get_source_inputs
+
+        return get_source_inputs
+    if name == "standardize_dtype":
+        from keras_b200.core.dtypes import standardize_dtype
+
+        return standardize_dtype
+    for mod in ("keras_b200.utils.misc_utils", "keras_b200.utils.summary_utils", "keras_b200.utils.dataset_utils", "keras_b200.utils.image_utils",
+                "keras_b200.utils.file_utils", "keras_b200.utils.config_utils", "keras_b200.utils.model_visualization"):
         try:
             m = importlib.import_module(mod)
         except ImportError:
