@@ -64,6 +64,8 @@ class _TrackedList(list):
 
 
 class _TrackedDict(dict):
+    _tree_rebuild_as_dict = True
+
     def __init__(self, owner, values=None):
         self._owner = owner
         super().__init__()
@@ -88,6 +90,8 @@ class _TrackedDict(dict):
 
 class _CallPlan:
     """Per-class facts about ``call`` / ``build`` signatures, computed once."""
+
+    _tree_rebuild_as_dict = True
 
     __slots__ = ("arg_names", "has_training", "has_mask", "has_var_kw", "build_names", "build_by_name", "signature", "context_args", "n_positional")
 

@@ -67,6 +67,8 @@ def _children(x):
                 for k in _x:
                     out[k] = mapping[k]
                 return out
+            if type(_x) is dict or getattr(type(_x), "_tree_rebuild_as_dict", False):
+                return {k: mapping[k] for k in _x}
             try:
                 return type(_x)((k, mapping[k]) for k in _x)
             except TypeError:
