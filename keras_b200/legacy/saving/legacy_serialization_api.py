@@ -1,0 +1,3 @@
+"""``keras.utils.legacy`` namespace."""
+
+from keras_b200.legacy.saving.legacy_serialization import deserialize_keras_object, serialize_keras_object  # noqa: F401

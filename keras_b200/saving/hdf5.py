@@ -805,8 +805,17 @@ class Writer:
                     msgs.append(("vlen", body, data, payload))
                 else:
                     arr = np.asarray(value)
-                    if arr.dtype == np.float64 and isinstance(value, float):
-                        pass
+                    if arr.dtype.kind in "UO" and arr.size and all(isinstance(v, (str, bytes)) for v in arr.reshape(-1).tolist()):
+                        enc = [v.encode("utf-8") if isinstance(v, str) else v for v in arr.reshape(-1).tolist()]
+                        arr = np.array(enc, dtype=f"S{max(1, max(len(e) for e in enc))}").reshape(arr.shape)
+                    elif arr.dtype.kind in "UO" and arr.size == 0:
+                        arr = np.zeros(arr.shape, dtype="S1")
+                    if arr.dtype.kind == "S":
+                        dt = _datatype_message(f"S{arr.dtype.itemsize}")
+                        ds = _dataspace_message(arr.shape)
+                        body = struct.pack("<BxHHH", 1, len(name), len(dt), len(ds)) + _pad8(name) + _pad8(dt) + _pad8(ds)
+                        msgs.append(("plain", body, arr.tobytes(), None))
+                        continue
                     dname = arr.dtype.name
                     if dname == "bool":
                         arr = arr.astype(np.int8)
