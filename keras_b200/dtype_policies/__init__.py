@@ -313,3 +313,11 @@ def get(identifier):
         return DTypePolicy(standardize_dtype(identifier))
     except Exception:
         raise ValueError(f"Cannot interpret `dtype` argument. Expected a string or an instance of DTypePolicy. Received: dtype={identifier}")
+
+
+def __getattr__(name):
+    if name == "DTypePolicyMap":
+        from keras_b200.dtype_policies.dtype_policy_map import DTypePolicyMap
+
+        return DTypePolicyMap
+    raise AttributeError(f"module 'keras_b200.dtype_policies' has no attribute {name!r}")

@@ -180,10 +180,11 @@ def _wrap_quantize(fn):
         self._check_quantize_args(mode, self.compute_dtype)
         self._tracker_unlock()
         try:
-            fn(self, mode, config=config, **kwargs) if _accepts_config(fn) else fn(self, mode, **kwargs)
+            result = fn(self, mode, config=config, **kwargs) if _accepts_config(fn) else fn(self, mode, **kwargs)
         finally:
             self._lock_state()
         self._post_quantize(mode, **kwargs)
+        return result
 
     quantize._is_quantize_wrapper = True
     quantize.__wrapped__ = fn

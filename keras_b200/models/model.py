@@ -101,23 +101,50 @@ class Model(Trainer, Layer):
             calibration.calibrated_quantize(self, mode, config, filters)
             self._reset_step_functions()
             return
+        from keras_b200.quantizers.report import QuantizationReport
+
+        verbose = getattr(self, "_quantize_verbose", False)
+        report = QuantizationReport(mode=mode)
         graph_modified = False
         for layer in self._flatten_layers():
             if len(list(layer._flatten_layers())) != 1:
                 continue
+            path = getattr(layer, "path", None) or layer.name
             if not _should_quantize(layer, filters):
+                report.add_skipped(path, QuantizationReport.SKIP_FILTERED)
+                continue
+            if getattr(layer, "_is_quantized", False):
+                report.add_skipped(path, QuantizationReport.SKIP_ALREADY_QUANTIZED)
+                continue
+            if type(layer).quantize is Layer.quantize:
+                if layer.weights:
+                    report.add_skipped(path, QuantizationReport.SKIP_NO_SUPPORT)
                 continue
             try:
-                if getattr(layer, "_is_quantized", False):
-                    continue
                 layer.quantize(mode, type_check=type_check, config=config)
                 graph_modified = True
+                report.add_quantized(path, mode, getattr(layer.dtype_policy, "name", mode))
             except NotImplementedError as e:
-                warnings.warn(str(e))
+                report.add_skipped(path, QuantizationReport.SKIP_NO_SUPPORT)
+                report.add_error(path, e) if "Invalid quantization mode" in str(e) else None
             except AttributeError:
-                pass
+                report.add_skipped(path, QuantizationReport.SKIP_NO_SUPPORT)
         if graph_modified:
             self._reset_step_functions()
+        message = report.summary_warning()
+        if message and report.errors:
+            warnings.warn(message)
+        self._quantization_report = report
+        return report
+
+    def quantization_summary(self, print_fn=None):
+        """Print (and return) the report of the last ``quantize()`` call."""
+        from keras_b200.quantizers.report import QuantizationReport
+        from keras_b200.utils import io_utils
+
+        report = QuantizationReport.from_model(self)
+        (print_fn or io_utils.print_msg)(report.render())
+        return report
 
     def _reset_step_functions(self):
         self.train_function = None

@@ -402,3 +402,5 @@ def get(identifier, **kwargs):
     if callable(obj):
         return obj(**kwargs) if isinstance(obj, type) else obj
     raise ValueError(f"Could not interpret quantizer identifier: {identifier}")
+
+from keras_b200.quantizers.report import QuantizationReport  # noqa: F401,E402
