@@ -161,3 +161,13 @@ def preprocess_input(x, data_format=None):
 @keras_export(["keras.applications.resnet50.decode_predictions", "keras.applications.resnet.decode_predictions"])
 def decode_predictions(preds, top=5):
     return imagenet_utils.decode_predictions(preds, top=top)
+
+
+@keras_export("keras.applications.resnet_v2.preprocess_input")
+def preprocess_input_v2(x, data_format=None):
+    return imagenet_utils.preprocess_input(x, data_format=data_format, mode="tf")
+
+
+@keras_export("keras.applications.resnet_v2.decode_predictions")
+def decode_predictions_v2(preds, top=5):
+    return imagenet_utils.decode_predictions(preds, top=top)

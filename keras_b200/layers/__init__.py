@@ -59,6 +59,7 @@ _optional("keras_b200.layers.attention.attention_layers", ["MultiHeadAttention",
 _optional("keras_b200.layers.rnn.rnn_layers", ["RNN", "SimpleRNN", "SimpleRNNCell", "LSTM", "LSTMCell", "GRU", "GRUCell", "StackedRNNCells", "Bidirectional", "TimeDistributed", "ConvLSTM1D", "ConvLSTM2D", "ConvLSTM3D"])
 _optional("keras_b200.layers.core.torch_module_wrapper", ["TorchModuleWrapper"])
 _optional("keras_b200.layers.core.ternary_dense", ["TernaryDense"])
+_optional("keras_b200.layers.core.bridge_layers", ["JaxLayer", "FlaxLayer", "TFSMLayer"])
 _optional("keras_b200.layers.preprocessing", ["DataLayer", "CategoryEncoding", "Discretization", "HashedCrossing", "Hashing", "MelSpectrogram",
                                                "Normalization", "Pipeline", "Rescaling", "STFTSpectrogram", "IndexLookup", "IntegerLookup",
                                                "StringLookup", "TextVectorization", "AugMix", "AutoContrast", "CenterCrop",
