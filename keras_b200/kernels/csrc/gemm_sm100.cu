@@ -17,6 +17,7 @@
 // Every wait on an mbarrier is bounded: on expiry the kernel records a code in `*err`, drains its
 // outstanding copies (also bounded), releases TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -308,6 +309,227 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Persistent variant for large problems: 128x256 output tiles, four 48 KB operand stages, the whole
+// tensor memory (512 columns) split into two 256-column accumulators so that the epilogue of tile i
+// overlaps the main loop of tile i+1.  One CTA per SM; tiles are handed out round-robin in an order
+// that keeps the CTAs running at the same time on neighbouring tiles (8 row-tiles per group) for L2 reuse.
+namespace v2 {
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+}  // namespace v2
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& m0, int& n0) {
+  const int per_group = v2::GROUP_M * n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * v2::GROUP_M;
+  const int rows = min(v2::GROUP_M, m_tiles - first_m);
+  const int r = t - g * per_group;
+  m0 = (first_m + r % rows) * v2::BM;
+  n0 = (r / rows) * v2::BN;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  constexpr int BM = v2::BM, BN = v2::BN, BK = v2::BK, STAGES = v2::STAGES, STAGE_BYTES = v2::STAGE_BYTES, A_BYTES = v2::A_BYTES;
+  constexpr uint32_t TMEM_COLS = v2::TMEM_COLS;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * STAGE_BYTES);
+  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      uint32_t issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m0, n0;
+        tile_coords(t, m_tiles, n_tiles, m0, n0);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (p.a_mn_major) {
+            tma_load_2d(sa, &map_a, full_bar(s), m0, k0);
+            tma_load_2d(sa + 8192, &map_a, full_bar(s), m0 + 64, k0);
+          } else {
+            tma_load_2d(sa, &map_a, full_bar(s), k0, m0);
+          }
+          if (p.b_mn_major) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &map_b, full_bar(s), n0 + j * 64, k0);
+          } else {
+            tma_load_2d(sb, &map_b, full_bar(s), k0, n0);
+          }
+          issued = it + 1;
+        }
+      }
+      if (!ok) {
+        if (p.err) atomicExch(p.err, 11);
+        *abort_flag = 1;
+        const uint32_t first = issued > STAGES ? issued - STAGES : 0;
+        for (uint32_t i = first; i < issued; ++i) {
+          for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+            if (mbar_try_wait(full_bar(i % STAGES), (i / STAGES) & 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t a_step = p.a_mn_major ? (2048u >> 4) : (32u >> 4);
+      const uint32_t b_step = p.b_mn_major ? (2048u >> 4) : (32u >> 4);
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const uint32_t acc = local & 1;
+        ok = mbar_wait(acc_empty_bar(acc), ((local >> 1) & 1) ^ 1, abort_flag);  // epilogue has drained this accumulator
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + acc * (uint32_t)BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, p.a_mn_major), bdesc = make_smem_desc(sb, p.b_mn_major);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(acc_full_bar(acc));
+      }
+      if (!ok) {
+        if (p.err) atomicExch(p.err, 12);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    uint32_t local = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      int m0, n0;
+      tile_coords(t, m_tiles, n_tiles, m0, n0);
+      const uint32_t acc = local & 1;
+      ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1, abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + acc * (uint32_t)BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+        }
+        if (p.act != ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+        }
+        if (p.out_fp32) {
+          float* dst = reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 + 3 < p.N) {
+              *reinterpret_cast<float4*>(dst + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+            } else {
+              for (int j = 0; j < 4; ++j)
+                if (col0 + g * 4 + j < p.N) dst[g * 4 + j] = v[g * 4 + j];
+            }
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 + 7 < p.N) {
+              *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(v + g * 8);
+            } else {
+              for (int j = 0; j < 8; ++j)
+                if (col0 + g * 8 + j < p.N) dst[g * 8 + j] = __float2bfloat16_rn(v[g * 8 + j]);
+            }
+          }
+        }
+      }
+      // this warp has finished reading the accumulator: hand it back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+    if (!ok) {
+      if (lane == 0 && p.err) atomicExch(p.err, 13);
+      *abort_flag = 1;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(v2::TMEM_COLS) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -351,8 +573,19 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
     return -2;
   }
   CUtensorMap map_a, map_b;
+  static int force_v1 = -1, sm_count = 0;
+  if (force_v1 < 0) {
+    const char* e = getenv("KB200_GEMM_V1");
+    force_v1 = (e != nullptr && e[0] == '1') ? 1 : 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  const long long tiles_v2 = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
+  const bool use_v2 = !force_v1 && N > 128 && tiles_v2 >= sm_count / 2;
+  const int bn = use_v2 ? v2::BN : BN;
   bool ok = a_mn_major ? make_map(&map_a, a, M, K, lda, 64, BK) : make_map(&map_a, a, K, M, lda, BK, BM);
-  ok = ok && (b_mn_major ? make_map(&map_b, b, N, K, ldb, 64, BK) : make_map(&map_b, b, K, N, ldb, BK, BN));
+  ok = ok && (b_mn_major ? make_map(&map_b, b, N, K, ldb, 64, BK) : make_map(&map_b, b, K, N, ldb, BK, bn));
   if (!ok) {
     kb200_set_error("gemm_bf16: cuTensorMapEncodeTiled failed");
     return -3;
@@ -360,11 +593,17 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
     attr_set = true;
   }
   GemmParams p{c, bias, M, N, K, ldc, a_mn_major, b_mn_major, act, out_fp32, err};
-  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  gemm_bf16_tcgen05_kernel<<<(unsigned)tiles, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  if (use_v2) {
+    const unsigned grid = (unsigned)(tiles_v2 < sm_count ? tiles_v2 : sm_count);
+    gemm_bf16_tcgen05_persistent<<<grid, THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, p);
+  } else {
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    gemm_bf16_tcgen05_kernel<<<(unsigned)tiles, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  }
   KB_CHECK_LAUNCH("gemm_bf16");
   return 0;
 }

@@ -1,0 +1,135 @@
+"""Kernel micro-benchmarks with CUDA-event timing and roofline fractions.
+
+    python -m keras_b200.kernels.microbench gemm --m 8192 --n 8192 --k 8192
+    python -m keras_b200.kernels.microbench bn --rows 802816 --channels 256
+    python -m keras_b200.kernels.microbench pool --batch 256
+
+Each prints one JSON line per case: time (median of ``--iters`` after ``--warmup``), achieved TFLOP/s or GB/s and the
+fraction of the measured peak (``MEASURED_PEAKS.json`` beside the package's parent directory when present, else the
+fall-back 1590 TFLOP/s / 6650 GB/s).  A buffer larger than L2 is written between iterations so inputs come from HBM.
+With ``--once`` exactly one launch of the kernel under test is made after set-up (for profiler captures of a single launch).
+"""
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def _time(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.add_(1.0)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return statistics.median(times)
+
+
+def bench_gemm(args, flush):
+    from keras_b200.kernels import gemm
+
+    M, N, K = args.m, args.n, args.k
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    ours = lambda: gemm.gemm(a, b, False, True, M, N, K)
+    lib = lambda: torch.matmul(a, b)
+    if args.once:
+        ours()
+        torch.cuda.synchronize()
+        return []
+    ref = torch.matmul(a.float()[:256], b.float())
+    err = float((ours()[:256].float() - ref).abs().max() / ref.abs().max())
+    t_ours, t_lib = _time(ours, args.iters, args.warmup, flush), _time(lib, args.iters, args.warmup, flush)
+    tf, _, src = _peaks()
+    flops = 2.0 * M * N * K
+    return [{"kernel": "kb200_gemm_bf16 (tcgen05)", "shape": [M, N, K], "ms": t_ours, "tflops": flops / t_ours / 1e9, "frac_of_peak": flops / t_ours / 1e9 / tf,
+             "peak": src, "rel_err_vs_fp32": err},
+            {"kernel": "torch.matmul (cuBLAS)", "shape": [M, N, K], "ms": t_lib, "tflops": flops / t_lib / 1e9, "frac_of_peak": flops / t_lib / 1e9 / tf, "peak": src}]
+
+
+def bench_bn(args, flush):
+    from keras_b200.kernels import ops as kops
+
+    M, C = args.rows, args.channels
+    x = torch.randn(M, C, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    gamma = torch.ones(C, device="cuda", requires_grad=True)
+    beta = torch.zeros(C, device="cuda", requires_grad=True)
+    mm, mv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    fwd = lambda: kops.FusedBatchNormAct.apply(x, gamma, beta, None, mm, mv, 0.99, 1e-3, True, None)
+    if args.once:
+        fwd()
+        torch.cuda.synchronize()
+        return []
+    y = fwd()
+    dy = torch.randn_like(y)
+    bwd = lambda: torch.autograd.grad(fwd(), (x, gamma, beta), dy)
+    t_f = _time(lambda: fwd(), args.iters, args.warmup, flush)
+    t_fb = _time(bwd, args.iters, args.warmup, flush)
+    _, bw, src = _peaks()
+    nbytes = M * C * 2
+    fwd_bytes = 3 * nbytes + nbytes // 16          # stats read + apply read/write + mask write
+    bwd_bytes = 5 * nbytes + 2 * (nbytes // 16)    # reduce reads dy,x ; apply reads dy,x writes dx ; mask twice
+    return [{"kernel": "bn forward (stats+apply+relu)", "shape": [M, C], "ms": t_f, "gbs": fwd_bytes / t_f / 1e6, "frac_of_peak": fwd_bytes / t_f / 1e6 / bw, "peak": src},
+            {"kernel": "bn forward+backward", "shape": [M, C], "ms": t_fb, "gbs": (fwd_bytes + bwd_bytes) / t_fb / 1e6,
+             "frac_of_peak": (fwd_bytes + bwd_bytes) / t_fb / 1e6 / bw, "peak": src}]
+
+
+def bench_pool(args, flush):
+    from keras_b200.kernels import dispatch
+
+    x = torch.randn(args.batch, 112, 112, 64, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    fwd = lambda: dispatch.max_pool2d(x, (3, 3), (2, 2), "valid", zero_pad=((1, 1), (1, 1)))
+    if args.once:
+        fwd()
+        torch.cuda.synchronize()
+        return []
+    y = fwd()
+    dy = torch.randn_like(y)
+    t_f = _time(lambda: fwd(), args.iters, args.warmup, flush)
+    t_fb = _time(lambda: torch.autograd.grad(fwd(), x, dy), args.iters, args.warmup, flush)
+    _, bw, src = _peaks()
+    fb = x.numel() * 2 + y.numel() * 3
+    bb = y.numel() * 3 + x.numel() * 2
+    return [{"kernel": "zero-pad+maxpool forward", "shape": list(x.shape), "ms": t_f, "gbs": fb / t_f / 1e6, "frac_of_peak": fb / t_f / 1e6 / bw, "peak": src},
+            {"kernel": "zero-pad+maxpool forward+backward", "shape": list(x.shape), "ms": t_fb, "gbs": (fb + bb) / t_fb / 1e6,
+             "frac_of_peak": (fb + bb) / t_fb / 1e6 / bw, "peak": src}]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "bn", "pool"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--rows", type=int, default=802816)
+    ap.add_argument("--channels", type=int, default=256)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--once", action="store_true")
+    args = ap.parse_args()
+    flush = torch.zeros(96 * 1024 * 1024, device="cuda")  # 384 MB > 126 MB L2
+    for row in {"gemm": bench_gemm, "bn": bench_bn, "pool": bench_pool}[args.what](args, flush):
+        print(json.dumps(row))
+
+
+if __name__ == "__main__":
+    main()

@@ -213,6 +213,12 @@ class MultiHeadAttention(Layer):
         else:
             attention_mask = self._compute_attention_mask(query, value, query_mask=query_mask, value_mask=value_mask, key_mask=key_mask,
                                                           attention_mask=attention_mask, use_causal_mask=use_causal_mask)
+        tp = None
+        if getattr(self._query_dense._kernel, "_shard_slices", None) is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            projections = [self._query_dense, self._key_dense, self._value_dense] + ([self._gate_dense] if self._use_gate else [])
+            tp = tensor_parallel.mark_attention(self, projections, self._output_dense)
         gate = self._gate_dense(query) if self._use_gate else None
         q = self._query_dense(query)
         k = self._key_dense(key)
@@ -228,6 +234,8 @@ class MultiHeadAttention(Layer):
             except AttributeError:
                 pass
         if return_attention_scores:
+            if tp is not None and scores is not None:
+                scores = tensor_parallel.gather_dim(scores, 1, *tp[1:])
             return out, scores
         return out
 
@@ -363,6 +371,12 @@ class GroupedQueryAttention(Layer):
             key = value
         attention_mask = self._compute_attention_mask(query, value, query_mask=query_mask, value_mask=value_mask, key_mask=key_mask,
                                                       attention_mask=attention_mask, use_causal_mask=use_causal_mask)
+        tp = None
+        if getattr(self._query_dense._kernel, "_shard_slices", None) is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            projections = [self._query_dense, self._key_dense, self._value_dense] + ([self._gate_dense] if self.use_gate else [])
+            tp = tensor_parallel.mark_attention(self, projections, self._output_dense)
         gate = self._gate_dense(query) if self.use_gate else None
         q = self._query_dense(query)
         k = self._key_dense(key)
@@ -372,6 +386,8 @@ class GroupedQueryAttention(Layer):
             out = ops.multiply(out, gate)
         out = self._output_dense(out)
         if return_attention_scores:
+            if tp is not None and scores is not None:
+                scores = tensor_parallel.gather_dim(scores, 1, *tp[1:])
             return out, scores
         return out
 

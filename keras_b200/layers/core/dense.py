@@ -72,6 +72,12 @@ class Dense(Layer):
         return k
 
     def call(self, inputs, training=None):
+        if getattr(self._kernel, "_shard_slices", None) is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            out = tensor_parallel.dense(self, inputs)
+            if out is not None:
+                return out
         kernel = self.kernel
         act = self.activation
         fused = dispatch.dense(inputs, kernel, self.bias, getattr(act, "__name__", None))

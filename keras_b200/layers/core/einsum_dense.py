@@ -186,6 +186,12 @@ class EinsumDense(Layer):
         return ops.einsum(self.equation, inputs, kernel)
 
     def call(self, inputs, training=None):
+        if getattr(self._kernel, "_shard_slices", None) is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            out = tensor_parallel.einsum_dense(self, inputs)
+            if out is not None:
+                return out
         x = self._contract(inputs, self.kernel)
         if self.bias is not None:
             x = ops.add(x, self.bias)

@@ -694,7 +694,7 @@ class Layer(Operation):
         first_arg = args[0] if args else (kwargs.get(plan.arg_names[0]) if plan.arg_names and plan.arg_names[0] in kwargs else None)
 
         # 3. input spec + build
-        if self._input_spec is not None and first_arg is not None:
+        if self._input_spec is not None and first_arg is not None and (symbolic or not getattr(self, "_tp_local_input", False)):
             assert_input_compatibility(self._input_spec, first_arg, self.name)
         if not self.built:
             with self._open_name_scope():
@@ -1002,9 +1002,11 @@ class Layer(Operation):
         for i in range(len(pos_names), len(args)):
             bound[f"arg{i}"] = args[i]  # call(*args): positional inputs beyond the named parameters
         bound.update(kwargs)
-        shape_params = list(inspect.signature(self.compute_output_shape).parameters)
+        sig_params = inspect.signature(self.compute_output_shape).parameters
+        shape_params = list(sig_params)
+        required = [p for p, v in sig_params.items() if v.default is inspect.Parameter.empty and p.endswith("_shape")]
         shapes = {f"{k}_shape": _shape_structure(v) for k, v in bound.items() if _shape_structure(v) is not None and k not in ("training", "mask")}
-        if len(shape_params) == 1 or not all(p in shapes for p in shape_params if p.endswith("_shape")):
+        if len(shape_params) == 1 or not all(p in shapes for p in required):
             out_shape = self.compute_output_shape(next(iter(shapes.values())))
         else:
             out_shape = self.compute_output_shape(**{p: shapes[p] for p in shape_params if p in shapes})

@@ -120,9 +120,318 @@ def in_local_shards():
 
 def plan_for_model(distribution, model):
     """{variable path: layout axes} of every sharded variable of ``model`` (diagnostics and checkpoints)."""
-    plan = {}
+    plan = {"kept_sharded": mark_pairs(model)} if hasattr(model, "_flatten_layers") else {}
     for v in model.variables:
         layout = getattr(v, "_layout", None)
         if layout is not None and any(a is not None for a in layout.axes):
             plan[v.path] = tuple(layout.axes)
     return plan
+
+
+# ---------------------------------------------------------------------------- tensor-parallel layers
+# A kernel sharded on a *free* dimension (one that survives into the output) makes the layer column-parallel: every rank
+# computes its slice of the output from the full input.  A kernel sharded on a *contracted* dimension makes it
+# row-parallel: every rank multiplies its slice of the input with its slice of the kernel and the partial products are
+# summed over the model axis.  Outputs of column-parallel layers are all-gathered (correct for any consumer) unless
+# the layer is marked ``_tp_keep_sharded`` — set by ``plan_for_model`` for layers whose outputs reach only
+# row-parallel layers through elementwise layers, and by the attention layers for their head-sharded projections.
+class _CopyToRegion(torch.autograd.Function):
+    """Identity forward; backward sums the input gradient over the model axis (each rank holds a partial)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, grad):
+        grad = grad.contiguous()
+        dist.all_reduce(grad, group=ctx.group)
+        return grad, None
+
+
+class _ReduceFromRegion(torch.autograd.Function):
+    """Sum over the model axis forward; identity backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
+
+
+class _GatherDim(torch.autograd.Function):
+    """All-gather along ``dim`` forward; backward keeps this rank's slice."""
+
+    @staticmethod
+    def forward(ctx, x, dim, group, index, parts):
+        ctx.dim, ctx.index, ctx.parts = dim, index, parts
+        pieces = [torch.empty_like(x) for _ in range(parts)]
+        dist.all_gather(pieces, x.contiguous(), group=group)
+        return torch.cat(pieces, dim=dim)
+
+    @staticmethod
+    def backward(ctx, grad):
+        size = grad.shape[ctx.dim] // ctx.parts
+        return grad.narrow(ctx.dim, ctx.index * size, size).contiguous(), None, None, None, None
+
+
+class _ScatterDim(torch.autograd.Function):
+    """Keep this rank's slice along ``dim`` forward; backward all-gathers the gradient slices."""
+
+    @staticmethod
+    def forward(ctx, x, dim, group, index, parts):
+        ctx.dim, ctx.group, ctx.parts = dim, group, parts
+        size = x.shape[dim] // parts
+        return x.narrow(dim, index * size, size).contiguous()
+
+    @staticmethod
+    def backward(ctx, grad):
+        pieces = [torch.empty_like(grad) for _ in range(ctx.parts)]
+        dist.all_gather(pieces, grad.contiguous(), group=ctx.group)
+        return torch.cat(pieces, dim=ctx.dim), None, None, None, None
+
+
+def _single_shard(variable):
+    """(dim, parts, index, group) when exactly one dimension of ``variable`` is sharded, else None."""
+    if variable is None or getattr(variable, "_shard_slices", None) is None:
+        return None
+    info = _axis_info(variable._layout, variable._layout.device_mesh.backend_mesh)
+    if len(info) != 1:
+        return None
+    return info[0]
+
+
+def _local(variable, dtype):
+    v = variable._value
+    return v.to(dtype) if v.dtype != dtype else v
+
+
+def dense(layer, inputs):
+    """Tensor-parallel ``Dense``; returns ``None`` when the layout is not a plain column/row split."""
+    shard = _single_shard(layer._kernel)
+    if shard is None or layer.lora_enabled or getattr(layer, "_is_quantized", False) or not isinstance(inputs, torch.Tensor):
+        return None
+    dim, parts, index, group = shard
+    w = _local(layer._kernel, inputs.dtype)
+    bias = layer.bias
+    if dim == 1:  # column parallel
+        x = _CopyToRegion.apply(inputs, group)
+        y = torch.matmul(x, w)
+        if bias is not None:
+            b = _local(bias, y.dtype) if getattr(bias, "_shard_slices", None) is not None else bias.value.to(y.dtype).chunk(parts)[index]
+            y = y + b
+        y = _activate(layer, y)
+        if getattr(layer, "_tp_keep_sharded", False):
+            return y
+        return _GatherDim.apply(y, y.ndim - 1, group, index, parts)
+    # row parallel
+    k_local = w.shape[0]
+    if inputs.shape[-1] == k_local * parts:
+        x = _ScatterDim.apply(inputs, inputs.ndim - 1, group, index, parts)
+    elif inputs.shape[-1] == k_local:
+        x = inputs
+    else:
+        return None
+    y = _ReduceFromRegion.apply(torch.matmul(x, w), group)
+    if bias is not None:
+        y = y + (bias.value.to(y.dtype) if getattr(bias, "_shard_slices", None) is None else gather_variable(bias).to(y.dtype))
+    return _activate(layer, y)
+
+
+def _activate(layer, y):
+    from keras_b200 import activations
+
+    act = layer.activation
+    if act is not None and act is not activations.linear:
+        y = act(y)
+    return y
+
+
+def einsum_dense(layer, inputs):
+    """Tensor-parallel ``EinsumDense`` for kernels sharded on one dimension."""
+    shard = _single_shard(layer._kernel)
+    if shard is None or layer.lora_enabled or getattr(layer, "_is_quantized", False) or not isinstance(inputs, torch.Tensor):
+        return None
+    dim, parts, index, group = shard
+    lhs, out_spec = layer.equation.replace(" ", "").split("->")
+    in_spec, k_spec = lhs.split(",")
+    if "." in layer.equation:
+        return None
+    letter = k_spec[dim]
+    w = _local(layer._kernel, inputs.dtype)
+    bias = layer.bias
+    if letter in out_spec:  # column-like: the sharded letter survives into the output
+        x = _CopyToRegion.apply(inputs, group)
+        y = torch.einsum(layer.equation, x, w)
+        odim = out_spec.index(letter)
+        if bias is not None:
+            b = bias.value.to(y.dtype)
+            if getattr(bias, "_shard_slices", None) is not None:
+                b = _local(bias, y.dtype)
+            elif layer.bias_axes and letter in layer.bias_axes:
+                # bias dims follow the trailing output dims starting at the first bias axis
+                first = min(out_spec.find(c) for c in layer.bias_axes)
+                bdim = odim - first
+                if 0 <= bdim < b.ndim and b.shape[bdim] == y.shape[odim] * parts:
+                    b = b.chunk(parts, dim=bdim)[index]
+            y = y + b
+        y = _activate(layer, y)
+        if getattr(layer, "_tp_keep_sharded", False):
+            return y
+        return _GatherDim.apply(y, odim, group, index, parts)
+    # row-like: contraction over the sharded letter
+    if letter not in in_spec:
+        return None
+    idim = in_spec.index(letter)
+    local = w.shape[dim]
+    if inputs.shape[idim] == local * parts:
+        x = _ScatterDim.apply(inputs, idim, group, index, parts)
+    elif inputs.shape[idim] == local:
+        x = inputs
+    else:
+        return None
+    y = _ReduceFromRegion.apply(torch.einsum(layer.equation, x, w), group)
+    if bias is not None:
+        y = y + (bias.value.to(y.dtype) if getattr(bias, "_shard_slices", None) is None else gather_variable(bias).to(y.dtype))
+    return _activate(layer, y)
+
+
+def _is_row_parallel(layer):
+    from keras_b200.layers.core.dense import Dense
+    from keras_b200.layers.core.einsum_dense import EinsumDense
+
+    k = getattr(layer, "_kernel", None)
+    shard = _single_shard(k) if k is not None else None
+    if shard is None:
+        return False
+    if isinstance(layer, Dense):
+        return shard[0] == 0
+    if isinstance(layer, EinsumDense):
+        lhs, out_spec = layer.equation.replace(" ", "").split("->")
+        return lhs.split(",")[1][shard[0]] not in out_spec
+    return False
+
+
+def _is_column_parallel(layer):
+    from keras_b200.layers.core.dense import Dense
+    from keras_b200.layers.core.einsum_dense import EinsumDense
+
+    k = getattr(layer, "_kernel", None)
+    shard = _single_shard(k) if k is not None else None
+    if shard is None:
+        return False
+    if isinstance(layer, Dense):
+        return shard[0] == 1
+    if isinstance(layer, EinsumDense):
+        lhs, out_spec = layer.equation.replace(" ", "").split("->")
+        letter = lhs.split(",")[1][shard[0]]
+        return letter in out_spec and out_spec.index(letter) == len(out_spec) - 1
+    return False
+
+
+def mark_pairs(model):
+    """In a Functional model, let a column-parallel layer keep its output sharded when every path from it reaches a
+    row-parallel layer through elementwise layers only (activation, dropout, multiply/add of equally sharded tensors)."""
+    from keras_b200.layers.activations.activation_layers import Activation, ELU, LeakyReLU, ReLU
+    from keras_b200.layers.merging.merging_layers import Add, Multiply, Subtract
+    from keras_b200.layers.regularization.regularization_layers import Dropout
+    from keras_b200.models.functional import Functional
+
+    marked = []
+    for m in [model] + [l for l in model._flatten_layers() if isinstance(l, Functional) and l is not model]:
+        if not isinstance(m, Functional):
+            continue
+        nodes = m._ordered_nodes()
+        consumers = {}
+        producer = {}
+        for n in nodes:
+            for t in n.input_tensors:
+                consumers.setdefault(id(t), []).append(n)
+            for t in n.outputs:
+                producer[id(t)] = n
+        outputs = {id(t) for t in m._outputs}
+        elementwise = (Activation, ReLU, LeakyReLU, ELU, Dropout)
+        merges = (Multiply, Add, Subtract)
+
+        def sharded_source(t, seen):
+            """True when tensor ``t`` is (an elementwise function of) column-parallel outputs only."""
+            n = producer.get(id(t))
+            if n is None or id(n) in seen:
+                return False
+            seen.add(id(n))
+            op = n.operation
+            if _is_column_parallel(op):
+                return True
+            if isinstance(op, elementwise) or isinstance(op, merges):
+                return all(sharded_source(i, seen) for i in n.input_tensors)
+            return False
+
+        def reaches_only_rows(t, seen):
+            if id(t) in outputs:
+                return False
+            cons = consumers.get(id(t), [])
+            if not cons:
+                return False
+            for c in cons:
+                op = c.operation
+                if _is_row_parallel(op):
+                    rows.append(op)
+                    continue
+                if isinstance(op, elementwise):
+                    if not reaches_only_rows(c.outputs[0], seen):
+                        return False
+                elif isinstance(op, merges):
+                    if not all(sharded_source(i, set()) for i in c.input_tensors) or not reaches_only_rows(c.outputs[0], seen):
+                        return False
+                else:
+                    return False
+            return True
+
+        for n in nodes:
+            op = n.operation
+            rows = []
+            if _is_column_parallel(op) and len(op._inbound_nodes) == 1 and reaches_only_rows(n.outputs[0], set()):
+                op._tp_keep_sharded = True
+                for r in rows:
+                    r._tp_local_input = True  # the layer's input-spec check sees the local width
+                marked.append(op.path if hasattr(op, "path") else op.name)
+    return marked
+
+
+def mark_attention(layer, projections, output_dense):
+    """Head-sharded attention: when every projection kernel is sharded on its heads dimension and the output kernel on
+    the matching contracted heads dimension, the projections keep their outputs sharded (each rank attends over its
+    own heads) and the output projection sums the partial results.  Returns (heads output dim, parts, index, group) or
+    None when the layouts do not form that pattern."""
+    cached = getattr(layer, "_tp_attention", False)
+    if cached is not False:
+        return cached
+    result = None
+    shards = [_single_shard(getattr(p, "_kernel", None)) for p in projections]
+    out_shard = _single_shard(getattr(output_dense, "_kernel", None))
+    if all(s is not None for s in shards) and out_shard is not None and _is_row_parallel(output_dense):
+        dims = set()
+        ok = True
+        for p, sh in zip(projections, shards):
+            lhs, out_spec = p.equation.replace(" ", "").split("->")
+            letter = lhs.split(",")[1][sh[0]]
+            # heads are the second-to-last output dimension of every projection
+            if letter not in out_spec or out_spec.index(letter) != len(out_spec) - 2:
+                ok = False
+            dims.add(sh[1])
+        if ok and len(dims) == 1 and out_shard[1] in dims:
+            for p in projections:
+                p._tp_keep_sharded = True
+            output_dense._tp_local_input = True
+            result = (-2, out_shard[1], out_shard[2], out_shard[3])
+    layer._tp_attention = result
+    return result
+
+
+def gather_dim(x, dim, parts, index, group):
+    return _GatherDim.apply(x, dim % x.ndim, group, index, parts)

@@ -138,3 +138,108 @@ def test_model_parallel_sharded_variables_match_unsharded():
         np.testing.assert_allclose(out[r]["before"], before, rtol=1e-6)
         np.testing.assert_allclose(out[r]["after"], m.layers[-1].kernel.numpy(), rtol=1e-5, atol=1e-6)
         np.testing.assert_allclose(out[r]["pred"], m.predict(x, verbose=0), rtol=1e-5, atol=1e-6)
+
+
+def _tp_mlp(keras):
+    keras.utils.set_random_seed(11)
+    inp = keras.Input((6,))
+    x = keras.layers.Dense(16, activation="relu", name="up")(inp)
+    x = keras.layers.Dropout(0.0)(x)
+    x = keras.layers.Dense(6, name="down")(x)
+    x = keras.layers.EinsumDense("ab,bcd->acd", output_shape=(4, 2), bias_axes="cd", name="heads")(x)
+    x = keras.layers.EinsumDense("acd,cde->ae", output_shape=(5,), bias_axes="e", name="merge")(x)
+    out = keras.layers.Dense(3, name="plain")(x)
+    m = keras.Model(inp, out)
+    m.compile(optimizer=keras.optimizers.Adam(0.01), loss="mse")
+    return m
+
+
+def _tp_pair_worker(rank, world):
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    mesh = keras.distribution.DeviceMesh((1, 2), ["batch", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["up/kernel"] = (None, "model")
+    lm["up/bias"] = ("model",)
+    lm["down/kernel"] = ("model", None)
+    lm["heads/kernel"] = (None, "model", None)
+    lm["heads/bias"] = ("model", None)
+    lm["merge/kernel"] = ("model", None, None)
+    keras.distribution.set_distribution(keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="batch"))
+    m = _tp_mlp(keras)
+    x, y = _data()
+    losses = [float(m.train_on_batch(x[:8], y[:8])) for _ in range(3)]
+    out = {f"w{i}": w for i, w in enumerate(m.get_weights())}
+    out["losses"] = np.array(losses)
+    out["pred"] = m.predict(x[:8], verbose=0)
+    out["kept"] = np.array(sorted(m._parallel_engine.plan["kept_sharded"]))
+    out["up_local"] = np.array(tuple(m.get_layer("up").kernel._value.shape))
+    return out
+
+
+def test_tensor_parallel_column_row_layers_match_unsharded():
+    codes, out = _run(_tp_pair_worker, 2)
+    assert codes == [0, 0], codes
+    import keras_b200 as keras
+
+    m = _tp_mlp(keras)
+    x, y = _data()
+    losses = [float(m.train_on_batch(x[:8], y[:8])) for _ in range(3)]
+    for r in (0, 1):
+        assert tuple(out[r]["up_local"]) == (6, 8)
+        assert [str(s) for s in out[r]["kept"]] == ["up"], out[r]["kept"]
+        np.testing.assert_allclose(out[r]["losses"], losses, rtol=1e-5)
+        for i, w in enumerate(m.get_weights()):
+            np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(out[r]["pred"], m.predict(x[:8], verbose=0), rtol=1e-4, atol=1e-6)
+
+
+def _tp_attention_model(keras):
+    keras.utils.set_random_seed(5)
+    inp = keras.Input((5, 8))
+    x = keras.layers.MultiHeadAttention(num_heads=4, key_dim=3, name="mha")(inp, inp, use_causal_mask=True)
+    x = keras.layers.LayerNormalization(name="ln")(x + inp)
+    x = keras.layers.GroupedQueryAttention(head_dim=4, num_query_heads=4, num_key_value_heads=2, name="gqa")(x, x)
+    out = keras.layers.Dense(2, name="head")(x)
+    m = keras.Model(inp, out)
+    m.compile(optimizer=keras.optimizers.SGD(0.1), loss="mse")
+    return m
+
+
+def _tp_attention_worker(rank, world):
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    mesh = keras.distribution.DeviceMesh((1, 2), ["batch", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["(mha|gqa)/(query|key|value)/kernel"] = (None, "model", None)
+    lm["(mha|gqa)/(query|key|value)/bias"] = ("model", None)
+    lm["(mha|gqa)/attention_output/kernel"] = ("model", None, None)
+    keras.distribution.set_distribution(keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="batch"))
+    m = _tp_attention_model(keras)
+    rng = np.random.RandomState(1)
+    x, y = rng.randn(4, 5, 8).astype("float32"), rng.randn(4, 5, 2).astype("float32")
+    losses = [float(m.train_on_batch(x, y)) for _ in range(3)]
+    out = {f"w{i}": w for i, w in enumerate(m.get_weights())}
+    out["losses"] = np.array(losses)
+    out["q_local"] = np.array(tuple(m.get_layer("mha")._query_dense.kernel._value.shape))
+    out["kept"] = np.array([bool(getattr(m.get_layer(n)._query_dense, "_tp_keep_sharded", False)) for n in ("mha", "gqa")])
+    return out
+
+
+def test_tensor_parallel_attention_heads_match_unsharded():
+    codes, out = _run(_tp_attention_worker, 2)
+    assert codes == [0, 0], codes
+    import keras_b200 as keras
+
+    m = _tp_attention_model(keras)
+    rng = np.random.RandomState(1)
+    x, y = rng.randn(4, 5, 8).astype("float32"), rng.randn(4, 5, 2).astype("float32")
+    losses = [float(m.train_on_batch(x, y)) for _ in range(3)]
+    for r in (0, 1):
+        assert tuple(out[r]["q_local"]) == (8, 2, 3)
+        assert out[r]["kept"].all()
+        np.testing.assert_allclose(out[r]["losses"], losses, rtol=1e-5)
+        for i, w in enumerate(m.get_weights()):
+            np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=1e-4, atol=1e-6)
