@@ -141,8 +141,82 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+// Epilogue of one 32-row slice of an accumulator tile (rows `row0`.., `ncols` columns from TMEM address `tmem_row`).
+// The warp converts 128 bytes of each row at a time (64 bf16 or 32 fp32 columns), writes them into a swizzled
+// 32 x 128 B staging buffer (`stage`: two such buffers, 1024-byte aligned) and lets the TMA engine store that box, so
+// global memory sees full 128-byte lines and rows/columns beyond M/N are clipped by the tensor map.  `stores` counts
+// the boxes this warp has issued (selects the staging buffer).  Lane 0 must run `cp.async.bulk.wait_group 0` before
+// the CTA exits.
+__device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int n0, int row0, uint32_t stage, uint32_t& stores,
+                                               const CUtensorMap* map_c, const GemmParams& p, int lane) {
+  const int cols_per_chunk = p.out_fp32 ? 32 : 64;
+  const int chunks = ncols / cols_per_chunk;
+  const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+  for (int c = 0; c < chunks; ++c) {
+    const int col0 = n0 + c * cols_per_chunk;
+    if (col0 >= p.N) break;
+    uint32_t r[64];
+    tmem_ld32(tmem_row + (uint32_t)(c * cols_per_chunk), r);
+    if (!p.out_fp32) tmem_ld32(tmem_row + (uint32_t)(c * cols_per_chunk + 32), r + 32);
+    // the staging buffer used two stores ago must have been read out by the TMA engine
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    __syncwarp();
+    const uint32_t buf = stage + (stores & 1u) * 4096u + (uint32_t)lane * 128u;
+    if (p.out_fp32) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + j, p.N - 1));
+      }
+      if (p.act != ACT_NONE) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(buf + (((uint32_t)u ^ sw) << 4)), "f"(v[u * 4]), "f"(v[u * 4 + 1]),
+                     "f"(v[u * 4 + 2]), "f"(v[u * 4 + 3]) : "memory");
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h * 32 + j]);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + h * 32 + j, p.N - 1));
+        }
+        if (p.act != ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const bf16x8 pk = pack8(v + u * 8);
+          const uint4 w = *reinterpret_cast<const uint4*>(&pk);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + (((uint32_t)(h * 4 + u) ^ sw) << 4)), "r"(w.x), "r"(w.y),
+                       "r"(w.z), "r"(w.w) : "memory");
+        }
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0 && row0 < p.M) {
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
+                   "r"(stage + (stores & 1u) * 4096u), "r"(col0), "r"(row0) : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    ++stores;
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 2)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -255,51 +329,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int q = warp & 3;  // TMEM lane quarter this warp may access
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
-        }
-        if (p.act != ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-        }
-        if (p.out_fp32) {
-          float* dst = reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (col0 + g * 4 + 3 < p.N) {
-              *reinterpret_cast<float4*>(dst + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-            } else {
-              for (int j = 0; j < 4; ++j)
-                if (col0 + g * 4 + j < p.N) dst[g * 4 + j] = v[g * 4 + j];
-            }
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 + 7 < p.N) {
-              *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(v + g * 8);
-            } else {
-              for (int j = 0; j < 8; ++j)
-                if (col0 + g * 8 + j < p.N) dst[g * 8 + j] = __float2bfloat16_rn(v[g * 8 + j]);
-            }
-          }
-        }
-      }
+      // every MMA of this CTA's only tile has completed, so the operand ring is free: stage 0 holds the staging buffers
+      uint32_t stores = 0;
+      store_rows_tma(tmem_base + ((uint32_t)(q * 32) << 16), BN, n0, m0 + q * 32, base + (uint32_t)(warp - 2) * 8192u, stores, &map_c, p, lane);
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -320,7 +353,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int OUT_BYTES = 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte staging buffers for TMA stores
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 1024 + 256;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 }  // namespace v2
@@ -340,14 +374,17 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                             const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
   constexpr int BM = v2::BM, BN = v2::BN, BK = v2::BK, STAGES = v2::STAGES, STAGE_BYTES = v2::STAGE_BYTES, A_BYTES = v2::A_BYTES;
   constexpr uint32_t TMEM_COLS = v2::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * STAGE_BYTES);
-  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  // after the operand ring: 4 epilogue warps x 2 staging buffers of 4 KB (32 rows x 128 B, swizzled), then the barriers
+  const uint32_t stage_out = base + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * STAGE_BYTES + v2::OUT_BYTES);
+  const uint32_t bar_base = stage_out + v2::OUT_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
@@ -459,7 +496,8 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
-    uint32_t local = 0;
+    const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;
+    uint32_t local = 0, stores = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
       int m0, n0;
@@ -468,56 +506,14 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
       ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + acc * (uint32_t)BN + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
-        }
-        if (p.act != ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-        }
-        if (p.out_fp32) {
-          float* dst = reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (col0 + g * 4 + 3 < p.N) {
-              *reinterpret_cast<float4*>(dst + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-            } else {
-              for (int j = 0; j < 4; ++j)
-                if (col0 + g * 4 + j < p.N) dst[g * 4 + j] = v[g * 4 + j];
-            }
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)row * p.ldc + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 + 7 < p.N) {
-              *reinterpret_cast<bf16x8*>(dst + g * 8) = pack8(v + g * 8);
-            } else {
-              for (int j = 0; j < 8; ++j)
-                if (col0 + g * 8 + j < p.N) dst[g * 8 + j] = __float2bfloat16_rn(v[g * 8 + j]);
-            }
-          }
-        }
-      }
+      const uint32_t tmem_row = tmem_base + acc * (uint32_t)BN + ((uint32_t)(q * 32) << 16);
+      store_rows_tma(tmem_row, BN, n0, m0 + q * 32, my_stage, stores, &map_c, p, lane);
       // this warp has finished reading the accumulator: hand it back to the MMA issuer
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     if (!ok) {
       if (lane == 0 && p.err) atomicExch(p.err, 13);
       *abort_flag = 1;
@@ -545,14 +541,15 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `pitch_elems`.
-bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long pitch_elems, int box_inner, int box_outer) {
+bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long pitch_elems, int box_inner, int box_outer,
+              bool fp32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * (fp32 ? 4 : 2)};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -572,7 +569,7 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
     kb200_set_error("gemm_bf16: operands must be 16-byte aligned with pitches that are multiples of 8 elements");
     return -2;
   }
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_c;
   static int force_v1 = -1, sm_count = 0;
   if (force_v1 < 0) {
     const char* e = getenv("KB200_GEMM_V1");
@@ -586,6 +583,7 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
   const int bn = use_v2 ? v2::BN : BN;
   bool ok = a_mn_major ? make_map(&map_a, a, M, K, lda, 64, BK) : make_map(&map_a, a, K, M, lda, BK, BM);
   ok = ok && (b_mn_major ? make_map(&map_b, b, N, K, ldb, 64, BK) : make_map(&map_b, b, K, N, ldb, BK, bn));
+  ok = ok && make_map(&map_c, c, N, M, ldc, out_fp32 ? 32 : 64, 32, out_fp32 != 0);
   if (!ok) {
     kb200_set_error("gemm_bf16: cuTensorMapEncodeTiled failed");
     return -3;
@@ -599,10 +597,10 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
   GemmParams p{c, bias, M, N, K, ldc, a_mn_major, b_mn_major, act, out_fp32, err};
   if (use_v2) {
     const unsigned grid = (unsigned)(tiles_v2 < sm_count ? tiles_v2 : sm_count);
-    gemm_bf16_tcgen05_persistent<<<grid, THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, p);
+    gemm_bf16_tcgen05_persistent<<<grid, THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   } else {
     const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    gemm_bf16_tcgen05_kernel<<<(unsigned)tiles, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+    gemm_bf16_tcgen05_kernel<<<(unsigned)tiles, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   }
   KB_CHECK_LAUNCH("gemm_bf16");
   return 0;

@@ -166,7 +166,7 @@ def test_training_on_gpu_transformer_block():
     assert np.isfinite(losses).all() and losses[-1] < losses[0]
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 192), (1000, 264, 520), (4096, 1024, 768), (136, 8, 8)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 192), (1000, 264, 520), (4096, 1024, 768), (136, 8, 8), (5000, 1000, 520), (9504, 520, 72)])
 def test_tcgen05_gemm_all_operand_majors(M, N, K):
     from keras_b200.kernels import gemm
 
