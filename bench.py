@@ -22,9 +22,76 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
 CONFIGS = {
-    "resnet50": {"model": "ResNet-50 v1", "per_gpu_batch": 256, "image": 224, "classes": 1000},
-    "resnet50_small": {"model": "ResNet-50 v1 (smoke size)", "per_gpu_batch": 16, "image": 64, "classes": 1000},
+    "resnet50": {"kind": "resnet", "model": "ResNet-50 v1", "per_gpu_batch": 256, "image": 224, "classes": 1000},
+    "resnet50_small": {"kind": "resnet", "model": "ResNet-50 v1 (smoke size)", "per_gpu_batch": 16, "image": 64, "classes": 1000},
+    "gpt2": {"kind": "decoder", "model": "GPT-2 small (12 x 768, 12 heads, MLP 3072, vocab 50257)", "per_gpu_batch": 16, "seq": 1024, "vocab": 50257,
+             "layers": 12, "d": 768, "heads": 12, "ffn": 3072},
+    "gpt2_small": {"kind": "decoder", "model": "GPT-2 shaped (smoke size)", "per_gpu_batch": 4, "seq": 128, "vocab": 1024, "layers": 2, "d": 128,
+                   "heads": 4, "ffn": 512},
 }
+
+
+def build_model(keras, cfg):
+    """Model + optimizer of a config, written against the public Keras API only (both arms call this)."""
+    if cfg["kind"] == "resnet":
+        img = cfg["image"]
+        model = keras.applications.ResNet50(weights=None, input_shape=(img, img, 3), classes=cfg["classes"])
+        model.compile(optimizer=keras.optimizers.SGD(learning_rate=0.1, momentum=0.9), loss="sparse_categorical_crossentropy")
+        return model
+    seq, d = cfg["seq"], cfg["d"]
+
+    class PositionEmbedding(keras.layers.Layer):
+        def build(self, input_shape):
+            self.table = self.add_weight(shape=(seq, d), initializer="random_normal", name="table")
+
+        def call(self, x):
+            return x + keras.ops.cast(self.table, x.dtype)
+
+    tokens = keras.Input((seq,), dtype="int32")
+    h = keras.layers.Embedding(cfg["vocab"], d, name="wte")(tokens)
+    h = PositionEmbedding(name="wpe")(h)
+    for i in range(cfg["layers"]):
+        a = keras.layers.LayerNormalization(epsilon=1e-5, name=f"ln1_{i}")(h)
+        a = keras.layers.MultiHeadAttention(cfg["heads"], d // cfg["heads"], name=f"attn_{i}")(a, a, use_causal_mask=True)
+        h = keras.layers.Add(name=f"res1_{i}")([h, a])
+        m = keras.layers.LayerNormalization(epsilon=1e-5, name=f"ln2_{i}")(h)
+        m = keras.layers.Dense(cfg["ffn"], activation="gelu", name=f"up_{i}")(m)
+        m = keras.layers.Dense(d, name=f"down_{i}")(m)
+        h = keras.layers.Add(name=f"res2_{i}")([h, m])
+    h = keras.layers.LayerNormalization(epsilon=1e-5, name="ln_f")(h)
+    logits = keras.layers.Dense(cfg["vocab"], use_bias=False, name="lm_head")(h)
+    model = keras.Model(tokens, logits)
+    model.compile(optimizer=keras.optimizers.AdamW(learning_rate=3e-4, weight_decay=0.1),
+                  loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
+    return model
+
+
+def make_batches(torch, cfg, rank, n_buf=3):
+    """Pinned host batches of the config's shape (synthetic)."""
+    gen = torch.Generator().manual_seed(1234 + rank)
+    bs = cfg["per_gpu_batch"]
+    if cfg["kind"] == "resnet":
+        img, classes = cfg["image"], cfg["classes"]
+        xs = [torch.randn((bs, img, img, 3), generator=gen, dtype=torch.float32).pin_memory() for _ in range(n_buf)]
+        ys = [torch.randint(0, classes, (bs,), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_buf)]
+    else:
+        xs = [torch.randint(0, cfg["vocab"], (bs, cfg["seq"]), generator=gen, dtype=torch.int32).pin_memory() for _ in range(n_buf)]
+        ys = [torch.randint(0, cfg["vocab"], (bs, cfg["seq"]), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_buf)]
+    return xs, ys
+
+
+def describe(cfg, world):
+    """(metric, unit, samples per step per GPU, config dict) for the JSON line."""
+    bs = cfg["per_gpu_batch"]
+    if cfg["kind"] == "resnet":
+        return ("ResNet-50 training throughput", "images/sec", bs,
+                {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "image_size": cfg["image"], "seq_len": None,
+                 "parallelism": f"dp{world}", "optimizer": "SGD(momentum=0.9, lr=0.1)", "policy": "mixed_bfloat16",
+                 "l2_hygiene": "inputs_larger_than_L2 (per-step batch and activations exceed 126 MB)"})
+    return ("decoder training throughput", "tokens/sec", bs * cfg["seq"],
+            {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "seq_len": cfg["seq"], "parallelism": f"dp{world}",
+             "optimizer": "AdamW(lr=3e-4, weight_decay=0.1)", "policy": "mixed_bfloat16",
+             "l2_hygiene": "inputs_larger_than_L2 (weights, logits and activations of a step exceed 126 MB)"})
 
 
 class ClockSampler:
@@ -116,16 +183,12 @@ def run_ours(args, cfg):
 
         keras.distribution.set_distribution(keras.distribution.DataParallel())
     keras.config.set_dtype_policy("mixed_bfloat16")
-    bs, img, classes = cfg["per_gpu_batch"], cfg["image"], cfg["classes"]
-    model = keras.applications.ResNet50(weights=None, input_shape=(img, img, 3), classes=classes)
-    model.compile(optimizer=keras.optimizers.SGD(learning_rate=0.1, momentum=0.9), loss="sparse_categorical_crossentropy")
-
-    gen = torch.Generator().manual_seed(1234 + rank)
+    model = build_model(keras, cfg)
     n_buf = 3
-    host_x = [torch.randn((bs, img, img, 3), generator=gen, dtype=torch.float32).pin_memory() for _ in range(n_buf)]
-    host_y = [torch.randint(0, classes, (bs,), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_buf)]
+    host_x, host_y = make_batches(torch, cfg, rank, n_buf)
     dev_x = [t.cuda() for t in host_x]
     dev_y = [t.cuda() for t in host_y]
+    metric, unit, per_step, cfg_out = describe(cfg, world)
 
     model.train_on_batch(host_x[0], host_y[0])  # builds model, optimizer, kernels
     train_fn = model.make_train_function()
@@ -160,20 +223,19 @@ def run_ours(args, cfg):
     ms_e2e = _timed(torch, dist, world, args.steps, e2e_step)
 
     if rank == 0:
-        total = bs * world * args.steps
+        total = per_step * world * args.steps
         value = total / (ms / 1e3)
         e2e_value = total / (ms_e2e / 1e3)
         baseline = _published_baseline()
         out = {
-            "metric": "ResNet-50 training throughput", "value": value, "unit": "images/sec", "n_gpus": world, "steps": args.steps,
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / baseline) if baseline else None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-            "config": {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "image_size": img, "seq_len": None,
-                       "parallelism": f"dp{world}", "optimizer": "SGD(momentum=0.9, lr=0.1)", "policy": "mixed_bfloat16",
-                       "l2_hygiene": "inputs_larger_than_L2 (per-step batch and activations exceed 126 MB)"},
+            "config": cfg_out,
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "images/sec", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": int(host_x[0].numel() * 4 + host_y[0].numel() * 8), "d2h_bytes_per_step": 4,
+            "e2e": {"value": e2e_value, "unit": unit, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()),
+                    "d2h_bytes_per_step": 4,
                     "api": "Model.train_on_batch(pinned host tensors) -> float loss"},
             "gpu_launches": int(launches),
             "final_loss": float(last["loss"]) if not isinstance(last["loss"], (list, tuple)) else float(last["loss"][0]),
@@ -214,15 +276,13 @@ def run_reference(args, cfg):
 
         keras.distribution.set_distribution(keras.distribution.DataParallel())
     keras.config.set_dtype_policy("mixed_bfloat16")
-    bs, img, classes = cfg["per_gpu_batch"], cfg["image"], cfg["classes"]
-    model = keras.applications.ResNet50(weights=None, input_shape=(img, img, 3), classes=classes)
-    model.compile(optimizer=keras.optimizers.SGD(learning_rate=0.1, momentum=0.9), loss="sparse_categorical_crossentropy")
-    gen = torch.Generator().manual_seed(1234 + rank)
+    model = build_model(keras, cfg)
     n_buf = 3
-    host_x = [torch.randn((bs, img, img, 3), generator=gen, dtype=torch.float32).pin_memory() for _ in range(n_buf)]
-    host_y = [torch.randint(0, classes, (bs,), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_buf)]
+    host_x, host_y = make_batches(torch, cfg, rank, n_buf)
     dev_x = [t.cuda() for t in host_x]
     dev_y = [t.cuda() for t in host_y]
+    metric, unit, per_step, cfg_out = describe(cfg, world)
+    cfg_out["framework"] = f"keras {keras.__version__} (torch backend, stock code path)"
     last = {}
 
     def dev_step(i):
@@ -241,19 +301,17 @@ def run_reference(args, cfg):
         e2e_step(i)
     ms_e2e = _timed(torch, dist, world, args.steps, e2e_step)
     if rank == 0:
-        total = bs * world * args.steps
+        total = per_step * world * args.steps
         loss = last["loss"]
         out = {
-            "metric": "ResNet-50 training throughput", "value": total / (ms / 1e3), "unit": "images/sec", "n_gpus": world, "steps": args.steps,
+            "metric": metric, "value": total / (ms / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "image_size": img, "seq_len": None,
-                       "parallelism": f"dp{world}", "optimizer": "SGD(momentum=0.9, lr=0.1)", "policy": "mixed_bfloat16",
-                       "framework": f"keras {keras.__version__} (torch backend, stock code path)",
-                       "l2_hygiene": "inputs_larger_than_L2"},
+            "config": cfg_out,
             "clocks": clocks,
-            "e2e": {"value": total / (ms_e2e / 1e3), "unit": "images/sec", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": int(host_x[0].numel() * 4 + host_y[0].numel() * 8), "d2h_bytes_per_step": 4,
+            "e2e": {"value": total / (ms_e2e / 1e3), "unit": unit, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(host_x[0].numel() * host_x[0].element_size() + host_y[0].numel() * host_y[0].element_size()),
+                    "d2h_bytes_per_step": 4,
                     "api": "Model.train_on_batch(pinned host tensors) -> float loss"},
             "gpu_launches": 0,
             "final_loss": float(loss if not isinstance(loss, (list, tuple)) else loss[0]),

@@ -195,6 +195,14 @@ class Variable:
             # Uninitialized (created in a stateless scope): produce a throw-away value.
             v = self._initializer(self._shape, dtype=self._dtype)
             return self._maybe_autocast(convert_to_tensor(v, dtype=self._torch_dtype))
+        if global_state.get_global_attribute("symbolic_scope") is not None:
+            # shape inference runs on placeholder tensors of another device (meta, or the CPU fallback): follow it
+            dev = global_state.get_global_attribute("torch_device")
+            if dev is not None and dev != self._value.device:
+                shape = self._global_shape or self._shape
+                if dev.type == "meta" or self._shard_slices is not None:
+                    return self._maybe_autocast(torch.empty(tuple(shape), dtype=self._value.dtype, device=dev))
+                return self._maybe_autocast(self._value.to(dev))
         if self._shard_slices is not None:
             from keras_b200.parallel import tensor_parallel
 

@@ -44,6 +44,8 @@ struct GemmParams {
   int a_mn_major, b_mn_major;
   int act, out_fp32;
   int* err;
+  int split_k;        // >1: each work unit covers `kb_per_split` K blocks and adds its fp32 partial tile into C (zeroed by the caller)
+  int kb_per_split;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -206,8 +208,13 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0 && row0 < p.M) {
-      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
-                   "r"(stage + (stores & 1u) * 4096u), "r"(col0), "r"(row0) : "memory");
+      if (p.split_k > 1) {
+        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
+                     "r"(stage + (stores & 1u) * 4096u), "r"(col0), "r"(row0) : "memory");
+      } else {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
+                     "r"(stage + (stores & 1u) * 4096u), "r"(col0), "r"(row0) : "memory");
+      }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
     ++stores;
@@ -394,8 +401,10 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int split = p.split_k > 1 ? p.split_k : 1;
+  const int total_tiles = m_tiles * n_tiles * split;  // work units: (output tile, K slice)
+  const int k_blocks_all = (p.K + BK - 1) / BK;
+  const int kb_per = split > 1 ? p.kb_per_split : k_blocks_all;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -426,8 +435,9 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int m0, n0;
-        tile_coords(t, m_tiles, n_tiles, m0, n0);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        tile_coords(t / split, m_tiles, n_tiles, m0, n0);
+        const int kb0 = (t % split) * kb_per, kb1 = min(kb0 + kb_per, k_blocks_all);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
           if (!ok) break;
@@ -474,7 +484,8 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + acc * (uint32_t)BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int kb0 = (t % split) * kb_per, kb1 = min(kb0 + kb_per, k_blocks_all);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
           if (!ok) break;
@@ -483,7 +494,7 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
           const uint64_t adesc = make_smem_desc(sa, p.a_mn_major), bdesc = make_smem_desc(sb, p.b_mn_major);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(empty_bar(s));
         }
         if (ok) umma_commit(acc_full_bar(acc));
@@ -501,7 +512,7 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
       int m0, n0;
-      tile_coords(t, m_tiles, n_tiles, m0, n0);
+      tile_coords(t / split, m_tiles, n_tiles, m0, n0);
       const uint32_t acc = local & 1;
       ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1, abort_flag);
       if (!ok) break;
@@ -562,9 +573,17 @@ bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long oute
 // Requirements: bf16 operands, 16-byte aligned base pointers, pitches multiples of 8 elements;
 // C bf16 (out_fp32 = 0) or fp32, ldc multiple of 8 (bf16) / 4 (fp32).  `err` is an int in device
 // memory that receives a non-zero code if a bounded wait expires (0 otherwise untouched).
-KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, long long lda, long long ldb,
-                           long long ldc, int a_mn_major, int b_mn_major, int act, int out_fp32, int* err, cudaStream_t stream) {
+//
+// split_k > 1 (persistent kernel only): the K range is cut into `split_k` slices that run as separate work units and
+// add their fp32 partial tiles into C with TMA reduce stores; C must be fp32 and zero on entry, bias/act must be off.
+KB_API int kb200_gemm_bf16_splitk(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldc, int a_mn_major, int b_mn_major, int act, int out_fp32, int split_k, int* err,
+                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (split_k > 1 && (!out_fp32 || bias != nullptr || act != ACT_NONE)) {
+    kb200_set_error("gemm_bf16: split-K needs an fp32 output without bias or activation");
+    return -4;
+  }
   if ((lda % 8) || (ldb % 8) || (((uintptr_t)a | (uintptr_t)b) & 15) || (((uintptr_t)c) & 15) || (ldc % (out_fp32 ? 4 : 8))) {
     kb200_set_error("gemm_bf16: operands must be 16-byte aligned with pitches that are multiples of 8 elements");
     return -2;
@@ -579,7 +598,15 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   const long long tiles_v2 = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
-  const bool use_v2 = !force_v1 && N > 128 && tiles_v2 >= sm_count / 2;
+  int kb_per_split = 0;
+  if (split_k > 1) {
+    const int k_blocks = (K + v2::BK - 1) / v2::BK;
+    if (split_k > k_blocks) split_k = k_blocks;
+    kb_per_split = (k_blocks + split_k - 1) / split_k;
+    split_k = (k_blocks + kb_per_split - 1) / kb_per_split;  // every slice holds at least one K block
+  }
+  if (split_k < 1) split_k = 1;
+  const bool use_v2 = split_k > 1 || (!force_v1 && N > 128 && tiles_v2 >= sm_count / 2);
   const int bn = use_v2 ? v2::BN : BN;
   bool ok = a_mn_major ? make_map(&map_a, a, M, K, lda, 64, BK) : make_map(&map_a, a, K, M, lda, BK, BM);
   ok = ok && (b_mn_major ? make_map(&map_b, b, N, K, ldb, 64, BK) : make_map(&map_b, b, K, N, ldb, BK, bn));
@@ -594,9 +621,10 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
     cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
     attr_set = true;
   }
-  GemmParams p{c, bias, M, N, K, ldc, a_mn_major, b_mn_major, act, out_fp32, err};
+  GemmParams p{c, bias, M, N, K, ldc, a_mn_major, b_mn_major, act, out_fp32, err, split_k, kb_per_split};
   if (use_v2) {
-    const unsigned grid = (unsigned)(tiles_v2 < sm_count ? tiles_v2 : sm_count);
+    const long long units = tiles_v2 * split_k;
+    const unsigned grid = (unsigned)(units < sm_count ? units : sm_count);
     gemm_bf16_tcgen05_persistent<<<grid, THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   } else {
     const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -604,4 +632,9 @@ KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* b
   }
   KB_CHECK_LAUNCH("gemm_bf16");
   return 0;
+}
+
+KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, long long lda, long long ldb,
+                           long long ldc, int a_mn_major, int b_mn_major, int act, int out_fp32, int* err, cudaStream_t stream) {
+  return kb200_gemm_bf16_splitk(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, act, out_fp32, 1, err, stream);
 }

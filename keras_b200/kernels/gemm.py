@@ -39,15 +39,45 @@ def check_errors():
             raise RuntimeError(f"tcgen05 GEMM reported a pipeline time-out (code {code}).")
 
 
-def _ok_2d(t):
+def _ok_2d(t, any_width=False):
+    if any_width and t.is_cuda and t.dtype == torch.bfloat16 and t.ndim == 2 and t.is_contiguous() and t.data_ptr() % 16 == 0:
+        return True  # a weight whose width is padded to a multiple of 8 before the launch
     return t.is_cuda and t.dtype == torch.bfloat16 and t.ndim == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 and t.stride(0) >= t.shape[1]
 
 
-def gemm(a, b, a_mn, b_mn, M, N, K, bias=None, act=0, out_dtype=torch.bfloat16):
-    """Raw launch. ``a``/``b`` are 2-D bf16 tensors in the storage layout named by the major flags."""
+_SM_COUNT = {}
+
+
+def _sm_count(device):
+    n = _SM_COUNT.get(device.index)
+    if n is None:
+        n = _SM_COUNT[device.index] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
+def split_k_for(M, N, K, device):
+    """K slices for a product whose output has too few 128x256 tiles to fill the GPU (weight gradients: small M x N, K = tokens)."""
+    tiles = -(-M // 128) * -(-N // 256)
+    sms = _sm_count(device)
+    if tiles * 2 > sms or K < 2048:
+        return 1
+    return max(1, min(sms // tiles, K // 512))
+
+
+def gemm(a, b, a_mn, b_mn, M, N, K, bias=None, act=0, out_dtype=torch.bfloat16, split_k=1):
+    """Raw launch. ``a``/``b`` are 2-D bf16 tensors in the storage layout named by the major flags.
+
+    ``split_k > 1`` accumulates K slices into a zeroed fp32 buffer (TMA reduce stores) and casts to ``out_dtype``."""
     lib = kops._lib()
-    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     err = _err_flag(a.device)
+    if split_k > 1 and bias is None and act == 0:
+        acc = torch.zeros((M, N), dtype=torch.float32, device=a.device)
+        code = lib.kb200_gemm_bf16_splitk(kops._p(a), kops._p(b), kops._p(acc), None, kops._i(M), kops._i(N), kops._i(K), kops._ll(a.stride(0)),
+                                          kops._ll(b.stride(0)), kops._ll(acc.stride(0)), kops._i(a_mn), kops._i(b_mn), kops._i(0), kops._i(1),
+                                          kops._i(split_k), kops._p(err), kops._stream())
+        kops._check(code, "gemm_bf16")
+        return acc if out_dtype == torch.float32 else acc.to(out_dtype)
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     code = lib.kb200_gemm_bf16(kops._p(a), kops._p(b), kops._p(out), kops._p(bias), kops._i(M), kops._i(N), kops._i(K), kops._ll(a.stride(0)),
                                kops._ll(b.stride(0)), kops._ll(out.stride(0)), kops._i(a_mn), kops._i(b_mn), kops._i(act),
                                kops._i(1 if out_dtype == torch.float32 else 0), kops._p(err), kops._stream())
@@ -56,42 +86,63 @@ def gemm(a, b, a_mn, b_mn, M, N, K, bias=None, act=0, out_dtype=torch.bfloat16):
 
 
 class GemmFn(torch.autograd.Function):
-    """out[M,N] = x[M,K] @ w[K,N] (+ bias), all three products on the tcgen05 kernel."""
+    """out[M,N] = x[M,K] @ w[K,N] (+ bias), all three products on the tcgen05 kernel.
+
+    A width ``N`` that is not a multiple of 8 (a 50257-word vocabulary) runs on a zero-padded copy of the weight:
+    the padded output keeps its 16-byte row pitch and the caller sees its first ``N`` columns as a view."""
 
     @staticmethod
     def forward(ctx, x, w, bias):
         M, K = x.shape
         N = w.shape[1]
+        Np = (N + 7) // 8 * 8
         b32 = bias.float().contiguous() if bias is not None else None
-        out = gemm(x, w, 0, 1, M, N, K, bias=b32)
+        if Np != N:
+            w = torch.nn.functional.pad(w, (0, Np - N))
+            if b32 is not None:
+                b32 = torch.nn.functional.pad(b32, (0, Np - N))
+        out = gemm(x, w, 0, 1, M, Np, K, bias=b32)
         ctx.save_for_backward(x, w)
         ctx.has_bias = bias is not None
         ctx.bias_dtype = bias.dtype if bias is not None else None
-        return out
+        ctx.n = N
+        return out if Np == N else out[:, :N]
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         M, K = x.shape
-        N = w.shape[1]
-        if not _ok_2d(dy):
+        N, Np = ctx.n, w.shape[1]
+        if Np != N:
+            if dy.dtype == torch.bfloat16 and dy.stride(1) == 1 and dy.stride(0) == Np and dy.data_ptr() % 16 == 0:
+                # the gradient is itself the leading columns of a padded buffer (produced for a padded logits view)
+                dyp = dy.as_strided((M, Np), (Np, 1))
+                dyp[:, N:].zero_()
+            else:
+                dyp = torch.empty((M, Np), dtype=torch.bfloat16, device=dy.device)
+                dyp[:, :N].copy_(dy)
+                dyp[:, N:].zero_()
+            dy = dyp
+        elif not _ok_2d(dy):
             dy = dy.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy, w, 0, 0, M, K, N)
+            dx = gemm(dy, w, 0, 0, M, K, Np)
         if ctx.needs_input_grad[1]:
-            dw = gemm(x, dy, 1, 1, K, N, M)
+            dw = gemm(x, dy, 1, 1, K, Np, M, split_k=split_k_for(K, Np, M, x.device))
+            if Np != N:
+                dw = dw[:, :N]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.float().sum(0).to(ctx.bias_dtype)
+            db = dy.sum(0, dtype=torch.float32)[:N].to(ctx.bias_dtype)
         return dx, dw, db
 
 
 def _qualifies(x2, w):
-    if not (_ok_2d(x2) and _ok_2d(w)):
+    if not (_ok_2d(x2) and _ok_2d(w, any_width=True)):
         return False
     M, K = x2.shape
     N = w.shape[1]
-    if K % 8 or N % 8 or M % 8:
+    if K % 8 or M % 8 or (N % 8 and N < 256):
         return False
     return 2 * M * N * K >= _MIN_WORK
 
@@ -124,7 +175,14 @@ def dense(x, kernel, bias, activation_name):
         name = {"gelu": "gelu_erf"}.get(activation_name, activation_name)
         act = _ACT.get(name)
         fused_act = act is not None
-        out = gemm(x2, w, 0, 1, x2.shape[0], w.shape[1], x2.shape[1], bias=b.float().contiguous() if b is not None else None, act=act or 0)
-        return out.reshape(tuple(lead) + (w.shape[1],)), fused_act
+        N = w.shape[1]
+        b32 = b.float().contiguous() if b is not None else None
+        if N % 8:
+            w = torch.nn.functional.pad(w, (0, 8 - N % 8))
+            b32 = torch.nn.functional.pad(b32, (0, 8 - N % 8)) if b32 is not None else None
+        out = gemm(x2, w, 0, 1, x2.shape[0], w.shape[1], x2.shape[1], bias=b32, act=act or 0)
+        if N % 8:
+            out = out[:, :N]
+        return out.reshape(tuple(lead) + (N,)), fused_act
     out = GemmFn.apply(x2, w, b)
     return out.reshape(tuple(lead) + (w.shape[1],)), activation_name in (None, "linear")

@@ -209,30 +209,40 @@ class FusedNorm(torch.autograd.Function):
 
 # ----------------------------------------------------------------- softmax cross-entropy
 class FusedSoftmaxXent(torch.autograd.Function):
+    """Per-row loss in float32 from logits of any float dtype.  Logits may be the leading columns of a wider buffer
+    (rows with a uniform pitch, as a padded GEMM returns them); the gradient then has the same pitch and zeroed padding."""
+
     @staticmethod
     def forward(ctx, logits, labels):
         lib = _lib()
         V = logits.shape[-1]
         rows = logits.numel() // V
-        logits = logits.contiguous()
+        flat = logits.reshape(rows, V)  # a view whenever the leading dimensions collapse
+        if flat.stride(1) != 1 or (rows > 1 and flat.stride(0) < V):
+            flat = flat.contiguous()
+        ld = flat.stride(0) if rows > 1 else V
         labels64 = labels.reshape(-1).to(torch.int64).contiguous()
         out = torch.empty(2 * rows, dtype=torch.float32, device=logits.device)
         loss, lse = out[:rows], out[rows:]
-        _check(lib.kb200_xent_fwd(_p(logits), _p(labels64), _p(loss), _p(lse), _ll(rows), _i(V), _i(_dt(logits)), _stream()), "xent_fwd")
-        ctx.save_for_backward(logits, labels64, lse)
-        ctx.out_shape = labels.shape
-        return loss.reshape(labels.shape).to(logits.dtype) if logits.dtype != torch.float32 else loss.reshape(labels.shape)
+        _check(lib.kb200_xent_fwd(_p(flat), _p(labels64), _p(loss), _p(lse), _ll(rows), _i(V), _ll(ld), _i(_dt(flat)), _stream()), "xent_fwd")
+        ctx.save_for_backward(flat, labels64, lse)
+        ctx.logits_shape = tuple(logits.shape)
+        ctx.ld = ld
+        return loss.reshape(labels.shape)
 
     @staticmethod
     def backward(ctx, dloss):
         lib = _lib()
-        logits, labels64, lse = ctx.saved_tensors
-        V = logits.shape[-1]
-        rows = logits.numel() // V
+        flat, labels64, lse = ctx.saved_tensors
+        rows, V = flat.shape
+        ld = ctx.ld
         dl = dloss.reshape(-1).float().contiguous()
-        dlogits = torch.empty_like(logits)
-        _check(lib.kb200_xent_bwd(_p(logits), _p(labels64), _p(lse), _p(dl), _p(dlogits), _ll(rows), _i(V), _i(_dt(logits)), _stream()), "xent_bwd")
-        return dlogits, None
+        buf = torch.empty((rows, ld), dtype=flat.dtype, device=flat.device)
+        zero_to = ld if ld - V < 16 else V
+        _check(lib.kb200_xent_bwd(_p(flat), _p(labels64), _p(lse), _p(dl), _p(buf), _ll(rows), _i(V), _ll(ld), _i(zero_to), _i(_dt(flat)), _stream()),
+               "xent_bwd")
+        dlogits = buf if ld == V else buf[:, :V]
+        return dlogits.reshape(ctx.logits_shape), None
 
 
 # ------------------------------------------------------------------------ fused optimizers

@@ -169,8 +169,11 @@ class EinsumDense(Layer):
     def compute_output_shape(self, _):
         return self.full_output_shape
 
-    def _contract(self, inputs, kernel):
-        """einsum(equation, inputs, kernel) lowered to a single GEMM when the equation allows."""
+    def _contract(self, inputs, kernel, bias=None):
+        """einsum(equation, inputs, kernel) lowered to a single GEMM when the equation allows.
+
+        With ``bias`` given, returns ``(output, bias_applied)``: a bias spanning the trailing output dimensions is added
+        in the GEMM epilogue."""
         plan = self._gemm
         if plan is not None and isinstance(inputs, torch.Tensor):
             nk, nn = plan
@@ -181,9 +184,19 @@ class EinsumDense(Layer):
             lead = inputs.shape[: inputs.ndim - nk]
             x2 = inputs.reshape(tuple(lead) + (kdim,))
             w2 = kv.reshape(kdim, -1)
+            if bias is not None:
+                bv = bias.value if hasattr(bias, "value") else bias
+                if tuple(bv.shape) == tuple(kv.shape[nk:]):
+                    from keras_b200.kernels import dispatch
+
+                    fused = dispatch.dense(x2, w2, bv.reshape(-1), None)
+                    if fused is not None:
+                        return fused[0].reshape(tuple(lead) + tuple(kv.shape[nk:])), True
             out = ops.matmul(x2, w2)
-            return out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
-        return ops.einsum(self.equation, inputs, kernel)
+            out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+            return out if bias is None else (out, False)
+        out = ops.einsum(self.equation, inputs, kernel)
+        return out if bias is None else (out, False)
 
     def call(self, inputs, training=None):
         if getattr(self._kernel, "_shard_slices", None) is not None:
@@ -192,9 +205,12 @@ class EinsumDense(Layer):
             out = tensor_parallel.einsum_dense(self, inputs)
             if out is not None:
                 return out
-        x = self._contract(inputs, self.kernel)
         if self.bias is not None:
-            x = ops.add(x, self.bias)
+            x, applied = self._contract(inputs, self.kernel, self.bias)
+            if not applied:
+                x = ops.add(x, self.bias)
+        else:
+            x = self._contract(inputs, self.kernel)
         if self.activation is not None and self.activation is not activations.linear:
             x = self.activation(x)
         return x

@@ -27,10 +27,15 @@ class Loss(KerasSaveable):
     def dtype(self):
         return self._dtype
 
+    def _accepts_low_precision(self, y_pred):
+        """True when ``call`` computes in float32 from half-precision predictions by itself (no up-cast copy needed)."""
+        return False
+
     def __call__(self, y_true, y_pred, sample_weight=None):
         in_mask = getattr(y_pred, "_keras_mask", None)
         td = to_torch_dtype(self.dtype)
-        y_pred = tree.map_structure(lambda x: convert_to_tensor(x, dtype=td), y_pred)
+        if not self._accepts_low_precision(y_pred):
+            y_pred = tree.map_structure(lambda x: convert_to_tensor(x, dtype=td), y_pred)
         y_true = tree.map_structure(lambda x: _convert_true(x, td), y_true)
         losses = self.call(y_true, y_pred)
         out_mask = getattr(losses, "_keras_mask", None)

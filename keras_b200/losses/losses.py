@@ -26,6 +26,19 @@ class LossFunctionWrapper(Loss):
         self.fn = fn
         self._fn_kwargs = kwargs
 
+    def _accepts_low_precision(self, y_pred):
+        # the fused softmax cross-entropy kernel reads bf16 logits and accumulates in float32
+        import torch
+
+        if self.fn is not sparse_categorical_crossentropy or not isinstance(y_pred, torch.Tensor) or y_pred.dtype != torch.bfloat16:
+            return False
+        kw = self._fn_kwargs
+        if not kw.get("from_logits") or kw.get("ignore_class") is not None or kw.get("axis", -1) not in (-1, y_pred.ndim - 1):
+            return False
+        from keras_b200.kernels import dispatch
+
+        return self.dtype == "float32" and dispatch.enabled(y_pred) and y_pred.shape[-1] >= 64
+
     def call(self, y_true, y_pred):
         y_true_y_pred = tree.map_structure(squeeze_or_expand_to_same_rank, y_true, y_pred)
         y_true = tree.map_structure_up_to(y_true, lambda x: x[0], y_true_y_pred)

@@ -71,3 +71,10 @@ def test_autocast_scope():
     with AutocastScope("bfloat16"):
         assert v.value.dtype == torch.bfloat16
     assert v.value.dtype == torch.float32
+
+
+def test_kernel_front_ends_import_without_gpu():
+    import importlib
+
+    for name in ("gemm", "ops", "dispatch", "conv", "attention", "microbench", "build", "loader"):
+        importlib.import_module(f"keras_b200.kernels.{name}")

@@ -232,3 +232,69 @@ def test_fused_max_pool_matches_torch(dtype, case):
     y.backward(g.to(dtype))
     ref.backward(g.to(dtype).float())
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=1e-2 if dtype == torch.bfloat16 else 1e-6, atol=1e-2 if dtype == torch.bfloat16 else 1e-6)
+
+
+@pytest.mark.gpu
+def test_custom_layer_with_weight_traces_symbolically_on_gpu():
+    class Shift(keras.layers.Layer):
+        def build(self, input_shape):
+            self.offset = self.add_weight(shape=(input_shape[-1],), initializer="ones", name="offset")
+
+        def call(self, x):
+            return x + keras.ops.cast(self.offset, x.dtype)
+
+    keras.config.set_dtype_policy("float32")
+    inp = keras.Input((5,))
+    model = keras.Model(inp, Shift()(inp))
+    out = model(np.zeros((2, 5), "float32"))
+    assert out.device.type == "cuda" and float(out.sum()) == 10.0
+
+
+@pytest.mark.gpu
+def test_tcgen05_gemm_padded_width_and_split_k_gradients():
+    from keras_b200.kernels import gemm
+
+    torch.manual_seed(2)
+    for M, K, N in [(8192, 256, 1001), (8192, 256, 384)]:
+        x = torch.randn(M, K, device="cuda").bfloat16().requires_grad_(True)
+        w = (torch.randn(K, N, device="cuda") * 0.1).bfloat16().requires_grad_(True)
+        b = torch.randn(N, device="cuda").requires_grad_(True)
+        assert gemm.split_k_for(K, (N + 7) // 8 * 8, M, x.device) > 1
+        y = gemm.GemmFn.apply(x, w, b)
+        assert tuple(y.shape) == (M, N)
+        dy = torch.randn(M, N, device="cuda").bfloat16()
+        y.backward(dy)
+        gemm.check_errors()
+        xf, wf, bf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True), b.detach().clone().requires_grad_(True)
+        ref = xf @ wf + bf
+        ref.backward(dy.float())
+        assert torch.allclose(y.float(), ref, atol=0.3, rtol=2e-2)
+        assert torch.allclose(x.grad.float(), xf.grad, atol=0.3, rtol=3e-2)
+        assert tuple(w.grad.shape) == (K, N)
+        assert torch.allclose(w.grad.float(), wf.grad, atol=2.0, rtol=3e-2)
+        assert torch.allclose(b.grad, bf.grad, atol=1.0, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_softmax_xent_on_padded_logits_view(dtype):
+    import torch.nn.functional as F
+
+    from keras_b200.kernels import ops as kops
+
+    torch.manual_seed(3)
+    rows, V, ld = 64, 1001, 1008
+    buf = (torch.randn(rows, ld, device="cuda") * 3).to(dtype)
+    for logits in (buf[:, :V], buf[:, :V].contiguous()):
+        logits = logits.detach().requires_grad_(True)
+        labels = torch.randint(0, V, (rows,), device="cuda")
+        loss = kops.FusedSoftmaxXent.apply(logits.reshape(8, 8, V), labels.reshape(8, 8))
+        assert loss.dtype == torch.float32
+        g = torch.rand(8, 8, device="cuda")
+        (loss * g).sum().backward()
+        ref_in = logits.detach().float().requires_grad_(True)
+        ref = F.cross_entropy(ref_in, labels, reduction="none")
+        (ref * g.reshape(-1)).sum().backward()
+        assert torch.allclose(loss.reshape(-1), ref, atol=2e-3, rtol=1e-3)
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol, rtol=2e-2)
