@@ -3,6 +3,8 @@
     python -m keras_b200.kernels.microbench gemm --m 8192 --n 8192 --k 8192
     python -m keras_b200.kernels.microbench bn --rows 802816 --channels 256
     python -m keras_b200.kernels.microbench pool --batch 256
+    python -m keras_b200.kernels.microbench norm --rows 16384 --channels 768
+    python -m keras_b200.kernels.microbench xent --rows 16384 --channels 50257
 
 Each prints one JSON line per case: time (median of ``--iters`` after ``--warmup``), achieved TFLOP/s or GB/s and the
 fraction of the measured peak (``MEASURED_PEAKS.json`` beside the package's parent directory when present, else the
@@ -113,9 +115,53 @@ def bench_pool(args, flush):
              "frac_of_peak": (fb + bb) / t_fb / 1e6 / bw, "peak": src}]
 
 
+def bench_norm(args, flush):
+    from keras_b200.kernels import ops as kops
+
+    rows, D = args.rows, args.channels
+    x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    g = torch.ones(D, device="cuda", requires_grad=True)
+    b = torch.zeros(D, device="cuda", requires_grad=True)
+    fwd = lambda: kops.FusedNorm.apply(x, g, b, 1e-5, False)
+    if args.once:
+        fwd().backward(torch.ones(rows, D, device="cuda", dtype=torch.bfloat16))
+        torch.cuda.synchronize()
+        return []
+    dy = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+    t_f = _time(lambda: fwd(), args.iters, args.warmup, flush)
+    t_fb = _time(lambda: torch.autograd.grad(fwd(), (x, g, b), dy), args.iters, args.warmup, flush)
+    _, bw, src = _peaks()
+    fb, bb = rows * D * 4, rows * D * 6
+    return [{"kernel": "layer-norm forward", "shape": [rows, D], "ms": t_f, "gbs": fb / t_f / 1e6, "frac_of_peak": fb / t_f / 1e6 / bw, "peak": src},
+            {"kernel": "layer-norm forward+backward", "shape": [rows, D], "ms": t_fb, "gbs": (fb + bb) / t_fb / 1e6,
+             "frac_of_peak": (fb + bb) / t_fb / 1e6 / bw, "peak": src}]
+
+
+def bench_xent(args, flush):
+    from keras_b200.kernels import ops as kops
+
+    rows, V = args.rows, args.channels
+    ld = (V + 7) // 8 * 8
+    logits = torch.randn(rows, ld, device="cuda", dtype=torch.bfloat16)[:, :V].requires_grad_(True)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    fwd = lambda: kops.FusedSoftmaxXent.apply(logits, labels)
+    if args.once:
+        fwd().sum().backward()
+        torch.cuda.synchronize()
+        return []
+    g = torch.ones(rows, device="cuda")
+    t_f = _time(lambda: fwd(), args.iters, args.warmup, flush)
+    t_fb = _time(lambda: torch.autograd.grad(fwd(), logits, g), args.iters, args.warmup, flush)
+    _, bw, src = _peaks()
+    fb, bb = rows * V * 2, rows * V * 4
+    return [{"kernel": "softmax-xent forward", "shape": [rows, V], "ms": t_f, "gbs": fb / t_f / 1e6, "frac_of_peak": fb / t_f / 1e6 / bw, "peak": src},
+            {"kernel": "softmax-xent forward+backward", "shape": [rows, V], "ms": t_fb, "gbs": (fb + bb) / t_fb / 1e6,
+             "frac_of_peak": (fb + bb) / t_fb / 1e6 / bw, "peak": src}]
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "bn", "pool"])
+    ap.add_argument("what", choices=["gemm", "bn", "pool", "norm", "xent"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -127,7 +173,7 @@ def main():
     ap.add_argument("--once", action="store_true")
     args = ap.parse_args()
     flush = torch.zeros(96 * 1024 * 1024, device="cuda")  # 384 MB > 126 MB L2
-    for row in {"gemm": bench_gemm, "bn": bench_bn, "pool": bench_pool}[args.what](args, flush):
+    for row in {"gemm": bench_gemm, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
         print(json.dumps(row))
 
 

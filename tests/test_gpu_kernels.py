@@ -52,7 +52,7 @@ def test_fused_batchnorm_forward_backward(dtype, tol, relu, res):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("rms", [False, True])
-@pytest.mark.parametrize("D", [768, 1000, 4096])
+@pytest.mark.parametrize("D", [64, 768, 1000, 1001, 2048, 4096, 8192])
 def test_fused_norm(dtype, tol, rms, D):
     torch.manual_seed(1)
     x = torch.randn(37, D, device="cuda").to(dtype).requires_grad_(True)
