@@ -143,3 +143,75 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     lib.kb200_wait_selftest(ctypes.c_void_p(flag.data_ptr()), ctypes.c_void_p(status.data_ptr()), ctypes.c_longlong(200), kops._stream())
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+def _fused_gemm_worker(rank, world):
+    import torch.distributed as dist
+
+    import keras_b200 as keras
+    from keras_b200.parallel.fused_gemm import ColumnParallelLinear, FusedGemmContext, RowParallelLinear
+
+    keras.distribution.initialize()
+    fused = FusedGemmContext()
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    errs = []
+    for Ms, K, N in [(256, 512, 768), (1024, 1024, 2048), (256, 512, 768)]:
+        M = Ms * world
+        # all-gather -> GEMM
+        x_rows = torch.randn(Ms, K, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(K, N, device="cuda", generator=g) * 0.05).bfloat16()
+        parts = [torch.empty_like(x_rows) for _ in range(world)]
+        dist.all_gather(parts, x_rows)
+        ref = torch.cat(parts).float() @ w.float()
+        out, gathered = fused.all_gather_gemm(x_rows, w)
+        torch.cuda.synchronize()
+        errs.append(float((out.float() - ref).abs().max() / ref.abs().max()))
+        errs.append(float((gathered.float() - torch.cat(parts).float()).abs().max()))
+        # GEMM -> reduce-scatter
+        a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        full = a.float() @ w.float()
+        dist.all_reduce(full)
+        got = fused.gemm_reduce_scatter(a, w)
+        torch.cuda.synchronize()
+        ref_rows = full[rank * Ms:(rank + 1) * Ms]
+        errs.append(float((got.float() - ref_rows).abs().max() / ref_rows.abs().max()))
+        dist.barrier()
+    # autograd pair: column-parallel up projection, row-parallel down projection on row-sharded activations
+    Ms, D, F = 256, 512, 1024
+    x_rows = torch.randn(Ms, D, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    w1 = (torch.randn(D, F, device="cuda", generator=g) * 0.05).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(F, D, device="cuda", generator=g) * 0.05).bfloat16().requires_grad_(True)
+    h = ColumnParallelLinear.apply(x_rows, w1, None, fused)
+    y_rows = RowParallelLinear.apply(torch.relu(h), w2, fused)
+    dy = torch.randn(Ms, D, device="cuda", generator=g).bfloat16()
+    y_rows.backward(dy)
+    torch.cuda.synchronize()
+    # reference with NCCL collectives and fp32 math
+    parts = [torch.empty_like(x_rows) for _ in range(world)]
+    dist.all_gather(parts, x_rows.detach())
+    xf = torch.cat(parts).float().requires_grad_(True)
+    w1f, w2f = w1.detach().float().requires_grad_(True), w2.detach().float().requires_grad_(True)
+    yf = torch.relu(xf @ w1f) @ w2f
+    dist.all_reduce(yf.data)
+    dparts = [torch.empty_like(dy) for _ in range(world)]
+    dist.all_gather(dparts, dy)
+    yf.backward(torch.cat(dparts).float())
+    dxf = xf.grad.clone()
+    dist.all_reduce(dxf)
+    rel = lambda a, b: float((a.float() - b).abs().max() / (b.abs().max() + 1e-6))
+    errs.append(rel(y_rows, yf.data[rank * Ms:(rank + 1) * Ms]))
+    errs.append(rel(x_rows.grad, dxf[rank * Ms:(rank + 1) * Ms]))
+    errs.append(rel(w1.grad, w1f.grad))
+    errs.append(rel(w2.grad, w2f.grad))
+    fused.check()
+    dist.barrier()
+    fused.close()
+    return {"errs": np.array(errs)}
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_allgather_gemm_and_gemm_reduce_scatter_match_nccl():
+    codes, out = _spawn("_fused_gemm_worker", 2)
+    assert codes == [0, 0], codes
+    for r in (0, 1):
+        assert (out[r]["errs"] < 3e-2).all(), out[r]["errs"]
