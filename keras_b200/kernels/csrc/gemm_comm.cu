@@ -9,9 +9,9 @@
 //     a block's flag only when their TMA producer reaches it, so the transfer hides behind the math.
 //
 //   GEMM -> reduce-scatter   out_r[Ms, N] = sum_s (A_s x B_s)[rows of r].  Every rank computes the full
-//     [world*Ms, N] partial product, remote row blocks first.  The epilogue stores each bf16 tile with a TMA store
-//     straight into the owner's staging slot for this rank and bumps the owner's arrival counter; when its own tiles
-//     are done every CTA waits for the counters of its rank and sums the `world` staged partials into `out`.
+//     [world*Ms, N] partial product, cycling through the owners block by block.  The epilogue stores each bf16 tile with a TMA store
+//     straight into the owner's staging slot for this rank; when its own tiles are done a CTA adds what it delivered
+//     to each owner's arrival counter, then waits for the counters of its rank and sums the `world` staged partials into `out`.
 //
 // The reference has no counterpart: its torch backend runs sharded layers as unsharded ones and its JAX backend
 // leaves the collectives to XLA (keras/src/backend/jax/distribution_lib.py:32-106).
@@ -109,12 +109,18 @@ __device__ bool wait_reach(const unsigned* flag, unsigned target, const CommPara
   }
 }
 
-// Physical 128-row block of logical block `lm`: mode 1 starts on the local slice, mode 2 ends on it.
+// Physical 128-row block of logical block `lm`.  Mode 1 starts on the local slice and then walks the peers' slices in
+// ring order (the order in which the copy CTAs bring them in).  Mode 2 cycles through the owners block by block
+// (rank+1, rank+2, ..., rank), which spreads the remote stores evenly over the whole run of the kernel.
 __device__ __forceinline__ int rotate_block(int lm, int m_tiles, int tpr, const CommParams& c) {
-  const int shift = (c.mode == 1 ? c.rank : c.rank + 1) * tpr;
-  int pm = lm + shift;
-  if (pm >= m_tiles) pm -= m_tiles;
-  return pm;
+  if (c.mode == 1) {
+    int pm = lm + c.rank * tpr;
+    if (pm >= m_tiles) pm -= m_tiles;
+    return pm;
+  }
+  int owner = c.rank + 1 + lm % c.world;
+  if (owner >= c.world) owner -= c.world;
+  return owner * tpr + lm / c.world;
 }
 
 __device__ __forceinline__ void tile_coords_rot(int t, int m_tiles, int n_tiles, int tpr, const CommParams& c, int& m0, int& n0) {
@@ -352,17 +358,9 @@ gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_c
       if (c.mode == 2) {
         const int owner = m0 / c.rows_per_rank;
         store_rows_tma(tmem_row, BN, n0, m0 - owner * c.rows_per_rank + q * 32, my_stage, stores, &maps_c.m[owner], p, lane);
-        // the accumulator is free as soon as it has been read
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(acc_empty_bar(acc));
-          // this warp's rows of the tile are in the owner's staging slot: count them there
-          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-          asm volatile("fence.proxy.async;" ::: "memory");
-          __threadfence_system();
-          red_release_sys_add(c.sig[owner] + SIG_COUNT + parity * MAX_RANKS + c.rank, 1u);
-        }
+        if (lane == 0) mbar_arrive(acc_empty_bar(acc));
       } else {
         store_rows_tma(tmem_row, BN, n0, m0 + q * 32, my_stage, stores, &maps_c.m[0], p, lane);
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -370,7 +368,12 @@ gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (lane == 0) mbar_arrive(acc_empty_bar(acc));
       }
     }
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (lane == 0) {
+      // every tile this warp stored, local or in a peer's staging slot, is complete and visible system-wide
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
+      if (c.mode == 2) __threadfence_system();
+    }
     if (!ok) {
       if (lane == 0 && p.err) atomicExch(p.err, 23);
       *abort_flag = 1;
@@ -382,6 +385,25 @@ gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_c
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(v2::TMEM_COLS) : "memory");
   }
   if (c.mode != 2) return;
+
+  // One counter update per owner and CTA (remote atomics on one address are slow when sent per tile): the number of
+  // warp-level tile slices this CTA delivered to each owner, recomputed from the tile order.
+  if (threadIdx.x == 0 && *abort_flag == 0) {
+    unsigned sent[MAX_RANKS];
+#pragma unroll
+    for (int s = 0; s < MAX_RANKS; ++s) sent[s] = 0u;
+    for (int t = cta; t < total_tiles; t += ctas) {
+      int m0, n0;
+      tile_coords_rot(t, m_tiles, n_tiles, tpr, c, m0, n0);
+      const int owner = m0 / c.rows_per_rank;
+#pragma unroll
+      for (int s = 0; s < MAX_RANKS; ++s)
+        if (s == owner) sent[s] += 4u;
+    }
+#pragma unroll
+    for (int s = 0; s < MAX_RANKS; ++s)
+      if (s < c.world && sent[s] != 0u) red_release_sys_add(c.sig[s] + SIG_COUNT + parity * MAX_RANKS + c.rank, sent[s]);
+  }
 
   // ------------------------------------------------------------------ reduce the staged partials of this rank's rows
   if (threadIdx.x == 0) {
@@ -396,17 +418,24 @@ gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint4* st = reinterpret_cast<const uint4*>(c.stage);
     uint4* out = reinterpret_cast<uint4*>(c.out);
     for (long long i = (long long)cta * THREADS + threadIdx.x; i < vecs; i += (long long)ctas * THREADS) {
+      // all partials of this vector are requested before any is used (one load per rank in flight)
+      uint4 raw[MAX_RANKS];
+#pragma unroll
+      for (int s = 0; s < MAX_RANKS; ++s)
+        if (s < c.world) raw[s] = __ldcg(st + (long long)s * vecs + i);
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int s = 0; s < c.world; ++s) {
-        const uint4 raw = __ldcg(st + (long long)s * vecs + i);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(h[j]);
-          acc[2 * j] += f.x;
-          acc[2 * j + 1] += f.y;
+      for (int s = 0; s < MAX_RANKS; ++s) {
+        if (s < c.world) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[s]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
         }
       }
       const bf16x8 pk = pack8(acc);
@@ -487,8 +516,16 @@ KB_API int kb200_gemm_allgather(void* const* gather, void* const* sig, const voi
     cp.gather[i] = (const uint8_t*)gather[i];
   }
   const int sms = sm_count();
-  if (world == 1) copy_ctas = 0;
-  else if (copy_ctas < 1) copy_ctas = 16;
+  if (world == 1) {
+    copy_ctas = 0;
+  } else if (copy_ctas < 1) {
+    // enough copy CTAs to bring the remote slices in within the time the GEMM takes: one CTA streams about 40 GB/s
+    // (four 32 KB pieces in flight), the GEMM runs at roughly 1.3 PFLOP/s
+    const double gemm_s = 2.0 * M * (double)N * K / 1.3e15;
+    const double remote_bytes = (double)(world - 1) * Ms * K * 2.0;
+    copy_ctas = (int)(1.5 * remote_bytes / (gemm_s * 40e9)) + 2;
+    if (copy_ctas > 24) copy_ctas = 24;
+  }
   if (copy_ctas > sms / 2) copy_ctas = sms / 2;
   cp.copy_ctas = copy_ctas;
   cp.rows_per_rank = Ms;
