@@ -10,6 +10,7 @@ without dictionary-of-depth lookups or structure packing.
 import collections
 
 from keras_b200 import tree
+from keras_b200.core import global_state
 from keras_b200.core.export_registry import keras_export
 from keras_b200.core.keras_tensor import KerasTensor
 from keras_b200.ops.operation import Operation
@@ -96,12 +97,18 @@ class Function(Operation):
             nodes = self._node_order = self._ordered_nodes()
         if fusion is not None and flat_in and fusion.applicable(flat_in[0]):
             return self._run_fused(env, nodes, operation_fn, fusion)
+        sp = global_state.get_global_attribute("tp_sequence_parallel") if call_fn is None else None
         for node in nodes:
             if any(id(t) not in env for t in node.input_tensors):
                 continue
             args, kwargs = node.arguments.fill_in(env)
             op = node.operation if operation_fn is None else operation_fn(node.operation)
-            result = call_fn(op, *args, **kwargs) if call_fn is not None else op(*args, **kwargs)
+            if call_fn is not None:
+                result = call_fn(op, *args, **kwargs)
+            elif sp is not None:
+                result = sp.call(node.operation, op, args, kwargs)
+            else:
+                result = op(*args, **kwargs)
             outs = node.outputs
             if len(outs) == 1 and not isinstance(result, (list, tuple, dict)):
                 env[id(outs[0])] = result
@@ -113,7 +120,7 @@ class Function(Operation):
             if id(ref) not in env:
                 path = tree.flatten_with_path(self._outputs_struct)[i][0]
                 raise ValueError(f"Output with path `{'.'.join(map(str, path))}` is not connected to `inputs`")
-            flat_out.append(env[id(ref)])
+            flat_out.append(env[id(ref)] if sp is None else sp.finish(env[id(ref)]))
         return tree.pack_sequence_as(self._outputs_struct, flat_out)
 
     def _run_fused(self, env, nodes, operation_fn, fusion):
@@ -122,6 +129,7 @@ class Function(Operation):
         if plan is None:
             plan = self._fusion_plan = fusion.build_plan(self)
         training = fusion.training
+        sp = global_state.get_global_attribute("tp_sequence_parallel")
         for node in nodes:
             ins = node.input_tensors
             if any(id(t) not in env for t in ins):
@@ -177,7 +185,7 @@ class Function(Operation):
                 continue
             args, kwargs = node.arguments.fill_in(env)
             op = node.operation if operation_fn is None else operation_fn(node.operation)
-            result = op(*args, **kwargs)
+            result = op(*args, **kwargs) if sp is None else sp.call(node.operation, op, args, kwargs)
             if len(outs) == 1 and not isinstance(result, (list, tuple, dict)):
                 env[id(outs[0])] = result
             else:
@@ -188,7 +196,7 @@ class Function(Operation):
             v = env[id(ref)]
             if isinstance(v, fusion.Deferred):
                 v = fusion.run_bn(v.layer, v.x, training, pre_bias=v.pre_bias)
-            flat_out.append(v)
+            flat_out.append(v if sp is None else sp.finish(v))
         return tree.pack_sequence_as(self._outputs_struct, flat_out)
 
     def _assert_input_compatibility(self, inputs):

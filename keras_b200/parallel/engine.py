@@ -104,6 +104,7 @@ class DataParallelEngine:
         arena = self._gradient_arena(trainable_weights)
         arena.bind()
         loss.backward()
+        self._after_backward(trainable_weights)
         if self.world > 1:
             if self._reducer is not None:
                 if first:
@@ -119,6 +120,9 @@ class DataParallelEngine:
         if not opt._fused_zeroed_grads:
             arena.zero()
         self._steps += 1
+
+    def _after_backward(self, trainable_weights):
+        """Hook between the backward pass and the replica reduction."""
 
     # -- metrics -------------------------------------------------------------------------
     def reduced_metric_state(self, model):
@@ -163,6 +167,24 @@ class ModelParallelEngine(DataParallelEngine):
         from keras_b200.parallel import tensor_parallel
 
         self.plan = tensor_parallel.plan_for_model(distribution, model)
+        self.sequence_parallel = tensor_parallel.enable_sequence_parallel(distribution, model)
+
+    def _after_backward(self, trainable_weights):
+        if self.sequence_parallel is not None:
+            self.sequence_parallel.reduce_partial_gradients(trainable_weights)
+
+    def check(self, wait=False):
+        super().check(wait=wait)
+        if self.sequence_parallel is not None and self.sequence_parallel.fused is not None and wait:
+            self.sequence_parallel.fused.check()
+
+    def close(self):
+        if self.sequence_parallel is not None:
+            from keras_b200.parallel import tensor_parallel
+
+            tensor_parallel.disable_sequence_parallel()
+            self.sequence_parallel = None
+        super().close()
 
     def _replicated_variables(self, model):
         return [v for v in super()._replicated_variables(model) if getattr(v, "_layout", None) is None or all(a is None for a in v._layout)]

@@ -219,12 +219,19 @@ def dense(layer, inputs):
     dim, parts, index, group = shard
     w = _local(layer._kernel, inputs.dtype)
     bias = layer.bias
+    sp, scope = _sp_state(), _call_scope()
     if dim == 1:  # column parallel
-        x = _CopyToRegion.apply(inputs, group)
-        y = torch.matmul(x, w)
+        b = None
         if bias is not None:
-            b = _local(bias, y.dtype) if getattr(bias, "_shard_slices", None) is not None else bias.value.to(y.dtype).chunk(parts)[index]
-            y = y + b
+            b = _local(bias, inputs.dtype) if getattr(bias, "_shard_slices", None) is not None else bias.value.to(inputs.dtype).chunk(parts)[index]
+        y = _fused_column(sp, scope, inputs, w, b)
+        if y is None:
+            if scope is not None and scope.is_shard(inputs):
+                inputs = _GatherDim.apply(inputs, 0, group, index, parts)
+            x = _CopyToRegion.apply(inputs, group)
+            y = torch.matmul(x, w)
+            if b is not None:
+                y = y + b
         y = _activate(layer, y)
         if getattr(layer, "_tp_keep_sharded", False):
             return y
@@ -237,10 +244,21 @@ def dense(layer, inputs):
         x = inputs
     else:
         return None
-    y = _ReduceFromRegion.apply(torch.matmul(x, w), group)
+    if scope is not None and scope.is_shard(x):
+        # a row-parallel layer fed by a batch shard has no pairing column layer before it: work on the full batch
+        x = _GatherDim.apply(x, 0, group, index, parts)
+    y = _fused_row(sp, scope, x, w)
+    sharded_out = y is not None
+    if y is None:
+        y = _ReduceFromRegion.apply(torch.matmul(x, w), group)
     if bias is not None:
         y = y + (bias.value.to(y.dtype) if getattr(bias, "_shard_slices", None) is None else gather_variable(bias).to(y.dtype))
-    return _activate(layer, y)
+        if sharded_out:
+            sp.mark_partial(bias)
+    y = _activate(layer, y)
+    if sharded_out:
+        scope.emitted.add(id(y))
+    return y
 
 
 def _activate(layer, y):
@@ -265,10 +283,31 @@ def einsum_dense(layer, inputs):
     letter = k_spec[dim]
     w = _local(layer._kernel, inputs.dtype)
     bias = layer.bias
+    sp, scope = _sp_state(), _call_scope()
+    plan = getattr(layer, "_gemm", None)
     if letter in out_spec:  # column-like: the sharded letter survives into the output
+        odim = out_spec.index(letter)
+        if plan is not None and scope is not None and scope.is_shard(inputs):
+            nk = plan[0]
+            kdim = 1
+            for d in w.shape[:nk]:
+                kdim *= d
+            bflat = None
+            if bias is not None and getattr(bias, "_shard_slices", None) is not None and tuple(bias._value.shape) == tuple(w.shape[nk:]):
+                bflat = _local(bias, inputs.dtype).reshape(-1)
+            if bias is None or bflat is not None:
+                x2 = inputs.reshape(tuple(inputs.shape[: inputs.ndim - nk]) + (kdim,))
+                y = _fused_column(sp, scope, x2, w.reshape(kdim, -1), bflat)
+                if y is not None:
+                    y = y.reshape(tuple(y.shape[:-1]) + tuple(w.shape[nk:]))
+                    y = _activate(layer, y)
+                    if getattr(layer, "_tp_keep_sharded", False):
+                        return y
+                    return _GatherDim.apply(y, odim, group, index, parts)
+        if scope is not None and scope.is_shard(inputs):
+            inputs = _GatherDim.apply(inputs, 0, group, index, parts)
         x = _CopyToRegion.apply(inputs, group)
         y = torch.einsum(layer.equation, x, w)
-        odim = out_spec.index(letter)
         if bias is not None:
             b = bias.value.to(y.dtype)
             if getattr(bias, "_shard_slices", None) is not None:
@@ -295,10 +334,30 @@ def einsum_dense(layer, inputs):
         x = inputs
     else:
         return None
-    y = _ReduceFromRegion.apply(torch.einsum(layer.equation, x, w), group)
+    if scope is not None and scope.is_shard(x):
+        x = _GatherDim.apply(x, 0, group, index, parts)
+    y = None
+    if plan is not None and dim < plan[0]:
+        nk = plan[0]
+        kdim = 1
+        for d in w.shape[:nk]:
+            kdim *= d
+        if x.shape[x.ndim - nk:] == w.shape[:nk]:
+            x2 = x.reshape(tuple(x.shape[: x.ndim - nk]) + (kdim,))
+            y = _fused_row(sp, scope, x2, w.reshape(kdim, -1))
+            if y is not None:
+                y = y.reshape(tuple(y.shape[:-1]) + tuple(w.shape[nk:]))
+    sharded_out = y is not None
+    if y is None:
+        y = _ReduceFromRegion.apply(torch.einsum(layer.equation, x, w), group)
     if bias is not None:
         y = y + (bias.value.to(y.dtype) if getattr(bias, "_shard_slices", None) is None else gather_variable(bias).to(y.dtype))
-    return _activate(layer, y)
+        if sharded_out:
+            sp.mark_partial(bias)
+    y = _activate(layer, y)
+    if sharded_out:
+        scope.emitted.add(id(y))
+    return y
 
 
 def _is_row_parallel(layer):
@@ -435,3 +494,246 @@ def mark_attention(layer, projections, output_dense):
 
 def gather_dim(x, dim, parts, index, group):
     return _GatherDim.apply(x, dim % x.ndim, group, index, parts)
+
+
+# ------------------------------------------------------------------------ sequence-parallel execution of Functional graphs
+# Between tensor-parallel blocks an activation is needed in full by nobody: it is the output of a row-parallel layer (a
+# sum over the model axis) and feeds per-sample layers (normalisation, dropout, residual adds) until the next
+# column-parallel layer.  So the row-parallel layer reduce-scatters its output over the batch dimension inside its GEMM
+# (each rank keeps the samples [index*B/parts, (index+1)*B/parts)), the per-sample layers run on that shard, and the
+# next column-parallel layer all-gathers the shard inside its GEMM (``fused_gemm``).  The Functional executor drives
+# this: it wraps a batch shard in ``BatchShard``, unwraps it for layers that can work on a shard and gathers it for every
+# other layer, so an unknown layer always sees the full tensor.
+class BatchShard:
+    """A tensor of which this rank holds the samples of its model-axis index (dimension 0)."""
+
+    __slots__ = ("local",)
+
+    def __init__(self, local):
+        self.local = local
+
+
+class _CallScope:
+    """One executor-level layer call.  ``shard_batch``: leading extent of the batch shards handed to the layer (None when
+    it received full tensors); a nested layer tells a shard from a full-batch tensor by that extent."""
+
+    __slots__ = ("shard_batch", "emitted")
+
+    def __init__(self, shard_batch):
+        self.shard_batch = shard_batch
+        self.emitted = set()
+
+    def is_shard(self, x):
+        return self.shard_batch is not None and x.ndim >= 1 and x.shape[0] == self.shard_batch
+
+
+def _sp_state():
+    return global_state.get_global_attribute("tp_sequence_parallel")
+
+
+def _call_scope():
+    sp = _sp_state()
+    return sp.scope if sp is not None else None
+
+
+class SequenceParallel:
+    """Executor hook (``global_state`` attribute ``tp_sequence_parallel``) of one model-parallel group."""
+
+    def __init__(self, parts, index, group, fused, emulate=False):
+        self.parts, self.index, self.group, self.fused = parts, index, group, fused
+        self.emulate = emulate  # no fused kernels (CPU): same data flow with library collectives around a plain matmul
+        self.scope = None
+        self.partial_variables = {}  # id -> variable whose gradient was computed from this rank's samples only
+
+    # -- classification ----------------------------------------------------------------------------
+    def _kind(self, op):
+        from keras_b200.layers.activations.activation_layers import Activation, ELU, LeakyReLU, ReLU
+        from keras_b200.layers.attention.attention_layers import GroupedQueryAttention, MultiHeadAttention
+        from keras_b200.layers.core.dense import Dense
+        from keras_b200.layers.core.einsum_dense import EinsumDense
+        from keras_b200.layers.merging.merging_layers import Add, Multiply, Subtract
+        from keras_b200.layers.normalization.normalization_layers import LayerNormalization, RMSNormalization
+        from keras_b200.layers.regularization.regularization_layers import Dropout
+
+        cached = getattr(op, "_tp_sp_kind", False)
+        if cached is not False:
+            return cached
+        kind = None
+        if isinstance(op, (Dense, EinsumDense)):
+            if getattr(getattr(op, "_kernel", None), "_shard_slices", None) is not None and _single_shard(op._kernel) is not None:
+                kind = "tp"
+        elif isinstance(op, (MultiHeadAttention, GroupedQueryAttention)):
+            q = getattr(op, "_query_dense", None)
+            if q is not None and getattr(q._kernel, "_shard_slices", None) is not None:
+                projections = [op._query_dense, op._key_dense, op._value_dense]
+                gate = getattr(op, "_gate_dense", None)
+                if gate is not None:
+                    projections.append(gate)
+                if mark_attention(op, projections, op._output_dense) is not None:
+                    kind = "tp"
+        elif isinstance(op, (LayerNormalization, RMSNormalization)):
+            axis = op.axis if isinstance(op.axis, (list, tuple)) else [op.axis]
+            if all(a != 0 for a in axis):
+                kind = "per_sample"
+        elif isinstance(op, (Dropout, Activation, ReLU, LeakyReLU, ELU, Add, Multiply, Subtract)):
+            kind = "per_sample"
+        if getattr(op, "built", True):
+            try:
+                op._tp_sp_kind = kind
+            except Exception:
+                pass
+        return kind
+
+    # -- executor entry points -----------------------------------------------------------------------
+    def call(self, op, fn, args, kwargs):
+        from keras_b200 import tree
+
+        flat = tree.flatten((args, kwargs))
+        shards = [a for a in flat if isinstance(a, BatchShard)]
+        kind = self._kind(op)
+        if shards and kind is None:
+            args, kwargs = tree.map_structure(lambda a: self.gather(a) if isinstance(a, BatchShard) else a, (args, kwargs))
+            shards = []
+        if shards:
+            full_batch = shards[0].local.shape[0] * self.parts
+
+            def unwrap(a):
+                if isinstance(a, BatchShard):
+                    return a.local
+                if isinstance(a, torch.Tensor) and a.ndim >= 1 and a.shape[0] == full_batch:
+                    return _ScatterDim.apply(a, 0, self.group, self.index, self.parts)
+                return a
+
+            args, kwargs = tree.map_structure(unwrap, (args, kwargs))
+            if kind == "per_sample":
+                for v in getattr(op, "trainable_variables", ()):
+                    self.partial_variables[id(v)] = v
+        outer = self.scope
+        scope = self.scope = _CallScope(shards[0].local.shape[0] if shards else None)
+        try:
+            result = fn(*args, **kwargs)
+        finally:
+            self.scope = outer
+        per_sample = bool(shards) and kind == "per_sample"
+
+        def wrap(r):
+            if isinstance(r, torch.Tensor) and (per_sample or id(r) in scope.emitted):
+                return BatchShard(r)
+            return r
+
+        return tree.map_structure(wrap, result)
+
+    def gather(self, value):
+        if isinstance(value, BatchShard):
+            return _GatherDim.apply(value.local, 0, self.group, self.index, self.parts)
+        return value
+
+    finish = gather
+
+    # -- used by the tensor-parallel layers -----------------------------------------------------------
+    def fused_ok(self, rows, k, n, *tensors):
+        from keras_b200.parallel import fused_gemm
+
+        if rows % self.parts:
+            return False
+        if self.emulate:
+            return True
+        if self.fused is None:
+            return False
+        if not all(isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16 for t in tensors):
+            return False
+        return fused_gemm.supported(rows // self.parts, k, n)
+
+    def mark_partial(self, variable):
+        if variable is not None:
+            self.partial_variables[id(variable)] = variable
+
+    def reduce_partial_gradients(self, trainable_weights):
+        """Sum over the model axis the gradients that were computed from this rank's samples only (one packed all-reduce)."""
+        todo = [v._value for v in trainable_weights if id(v) in self.partial_variables and v._value.grad is not None]
+        if not todo:
+            return
+        flat = torch.cat([p.grad.reshape(-1).float() for p in todo])
+        dist.all_reduce(flat, group=self.group)
+        off = 0
+        for p in todo:
+            n = p.grad.numel()
+            p.grad.copy_(flat[off:off + n].view(p.grad.shape))
+            off += n
+
+
+def enable_sequence_parallel(distribution, model):
+    """Install the executor hook when the mesh has one sharded (model) axis of more than one rank on CUDA."""
+    import os
+
+    if os.environ.get("KERAS_B200_TP_FUSED", "1") == "0" or not process_groups.is_initialized():
+        return None
+    mesh = distribution.device_mesh
+    groups = mesh.backend_mesh
+    axes = [a for a in mesh.axis_names if a != distribution.batch_dim_name and groups.size(a) > 1]
+    if len(axes) != 1:
+        return None
+    axis = axes[0]
+    from keras_b200.core.tensor import get_device
+
+    if get_device().type != "cuda":
+        if os.environ.get("KERAS_B200_TP_SP_EMULATE") != "1":
+            return None
+        sp = SequenceParallel(groups.size(axis), groups.index(axis), groups.get_group(axis), None, emulate=True)
+        global_state.set_global_attribute("tp_sequence_parallel", sp)
+        return sp
+    from keras_b200.kernels import loader
+
+    if loader.get() is None:
+        return None
+    from keras_b200.parallel.fused_gemm import FusedGemmContext
+
+    members = groups.members(axis)
+    fused = FusedGemmContext(ranks=members, group=groups.get_group(axis))
+    sp = SequenceParallel(groups.size(axis), groups.index(axis), groups.get_group(axis), fused)
+    global_state.set_global_attribute("tp_sequence_parallel", sp)
+    return sp
+
+
+def disable_sequence_parallel():
+    sp = _sp_state()
+    if sp is not None:
+        global_state.set_global_attribute("tp_sequence_parallel", None)
+        if sp.fused is not None:
+            sp.fused.close()
+
+
+def _fused_column(sp, scope, x, w, bias):
+    """Column-parallel product of a batch shard ``x`` [..., K]: all-gather -> GEMM.  None when the shapes do not qualify."""
+    from keras_b200.parallel.fused_gemm import ColumnParallelLinear
+
+    if sp is None or scope is None or not scope.is_shard(x):
+        return None
+    K, N = w.shape
+    rows_local = x.numel() // K
+    if not sp.fused_ok(rows_local * sp.parts, K, N, x, w):
+        return None
+    if sp.emulate:
+        full = _CopyToRegion.apply(_GatherDim.apply(x, 0, sp.group, sp.index, sp.parts), sp.group)
+        y = torch.matmul(full, w)
+        return y if bias is None else y + bias
+    x = x.contiguous()
+    y = ColumnParallelLinear.apply(x.reshape(rows_local, K), w, bias, sp.fused)
+    return y.reshape((x.shape[0] * sp.parts,) + tuple(x.shape[1:-1]) + (N,))
+
+
+def _fused_row(sp, scope, x, w):
+    """Row-parallel product reduce-scattered over the batch: GEMM -> reduce-scatter.  ``x``: [B, ..., K_local]."""
+    from keras_b200.parallel.fused_gemm import RowParallelLinear
+
+    if sp is None or scope is None or x.ndim < 2 or x.shape[0] % sp.parts:
+        return None
+    K, N = w.shape
+    rows = x.numel() // K
+    if not sp.fused_ok(rows, K, N, x, w):
+        return None
+    if sp.emulate:
+        return _ScatterDim.apply(_ReduceFromRegion.apply(torch.matmul(x, w), sp.group), 0, sp.group, sp.index, sp.parts)
+    x = x.contiguous()
+    y = RowParallelLinear.apply(x.reshape(rows, K), w, sp.fused)
+    return y.reshape((x.shape[0] // sp.parts,) + tuple(x.shape[1:-1]) + (N,))

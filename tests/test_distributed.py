@@ -243,3 +243,68 @@ def test_tensor_parallel_attention_heads_match_unsharded():
         np.testing.assert_allclose(out[r]["losses"], losses, rtol=1e-5)
         for i, w in enumerate(m.get_weights()):
             np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=1e-4, atol=1e-6)
+
+
+def _sp_model(keras):
+    keras.utils.set_random_seed(21)
+    inp = keras.Input((5, 8))
+    h = keras.layers.Dense(8, name="embed")(inp)
+    for i in range(2):
+        a = keras.layers.LayerNormalization(name=f"ln1_{i}")(h)
+        a = keras.layers.MultiHeadAttention(num_heads=4, key_dim=2, name=f"attn_{i}")(a, a, use_causal_mask=True)
+        h = keras.layers.Add(name=f"res1_{i}")([h, a])
+        m = keras.layers.LayerNormalization(name=f"ln2_{i}")(h)
+        m = keras.layers.Dense(16, activation="relu", name=f"up_{i}")(m)
+        m = keras.layers.Dense(8, name=f"down_{i}")(m)
+        h = keras.layers.Add(name=f"res2_{i}")([h, m])
+    h = keras.layers.LayerNormalization(name="ln_f")(h)
+    out = keras.layers.Dense(3, name="head")(h)
+    m = keras.Model(inp, out)
+    m.compile(optimizer=keras.optimizers.SGD(0.1), loss="mse")
+    return m
+
+
+def _sp_worker(rank, world):
+    os.environ["KERAS_B200_TP_SP_EMULATE"] = "1"
+    import keras_b200 as keras
+    from keras_b200.core import global_state
+
+    keras.distribution.initialize()
+    mesh = keras.distribution.DeviceMesh((1, 2), ["batch", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["attn_.*/(query|key|value)/kernel"] = (None, "model", None)
+    lm["attn_.*/(query|key|value)/bias"] = ("model", None)
+    lm["attn_.*/attention_output/kernel"] = ("model", None, None)
+    lm["up_.*/kernel"] = (None, "model")
+    lm["up_.*/bias"] = ("model",)
+    lm["down_.*/kernel"] = ("model", None)
+    keras.distribution.set_distribution(keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="batch"))
+    m = _sp_model(keras)
+    rng = np.random.RandomState(2)
+    x, y = rng.randn(4, 5, 8).astype("float32"), rng.randn(4, 5, 3).astype("float32")
+    losses = [float(m.train_on_batch(x, y)) for _ in range(3)]
+    sp = global_state.get_global_attribute("tp_sequence_parallel")
+    out = {f"w{i}": w for i, w in enumerate(m.get_weights())}
+    out["losses"] = np.array(losses)
+    out["partial"] = np.array(sorted(v.path for v in sp.partial_variables.values())) if sp is not None else np.array([])
+    out["pred"] = m.predict(x, verbose=0)
+    return out
+
+
+def test_sequence_parallel_executor_matches_unsharded():
+    codes, out = _run(_sp_worker, 2)
+    assert codes == [0, 0], codes
+    import keras_b200 as keras
+
+    m = _sp_model(keras)
+    rng = np.random.RandomState(2)
+    x, y = rng.randn(4, 5, 8).astype("float32"), rng.randn(4, 5, 3).astype("float32")
+    losses = [float(m.train_on_batch(x, y)) for _ in range(3)]
+    for r in (0, 1):
+        partial = [str(p) for p in out[r]["partial"]]
+        # the per-sample layers between the blocks ran on batch shards
+        assert any("ln2_0" in p for p in partial) and any("ln_f" in p for p in partial), partial
+        np.testing.assert_allclose(out[r]["losses"], losses, rtol=1e-5)
+        for i, w in enumerate(m.get_weights()):
+            np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=2e-4, atol=1e-6)
+        np.testing.assert_allclose(out[r]["pred"], m.predict(x, verbose=0), rtol=1e-4, atol=1e-6)

@@ -215,3 +215,63 @@ def test_fused_allgather_gemm_and_gemm_reduce_scatter_match_nccl():
     assert codes == [0, 0], codes
     for r in (0, 1):
         assert (out[r]["errs"] < 3e-2).all(), out[r]["errs"]
+
+
+def _sp_gpu_worker(rank, world):
+    import keras_b200 as keras
+    from keras_b200.core import global_state
+
+    keras.distribution.initialize()
+    mesh = keras.distribution.DeviceMesh((1, 2), ["batch", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["attn_.*/(query|key|value)/kernel"] = (None, "model", None)
+    lm["attn_.*/(query|key|value)/bias"] = ("model", None)
+    lm["attn_.*/attention_output/kernel"] = ("model", None, None)
+    lm["up_.*/kernel"] = (None, "model")
+    lm["up_.*/bias"] = ("model",)
+    lm["down_.*/kernel"] = ("model", None)
+    keras.distribution.set_distribution(keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="batch"))
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    keras.utils.set_random_seed(5)
+    d, T, B = 256, 128, 8
+    inp = keras.Input((T, d))
+    h = inp
+    for i in range(2):
+        a = keras.layers.LayerNormalization(name=f"ln1_{i}")(h)
+        a = keras.layers.MultiHeadAttention(num_heads=4, key_dim=64, name=f"attn_{i}")(a, a, use_causal_mask=True)
+        h = keras.layers.Add(name=f"res1_{i}")([h, a])
+        m = keras.layers.LayerNormalization(name=f"ln2_{i}")(h)
+        m = keras.layers.Dense(1024, activation="relu", name=f"up_{i}")(m)
+        m = keras.layers.Dense(d, name=f"down_{i}")(m)
+        h = keras.layers.Add(name=f"res2_{i}")([h, m])
+    out = keras.layers.Dense(8, name="head")(keras.layers.LayerNormalization(name="ln_f")(h))
+    model = keras.Model(inp, out)
+    model.compile(optimizer=keras.optimizers.SGD(0.05), loss="mse")
+    rng = np.random.RandomState(3)
+    x, y = rng.randn(B, T, d).astype("float32"), rng.randn(B, T, 8).astype("float32")
+    losses = [float(model.train_on_batch(x, y)) for _ in range(4)]
+    sp = global_state.get_global_attribute("tp_sequence_parallel")
+    used = 0 if sp is None or sp.fused is None else sp.fused.epoch
+    model._parallel_engine.check(wait=True)
+    torch.cuda.synchronize()
+    import torch.distributed as dist
+
+    dist.barrier()
+    model._parallel_engine.close()
+    return {"losses": np.array(losses), "fused_calls": np.array(used)}
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sequence_parallel_training_uses_fused_gemms_and_matches_unfused():
+    codes, fused = _spawn("_sp_gpu_worker", 2)
+    assert codes == [0, 0], codes
+    os.environ["KERAS_B200_TP_FUSED"] = "0"
+    try:
+        codes, plain = _spawn("_sp_gpu_worker", 2)
+    finally:
+        del os.environ["KERAS_B200_TP_FUSED"]
+    assert codes == [0, 0], codes
+    assert int(fused[0]["fused_calls"]) > 0 and int(plain[0]["fused_calls"]) == 0
+    np.testing.assert_allclose(fused[0]["losses"], fused[1]["losses"], rtol=1e-6)
+    np.testing.assert_allclose(fused[0]["losses"], plain[0]["losses"], rtol=3e-2)
+    assert fused[0]["losses"][-1] < fused[0]["losses"][0]
