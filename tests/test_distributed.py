@@ -12,12 +12,26 @@ import torch
 import torch.multiprocessing as mp
 
 
+_PORT_STATE = {"next": None}
+
+
 def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
-    return port
+    """A listening port below the ephemeral range (so no outgoing connection of a worker can grab it between the probe
+    and the rendezvous), different for every call of this process."""
+    if _PORT_STATE["next"] is None:
+        _PORT_STATE["next"] = 20000 + (os.getpid() * 37) % 8000
+    for _ in range(200):
+        port = _PORT_STATE["next"]
+        _PORT_STATE["next"] = 20000 + (port - 20000 + 1) % 8000
+        s = socket.socket()
+        try:
+            s.bind(("127.0.0.1", port))
+        except OSError:
+            continue
+        finally:
+            s.close()
+        return port
+    raise RuntimeError("no free rendezvous port found")
 
 
 def _run(fn, world, *args, timeout=240):
