@@ -26,6 +26,11 @@ CONFIGS = {
     "resnet50_small": {"kind": "resnet", "model": "ResNet-50 v1 (smoke size)", "per_gpu_batch": 16, "image": 64, "classes": 1000},
     "gpt2": {"kind": "decoder", "model": "GPT-2 small (12 x 768, 12 heads, MLP 3072, vocab 50257)", "per_gpu_batch": 16, "seq": 1024, "vocab": 50257,
              "layers": 12, "d": 768, "heads": 12, "ffn": 3072},
+    "llama8b": {"kind": "llama", "model": "Llama-style 8B decoder (32 x 4096, 32 query / 8 KV heads, SwiGLU 14336, vocab 128256, RoPE theta 5e5)",
+                "global_batch": 16, "seq": 4096, "vocab": 128256, "layers": 32, "d": 4096, "q_heads": 32, "kv_heads": 8, "ffn": 14336,
+                "rope_theta": 5e5, "model_axis": 4},
+    "llama_small": {"kind": "llama", "model": "Llama-style decoder (smoke size)", "global_batch": 8, "seq": 256, "vocab": 2048, "layers": 2, "d": 512,
+                    "q_heads": 8, "kv_heads": 4, "ffn": 1536, "rope_theta": 5e5, "model_axis": 4},
     "gpt2_small": {"kind": "decoder", "model": "GPT-2 shaped (smoke size)", "per_gpu_batch": 4, "seq": 128, "vocab": 1024, "layers": 2, "d": 128,
                    "heads": 4, "ffn": 512},
 }
@@ -38,6 +43,8 @@ def build_model(keras, cfg):
         model = keras.applications.ResNet50(weights=None, input_shape=(img, img, 3), classes=cfg["classes"])
         model.compile(optimizer=keras.optimizers.SGD(learning_rate=0.1, momentum=0.9), loss="sparse_categorical_crossentropy")
         return model
+    if cfg["kind"] == "llama":
+        return build_llama(keras, cfg)
     seq, d = cfg["seq"], cfg["d"]
 
     class PositionEmbedding(keras.layers.Layer):
@@ -66,10 +73,70 @@ def build_model(keras, cfg):
     return model
 
 
+def build_llama(keras, cfg):
+    """Llama-style decoder from Keras layers: RMSNormalization, GroupedQueryAttention (rotary embedding added by
+    overriding its attention hook), SwiGLU MLP from three bias-free Dense layers."""
+    ops = keras.ops
+    seq, d, hd = cfg["seq"], cfg["d"], cfg["d"] // cfg["q_heads"]
+
+    class RotaryGQA(keras.layers.GroupedQueryAttention):
+        def _rope(self, x):
+            half = hd // 2
+            pos = ops.cast(ops.arange(seq), "float32")
+            inv = ops.exp(ops.cast(ops.arange(half), "float32") * (-float(np_log(cfg["rope_theta"])) / half))
+            ang = ops.expand_dims(ops.expand_dims(pos, -1) * ops.expand_dims(inv, 0), 1)  # [T, 1, half]
+            cos, sin = ops.cast(ops.cos(ang), x.dtype), ops.cast(ops.sin(ang), x.dtype)
+            x1, x2 = x[..., :half], x[..., half:]
+            return ops.concatenate([x1 * cos - x2 * sin, x2 * cos + x1 * sin], axis=-1)
+
+        def _compute_attention(self, query, key, value, attention_mask=None, training=None):
+            return super()._compute_attention(self._rope(query), self._rope(key), value, attention_mask=attention_mask, training=training)
+
+    tokens = keras.Input((seq,), dtype="int32")
+    h = keras.layers.Embedding(cfg["vocab"], d, name="embed")(tokens)
+    for i in range(cfg["layers"]):
+        a = keras.layers.RMSNormalization(epsilon=1e-5, name=f"attn_norm_{i}")(h)
+        a = RotaryGQA(head_dim=hd, num_query_heads=cfg["q_heads"], num_key_value_heads=cfg["kv_heads"], use_bias=False, name=f"attn_{i}")(
+            a, a, use_causal_mask=True)
+        h = keras.layers.Add(name=f"res1_{i}")([h, a])
+        m = keras.layers.RMSNormalization(epsilon=1e-5, name=f"mlp_norm_{i}")(h)
+        g = keras.layers.Dense(cfg["ffn"], use_bias=False, name=f"gate_{i}")(m)
+        u = keras.layers.Dense(cfg["ffn"], use_bias=False, name=f"up_{i}")(m)
+        m = keras.layers.Multiply(name=f"glu_{i}")([keras.layers.Activation("silu", name=f"silu_{i}")(g), u])
+        m = keras.layers.Dense(d, use_bias=False, name=f"down_{i}")(m)
+        h = keras.layers.Add(name=f"res2_{i}")([h, m])
+    h = keras.layers.RMSNormalization(epsilon=1e-5, name="final_norm")(h)
+    logits = keras.layers.Dense(cfg["vocab"], use_bias=False, name="lm_head")(h)
+    model = keras.Model(tokens, logits)
+    model.compile(optimizer=keras.optimizers.AdamW(learning_rate=3e-4, weight_decay=0.1),
+                  loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
+    return model
+
+
+def np_log(x):
+    import math
+
+    return math.log(x)
+
+
+def llama_layout(keras, cfg, world):
+    """(distribution, data replicas) for the decoder: DeviceMesh (data, model), q/k/v/gate/up sharded by columns (heads /
+    hidden units), o/down by rows."""
+    model_axis = min(cfg["model_axis"], world)
+    data_axis = world // model_axis
+    mesh = keras.distribution.DeviceMesh((data_axis, model_axis), ["data", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["attn_.*/(query|key|value)/kernel"] = (None, "model", None)
+    lm["attn_.*/attention_output/kernel"] = ("model", None, None)
+    lm["(gate|up)_.*/kernel"] = (None, "model")
+    lm["down_.*/kernel"] = ("model", None)
+    return keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="data"), data_axis
+
+
 def make_batches(torch, cfg, rank, n_buf=3):
     """Pinned host batches of the config's shape (synthetic)."""
     gen = torch.Generator().manual_seed(1234 + rank)
-    bs = cfg["per_gpu_batch"]
+    bs = cfg["per_gpu_batch"]  # for the llama configs: the batch of this rank's data replica (set by run_ours)
     if cfg["kind"] == "resnet":
         img, classes = cfg["image"], cfg["classes"]
         xs = [torch.randn((bs, img, img, 3), generator=gen, dtype=torch.float32).pin_memory() for _ in range(n_buf)]
@@ -88,6 +155,14 @@ def describe(cfg, world):
                 {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "image_size": cfg["image"], "seq_len": None,
                  "parallelism": f"dp{world}", "optimizer": "SGD(momentum=0.9, lr=0.1)", "policy": "mixed_bfloat16",
                  "l2_hygiene": "inputs_larger_than_L2 (per-step batch and activations exceed 126 MB)"})
+    if cfg["kind"] == "llama":
+        model_axis = min(cfg["model_axis"], world)
+        data_axis = world // model_axis
+        return ("decoder training throughput (ModelParallel)", "tokens/sec", cfg["global_batch"] * cfg["seq"] / world,
+                {"model": cfg["model"], "global_batch": cfg["global_batch"], "seq_len": cfg["seq"], "parallelism": f"dp{data_axis}xtp{model_axis}",
+                 "sharding": "q/k/v/gate/up by columns, o/down by rows; batch-sharded activations between blocks (fused all-gather->GEMM, GEMM->reduce-scatter)",
+                 "optimizer": "AdamW(lr=3e-4, weight_decay=0.1)", "policy": "mixed_bfloat16",
+                 "l2_hygiene": "inputs_larger_than_L2 (weights and activations of a step exceed 126 MB)"})
     return ("decoder training throughput", "tokens/sec", bs * cfg["seq"],
             {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "seq_len": cfg["seq"], "parallelism": f"dp{world}",
              "optimizer": "AdamW(lr=3e-4, weight_decay=0.1)", "policy": "mixed_bfloat16",
@@ -177,15 +252,24 @@ def run_ours(args, cfg):
     from keras_b200.kernels import ops as kops
 
     dist = None
+    data_rank = rank
     if world > 1:
         keras.distribution.initialize()
         import torch.distributed as dist
 
-        keras.distribution.set_distribution(keras.distribution.DataParallel())
+        if cfg["kind"] == "llama":
+            distribution, data_axis = llama_layout(keras, cfg, world)
+            keras.distribution.set_distribution(distribution)
+            cfg = dict(cfg, per_gpu_batch=cfg["global_batch"] // data_axis)
+            data_rank = rank // (world // data_axis)  # ranks of one model-parallel group read the same batch
+        else:
+            keras.distribution.set_distribution(keras.distribution.DataParallel())
+    elif cfg["kind"] == "llama":
+        cfg = dict(cfg, per_gpu_batch=cfg["global_batch"])
     keras.config.set_dtype_policy("mixed_bfloat16")
     model = build_model(keras, cfg)
     n_buf = 3
-    host_x, host_y = make_batches(torch, cfg, rank, n_buf)
+    host_x, host_y = make_batches(torch, cfg, data_rank, n_buf)
     dev_x = [t.cuda() for t in host_x]
     dev_y = [t.cuda() for t in host_y]
     metric, unit, per_step, cfg_out = describe(cfg, world)
@@ -262,6 +346,14 @@ def run_reference(args, cfg):
     import torch
 
     rank, world, local = _dist_env()
+    if cfg["kind"] == "llama" and (world > 1 or cfg["layers"] > 8):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's torch backend never applies ModelParallel layouts to variables "
+                              "(keras/src/backend/torch/core.py creates plain tensors), so every GPU would hold the whole model: 8B parameters "
+                              "with fp32 master weights and Adam state plus activations do not fit 180 GB"}))
+        return
+    if cfg["kind"] == "llama":
+        cfg = dict(cfg, per_gpu_batch=cfg["global_batch"])
     torch.cuda.set_device(local)
     try:
         import keras

@@ -369,8 +369,12 @@ class GroupedQueryAttention(Layer):
         self._return_attention_scores = return_attention_scores
         if key is None:
             key = value
-        attention_mask = self._compute_attention_mask(query, value, query_mask=query_mask, value_mask=value_mask, key_mask=key_mask,
-                                                      attention_mask=attention_mask, use_causal_mask=use_causal_mask)
+        # a purely causal mask is passed to the fused attention kernel as a flag instead of a [T, T] tensor
+        self._causal_only = bool(use_causal_mask and query_mask is None and value_mask is None and key_mask is None and attention_mask is None
+                                 and self.dropout == 0.0 and not return_attention_scores and self._flash_attention is not False)
+        if not self._causal_only:
+            attention_mask = self._compute_attention_mask(query, value, query_mask=query_mask, value_mask=value_mask, key_mask=key_mask,
+                                                          attention_mask=attention_mask, use_causal_mask=use_causal_mask)
         tp = None
         if getattr(self._query_dense._kernel, "_shard_slices", None) is not None:
             from keras_b200.parallel import tensor_parallel
@@ -410,6 +414,7 @@ class GroupedQueryAttention(Layer):
                     attention_mask = ops.expand_dims(attention_mask, axis=-3)
                 attention_mask = ops.cast(attention_mask, "bool")
             out = ops.dot_product_attention(query, key, value, mask=attention_mask, scale=self._inverse_sqrt_head_dim,
+                                            is_causal=bool(getattr(self, "_causal_only", False)) and attention_mask is None,
                                             flash_attention=self._flash_attention or None)
             return out, None
         key = ops.repeat(key, self.num_repeats, axis=2)

@@ -39,6 +39,7 @@ class FusedGemmContext:
         self.gather = [None, None]
         self.stage = [None, None]
         self.epoch = 0
+        self._gather_cache = None
         self.copy_ctas = int(copy_ctas)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize()
@@ -77,6 +78,25 @@ class FusedGemmContext:
                     b.close()
                     slots[i] = None
         self.signals.close()
+
+    def gathered_rows(self, x_rows):
+        """All-gather of a row shard for a weight-gradient product.  Projections that read the same activation (query, key
+        and value; gate and up) run their backward passes one after the other, so the last result is kept and reused."""
+        import torch.distributed as dist
+
+        key = (x_rows.data_ptr(), x_rows._version, tuple(x_rows.shape))
+        if self._gather_cache is not None and self._gather_cache[0] == key:
+            return self._gather_cache[1]
+        full = torch.empty((x_rows.shape[0] * self.world,) + tuple(x_rows.shape[1:]), dtype=x_rows.dtype, device=x_rows.device)
+        if self.world > 1:
+            dist.all_gather_into_tensor(full, x_rows.contiguous(), group=self.group)
+        else:
+            full.copy_(x_rows)
+        self._gather_cache = (key, full)
+        return full
+
+    def drop_cache(self):
+        self._gather_cache = None
 
     # ------------------------------------------------------------------------------------------------
     def all_gather_gemm(self, x_rows, w, b_mn=1, bias=None, act=0, out_dtype=torch.bfloat16):
@@ -138,13 +158,15 @@ class ColumnParallelLinear(torch.autograd.Function):
         ctx.fused = fused
         ctx.has_bias = bias is not None
         ctx.bias_dtype = bias.dtype if bias is not None else None
-        ctx.save_for_backward(gathered.clone() if ctx.needs_input_grad[1] else None, w)
+        # the gathered operand is not kept: backward gathers the shard again (once per distinct input, see gathered_rows)
+        ctx.save_for_backward(x_rows, w)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        xg, w = ctx.saved_tensors
+        x_rows, w = ctx.saved_tensors
         fused = ctx.fused
+        xg = fused.gathered_rows(x_rows) if ctx.needs_input_grad[1] else None
         dy = dy if kgemm._ok_2d(dy) else dy.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:

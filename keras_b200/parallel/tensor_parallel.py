@@ -650,6 +650,8 @@ class SequenceParallel:
 
     def reduce_partial_gradients(self, trainable_weights):
         """Sum over the model axis the gradients that were computed from this rank's samples only (one packed all-reduce)."""
+        if self.fused is not None:
+            self.fused.drop_cache()
         todo = [v._value for v in trainable_weights if id(v) in self.partial_variables and v._value.grad is not None]
         if not todo:
             return
