@@ -433,11 +433,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="resnet50", choices=sorted(CONFIGS))
+    ap.add_argument("--model-axis", type=int, default=0, help="llama configs: ranks per model-parallel group (default: the config's, at most N)")
     ap.add_argument("--profile-range", action="store_true", help="run warm-up, then one step inside cudaProfilerStart/Stop, and exit")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     cfg = CONFIGS[args.config]
+    if args.model_axis > 0 and cfg["kind"] == "llama":
+        cfg = dict(cfg, model_axis=args.model_axis)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world and world == 1 and args.gpus > 1:
         # convenience: re-launch under torchrun when asked for N>1 from a plain python call

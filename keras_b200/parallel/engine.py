@@ -187,4 +187,4 @@ class ModelParallelEngine(DataParallelEngine):
         super().close()
 
     def _replicated_variables(self, model):
-        return [v for v in super()._replicated_variables(model) if getattr(v, "_layout", None) is None or all(a is None for a in v._layout)]
+        return [v for v in super()._replicated_variables(model) if getattr(v, "_shard_slices", None) is None]

@@ -322,3 +322,44 @@ def test_sequence_parallel_executor_matches_unsharded():
         for i, w in enumerate(m.get_weights()):
             np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=2e-4, atol=1e-6)
         np.testing.assert_allclose(out[r]["pred"], m.predict(x, verbose=0), rtol=1e-4, atol=1e-6)
+
+
+def _dp_tp_worker(rank, world):
+    os.environ["KERAS_B200_TP_SP_EMULATE"] = "1"
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    mesh = keras.distribution.DeviceMesh((2, 2), ["data", "model"], devices=keras.distribution.list_devices())
+    lm = keras.distribution.LayoutMap(mesh)
+    lm["attn_.*/(query|key|value)/kernel"] = (None, "model", None)
+    lm["attn_.*/(query|key|value)/bias"] = ("model", None)
+    lm["attn_.*/attention_output/kernel"] = ("model", None, None)
+    lm["up_.*/kernel"] = (None, "model")
+    lm["up_.*/bias"] = ("model",)
+    lm["down_.*/kernel"] = ("model", None)
+    keras.distribution.set_distribution(keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="data"))
+    m = _sp_model(keras)  # SGD: Adam would amplify the rounding noise of gradients that are zero in exact arithmetic (key bias)
+    rng = np.random.RandomState(2)
+    x, y = rng.randn(8, 5, 8).astype("float32"), rng.randn(8, 5, 3).astype("float32")
+    data_index = rank // 2  # ranks (0, 1) form the first model-parallel group and read the first half of the batch
+    xs, ys = x[data_index * 4:(data_index + 1) * 4], y[data_index * 4:(data_index + 1) * 4]
+    losses = [float(m.train_on_batch(xs, ys)) for _ in range(3)]
+    out = {f"w{i}": w for i, w in enumerate(m.get_weights())}
+    out["losses"] = np.array(losses)
+    return out
+
+
+def test_data_and_model_parallel_mesh_matches_single_process():
+    codes, out = _run(_dp_tp_worker, 4, timeout=300)
+    assert codes == [0, 0, 0, 0], codes
+    import keras_b200 as keras
+
+    m = _sp_model(keras)  # SGD: Adam would amplify the rounding noise of gradients that are zero in exact arithmetic (key bias)
+    rng = np.random.RandomState(2)
+    x, y = rng.randn(8, 5, 8).astype("float32"), rng.randn(8, 5, 3).astype("float32")
+    for _ in range(3):
+        m.train_on_batch(x, y)
+    for r in range(4):
+        for i, w in enumerate(m.get_weights()):
+            np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=5e-4, atol=2e-6)
+    assert abs(out[0]["losses"][-1] - out[2]["losses"][-1]) < 1e-6  # the loss is reduced over the data axis
