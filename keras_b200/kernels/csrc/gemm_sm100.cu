@@ -177,7 +177,8 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int split = p.split_k > 1 ? p.split_k : 1;
   const int total_tiles = m_tiles * n_tiles * split;  // work units: (output tile, K slice)
-  const int k_blocks_all = (p.K + BK - 1) / BK;
+  const int bk = p.fp8 ? 2 * BK : BK;  // elements per 128-byte K block
+  const int k_blocks_all = (p.K + bk - 1) / bk;
   const int kb_per = split > 1 ? p.kb_per_split : k_blocks_all;
 
   if (threadIdx.x == 0) {
@@ -217,7 +218,7 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
           if (!ok) break;
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
           mbar_expect_tx(full_bar(s), STAGE_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * bk;
           if (p.a_mn_major) {
             tma_load_2d(sa, &map_a, full_bar(s), m0, k0);
             tma_load_2d(sa + 8192, &map_a, full_bar(s), m0 + 64, k0);
@@ -246,7 +247,9 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+      // instruction descriptor: fp32 accumulate; operand formats bf16 (kind::f16: 1) or e4m3 / e5m2 (kind::f8f6f4: 0 / 1)
+      const uint32_t a_fmt = p.fp8 ? (uint32_t)((p.fp8 - 1) & 1) : 1u, b_fmt = p.fp8 ? (uint32_t)(((p.fp8 - 1) >> 1) & 1) : 1u;
+      const uint32_t idesc = (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       const uint32_t a_step = p.a_mn_major ? (2048u >> 4) : (32u >> 4);
       const uint32_t b_step = p.b_mn_major ? (2048u >> 4) : (32u >> 4);
@@ -266,9 +269,15 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
           const uint64_t adesc = make_smem_desc(sa, p.a_mn_major), bdesc = make_smem_desc(sb, p.b_mn_major);
+          if (p.fp8) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k)  // 32 one-byte elements per instruction: the same 32-byte descriptor step
+              umma_f8(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(empty_bar(s));
         }
         if (ok) umma_commit(acc_full_bar(acc));
@@ -383,4 +392,40 @@ KB_API int kb200_gemm_bf16_splitk(const void* a, const void* b, void* c, const f
 KB_API int kb200_gemm_bf16(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, long long lda, long long ldb,
                            long long ldc, int a_mn_major, int b_mn_major, int act, int out_fp32, int* err, cudaStream_t stream) {
   return kb200_gemm_bf16_splitk(a, b, c, bias, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, act, out_fp32, 1, err, stream);
+}
+
+// C[M,N] = act(alpha * (A x B^T) + bias) with one-byte floating-point operands on kind::f8f6f4 tensor-core instructions.
+//   A: [M, K] bytes, row pitch lda bytes;  B: [N, K] bytes, row pitch ldb bytes (both K-major)
+//   a_format / b_format: 0 = e4m3, 1 = e5m2;  alpha: device scalar (product of the operands' scales) or null
+// Pitches must be multiples of 16 bytes and base pointers 16-byte aligned.  Always runs the persistent kernel.
+KB_API int kb200_gemm_fp8(const void* a, const void* b, void* c, const float* bias, const float* alpha, int M, int N, int K, long long lda,
+                          long long ldb, long long ldc, int a_format, int b_format, int act, int out_fp32, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) || (ldb % 16) || (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) || (ldc % (out_fp32 ? 4 : 8)) || (a_format & ~1) || (b_format & ~1)) {
+    kb200_set_error("gemm_fp8: operands must be 16-byte aligned with pitches that are multiples of 16 bytes; formats 0 (e4m3) or 1 (e5m2)");
+    return -2;
+  }
+  CUtensorMap map_a, map_b, map_c;
+  bool ok = make_map_u8(&map_a, a, K, M, lda, 128, v2::BM) && make_map_u8(&map_b, b, K, N, ldb, 128, v2::BN);
+  ok = ok && make_map(&map_c, c, N, M, ldc, out_fp32 ? 32 : 64, 32, out_fp32 != 0);
+  if (!ok) {
+    kb200_set_error("gemm_fp8: cuTensorMapEncodeTiled failed");
+    return -3;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
+    attr_set = true;
+  }
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  GemmParams p{c, bias, M, N, K, ldc, 0, 0, act, out_fp32, err, 1, 0, 1 + a_format + 2 * b_format, alpha};
+  const long long tiles = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
+  gemm_bf16_tcgen05_persistent<<<(unsigned)(tiles < sm_count ? tiles : sm_count), THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
+  KB_CHECK_LAUNCH("gemm_fp8");
+  return 0;
 }

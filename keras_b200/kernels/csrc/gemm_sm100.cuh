@@ -33,6 +33,8 @@ struct GemmParams {
   int* err;
   int split_k;        // >1: each work unit covers `kb_per_split` K blocks and adds its fp32 partial tile into C (zeroed by the caller)
   int kb_per_split;
+  int fp8 = 0;        // 0: bf16 operands; else 1 + a_format + 2 * b_format with format 0 = e4m3, 1 = e5m2 (both operands K-major)
+  const float* alpha = nullptr;  // device scalar multiplied into the accumulator before bias and activation (fp8 de-scaling)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -101,6 +103,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -141,6 +151,7 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
   const int cols_per_chunk = p.out_fp32 ? 32 : 64;
   const int chunks = ncols / cols_per_chunk;
   const uint32_t sw = (uint32_t)(lane & 7);
+  const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.f;
 #pragma unroll 1
   for (int c = 0; c < chunks; ++c) {
     const int col0 = n0 + c * cols_per_chunk;
@@ -156,7 +167,7 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
     if (p.out_fp32) {
       float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
       if (p.bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + j, p.N - 1));
@@ -174,7 +185,7 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
       for (int h = 0; h < 2; ++h) {
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h * 32 + j]);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h * 32 + j]) * alpha;
         if (p.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + h * 32 + j, p.N - 1));
@@ -265,5 +276,18 @@ static inline bool make_map(CUtensorMap* map, const void* ptr, long long inner, 
   return r == CUDA_SUCCESS;
 }
 
+
+// 2-D byte tensor map (fp8 operands): `inner` contiguous bytes per row, `outer` rows, row pitch `pitch_bytes`.
+static inline bool make_map_u8(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long pitch_bytes, int box_inner, int box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
 
 }  // namespace kbgemm

@@ -45,7 +45,12 @@ def int8_matmul(q_inputs, kernel, out_scale):
 
 
 def fp8_matmul(layer, inputs, kernel, equation, training):
-    return None
+    """float8-policy product on the fp8 tensor-core GEMM (plain matmul on the last axis only); ``None`` otherwise."""
+    if equation is not None or not enabled(inputs):
+        return None
+    from keras_b200.kernels import fp8
+
+    return fp8.linear(layer, inputs, kernel, training)
 
 
 def conv(x, kernel, strides, padding, data_format, dilation):

@@ -1,6 +1,7 @@
 """Kernel micro-benchmarks with CUDA-event timing and roofline fractions.
 
     python -m keras_b200.kernels.microbench gemm --m 8192 --n 8192 --k 8192
+    python -m keras_b200.kernels.microbench gemm_fp8 --m 8192 --n 8192 --k 8192
     python -m keras_b200.kernels.microbench bn --rows 802816 --channels 256
     python -m keras_b200.kernels.microbench pool --batch 256
     python -m keras_b200.kernels.microbench norm --rows 16384 --channels 768
@@ -65,6 +66,34 @@ def bench_gemm(args, flush):
     return [{"kernel": "kb200_gemm_bf16 (tcgen05)", "shape": [M, N, K], "ms": t_ours, "tflops": flops / t_ours / 1e9, "frac_of_peak": flops / t_ours / 1e9 / tf,
              "peak": src, "rel_err_vs_fp32": err},
             {"kernel": "torch.matmul (cuBLAS)", "shape": [M, N, K], "ms": t_lib, "tflops": flops / t_lib / 1e9, "frac_of_peak": flops / t_lib / 1e9 / tf, "peak": src}]
+
+
+def bench_gemm_fp8(args, flush):
+    """e4m3 x e4m3 product of the float8 policy: quantisation kernels timed separately from the GEMM."""
+    from keras_b200.kernels import fp8
+
+    M, N, K = args.m, args.n, args.k
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    sa, sb = torch.tensor(0.01, device="cuda"), torch.tensor(0.01, device="cuda")
+    qa, _, _ = fp8.quantize(a, sa, False)
+    _, qbt, _ = fp8.quantize(b, sb, False, row_major=False, transposed=True)
+    alpha = (sa * sb).reshape(1)
+    ours = lambda: fp8.gemm(qa, qbt, alpha, M, N, K)
+    if args.once:
+        ours()
+        torch.cuda.synchronize()
+        return []
+    ref = (qa[:256, :K].view(torch.float8_e4m3fn).float() @ qbt[:, :K].view(torch.float8_e4m3fn).float().t()) * float(alpha)
+    err = float((ours()[:256].float() - ref).abs().max() / ref.abs().max())
+    t = _time(ours, args.iters, args.warmup, flush)
+    t_q = _time(lambda: fp8.quantize(a, sa, False, row_major=True, transposed=True), args.iters, args.warmup, flush)
+    tf, bw, src = _peaks()
+    flops = 2.0 * M * N * K
+    return [{"kernel": "kb200_gemm_fp8 (tcgen05 kind::f8f6f4)", "shape": [M, N, K], "ms": t, "tflops": flops / t / 1e9,
+             "x_measured_bf16_peak": flops / t / 1e9 / tf, "frac_of_nominal_fp8_peak": flops / t / 1e9 / 4500.0, "peak": src, "rel_err_vs_fp32": err},
+            {"kernel": "kb200_fp8_quantize (row-major + transposed + amax)", "shape": [M, K], "ms": t_q, "gbs": M * K * 4 / t_q / 1e6,
+             "frac_of_peak": M * K * 4 / t_q / 1e6 / bw, "peak": src}]
 
 
 def bench_bn(args, flush):
@@ -161,7 +190,7 @@ def bench_xent(args, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "bn", "pool", "norm", "xent"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "bn", "pool", "norm", "xent"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -173,7 +202,7 @@ def main():
     ap.add_argument("--once", action="store_true")
     args = ap.parse_args()
     flush = torch.zeros(96 * 1024 * 1024, device="cuda")  # 384 MB > 126 MB L2
-    for row in {"gemm": bench_gemm, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
+    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
         print(json.dumps(row))
 
 

@@ -298,3 +298,64 @@ def test_softmax_xent_on_padded_logits_view(dtype):
         assert torch.allclose(loss.reshape(-1), ref, atol=2e-3, rtol=1e-3)
         tol = 1e-5 if dtype == torch.float32 else 1e-2
         assert torch.allclose(logits.grad.float(), ref_in.grad, atol=tol, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_fp8_quantize_and_gemm_match_torch_float8():
+    from keras_b200.kernels import fp8
+
+    torch.manual_seed(4)
+    M, K, N = 512, 384, 640
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(K, N, device="cuda") * 0.2).bfloat16()
+    sx, sw = torch.tensor(0.01, device="cuda"), torch.tensor(0.002, device="cuda")
+    qx, qxt, amax = fp8.quantize(x, sx, False, row_major=True, transposed=True)
+    ref_q = torch.clip(x.float() / sx, -448, 448).to(torch.float8_e4m3fn)
+    assert torch.equal(qx[:, :K].view(torch.float8_e4m3fn).float(), ref_q.float())
+    assert torch.equal(qxt[:, :M].view(torch.float8_e4m3fn).float(), ref_q.float().t())
+    assert float(amax) == float(x.float().abs().max())
+    _, qwt, _ = fp8.quantize(w, sw, False, row_major=False, transposed=True)
+    ref_w = torch.clip(w.float() / sw, -448, 448).to(torch.float8_e4m3fn)
+    y = fp8.gemm(qx, qwt, (sx * sw).reshape(1), M, N, K)
+    ref = (ref_q.float() @ ref_w.float()) * float(sx * sw)
+    from keras_b200.kernels import gemm
+
+    gemm.check_errors()
+    assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    # e5m2 x e4m3 (gradient product)
+    g = torch.randn(M, N, device="cuda").bfloat16()
+    sg = torch.tensor(0.001, device="cuda")
+    qg, _, _ = fp8.quantize(g, sg, True, row_major=True, transposed=False)
+    _, _, _ = qg, None, None
+    qw, _, _ = fp8.quantize(w, sw, False, row_major=True, transposed=False)
+    dx = fp8.gemm(qg, qw, (sg * sw).reshape(1), M, K, N, a_e5m2=True)
+    ref_g = torch.clip(g.float() / sg, -57344, 57344).to(torch.float8_e5m2)
+    ref_dx = (ref_g.float() @ ref_w.float().t()) * float(sg * sw)
+    gemm.check_errors()
+    assert torch.allclose(dx.float(), ref_dx, atol=2e-2 * float(ref_dx.abs().max()), rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_float8_policy_dense_trains_on_fp8_gemm():
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    try:
+        keras.utils.set_random_seed(0)
+        inp = keras.Input((256,))
+        h = keras.layers.Dense(512, activation="relu", name="d1")(inp)
+        out = keras.layers.Dense(256, name="d2")(h)
+        model = keras.Model(inp, out)
+        model.quantize("float8")
+        model.compile(optimizer=keras.optimizers.Adam(1e-3), loss="mse")
+        rng = np.random.default_rng(0)
+        x = rng.standard_normal((512, 256)).astype("float32")
+        y = (x @ rng.standard_normal((256, 256)).astype("float32")) * 0.05
+        from keras_b200.kernels import ops as kops
+
+        before = kops.launch_count()
+        losses = [float(model.train_on_batch(x, y)) for _ in range(30)]
+        assert kops.launch_count() > before
+        assert np.isfinite(losses).all() and losses[-1] < 0.7 * losses[0], losses[::5]
+        d1 = model.get_layer("d1")
+        assert float(d1.inputs_amax_history.numpy()[0]) > 0.0 and float(d1.outputs_grad_amax_history.numpy()[0]) > 0.0
+    finally:
+        keras.config.set_dtype_policy("float32")
