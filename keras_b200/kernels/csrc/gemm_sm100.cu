@@ -177,7 +177,7 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
   const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
   const int split = p.split_k > 1 ? p.split_k : 1;
   const int total_tiles = m_tiles * n_tiles * split;  // work units: (output tile, K slice)
-  const int bk = p.fp8 ? 2 * BK : BK;  // elements per 128-byte K block
+  const int bk = (p.fp8 || p.int8) ? 2 * BK : BK;  // elements per 128-byte K block
   const int k_blocks_all = (p.K + bk - 1) / bk;
   const int kb_per = split > 1 ? p.kb_per_split : k_blocks_all;
 
@@ -249,8 +249,10 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
     if (elect_one()) {
       // instruction descriptor: fp32 accumulate; operand formats bf16 (kind::f16: 1) or e4m3 / e5m2 (kind::f8f6f4: 0 / 1)
       const uint32_t a_fmt = p.fp8 ? (uint32_t)((p.fp8 - 1) & 1) : 1u, b_fmt = p.fp8 ? (uint32_t)(((p.fp8 - 1) >> 1) & 1) : 1u;
-      const uint32_t idesc = (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // kind::i8: accumulator format 2 (s32), operand format 1 (signed 8-bit)
+      const uint32_t idesc = p.int8 ? ((2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24))
+                                    : ((1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24));
       const uint32_t a_step = p.a_mn_major ? (2048u >> 4) : (32u >> 4);
       const uint32_t b_step = p.b_mn_major ? (2048u >> 4) : (32u >> 4);
       uint32_t it = 0, local = 0;
@@ -269,7 +271,11 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
           const uint64_t adesc = make_smem_desc(sa, p.a_mn_major), bdesc = make_smem_desc(sb, p.b_mn_major);
-          if (p.fp8) {
+          if (p.int8) {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_i8(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          } else if (p.fp8) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)  // 32 one-byte elements per instruction: the same 32-byte descriptor step
               umma_f8(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
@@ -427,5 +433,39 @@ KB_API int kb200_gemm_fp8(const void* a, const void* b, void* c, const float* bi
   const long long tiles = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
   gemm_bf16_tcgen05_persistent<<<(unsigned)(tiles < sm_count ? tiles : sm_count), THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   KB_CHECK_LAUNCH("gemm_fp8");
+  return 0;
+}
+
+// C[M,N] = act((A x B^T) * row_scale[m] * col_scale[n] + bias) with signed 8-bit operands (kind::i8, int32 accumulation).
+//   A: [M, K] int8, row pitch lda bytes;  B: [N, K] int8, row pitch ldb bytes (both K-major)
+KB_API int kb200_gemm_i8(const void* a, const void* b, void* c, const float* bias, const float* row_scale, const float* col_scale, int M, int N, int K,
+                         long long lda, long long ldb, long long ldc, int act, int out_fp32, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) || (ldb % 16) || (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) || (ldc % (out_fp32 ? 4 : 8))) {
+    kb200_set_error("gemm_i8: operands must be 16-byte aligned with pitches that are multiples of 16 bytes");
+    return -2;
+  }
+  CUtensorMap map_a, map_b, map_c;
+  bool ok = make_map_u8(&map_a, a, K, M, lda, 128, v2::BM) && make_map_u8(&map_b, b, K, N, ldb, 128, v2::BN);
+  ok = ok && make_map(&map_c, c, N, M, ldc, out_fp32 ? 32 : 64, 32, out_fp32 != 0);
+  if (!ok) {
+    kb200_set_error("gemm_i8: cuTensorMapEncodeTiled failed");
+    return -3;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
+    attr_set = true;
+  }
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  GemmParams p{c, bias, M, N, K, ldc, 0, 0, act, out_fp32, err, 1, 0, 0, nullptr, 1, row_scale, col_scale};
+  const long long tiles = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
+  gemm_bf16_tcgen05_persistent<<<(unsigned)(tiles < sm_count ? tiles : sm_count), THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
+  KB_CHECK_LAUNCH("gemm_i8");
   return 0;
 }

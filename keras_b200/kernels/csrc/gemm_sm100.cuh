@@ -35,6 +35,9 @@ struct GemmParams {
   int kb_per_split;
   int fp8 = 0;        // 0: bf16 operands; else 1 + a_format + 2 * b_format with format 0 = e4m3, 1 = e5m2 (both operands K-major)
   const float* alpha = nullptr;  // device scalar multiplied into the accumulator before bias and activation (fp8 de-scaling)
+  int int8 = 0;                      // 1: signed 8-bit operands (kind::i8), int32 accumulators
+  const float* row_scale = nullptr;  // [M] and [N] factors applied to the accumulator (int8 de-quantisation)
+  const float* col_scale = nullptr;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -111,6 +114,14 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -151,7 +162,8 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
   const int cols_per_chunk = p.out_fp32 ? 32 : 64;
   const int chunks = ncols / cols_per_chunk;
   const uint32_t sw = (uint32_t)(lane & 7);
-  const float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.f;
+  float alpha = p.alpha != nullptr ? __ldg(p.alpha) : 1.f;
+  if (p.row_scale != nullptr) alpha *= __ldg(p.row_scale + min(row0 + lane, p.M - 1));
 #pragma unroll 1
   for (int c = 0; c < chunks; ++c) {
     const int col0 = n0 + c * cols_per_chunk;
@@ -167,7 +179,11 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
     if (p.out_fp32) {
       float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+      for (int j = 0; j < 32; ++j) v[j] = (p.int8 ? __int2float_rn((int)r[j]) : __uint_as_float(r[j])) * alpha;
+      if (p.col_scale != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= __ldg(p.col_scale + min(col0 + j, p.N - 1));
+      }
       if (p.bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + j, p.N - 1));
@@ -185,7 +201,11 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
       for (int h = 0; h < 2; ++h) {
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[h * 32 + j]) * alpha;
+        for (int j = 0; j < 32; ++j) v[j] = (p.int8 ? __int2float_rn((int)r[h * 32 + j]) : __uint_as_float(r[h * 32 + j])) * alpha;
+        if (p.col_scale != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= __ldg(p.col_scale + min(col0 + h * 32 + j, p.N - 1));
+        }
         if (p.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + h * 32 + j, p.N - 1));

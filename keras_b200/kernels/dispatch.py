@@ -40,8 +40,40 @@ def dense(x, kernel, bias, activation_name):
     return gemm.dense(x, kernel, bias, activation_name)
 
 
-def int8_matmul(q_inputs, kernel, out_scale):
-    return None
+_I8_TRANSPOSED = {}
+
+
+def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bfloat16):
+    """``(q_inputs @ kernel) / (inputs_scale * kernel_scale)`` on the int8 tensor-core GEMM, or ``None``.
+
+    ``q_inputs``: int8 [..., K] with per-row ``inputs_scale`` [..., 1]; ``kernel``: int8 [K, N] with ``kernel_scale`` [N]."""
+    if not (enabled(q_inputs) and enabled(kernel)) or q_inputs.dtype != torch.int8 or kernel.dtype != torch.int8 or kernel.ndim != 2:
+        return None
+    K, N = kernel.shape
+    a2 = q_inputs.reshape(-1, K)
+    M = a2.shape[0]
+    if K % 16 or N % 8 or M < 16 or not a2.is_contiguous() or inputs_scale is None or inputs_scale.numel() != M or kernel_scale.numel() != N:
+        return None
+    from keras_b200.kernels import gemm as kgemm
+
+    ops = _ops()
+    key = kernel.data_ptr()
+    hit = _I8_TRANSPOSED.get(key)
+    if hit is None or hit[0] != kernel._version or hit[1].shape != (N, K):
+        if len(_I8_TRANSPOSED) > 256:
+            _I8_TRANSPOSED.clear()
+        hit = (kernel._version, kernel.t().contiguous())  # the GEMM wants both operands K-major
+        _I8_TRANSPOSED[key] = hit
+    bt = hit[1]
+    row_scale = torch.reciprocal(inputs_scale.reshape(-1).float())
+    col_scale = torch.reciprocal(kernel_scale.reshape(-1).float())
+    out = torch.empty((M, N), dtype=out_dtype, device=a2.device)
+    err = kgemm._err_flag(a2.device)
+    code = ops._lib().kb200_gemm_i8(ops._p(a2), ops._p(bt), ops._p(out), None, ops._p(row_scale), ops._p(col_scale), ops._i(M), ops._i(N), ops._i(K),
+                                    ops._ll(a2.stride(0)), ops._ll(bt.stride(0)), ops._ll(out.stride(0)), ops._i(0),
+                                    ops._i(1 if out_dtype == torch.float32 else 0), ops._p(err), ops._stream())
+    ops._check(code, "gemm_i8")
+    return out.reshape(tuple(q_inputs.shape[:-1]) + (N,))
 
 
 def fp8_matmul(layer, inputs, kernel, equation, training):

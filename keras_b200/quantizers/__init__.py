@@ -260,9 +260,11 @@ class _Int8MatmulFn(torch.autograd.Function):
         if equation is None:
             from keras_b200.kernels import dispatch
 
-            fused = dispatch.int8_matmul(q_in, kernel, out_scale) if quantizer is not None else None
+            fused = None
+            if quantizer is not None and compute in (torch.bfloat16, torch.float32):
+                fused = dispatch.int8_matmul(q_in, kernel, in_scale, kernel_scale, out_dtype=compute)
             if fused is not None:
-                return fused.to(compute)
+                return fused
             lead = q_in.shape[:-1]
             a2 = q_in.reshape(-1, q_in.shape[-1])
             if a2.is_cuda and a2.dtype == torch.int8 and a2.shape[0] > 16 and a2.shape[0] % 8 == 0 and a2.shape[1] % 8 == 0 and kernel.shape[1] % 8 == 0:

@@ -359,3 +359,38 @@ def test_float8_policy_dense_trains_on_fp8_gemm():
         assert float(d1.inputs_amax_history.numpy()[0]) > 0.0 and float(d1.outputs_grad_amax_history.numpy()[0]) > 0.0
     finally:
         keras.config.set_dtype_policy("float32")
+
+
+@pytest.mark.gpu
+def test_int8_tensor_core_gemm_matches_integer_reference():
+    from keras_b200.kernels import dispatch, gemm
+
+    torch.manual_seed(5)
+    M, K, N = 384, 512, 768
+    a = torch.randint(-127, 128, (M, K), device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (K, N), device="cuda", dtype=torch.int8)
+    a_scale = torch.rand(M, 1, device="cuda") * 50 + 1
+    w_scale = torch.rand(N, device="cuda") * 50 + 1
+    out = dispatch.int8_matmul(a, w, a_scale, w_scale, out_dtype=torch.float32)
+    gemm.check_errors()
+    assert out is not None
+    ref = (a.double() @ w.double()) / (a_scale.double() * w_scale.double())
+    assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-6 * float(ref.abs().max()))
+
+
+@pytest.mark.gpu
+def test_int8_quantized_model_predicts_on_int8_gemm():
+    keras.config.set_dtype_policy("float32")
+    keras.utils.set_random_seed(1)
+    inp = keras.Input((256,))
+    out = keras.layers.Dense(128, name="d2")(keras.layers.Dense(512, activation="relu", name="d1")(inp))
+    model = keras.Model(inp, out)
+    x = np.random.default_rng(0).standard_normal((64, 256)).astype("float32")
+    ref = model.predict(x, verbose=0)
+    model.quantize("int8")
+    from keras_b200.kernels import ops as kops
+
+    before = kops.launch_count()
+    got = model.predict(x, verbose=0)
+    assert kops.launch_count() > before
+    assert np.abs(got - ref).max() < 0.05 * np.abs(ref).max()
