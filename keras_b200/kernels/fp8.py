@@ -76,9 +76,9 @@ class Fp8LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, x_scale, x_hist, w_scale, w_hist, g_scale, g_hist, training):
         M, K = x.shape
         N = w.shape[1]
-        need_grad = training and torch.is_grad_enabled()
-        qx, qxt, x_amax = quantize(x, x_scale, False, row_major=True, transposed=need_grad)
-        qw, qwt, w_amax = quantize(w, w_scale, False, row_major=need_grad, transposed=True)
+        # the weight-gradient product reads q(x) transposed, the input-gradient product q(w) row-major
+        qx, qxt, x_amax = quantize(x, x_scale, False, row_major=True, transposed=bool(ctx.needs_input_grad[1]))
+        qw, qwt, w_amax = quantize(w, w_scale, False, row_major=bool(ctx.needs_input_grad[0]), transposed=True)
         alpha = (x_scale.reshape(1) * w_scale.reshape(1)).float()
         y = gemm(qx, qwt, alpha, M, N, K)
         if training:
