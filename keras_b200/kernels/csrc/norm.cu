@@ -499,3 +499,72 @@ KB_API int kb200_norm_bwd(const void* dy, const void* x, const float* gamma, con
   KB_CHECK_LAUNCH("norm_partial_reduce");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Column sums of a [rows, cols] bf16/fp32 matrix into fp32 (bias gradients): blocks of 32 column vectors x 8 row lanes
+// accumulate a slab of rows in registers, combine the row lanes through shared memory and write one partial row per
+// slab; norm_partial_reduce2_kernel sums the slabs in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ x, long long ld, long long rows, int cols, float* __restrict__ partial) {
+  constexpr int VN = NVec<T>::N;
+  __shared__ float sm[8][32 * VN + 1];
+  const int cv = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + cv) * VN;
+  const long long per = (rows + gridDim.y - 1) / gridDim.y;
+  const long long r0 = (long long)blockIdx.y * per, r1 = min(rows, r0 + per);
+  float acc[VN];
+#pragma unroll
+  for (int j = 0; j < VN; ++j) acc[j] = 0.f;
+  if (c0 < cols) {
+    for (long long r = r0 + rl; r < r1; r += 8) {
+      float v[VN];
+      nv_unpack<T>(__ldg(reinterpret_cast<const uint4*>(x + r * ld + c0)), v);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VN; ++j) sm[rl][cv * VN + j] = acc[j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < 32 * VN; c += 256) {
+    const int col = blockIdx.x * 32 * VN + c;
+    if (col < cols) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += sm[k][c];
+      partial[(long long)blockIdx.y * cols + col] = s;
+    }
+  }
+}
+
+KB_API int kb200_colsum_slabs(long long rows, int cols, int dtype) {
+  const int vn = dtype == 1 ? 8 : 4;
+  const int col_blocks = (cols + 32 * vn - 1) / (32 * vn);
+  long long slabs = (148 * 6 + col_blocks - 1) / col_blocks;
+  if (slabs > (rows + 63) / 64) slabs = (rows + 63) / 64;
+  if (slabs < 1) slabs = 1;
+  if (slabs > 512) slabs = 512;
+  return (int)slabs;
+}
+
+// x: [rows, cols] with row pitch ld (elements), cols a multiple of the 16-byte vector and rows 16-byte aligned;
+// partial: scratch [kb200_colsum_slabs(rows, cols, dtype), cols] fp32; out: [cols] fp32.
+KB_API int kb200_colsum(const void* x, long long ld, long long rows, int cols, float* partial, float* out, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int vn = dtype == 1 ? 8 : 4;
+  if (cols % vn || ld % vn || ((uintptr_t)x & 15)) {
+    kb200_set_error("colsum: columns and pitch must be multiples of the 16-byte vector and the base pointer aligned");
+    return -2;
+  }
+  const int slabs = kb200_colsum_slabs(rows, cols, dtype);
+  dim3 grid((cols + 32 * vn - 1) / (32 * vn), slabs);
+  if (dtype == 1)
+    colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ld, rows, cols, partial);
+  else
+    colsum_partial_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ld, rows, cols, partial);
+  KB_CHECK_LAUNCH("colsum");
+  dim3 grid2((cols + 31) / 32, 1);
+  norm_partial_reduce2_kernel<<<grid2, 1024, 0, stream>>>(partial, out, nullptr, nullptr, slabs, cols);
+  KB_CHECK_LAUNCH("colsum_reduce");
+  return 0;
+}

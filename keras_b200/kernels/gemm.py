@@ -133,7 +133,7 @@ class GemmFn(torch.autograd.Function):
             if Np != N:
                 dw = dw[:, :N]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.sum(0, dtype=torch.float32)[:N].to(ctx.bias_dtype)
+            db = kops.column_sum(dy)[:N].to(ctx.bias_dtype)
         return dx, dw, db
 
 

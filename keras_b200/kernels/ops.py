@@ -207,6 +207,22 @@ class FusedNorm(torch.autograd.Function):
         return dx, dgamma, dbeta, None, None
 
 
+def column_sum(x):
+    """fp32 sums over the rows of a 2-D bf16/fp32 CUDA tensor (bias gradients); falls back to torch for other layouts."""
+    vn = 8 if x.dtype == torch.bfloat16 else 4
+    if (x.ndim != 2 or not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float32) or x.stride(1) != 1 or x.shape[1] % vn or x.stride(0) % vn
+            or x.data_ptr() % 16 or x.shape[0] < 256):
+        return x.sum(0, dtype=torch.float32)
+    lib = _lib()
+    rows, cols = x.shape
+    lib.kb200_colsum_slabs.restype = ctypes.c_int
+    slabs = lib.kb200_colsum_slabs(_ll(rows), _i(cols), _i(_dt(x)))
+    partial = torch.empty((slabs, cols), dtype=torch.float32, device=x.device)
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    _check(lib.kb200_colsum(_p(x), _ll(x.stride(0)), _ll(rows), _i(cols), _p(partial), _p(out), _i(_dt(x)), _stream()), "colsum")
+    return out
+
+
 # ----------------------------------------------------------------- softmax cross-entropy
 class FusedSoftmaxXent(torch.autograd.Function):
     """Per-row loss in float32 from logits of any float dtype.  Logits may be the leading columns of a wider buffer

@@ -23,12 +23,22 @@ def shadows_for(variables):
 
 
 class _ShadowRead(torch.autograd.Function):
+    """Reads the bf16 shadow; backward hands the gradient to the fp32 parameter.  When the parameter's ``.grad`` is bound
+    to persistent fp32 storage (the gradient arena), the bf16 gradient is added into it directly: one kernel instead of
+    a cast to fp32 followed by autograd's accumulation."""
+
     @staticmethod
     def forward(ctx, param, shadow):
+        ctx.param = param
         return shadow.view_as(shadow)
 
     @staticmethod
     def backward(ctx, grad):
+        p = ctx.param
+        g = p.grad
+        if g is not None and g.dtype == torch.float32 and g.shape == grad.shape and not g.requires_grad:
+            g.add_(grad)
+            return None, None
         return grad.float(), None
 
 

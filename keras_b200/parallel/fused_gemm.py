@@ -176,7 +176,7 @@ class ColumnParallelLinear(torch.autograd.Function):
             M = dy.shape[0]
             dw = kgemm.gemm(xg, dy, 1, 1, K, N, M, split_k=kgemm.split_k_for(K, N, M, dy.device))
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+            db = kops.column_sum(dy).to(ctx.bias_dtype)
         return dx, dw, db, None
 
 

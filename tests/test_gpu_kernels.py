@@ -394,3 +394,18 @@ def test_int8_quantized_model_predicts_on_int8_gemm():
     got = model.predict(x, verbose=0)
     assert kops.launch_count() > before
     assert np.abs(got - ref).max() < 0.05 * np.abs(ref).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_column_sum_kernel(dtype):
+    from keras_b200.kernels import ops as kops
+
+    torch.manual_seed(6)
+    for rows, cols, pitch in [(4096, 768, 768), (1000, 1000, 1008), (300, 8, 8)]:
+        buf = torch.randn(rows, pitch, device="cuda").to(dtype)
+        x = buf[:, :cols]
+        got = kops.column_sum(x)
+        ref = x.double().sum(0)
+        assert got.dtype == torch.float32
+        assert torch.allclose(got.double(), ref, rtol=1e-4, atol=1e-3)
