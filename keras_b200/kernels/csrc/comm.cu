@@ -64,9 +64,16 @@ __device__ bool wait_flags(const unsigned* flags, int n, unsigned epoch, unsigne
 
 __device__ __forceinline__ float4 ld_peer(const float* p) { return __ldcv(reinterpret_cast<const float4*>(p)); }
 
-// In-place all-reduce (sum, times `scale`) of `n` floats (n % 4 == 0) living at the same offset in every rank's arena.
+// In-place collective on `n` floats (n % 4 == 0) living at the same offset in every rank's arena.  The region is cut into
+// `world` slices; rank r works on slice r (broadcast: the root works on the whole region).
+//   mode 0  all-reduce       slice r of every arena := scale * sum over ranks of slice r
+//   mode 1  reduce-scatter   slice r of this arena  := scale * sum over ranks of slice r
+//   mode 2  all-gather       slice r of every arena := slice r of this arena
+//   mode 3  broadcast        every arena := arena of rank `root`
+enum { COMM_ALLREDUCE = 0, COMM_REDUCE_SCATTER = 1, COMM_ALLGATHER = 2, COMM_BROADCAST = 3 };
+
 __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(KbPeers peers, int rank, int world, long long n, float scale, unsigned epoch,
-                                                               unsigned long long timeout_ns, unsigned* status) {
+                                                               unsigned long long timeout_ns, unsigned* status, int mode, int root) {
   unsigned* my_sig = peers.signal[rank];
   // entry: tell every rank that this arena is complete, wait until every arena is
   if (blockIdx.x == 0 && (int)threadIdx.x < world) {
@@ -77,20 +84,35 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(KbPeers peers, i
 
   const long long vecs = n / 4;
   const long long per = (vecs + world - 1) / world;
-  const long long lo = per * rank, hi = min(vecs, lo + per);
+  long long lo = per * rank, hi = min(vecs, lo + per);
+  if (mode == COMM_BROADCAST) {
+    lo = 0;
+    hi = rank == root ? vecs : 0;
+  }
+  const bool reduce = mode == COMM_ALLREDUCE || mode == COMM_REDUCE_SCATTER;
+  const bool spread = mode != COMM_REDUCE_SCATTER;
   for (long long v = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < hi; v += (long long)gridDim.x * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 part[KB_MAX_RANKS];
+    float4 acc;
+    if (reduce) {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 part[KB_MAX_RANKS];
 #pragma unroll
-    for (int p = 0; p < KB_MAX_RANKS; ++p)
-      if (p < world) part[p] = ld_peer(peers.base[p] + v * 4);
+      for (int p = 0; p < KB_MAX_RANKS; ++p)
+        if (p < world) part[p] = ld_peer(peers.base[p] + v * 4);
 #pragma unroll
-    for (int p = 0; p < KB_MAX_RANKS; ++p)
-      if (p < world) { acc.x += part[p].x; acc.y += part[p].y; acc.z += part[p].z; acc.w += part[p].w; }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      for (int p = 0; p < KB_MAX_RANKS; ++p)
+        if (p < world) { acc.x += part[p].x; acc.y += part[p].y; acc.z += part[p].z; acc.w += part[p].w; }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    } else {
+      acc = *reinterpret_cast<const float4*>(peers.base[rank] + v * 4);
+    }
+    if (spread) {
 #pragma unroll
-    for (int p = 0; p < KB_MAX_RANKS; ++p)
-      if (p < world) *reinterpret_cast<float4*>(peers.base[p] + v * 4) = acc;
+      for (int p = 0; p < KB_MAX_RANKS; ++p)
+        if (p < world && (reduce || p != rank)) *reinterpret_cast<float4*>(peers.base[p] + v * 4) = acc;
+    } else {
+      *reinterpret_cast<float4*>(peers.base[rank] + v * 4) = acc;
+    }
   }
   // exit: the last block of this rank publishes "my slice is stored everywhere"
   __threadfence_system();
@@ -156,8 +178,18 @@ KB_API int kb200_ipc_free(void* ptr) {
 // bases / signals: arrays of `world` device pointers (as mapped in this process).  `offset_floats` selects a region
 // of the arenas (same in every rank), `n` its length in floats; both multiples of 4.  status: one unsigned word
 // that the host can read (0 = fine).  The reduction is complete on `stream` when both kernels have run.
+KB_API int kb200_collective_p2p(void* const* bases, void* const* signals, int rank, int world, long long offset_floats, long long n, float scale,
+                                unsigned epoch, long long timeout_ms, unsigned* status, int mode, int root, cudaStream_t stream);
+
 KB_API int kb200_allreduce_p2p(void* const* bases, void* const* signals, int rank, int world, long long offset_floats, long long n, float scale,
                                unsigned epoch, long long timeout_ms, unsigned* status, cudaStream_t stream) {
+  return kb200_collective_p2p(bases, signals, rank, world, offset_floats, n, scale, epoch, timeout_ms, status, COMM_ALLREDUCE, 0, stream);
+}
+
+// mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 broadcast from `root` (see allreduce_twoshot_kernel).
+KB_API int kb200_collective_p2p(void* const* bases, void* const* signals, int rank, int world, long long offset_floats, long long n, float scale,
+                                unsigned epoch, long long timeout_ms, unsigned* status, int mode, int root, cudaStream_t stream) {
+  if (mode < 0 || mode > 3 || root < 0 || root >= world) { kb200_set_error("collective_p2p: bad mode or root"); return -2; }
   if (world < 1 || world > KB_MAX_RANKS) { kb200_set_error("allreduce_p2p: world size must be in [1, 16]"); return -2; }
   if ((n & 3) != 0 || (offset_floats & 3) != 0) { kb200_set_error("allreduce_p2p: offset and length must be multiples of 4 floats"); return -2; }
   if (n == 0) return 0;
@@ -166,12 +198,12 @@ KB_API int kb200_allreduce_p2p(void* const* bases, void* const* signals, int ran
     peers.base[p] = p < world ? (float*)bases[p] + offset_floats : nullptr;
     peers.signal[p] = p < world ? (unsigned*)signals[p] : nullptr;
   }
-  const long long vecs_per_rank = (n / 4 + world - 1) / world;
+  const long long vecs_per_rank = mode == COMM_BROADCAST ? n / 4 : (n / 4 + world - 1) / world;
   long long blocks = (vecs_per_rank + 511) / 512;
   if (blocks > 148 * 2) blocks = 148 * 2;
   if (blocks < 1) blocks = 1;
   const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
-  allreduce_twoshot_kernel<<<(int)blocks, 512, 0, stream>>>(peers, rank, world, n, scale, epoch, timeout_ns, status);
+  allreduce_twoshot_kernel<<<(int)blocks, 512, 0, stream>>>(peers, rank, world, n, scale, epoch, timeout_ns, status, mode, root);
   KB_CHECK_LAUNCH("allreduce_twoshot");
   allreduce_wait_kernel<<<1, 32, 0, stream>>>(peers, rank, world, epoch, timeout_ns, status);
   KB_CHECK_LAUNCH("allreduce_wait");

@@ -47,20 +47,38 @@ class P2PAllReducer:
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._status_event = None
 
-    def all_reduce(self, offset=0, numel=None, scale=1.0):
+    def _collective(self, mode, offset, numel, scale=1.0, root=0):
         from keras_b200.kernels import ops as kops
 
         lib = kops._lib()
         n = self.numel - offset if numel is None else int(numel)
         self.check()
         self.epoch += 1
-        kops._check(lib.kb200_allreduce_p2p(self.buffer.ptr_array, self.signals.ptr_array, ctypes.c_int(self.rank), ctypes.c_int(self.world),
-                                            ctypes.c_longlong(offset), ctypes.c_longlong(n), ctypes.c_float(scale), ctypes.c_uint(self.epoch),
-                                            ctypes.c_longlong(comm_timeout_ms()), ctypes.c_void_p(self.status.data_ptr()), kops._stream()),
-                    "allreduce_p2p")
+        kops._check(lib.kb200_collective_p2p(self.buffer.ptr_array, self.signals.ptr_array, ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                             ctypes.c_longlong(offset), ctypes.c_longlong(n), ctypes.c_float(scale), ctypes.c_uint(self.epoch),
+                                             ctypes.c_longlong(comm_timeout_ms()), ctypes.c_void_p(self.status.data_ptr()), ctypes.c_int(mode),
+                                             ctypes.c_int(root), kops._stream()),
+                    "collective_p2p")
         self._status_host.copy_(self.status, non_blocking=True)
         self._status_event = torch.cuda.Event()
         self._status_event.record()
+
+    def all_reduce(self, offset=0, numel=None, scale=1.0):
+        """Region := scale * sum over ranks, in every arena."""
+        self._collective(0, offset, numel, scale)
+
+    def reduce_scatter(self, offset=0, numel=None, scale=1.0):
+        """Slice ``rank`` of the region (``ceil(numel / 4 / world)`` float4 vectors per slice) := scale * sum over ranks; the other
+        slices of this arena keep their local values."""
+        self._collective(1, offset, numel, scale)
+
+    def all_gather(self, offset=0, numel=None):
+        """Every rank's slice ``rank`` of the region is copied into the same slice of every arena."""
+        self._collective(2, offset, numel)
+
+    def broadcast(self, root=0, offset=0, numel=None):
+        """The region of rank ``root`` is copied into every arena."""
+        self._collective(3, offset, numel, root=root)
 
     def check(self, wait=False):
         """Raise if an earlier call timed out.  Without ``wait`` only completed status copies are inspected."""

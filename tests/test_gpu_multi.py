@@ -70,6 +70,30 @@ def _allreduce_worker(rank, world):
         torch.cuda.synchronize()
         errs.append(float((red.flat - 0.5 * ref).abs().max()))
         dist.barrier()
+    # the other collectives of the same kernel: reduce-scatter, all-gather, broadcast
+    per = ((red.numel // 4 + world - 1) // world) * 4
+    lo, hi = per * rank, min(red.numel, per * (rank + 1))
+    src = torch.randn(red.numel, device="cuda", generator=g)
+    red.flat.copy_(src)
+    ref = src.clone()
+    dist.all_reduce(ref)
+    torch.cuda.synchronize()
+    dist.barrier()
+    red.reduce_scatter()
+    torch.cuda.synchronize()
+    errs.append(float((red.flat[lo:hi] - ref[lo:hi]).abs().max()))
+    dist.barrier()
+    red.all_gather()
+    torch.cuda.synchronize()
+    errs.append(float((red.flat - ref).abs().max()))
+    dist.barrier()
+    red.flat.fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    dist.barrier()
+    red.broadcast(root=world - 1)
+    torch.cuda.synchronize()
+    errs.append(float((red.flat - float(world)).abs().max()))
+    dist.barrier()
     red.check(wait=True)
     red.close()
     return {"errs": np.array(errs)}
