@@ -106,7 +106,13 @@ def all_reduce(tensor, group=None, average=False):
     if not process_groups.is_initialized() or dist.get_world_size(group) == 1:
         return tensor
     if tensor.is_cuda or dist.get_backend(group) == "gloo":
-        dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=group)
+        try:
+            dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=group)
+        except RuntimeError as e:
+            from keras_b200.parallel import watchdog
+
+            watchdog.explain_collective_error(e)  # raises RankFailure when a peer is known to be lost
+            raise
     else:
         dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=process_groups.host_group())
     if average:

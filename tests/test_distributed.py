@@ -363,3 +363,93 @@ def test_data_and_model_parallel_mesh_matches_single_process():
         for i, w in enumerate(m.get_weights()):
             np.testing.assert_allclose(out[r][f"w{i}"], w, rtol=5e-4, atol=2e-6)
     assert abs(out[0]["losses"][-1] - out[2]["losses"][-1]) < 1e-6  # the loss is reduced over the data axis
+
+
+def _watchdog_worker(rank, world, scenario):
+    import time
+
+    import keras_b200 as keras
+    from keras_b200.parallel.watchdog import RankFailure, RankWatchdog
+
+    keras.distribution.initialize()
+    wd = RankWatchdog(interval_s=0.1, timeout_s=1.0).start()
+    detected, step_reached = [], 0
+    try:
+        for step in range(40):
+            wd.check()  # between steps: no collective in flight
+            step_reached = step
+            if rank == 1 and step == 3:
+                if scenario == "leave":
+                    wd.leave("simulated departure")
+                    return {"detected": np.array([]), "step": np.array(step)}
+                if scenario == "silent":
+                    wd.pause_heartbeat()  # the process stays alive but looks wedged from outside
+                if scenario == "raise":
+                    wd.report_failure(ValueError("injected on the host"))
+                    return {"detected": np.array([]), "step": np.array(step)}
+            time.sleep(0.1)
+    except RankFailure as e:
+        detected = e.ranks
+        reason = e.reasons[e.ranks[0]]
+        wd.stop()
+        return {"detected": np.array(detected), "step": np.array(step_reached), "reason": np.array(reason)}
+    wd.stop()
+    return {"detected": np.array(detected), "step": np.array(step_reached)}
+
+
+@pytest.mark.parametrize("scenario", ["leave", "silent", "raise"])
+def test_rank_watchdog_detects_lost_rank_on_the_host(scenario):
+    codes, out = _run(_watchdog_worker, 3, scenario, timeout=120)
+    assert codes == [0, 0, 0], codes
+    for r in (0, 2):
+        assert list(out[r]["detected"]) == [1], (r, out[r])
+        assert 3 <= int(out[r]["step"]) < 39
+    expected = {"leave": "simulated departure", "silent": "no heartbeat", "raise": "ValueError"}[scenario]
+    assert expected in str(out[0]["reason"])
+
+
+def _restart_worker(rank, world, backup_dir, fail):
+    import keras_b200 as keras
+    from keras_b200.parallel.watchdog import RankFailure
+
+    keras.distribution.initialize()
+    keras.distribution.set_distribution(keras.distribution.DataParallel())
+    m = _make_model(keras)
+    x, y = _data()
+
+    class Leave(keras.callbacks.Callback):
+        def on_epoch_begin(self, epoch, logs=None):
+            if fail and rank == 1 and epoch == 2:
+                fd.watchdog.leave("simulated crash before epoch 2")
+                raise SystemExit(0)
+
+    fd = keras.callbacks.FailureDetection(interval_s=0.1, timeout_s=2.0)
+    backup = keras.callbacks.BackupAndRestore(os.path.join(backup_dir, f"rank{rank}"))
+    epochs_run = []
+
+    class Record(keras.callbacks.Callback):
+        def on_epoch_begin(self, epoch, logs=None):
+            import time
+
+            epochs_run.append(epoch)
+            time.sleep(0.5)  # let a departure that happened at this epoch boundary be seen before the first batch
+
+    outcome = "finished"
+    try:
+        m.fit(x, y, batch_size=4, epochs=4, shuffle=False, verbose=0, callbacks=[backup, fd, Leave(), Record()])
+    except RankFailure as e:
+        outcome = f"lost {e.ranks}"
+    return {"outcome": np.array(outcome), "epochs": np.array(epochs_run)}
+
+
+def test_failure_detection_aborts_fit_and_backup_restores_the_epoch():
+    with tempfile.TemporaryDirectory() as d:
+        codes, out = _run(_restart_worker, 2, d, True, timeout=180)
+        assert codes[0] == 0, codes
+        assert "lost [1]" in str(out[0]["outcome"]), out[0]
+        assert list(out[0]["epochs"])[:2] == [0, 1]
+        # restart with fresh processes: training resumes at the interrupted epoch instead of epoch 0
+        codes, out = _run(_restart_worker, 2, d, False, timeout=180)
+        assert codes == [0, 0], codes
+        assert str(out[0]["outcome"]) == "finished"
+        assert list(out[0]["epochs"])[0] >= 2 and list(out[0]["epochs"])[-1] == 3, out[0]["epochs"]
