@@ -24,7 +24,10 @@ def set_global_attribute(name, value):
 
 
 def get_global_attribute(name, default=None, set_to_default=False):
-    bag = _bag()
+    try:
+        bag = _STATE.bag  # hot path: called several times per layer call
+    except AttributeError:
+        bag = _bag()
     value = bag.get(name)
     if value is None and default is not None:
         value = default

@@ -695,7 +695,14 @@ class Layer(Operation):
 
         # 3. input spec + build
         if self._input_spec is not None and first_arg is not None and (symbolic or not getattr(self, "_tp_local_input", False)):
-            assert_input_compatibility(self._input_spec, first_arg, self.name)
+            if type(first_arg) is torch.Tensor:
+                # eager tensors: a (spec, shape, dtype) combination that passed once passes again
+                sig = (id(self._input_spec), first_arg.shape, first_arg.dtype)
+                if sig != self.__dict__.get("_spec_checked"):
+                    assert_input_compatibility(self._input_spec, first_arg, self.name)
+                    self.__dict__["_spec_checked"] = sig
+            else:
+                assert_input_compatibility(self._input_spec, first_arg, self.name)
         if not self.built:
             with self._open_name_scope():
                 self._maybe_build(plan, args, kwargs)

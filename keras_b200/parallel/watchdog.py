@@ -13,6 +13,7 @@ ever waits for a peer that is known to be gone; waits that are already on the de
 restart from the last saved epoch).
 """
 
+import atexit
 import threading
 import time
 
@@ -81,6 +82,7 @@ class RankWatchdog:
         self._thread = threading.Thread(target=self._run, name="kb200-rank-watchdog", daemon=True)
         self._thread.start()
         _ACTIVE.append(self)
+        atexit.register(self.stop)  # the thread must not outlive the store's client at interpreter shutdown
         return self
 
     def stop(self):

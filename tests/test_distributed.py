@@ -386,6 +386,7 @@ def _watchdog_worker(rank, world, scenario):
                     wd.pause_heartbeat()  # the process stays alive but looks wedged from outside
                 if scenario == "raise":
                     wd.report_failure(ValueError("injected on the host"))
+                    wd.stop()
                     return {"detected": np.array([]), "step": np.array(step)}
             time.sleep(0.1)
     except RankFailure as e:
