@@ -2,6 +2,7 @@
 
     python -m keras_b200.kernels.microbench gemm --m 8192 --n 8192 --k 8192
     python -m keras_b200.kernels.microbench gemm_fp8 --m 8192 --n 8192 --k 8192
+    python -m keras_b200.kernels.microbench attention --batch 16 --seq 1024 --heads 12 --head-dim 64
     python -m keras_b200.kernels.microbench bn --rows 802816 --channels 256
     python -m keras_b200.kernels.microbench pool --batch 256
     python -m keras_b200.kernels.microbench norm --rows 16384 --channels 768
@@ -94,6 +95,31 @@ def bench_gemm_fp8(args, flush):
              "x_measured_bf16_peak": flops / t / 1e9 / tf, "frac_of_nominal_fp8_peak": flops / t / 1e9 / 4500.0, "peak": src, "rel_err_vs_fp32": err},
             {"kernel": "kb200_fp8_quantize (row-major + transposed + amax)", "shape": [M, K], "ms": t_q, "gbs": M * K * 4 / t_q / 1e6,
              "frac_of_peak": M * K * 4 / t_q / 1e6 / bw, "peak": src}]
+
+
+def bench_attention(args, flush):
+    """Causal self-attention forward, [B, T, H, D] layout: this package's tcgen05 kernel against the library's fused attention."""
+    import torch.nn.functional as F
+
+    from keras_b200.kernels import attention
+
+    B, T, H, D = args.batch, args.seq, args.heads, args.head_dim
+    q, k, v = (torch.randn(B, T, H, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    scale = D ** -0.5
+    ours = lambda: attention.forward(q, k, v, scale, True)
+    lib = lambda: F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, scale=scale)
+    if args.once:
+        ours()
+        torch.cuda.synchronize()
+        return []
+    err = float((ours()[0].float() - lib().transpose(1, 2).float()).abs().max())
+    t_ours, t_lib = _time(ours, args.iters, args.warmup, flush), _time(lib, args.iters, args.warmup, flush)
+    tf, _, src = _peaks()
+    flops = 4.0 * B * H * T * T * D / 2
+    return [{"kernel": "flash_fwd_kernel (tcgen05)", "shape": [B, T, H, D], "causal": True, "ms": t_ours, "tflops": flops / t_ours / 1e9,
+             "frac_of_peak": flops / t_ours / 1e9 / tf, "peak": src, "max_abs_diff_vs_library": err},
+            {"kernel": "F.scaled_dot_product_attention (library)", "shape": [B, T, H, D], "causal": True, "ms": t_lib, "tflops": flops / t_lib / 1e9,
+             "frac_of_peak": flops / t_lib / 1e9 / tf, "peak": src}]
 
 
 def bench_bn(args, flush):
@@ -190,19 +216,22 @@ def bench_xent(args, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_fp8", "bn", "pool", "norm", "xent"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "bn", "pool", "norm", "xent"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--rows", type=int, default=802816)
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--once", action="store_true")
     args = ap.parse_args()
     flush = torch.zeros(96 * 1024 * 1024, device="cuda")  # 384 MB > 126 MB L2
-    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
+    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
         print(json.dumps(row))
 
 

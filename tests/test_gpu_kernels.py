@@ -409,3 +409,52 @@ def test_column_sum_kernel(dtype):
         ref = x.double().sum(0)
         assert got.dtype == torch.float32
         assert torch.allclose(got.double(), ref, rtol=1e-4, atol=1e-3)
+
+
+def _attention_reference(q, k, v, scale, causal):
+    qf, kf, vf = q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2)
+    if kf.shape[1] != qf.shape[1]:
+        rep = qf.shape[1] // kf.shape[1]
+        kf, vf = kf.repeat_interleave(rep, dim=1), vf.repeat_interleave(rep, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        Tq, Tk = s.shape[-2:]
+        s = s.masked_fill(torch.triu(torch.ones(Tq, Tk, dtype=torch.bool, device=s.device), diagonal=1), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    return torch.matmul(torch.softmax(s, dim=-1), vf).transpose(1, 2), lse
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Tq,Tk,H,Hkv,D,causal", [(2, 256, 256, 4, 4, 64, True), (1, 200, 333, 4, 2, 128, False), (2, 1024, 1024, 3, 1, 64, True),
+                                                     (1, 384, 384, 2, 2, 128, True), (3, 128, 640, 2, 2, 64, False)])
+def test_flash_attention_forward_matches_fp32_reference(B, Tq, Tk, H, Hkv, D, causal):
+    from keras_b200.kernels import attention
+
+    torch.manual_seed(7)
+    q = torch.randn(B, Tq, H, D, device="cuda").bfloat16()
+    k = torch.randn(B, Tk, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B, Tk, Hkv, D, device="cuda").bfloat16()
+    scale = D ** -0.5
+    out, lse = attention.forward(q, k, v, scale, causal)
+    attention.check_errors()
+    ref, ref_lse = _attention_reference(q, k, v, scale, causal)
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2), float((out.float() - ref).abs().max())
+    assert torch.allclose(lse, ref_lse, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_flash_attention_training_path_gradients(monkeypatch):
+    from keras_b200.kernels import attention
+
+    monkeypatch.setenv("KERAS_B200_FLASH_ATTENTION", "1")
+    torch.manual_seed(8)
+    q, k, v = (torch.randn(2, 256, 4, 64, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
+    out = attention.flash_attention(q, k, v, None, 0.125, True)
+    assert out is not None
+    g = torch.randn_like(out)
+    out.backward(g)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref, _ = _attention_reference(qf, kf, vf, 0.125, True)
+    ref.backward(g.float())
+    for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
+        assert torch.allclose(a.float(), b, atol=5e-2, rtol=5e-2)
