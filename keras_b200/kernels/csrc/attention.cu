@@ -46,7 +46,7 @@ struct FlashCfg {
   static constexpr int Q_BYTES = CH * 16384;        // [chunk][128 rows][128 B]
   static constexpr int KV_BYTES = CH * 16384;       // K: [chunk][128 keys][128 B];  V: [64-key block][chunk][64 keys][128 B]
   static constexpr int P_BYTES = 2 * 16384;         // [64-key chunk][128 rows][128 B]
-  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;  // no alignment slack: two CTAs of the D = 64 variant fit one SM
   static constexpr uint32_t TMEM_COLS = 256;        // S: columns 0-127, O block: columns 128..128+D
 };
 
@@ -55,9 +55,13 @@ __global__ void __launch_bounds__(THREADS, D == 64 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                  const __grid_constant__ CUtensorMap map_o, const FlashParams p) {
   using C = FlashCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {  // the 128-byte swizzle needs 1024-byte aligned tiles; without static shared memory the window starts aligned
+    if (threadIdx.x == 0 && p.err) atomicExch(p.err, 30);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
   const uint32_t sQ = base, sK = sQ + C::Q_BYTES, sV = sK + 2 * C::KV_BYTES, sP = sV + 2 * C::KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + C::Q_BYTES + 4 * C::KV_BYTES + C::P_BYTES);
   const uint32_t bar_base = sP + C::P_BYTES;
@@ -187,15 +191,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // pass 1: row maximum of the scaled scores
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_S + lane_base + (uint32_t)(c * 32), r);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[64];
+        tmem_ld32(tmem_S + lane_base + (uint32_t)(c * 64), r);
+        tmem_ld32(tmem_S + lane_base + (uint32_t)(c * 64 + 32), r + 32);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 64; ++i) {
           float s = __uint_as_float(r[i]) * p.scale_log2;
           if (need_mask) {
-            const int kc = k0 + c * 32 + i;
+            const int kc = k0 + c * 64 + i;
             if (kc >= p.Tk || (p.causal && kc > qi)) s = -INFINITY;
           }
           mx = fmaxf(mx, s);
@@ -210,12 +215,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_O + lane_base + (uint32_t)(c * 32), r);
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld32(tmem_O + lane_base + (uint32_t)(c * 64), r);
+          tmem_ld32(tmem_O + lane_base + (uint32_t)(c * 64 + 32), r + 32);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = (o_acc[c * 32 + i] + __uint_as_float(r[i])) * alpha;
+          for (int i = 0; i < 64; ++i) o_acc[c * 64 + i] = (o_acc[c * 64 + i] + __uint_as_float(r[i])) * alpha;
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
@@ -224,29 +230,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       l *= alpha;
       // pass 2: probabilities, their sum, and P (bf16) into shared memory as the K-major A operand of P V
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_S + lane_base + (uint32_t)(c * 32), r);
+      for (int c = 0; c < 2; ++c) {  // 64 keys = one 128-byte row of P per step
+        uint32_t r[64];
+        tmem_ld32(tmem_S + lane_base + (uint32_t)(c * 64), r);
+        tmem_ld32(tmem_S + lane_base + (uint32_t)(c * 64 + 32), r + 32);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        float pv[32];
+        const uint32_t chunk = sP + (uint32_t)c * 16384u + (uint32_t)row * 128u;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]) * p.scale_log2;
-          if (need_mask) {
-            const int kc = k0 + c * 32 + i;
-            if (kc >= p.Tk || (p.causal && kc > qi)) s = -INFINITY;
+        for (int u = 0; u < 8; ++u) {
+          float pv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float s = __uint_as_float(r[u * 8 + i]) * p.scale_log2;
+            if (need_mask) {
+              const int kc = k0 + c * 64 + u * 8 + i;
+              if (kc >= p.Tk || (p.causal && kc > qi)) s = -INFINITY;
+            }
+            const float e = exp2f(s - m_use);
+            pv[i] = e;
+            l += e;
           }
-          const float e = exp2f(s - m_use);
-          pv[i] = e;
-          l += e;
-        }
-        const uint32_t chunk = sP + (uint32_t)(c >> 1) * 16384u + (uint32_t)row * 128u;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const bf16x8 pk = pack8(pv + u * 8);
+          const bf16x8 pk = pack8(pv);
           const uint4 w = *reinterpret_cast<const uint4*>(&pk);
-          const uint32_t unit = (uint32_t)((c & 1) * 4 + u);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk + ((unit ^ (uint32_t)(row & 7)) << 4)), "r"(w.x), "r"(w.y), "r"(w.z),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(chunk + (((uint32_t)u ^ (uint32_t)(row & 7)) << 4)), "r"(w.x), "r"(w.y), "r"(w.z),
                        "r"(w.w) : "memory");
         }
       }
