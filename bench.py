@@ -31,6 +31,10 @@ CONFIGS = {
                 "rope_theta": 5e5, "model_axis": 4},
     "llama_small": {"kind": "llama", "model": "Llama-style decoder (smoke size)", "global_batch": 8, "seq": 256, "vocab": 2048, "layers": 2, "d": 512,
                     "q_heads": 8, "kv_heads": 4, "ffn": 1536, "rope_theta": 5e5, "model_axis": 4},
+    "gpt_fp8": {"kind": "decoder", "model": "1.3B decoder (24 x 2048, 16 heads, MLP 8192, vocab 50257), float8 policy on Dense/EinsumDense",
+                "per_gpu_batch": 8, "seq": 2048, "vocab": 50257, "layers": 24, "d": 2048, "heads": 16, "ffn": 8192, "float8": True},
+    "gpt_bf16_1b3": {"kind": "decoder", "model": "1.3B decoder (24 x 2048, 16 heads, MLP 8192, vocab 50257), bf16", "per_gpu_batch": 8, "seq": 2048,
+                     "vocab": 50257, "layers": 24, "d": 2048, "heads": 16, "ffn": 8192},
     "gpt2_small": {"kind": "decoder", "model": "GPT-2 shaped (smoke size)", "per_gpu_batch": 4, "seq": 128, "vocab": 1024, "layers": 2, "d": 128,
                    "heads": 4, "ffn": 512},
 }
@@ -165,7 +169,7 @@ def describe(cfg, world):
                  "l2_hygiene": "inputs_larger_than_L2 (weights and activations of a step exceed 126 MB)"})
     return ("decoder training throughput", "tokens/sec", bs * cfg["seq"],
             {"model": cfg["model"], "global_batch": bs * world, "per_gpu_batch": bs, "seq_len": cfg["seq"], "parallelism": f"dp{world}",
-             "optimizer": "AdamW(lr=3e-4, weight_decay=0.1)", "policy": "mixed_bfloat16",
+             "optimizer": "AdamW(lr=3e-4, weight_decay=0.1)", "policy": "mixed_bfloat16" + (" + float8 quantization of Dense/EinsumDense" if cfg.get("float8") else ""),
              "l2_hygiene": "inputs_larger_than_L2 (weights, logits and activations of a step exceed 126 MB)"})
 
 
