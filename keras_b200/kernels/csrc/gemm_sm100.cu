@@ -337,11 +337,14 @@ gemm_bf16_tcgen05_persistent(const __grid_constant__ CUtensorMap map_a, const __
 //
 // split_k > 1 (persistent kernel only): the K range is cut into `split_k` slices that run as separate work units and
 // add their fp32 partial tiles into C with TMA reduce stores; C must be fp32 and zero on entry, bias/act must be off.
+// split_k < 0: |split_k| slices and the product is ADDED to what C holds (fp32 gradient accumulation in place).
 KB_API int kb200_gemm_bf16_splitk(const void* a, const void* b, void* c, const float* bias, int M, int N, int K, long long lda, long long ldb,
                                   long long ldc, int a_mn_major, int b_mn_major, int act, int out_fp32, int split_k, int* err,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (split_k > 1 && (!out_fp32 || bias != nullptr || act != ACT_NONE)) {
+  const int accumulate = split_k < 0 ? 1 : 0;
+  if (split_k < 0) split_k = -split_k;
+  if ((split_k > 1 || accumulate) && (!out_fp32 || bias != nullptr || act != ACT_NONE)) {
     kb200_set_error("gemm_bf16: split-K needs an fp32 output without bias or activation");
     return -4;
   }
@@ -383,6 +386,7 @@ KB_API int kb200_gemm_bf16_splitk(const void* a, const void* b, void* c, const f
     attr_set = true;
   }
   GemmParams p{c, bias, M, N, K, ldc, a_mn_major, b_mn_major, act, out_fp32, err, split_k, kb_per_split};
+  p.accumulate = accumulate;
   if (use_v2) {
     const long long units = tiles_v2 * split_k;
     const unsigned grid = (unsigned)(units < sm_count ? units : sm_count);

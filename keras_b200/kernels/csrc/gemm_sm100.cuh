@@ -38,6 +38,7 @@ struct GemmParams {
   int int8 = 0;                      // 1: signed 8-bit operands (kind::i8), int32 accumulators
   const float* row_scale = nullptr;  // [M] and [N] factors applied to the accumulator (int8 de-quantisation)
   const float* col_scale = nullptr;
+  int accumulate = 0;                // 1: add the fp32 tile into C (TMA reduce store) instead of overwriting it
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -226,7 +227,7 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     if (lane == 0 && row0 < p.M) {
-      if (p.split_k > 1) {
+      if (p.split_k > 1 || p.accumulate) {
         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c),
                      "r"(stage + (stores & 1u) * 4096u), "r"(col0), "r"(row0) : "memory");
       } else {

@@ -32,12 +32,12 @@ def matmul(a, b):
     return gemm.matmul(a, b)
 
 
-def dense(x, kernel, bias, activation_name):
+def dense(x, kernel, bias, activation_name, kernel_shape=None):
     if not enabled(x):
         return None
     from keras_b200.kernels import gemm
 
-    return gemm.dense(x, kernel, bias, activation_name)
+    return gemm.dense(x, kernel, bias, activation_name, kernel_shape)
 
 
 _I8_TRANSPOSED = {}

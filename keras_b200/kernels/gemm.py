@@ -64,12 +64,20 @@ def split_k_for(M, N, K, device):
     return max(1, min(sms // tiles, K // 512))
 
 
-def gemm(a, b, a_mn, b_mn, M, N, K, bias=None, act=0, out_dtype=torch.bfloat16, split_k=1):
+def gemm(a, b, a_mn, b_mn, M, N, K, bias=None, act=0, out_dtype=torch.bfloat16, split_k=1, accumulate_into=None):
     """Raw launch. ``a``/``b`` are 2-D bf16 tensors in the storage layout named by the major flags.
 
-    ``split_k > 1`` accumulates K slices into a zeroed fp32 buffer (TMA reduce stores) and casts to ``out_dtype``."""
+    ``split_k > 1`` accumulates K slices into a zeroed fp32 buffer (TMA reduce stores) and casts to ``out_dtype``.
+    ``accumulate_into``: fp32 [M, N] tensor that the product is added to in place (returned)."""
     lib = kops._lib()
     err = _err_flag(a.device)
+    if accumulate_into is not None:
+        acc = accumulate_into
+        code = lib.kb200_gemm_bf16_splitk(kops._p(a), kops._p(b), kops._p(acc), None, kops._i(M), kops._i(N), kops._i(K), kops._ll(a.stride(0)),
+                                          kops._ll(b.stride(0)), kops._ll(acc.stride(0)), kops._i(a_mn), kops._i(b_mn), kops._i(0), kops._i(1),
+                                          kops._i(-max(1, split_k)), kops._p(err), kops._stream())
+        kops._check(code, "gemm_bf16")
+        return acc
     if split_k > 1 and bias is None and act == 0:
         acc = torch.zeros((M, N), dtype=torch.float32, device=a.device)
         code = lib.kb200_gemm_bf16_splitk(kops._p(a), kops._p(b), kops._p(acc), None, kops._i(M), kops._i(N), kops._i(K), kops._ll(a.stride(0)),
@@ -92,9 +100,12 @@ class GemmFn(torch.autograd.Function):
     the padded output keeps its 16-byte row pitch and the caller sees its first ``N`` columns as a view."""
 
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, grad_target=None):
+        """``grad_target``: the fp32 parameter behind ``w`` (its bf16 shadow) when its ``.grad`` is persistent fp32 storage: the
+        weight gradient is then accumulated there by the GEMM itself and no bf16 gradient tensor is produced."""
         M, K = x.shape
         N = w.shape[1]
+        ctx.grad_target = grad_target
         Np = (N + 7) // 8 * 8
         b32 = bias.float().contiguous() if bias is not None else None
         if Np != N:
@@ -129,12 +140,19 @@ class GemmFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy, w, 0, 0, M, K, Np)
         if ctx.needs_input_grad[1]:
-            dw = gemm(x, dy, 1, 1, K, Np, M, split_k=split_k_for(K, Np, M, x.device))
-            if Np != N:
-                dw = dw[:, :N]
+            split = split_k_for(K, Np, M, x.device)
+            tgt = ctx.grad_target
+            g = tgt.grad if tgt is not None else None
+            if (g is not None and Np == N and g.dtype == torch.float32 and g.numel() == K * N and g.is_contiguous() and not g.requires_grad
+                    and g.data_ptr() % 16 == 0 and N % 4 == 0):
+                gemm(x, dy, 1, 1, K, N, M, split_k=split, accumulate_into=g.view(K, N))  # dw stays None: already accumulated
+            else:
+                dw = gemm(x, dy, 1, 1, K, Np, M, split_k=split)
+                if Np != N:
+                    dw = dw[:, :N]
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = kops.column_sum(dy)[:N].to(ctx.bias_dtype)
-        return dx, dw, db
+        return dx, dw, db, None
 
 
 def _qualifies(x2, w):
@@ -154,15 +172,28 @@ def matmul(a, b):
     a2 = a.reshape(-1, a.shape[-1])
     if not _qualifies(a2, b):
         return None
-    out = GemmFn.apply(a2, b, None)
+    out = GemmFn.apply(a2, b, None, None)
     return out.reshape(tuple(lead) + (b.shape[1],))
 
 
-def dense(x, kernel, bias, activation_name):
-    """Returns ``(output, activation_applied)`` or ``None``."""
+def _grad_target(variable, w):
+    """The fp32 parameter to accumulate the weight gradient into: only when ``w`` is the variable's bf16 shadow read."""
+    p = getattr(variable, "_value", None)
+    if p is None or getattr(variable, "_shadow", None) is None or not p.requires_grad or p.dtype != torch.float32 or w.dtype != torch.bfloat16:
+        return None
+    if getattr(variable, "_shard_slices", None) is not None or p.numel() != w.numel():
+        return None
+    return p
+
+
+def dense(x, kernel, bias, activation_name, kernel_shape=None):
+    """Returns ``(output, activation_applied)`` or ``None``.  ``kernel`` may be a ``Variable`` (reshaped to the 2-D
+    ``kernel_shape`` when given) or a tensor."""
     from keras_b200.core.variables import Variable
 
     w = kernel.value if isinstance(kernel, Variable) else kernel
+    if kernel_shape is not None:
+        w = w.reshape(kernel_shape)
     if not isinstance(x, torch.Tensor) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.ndim != 2 or x.ndim < 2:
         return None
     lead = x.shape[:-1]
@@ -184,5 +215,6 @@ def dense(x, kernel, bias, activation_name):
         if N % 8:
             out = out[:, :N]
         return out.reshape(tuple(lead) + (N,)), fused_act
-    out = GemmFn.apply(x2, w, b)
+    target = _grad_target(kernel, w) if isinstance(kernel, Variable) else None
+    out = GemmFn.apply(x2, w, b, target)
     return out.reshape(tuple(lead) + (w.shape[1],)), activation_name in (None, "linear")

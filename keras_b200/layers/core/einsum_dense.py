@@ -183,17 +183,22 @@ class EinsumDense(Layer):
                 kdim *= d
             lead = inputs.shape[: inputs.ndim - nk]
             x2 = inputs.reshape(tuple(lead) + (kdim,))
-            w2 = kv.reshape(kdim, -1)
+            out_dims = tuple(kv.shape[nk:])
+            from keras_b200.kernels import dispatch
+
+            # the Variable itself goes to the GEMM front end, which can then accumulate the weight gradient in place
+            source = kernel if hasattr(kernel, "_value") else kv
+            bflat = None
             if bias is not None:
                 bv = bias.value if hasattr(bias, "value") else bias
-                if tuple(bv.shape) == tuple(kv.shape[nk:]):
-                    from keras_b200.kernels import dispatch
-
-                    fused = dispatch.dense(x2, w2, bv.reshape(-1), None)
-                    if fused is not None:
-                        return fused[0].reshape(tuple(lead) + tuple(kv.shape[nk:])), True
-            out = ops.matmul(x2, w2)
-            out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+                if tuple(bv.shape) == out_dims:
+                    bflat = bv.reshape(-1)
+            if bias is None or bflat is not None:
+                fused = dispatch.dense(x2, source, bflat, None, kernel_shape=(kdim, -1))
+                if fused is not None:
+                    out = fused[0].reshape(tuple(lead) + out_dims)
+                    return out if bias is None else (out, True)
+            out = ops.matmul(x2, kv.reshape(kdim, -1)).reshape(tuple(lead) + out_dims)
             return out if bias is None else (out, False)
         out = ops.einsum(self.equation, inputs, kernel)
         return out if bias is None else (out, False)
