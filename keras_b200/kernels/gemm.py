@@ -152,7 +152,7 @@ class GemmFn(torch.autograd.Function):
                     dw = dw[:, :N]
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = kops.column_sum(dy)[:N].to(ctx.bias_dtype)
-        return dx, dw, db, None
+        return (dx, dw, db, None)[: len(ctx.needs_input_grad)]
 
 
 def _qualifies(x2, w):
