@@ -213,12 +213,15 @@ __global__ void bn_bwd_coeff_kernel(const float* __restrict__ sums, const float*
 
 // MODE 0: y  = relu?(x*p0 + p1 (+ res)), bits = (y > 0)      (p0 = scale, p1 = shift)
 // MODE 1: dx = p0*dy' + p1*x + p2, dres = dy'                 (in0 = dy, in1 = x, mask from bits or y)
-template <typename T, int MODE>
+// U rows in flight per thread: 4, or 8 for the forward pass without a residual input (one stream of loads only)
+template <typename T, int MODE, int U = BN_U>
 __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __restrict__ in0, const T* __restrict__ in1, const T* __restrict__ ymask,
                                                              unsigned char* __restrict__ bits, T* __restrict__ out0, T* __restrict__ out1,
                                                              const float* __restrict__ p0, const float* __restrict__ p1,
                                                              const float* __restrict__ p2, long long M, int C, int cx_log2, int relu) {
   constexpr int V = Vec<T>::N;
+  // the 8-row instance is the forward pass without a second input: known at compile time so that no registers are held for it
+  const bool has1 = (U == 8) ? false : in1 != nullptr;
   const int cvecs = C / V;
   const int cx = 1 << cx_log2, ry = BN_THREADS >> cx_log2;
   const int tx = threadIdx.x & (cx - 1), ty = threadIdx.x >> cx_log2;
@@ -232,17 +235,17 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __rest
     b[k] = p1[c0 + k];
     cc[k] = (MODE == 1) ? p2[c0 + k] : 0.f;
   }
-  const long long step = (long long)gridDim.x * ry * BN_U;
-  for (long long r0 = (long long)blockIdx.x * ry * BN_U + ty; r0 < M; r0 += step) {
-    typename Vec<T>::Raw q0[BN_U], q1[BN_U], qm[BN_U];
-    unsigned mb[BN_U];
+  const long long step = (long long)gridDim.x * ry * U;
+  for (long long r0 = (long long)blockIdx.x * ry * U + ty; r0 < M; r0 += step) {
+    typename Vec<T>::Raw q0[U], q1[U], qm[U];
+    unsigned mb[U];
 #pragma unroll
-    for (int u = 0; u < BN_U; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long long r = r0 + (long long)u * ry;
       if (r < M) {
         const long long e = r * C + c0;
         q0[u] = Vec<T>::load_raw(in0 + e);
-        if (in1 != nullptr) q1[u] = Vec<T>::load_raw(in1 + e);
+        if (has1) q1[u] = Vec<T>::load_raw(in1 + e);
         if (MODE == 1) {
           if (bits != nullptr) mb[u] = bits[r * cvecs + cv];
           else if (ymask != nullptr) qm[u] = Vec<T>::load_raw(ymask + e);
@@ -250,19 +253,19 @@ __global__ void __launch_bounds__(BN_THREADS, 2) bn_apply_kernel(const T* __rest
       }
     }
 #pragma unroll
-    for (int u = 0; u < BN_U; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long long r = r0 + (long long)u * ry;
       if (r >= M) continue;
       const long long e = r * C + c0;
       float o[V], v0[V], v1[V];
       Vec<T>::unpack(q0[u], v0);
-      if (in1 != nullptr) Vec<T>::unpack(q1[u], v1);
+      if (has1) Vec<T>::unpack(q1[u], v1);
       if (MODE == 0) {
         unsigned m = 0;
 #pragma unroll
         for (int k = 0; k < V; ++k) {
           float t = v0[k] * a[k] + b[k];
-          if (in1 != nullptr) t += v1[k];
+          if (has1) t += v1[k];
           m |= (t > 0.f ? 1u : 0u) << k;
           o[k] = relu ? fmaxf(t, 0.f) : t;
         }
@@ -331,6 +334,14 @@ static int bn_apply_launch(const void* x, const void* res, void* y, unsigned cha
                            int C, int relu, cudaStream_t stream) {
   constexpr int V = Vec<T>::N;
   if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
+  if (res == nullptr) {
+    static const int resident8 = bn_resident_blocks(bn_apply_kernel<T, 0, 8>);
+    const BnGeom g8 = bn_geom(M, C / V, resident8, 8);
+    bn_apply_kernel<T, 0, 8><<<dim3(g8.gx, g8.gy), BN_THREADS, 0, stream>>>((const T*)x, nullptr, nullptr, bits, (T*)y, nullptr, scale, shift, nullptr,
+                                                                           M, C, ilog2(g8.cx), relu);
+    KB_CHECK_LAUNCH("bn_apply");
+    return 0;
+  }
   static const int resident = bn_resident_blocks(bn_apply_kernel<T, 0>);
   const BnGeom g = bn_geom(M, C / V, resident, BN_U);
   bn_apply_kernel<T, 0><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, (const T*)res, nullptr, bits, (T*)y, nullptr, scale, shift,
