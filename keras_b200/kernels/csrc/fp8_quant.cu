@@ -79,6 +79,82 @@ __global__ void __launch_bounds__(256) fp8_quantize_kernel(const T* __restrict__
   }
 }
 
+
+// Vector variant for 16-byte aligned rows (ldx a multiple of 8 elements, aligned base, output pitches multiples of 16):
+// every thread converts 8 consecutive elements of a row per pass (one or two 16-byte loads, one 8-byte store) and the
+// transposed tile leaves shared memory as 16-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(256) fp8_quantize_vec_kernel(const T* __restrict__ x, long long ldx, int rows, int cols, const float* __restrict__ scale,
+                                                               int e5m2, uint8_t* __restrict__ q, long long ldq, uint8_t* __restrict__ qt, long long ldqt,
+                                                               unsigned* __restrict__ amax) {
+  __shared__ __align__(16) uint8_t tile[QT][QT + 16];
+  __shared__ float red[8];
+  const int r0 = blockIdx.y * QT, c0 = blockIdx.x * QT;
+  const float inv = 1.f / __ldg(scale);
+  const int seg = threadIdx.x & 7, rl = threadIdx.x >> 3;  // 8 column segments of 8 elements, 32 rows per pass
+  float m = 0.f;
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int r = r0 + pass * 32 + rl, c = c0 + seg * 8;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (r < rows && c < cols) {  // cols is a multiple of 8 here: a segment is inside or outside as a whole
+      const T* src = x + (long long)r * ldx + c;
+      if constexpr (sizeof(T) == 2) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          v[2 * j] = f.x;
+          v[2 * j + 1] = f.y;
+        }
+      } else {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      }
+    }
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      m = fmaxf(m, fabsf(v[j]));
+      const uint32_t b = __nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, e5m2 ? __NV_E5M2 : __NV_E4M3);
+      if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+    }
+    *reinterpret_cast<uint2*>(&tile[pass * 32 + rl][seg * 8]) = make_uint2(lo, hi);
+    if (q != nullptr && r < rows && c < cols) *reinterpret_cast<uint2*>(q + (long long)r * ldq + c) = make_uint2(lo, hi);
+  }
+  if (qt != nullptr) {
+    __syncthreads();
+    const int tc = threadIdx.x >> 2, ts = threadIdx.x & 3;  // transposed row (source column) and 16-row segment
+    const int c = c0 + tc, r = r0 + ts * 16;
+    if (c < cols && r < rows) {
+      uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i >> 2] |= (uint32_t)tile[ts * 16 + i][tc] << (8 * (i & 3));
+      if (r + 15 < rows) {
+        *reinterpret_cast<uint4*>(qt + (long long)c * ldqt + r) = make_uint4(w[0], w[1], w[2], w[3]);
+      } else {
+        for (int i = 0; i < 16; ++i)
+          if (r + i < rows) qt[(long long)c * ldqt + r + i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+      }
+    }
+  }
+  if (amax != nullptr) {
+    m = warp_max(m);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) red[wid] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = red[0];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) t = fmaxf(t, red[k]);
+      atomicMax(amax, __float_as_uint(t));
+    }
+  }
+}
+
 }  // namespace
 
 // x: [rows, cols] bf16 (dtype 1) or fp32 (0) with row pitch ldx elements.  q: [rows, ldq] bytes or null; qt: [cols, ldqt] bytes or
@@ -91,6 +167,17 @@ KB_API int kb200_fp8_quantize(const void* x, long long ldx, int rows, int cols, 
     return -2;
   }
   dim3 grid((cols + QT - 1) / QT, (rows + QT - 1) / QT);
+  const bool vec = cols % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && (q == nullptr || (ldq % 16 == 0 && ((uintptr_t)q & 15) == 0)) &&
+                   (qt == nullptr || (ldqt % 16 == 0 && ((uintptr_t)qt & 15) == 0));
+  if (vec) {
+    if (dtype == 1)
+      fp8_quantize_vec_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, rows, cols, scale, e5m2, (uint8_t*)q, ldq,
+                                                                       (uint8_t*)qt, ldqt, amax);
+    else
+      fp8_quantize_vec_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ldx, rows, cols, scale, e5m2, (uint8_t*)q, ldq, (uint8_t*)qt, ldqt, amax);
+    KB_CHECK_LAUNCH("fp8_quantize");
+    return 0;
+  }
   if (dtype == 1)
     fp8_quantize_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, rows, cols, scale, e5m2, (uint8_t*)q, ldq, (uint8_t*)qt,
                                                                  ldqt, amax);

@@ -322,6 +322,14 @@ def test_fp8_quantize_and_gemm_match_torch_float8():
 
     gemm.check_errors()
     assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    # ragged tile edges of the vector quantisation kernel, both input types
+    for dt in (torch.bfloat16, torch.float32):
+        xr = torch.randn(520, 392, device="cuda").to(dt)
+        qr, qrt, ar = fp8.quantize(xr, sx, True, row_major=True, transposed=True)
+        ref_r = torch.clip(xr.float() / sx, -57344, 57344).to(torch.float8_e5m2).float()
+        assert torch.equal(qr[:, :392].view(torch.float8_e5m2).float(), ref_r)
+        assert torch.equal(qrt[:, :520].view(torch.float8_e5m2).float(), ref_r.t())
+        assert float(ar) == float(xr.float().abs().max())
     # e5m2 x e4m3 (gradient product)
     g = torch.randn(M, N, device="cuda").bfloat16()
     sg = torch.tensor(0.001, device="cuda")
