@@ -21,7 +21,7 @@
 // peer has announced e, i.e. after the peer's earlier stream work, which wrote the slice, is complete.  Reuse of a
 // parity buffer two calls later is safe because finishing call e+1 requires every peer to have started it.  Every
 // wait (flags, counters, mbarriers) is bounded by an iteration count and wall-clock time; when one runs out the
-// kernel raises `*status`, releases TMEM and returns.  No load from peer memory uses cluster multicast.
+// kernel raises `*status`, releases TMEM and returns.  Every load from peer memory is a plain (single-CTA) bulk copy.
 #include "gemm_sm100.cuh"
 
 namespace {
