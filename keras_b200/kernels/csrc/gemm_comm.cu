@@ -197,6 +197,45 @@ __device__ void gather_stream(uint32_t ring, uint32_t bar_base, const CommParams
   }
 }
 
+// out[i] = sum over ranks s < world of stage[s][i] for the vectors first, first + step, ...; U vectors of up to R ranks are
+// requested before any is used.
+template <int U, int R>
+__device__ __forceinline__ void reduce_staged(const uint4* __restrict__ st, uint4* __restrict__ out, long long vecs, long long first, long long step,
+                                              int world) {
+  for (long long i0 = first; i0 < vecs; i0 += step * U) {
+    uint4 raw[U][R];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * step;
+#pragma unroll
+      for (int s = 0; s < R; ++s)
+        if (s < world && i < vecs) raw[u][s] = __ldcg(st + (long long)s * vecs + i);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * step;
+      if (i >= vecs) break;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int s = 0; s < R; ++s) {
+        if (s < world) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][s]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+      }
+      const bf16x8 pk = pack8(acc);
+      out[i] = *reinterpret_cast<const uint4*>(&pk);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CMaps maps_c,
                        const GemmParams p, const CommParams c) {
@@ -417,30 +456,11 @@ gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const long long vecs = (long long)c.rows_per_rank * p.N / 8;  // 16-byte vectors of the result
     const uint4* st = reinterpret_cast<const uint4*>(c.stage);
     uint4* out = reinterpret_cast<uint4*>(c.out);
-    for (long long i = (long long)cta * THREADS + threadIdx.x; i < vecs; i += (long long)ctas * THREADS) {
-      // all partials of this vector are requested before any is used (one load per rank in flight)
-      uint4 raw[MAX_RANKS];
-#pragma unroll
-      for (int s = 0; s < MAX_RANKS; ++s)
-        if (s < c.world) raw[s] = __ldcg(st + (long long)s * vecs + i);
-      float acc[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-      for (int s = 0; s < MAX_RANKS; ++s) {
-        if (s < c.world) {
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[s]);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h[j]);
-            acc[2 * j] += f.x;
-            acc[2 * j + 1] += f.y;
-          }
-        }
-      }
-      const bf16x8 pk = pack8(acc);
-      out[i] = *reinterpret_cast<const uint4*>(&pk);
-    }
+    const long long first = (long long)cta * THREADS + threadIdx.x, step = (long long)ctas * THREADS;
+    // eight 16-byte loads in flight per thread whatever the number of ranks
+    if (c.world <= 2) reduce_staged<4, 2>(st, out, vecs, first, step, c.world);
+    else if (c.world <= 4) reduce_staged<2, 4>(st, out, vecs, first, step, c.world);
+    else reduce_staged<1, 8>(st, out, vecs, first, step, c.world);
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -39,6 +39,28 @@ def _time(fn, iters, warmup):
     return statistics.median(times)
 
 
+def single(args):
+    """World size 1: the all-gather has no remote slices and the reduce-scatter reduces the rank's own staged tiles, so the
+    launch exercises the tcgen05 pipeline, the staging stores and the in-kernel reduction without any peer."""
+    torch.cuda.set_device(0)
+    from keras_b200.parallel.fused_gemm import FusedGemmContext
+
+    fused = FusedGemmContext()
+    M, D, F = args.tokens // 128 * 128, args.d, args.ffn // 8 * 8
+    x = torch.randn(M, D, device="cuda").bfloat16()
+    w_up = (torch.randn(D, F, device="cuda") * 0.02).bfloat16()
+    h = torch.randn(M, F, device="cuda").bfloat16()
+    w_down = (torch.randn(F, D, device="cuda") * 0.02).bfloat16()
+    y, _ = fused.all_gather_gemm(x, w_up)
+    z = fused.gemm_reduce_scatter(h, w_down)
+    torch.cuda.synchronize()
+    fused.check()
+    e1 = float((y.float() - x.float() @ w_up.float()).abs().max())
+    e2 = float((z.float() - h.float() @ w_down.float()).abs().max())
+    print(json.dumps({"single_rank": True, "tokens": M, "d": D, "ffn": F, "max_abs_err_allgather_gemm": e1, "max_abs_err_gemm_reduce_scatter": e2}))
+    fused.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=16384)
@@ -47,7 +69,11 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--copy-ctas", type=int, default=0)
+    ap.add_argument("--single", action="store_true",
+                    help="one process, one rank, no torch.distributed: one launch of each fused kernel (for a profiler capture of the kernel itself)")
     args = ap.parse_args()
+    if args.single:
+        return single(args)
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     import keras_b200 as keras
     from keras_b200.kernels.microbench import _peaks
