@@ -3,6 +3,7 @@
     python -m keras_b200.kernels.microbench gemm --m 8192 --n 8192 --k 8192
     python -m keras_b200.kernels.microbench gemm_fp8 --m 8192 --n 8192 --k 8192
     python -m keras_b200.kernels.microbench attention --batch 16 --seq 1024 --heads 12 --head-dim 64
+    python -m keras_b200.kernels.microbench optim --tensors 32 --rows 4096 --channels 1024
     python -m keras_b200.kernels.microbench bn --rows 802816 --channels 256
     python -m keras_b200.kernels.microbench pool --batch 256
     python -m keras_b200.kernels.microbench norm --rows 16384 --channels 768
@@ -122,6 +123,36 @@ def bench_attention(args, flush):
              "frac_of_peak": flops / t_lib / 1e9 / tf, "peak": src}]
 
 
+def bench_optim(args, flush):
+    """Fused multi-tensor AdamW step (update, decay, bf16 shadow write, gradient zeroing) over `--tensors` parameters of
+    `--rows` x `--channels` floats, against the library's fused AdamW."""
+    from keras_b200.kernels import ops as kops
+
+    n, numel = args.tensors, args.rows * args.channels
+    params = [torch.randn(numel, device="cuda") for _ in range(n)]
+    grads = [torch.randn(numel, device="cuda") for _ in range(n)]
+    m = [torch.zeros(numel, device="cuda") for _ in range(n)]
+    v = [torch.zeros(numel, device="cuda") for _ in range(n)]
+    shadows = [torch.empty(numel, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+    plan = kops.OptimizerPlan(params, grads, m, v, shadows, [1.0 - 3e-5] * n)
+    ours = lambda: plan.adam(3e-4, 0.9, 0.999, 1e-8, grad_scale=1.0, zero_grad=True)
+    if args.once:
+        ours()
+        torch.cuda.synchronize()
+        return []
+    for p_ in params:
+        p_.grad = torch.randn_like(p_)
+    ref = torch.optim.AdamW(params, lr=3e-4, weight_decay=0.1, fused=True)
+    t_ours, t_lib = _time(ours, args.iters, args.warmup, flush), _time(ref.step, args.iters, args.warmup, flush)
+    _, bw, src = _peaks()
+    ob = n * numel * (4 * 8 + 2)  # read p, g, m, v; write p, m, v and g := 0 (fp32); write the bf16 shadow
+    lb = n * numel * 4 * 7
+    return [{"kernel": "kb200_fused_adam (update + decay + bf16 shadow + zero grad)", "tensors": n, "numel": numel, "ms": t_ours, "gbs": ob / t_ours / 1e6,
+             "frac_of_peak": ob / t_ours / 1e6 / bw, "peak": src},
+            {"kernel": "torch.optim.AdamW(fused=True)", "tensors": n, "numel": numel, "ms": t_lib, "gbs": lb / t_lib / 1e6,
+             "frac_of_peak": lb / t_lib / 1e6 / bw, "peak": src}]
+
+
 def bench_bn(args, flush):
     from keras_b200.kernels import ops as kops
 
@@ -216,13 +247,14 @@ def bench_xent(args, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "bn", "pool", "norm", "xent"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "optim", "bn", "pool", "norm", "xent"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--rows", type=int, default=802816)
     ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--tensors", type=int, default=32)
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--head-dim", type=int, default=64)
@@ -231,7 +263,7 @@ def main():
     ap.add_argument("--once", action="store_true")
     args = ap.parse_args()
     flush = torch.zeros(96 * 1024 * 1024, device="cuda")  # 384 MB > 126 MB L2
-    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
+    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "optim": bench_optim, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
         print(json.dumps(row))
 
 
