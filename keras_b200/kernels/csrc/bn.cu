@@ -198,6 +198,42 @@ __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* 
   if (moving_var) moving_var[c] = moving_var[c] * momentum + var * (1.f - momentum);
 }
 
+// As bn_finalize_kernel, with the per-channel sums gathered from the per-warp partials that the convolution epilogue
+// (conv_sm100.cu) leaves behind: partials[(cta * 4 + warp)][2][ld]; CTA `cta` covers channels [(cta % n_tiles) * bn, + bn).
+// One warp per channel; the order of the additions is fixed, so the result is reproducible bit for bit.
+__global__ void bn_finalize_partials_kernel(const float* __restrict__ partials, int grid, int n_tiles, int bn, int ld,
+                                            const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ pre_bias,
+                                            float* __restrict__ moving_mean, float* __restrict__ moving_var, float momentum, float eps, float inv_m,
+                                            int C, float* __restrict__ mean_out, float* __restrict__ invstd_out, float* __restrict__ scale_out,
+                                            float* __restrict__ shift_out) {
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (c >= C) return;
+  const int ntile = c / bn;
+  const int count = ntile < grid ? ((grid - 1 - ntile) / n_tiles + 1) * 4 : 0;
+  float s = 0.f, q = 0.f;
+  for (int i = lane; i < count; i += 32) {
+    const int b = ntile + (i >> 2) * n_tiles;
+    const float* src = partials + (size_t)(b * 4 + (i & 3)) * 2 * ld + c;
+    s += src[0];
+    q += src[ld];
+  }
+  s = warp_sum(s);
+  q = warp_sum(q);
+  if (lane != 0) return;
+  const float mean = s * inv_m;
+  const float var = fmaxf(q * inv_m - mean * mean, 0.f);
+  const float invstd = rsqrtf(var + eps);
+  const float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
+  mean_out[c] = mean;
+  invstd_out[c] = invstd;
+  scale_out[c] = g * invstd;
+  shift_out[c] = b - mean * g * invstd;
+  const float full_mean = mean + (pre_bias ? pre_bias[c] : 0.f);
+  if (moving_mean) moving_mean[c] = moving_mean[c] * momentum + full_mean * (1.f - momentum);
+  if (moving_var) moving_var[c] = moving_var[c] * momentum + var * (1.f - momentum);
+}
+
 // Backward coefficients: dx = A*dy' + B*x + Cc
 __global__ void bn_bwd_coeff_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
                                     const float* __restrict__ invstd, float inv_m, int C, float* __restrict__ coef) {
@@ -326,6 +362,21 @@ KB_API int kb200_bn_finalize(const float* sums, const float* gamma, const float*
   bn_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, beta, pre_bias, moving_mean, moving_var, momentum, eps, 1.f / (float)M, C,
                                                           mean_out, invstd_out, scale_out, shift_out);
   KB_CHECK_LAUNCH("bn_finalize");
+  return 0;
+}
+
+// Finalize from the convolution epilogue's partial sums (see bn_finalize_partials_kernel); `grid`, `n_tiles`, `bn` are
+// the plan values that kb200_conv_igemm reported, `ld` the row pitch of `partials`.
+KB_API int kb200_bn_finalize_partials(const float* partials, int grid, int n_tiles, int bn, int ld, const float* gamma, const float* beta,
+                                      const float* pre_bias, float* moving_mean, float* moving_var, float momentum, float eps, long long M, int C,
+                                      float* mean_out, float* invstd_out, float* scale_out, float* shift_out, cudaStream_t stream) {
+  if (grid <= 0 || n_tiles <= 0 || bn <= 0 || C > n_tiles * bn || ld < n_tiles * bn) {
+    kb200_set_error("bn_finalize_partials: inconsistent plan");
+    return -2;
+  }
+  bn_finalize_partials_kernel<<<(C + 3) / 4, 128, 0, stream>>>(partials, grid, n_tiles, bn, ld, gamma, beta, pre_bias, moving_mean, moving_var, momentum,
+                                                                eps, 1.f / (float)M, C, mean_out, invstd_out, scale_out, shift_out);
+  KB_CHECK_LAUNCH("bn_finalize_partials");
   return 0;
 }
 

@@ -1,0 +1,652 @@
+// Channels-last 2-D convolution as an implicit GEMM on 5th-generation tensor cores (tcgen05), sm_100a.
+//
+// Replaces the cuDNN convolutions behind keras/src/backend/torch/nn.py:623-717 (forward) and their autograd
+// companions (input gradient, weight gradient), plus the statistics pass of the BatchNormalization that follows a
+// convolution (keras/src/backend/torch/nn.py:1020-1043).
+//
+// The im2col matrix never exists.  Pixels are tiled as boxes (wt x ht x nt, powers of two, 128 or 64 pixels) of the
+// NHWC tensor; one TMA box load `cp.async.bulk.tensor.4d` of 64 channels brings such a box into shared memory as 128-byte
+// rows in exactly the swizzled layout a tcgen05 operand needs, and the filter tap (r, s) is nothing but an offset added
+// to the box's (w, h) coordinates: positions outside the image read as zeros (TMA out-of-bounds fill), which is the zero
+// padding.  A strided convolution with a 1x1 filter reads a strided view (the tensor map carries the strides).
+//
+//   mode "igemm" (forward and input gradient):
+//       D[pixel, n] = sum over taps, channels c of  A[pixel + offset(tap), c] * B[tap][c][n]
+//       forward:        A = x,  B = kernel[r][s][cin][cout]  (rows are the contraction: MN-major operand)
+//       input gradient: A = dy, B = the same kernel array read as [cout -> contraction][cin -> n] (K-major operand),
+//                       taps applied with mirrored offsets
+//     Epilogue: bias / activation, bf16 TMA box store (or reduce-add into the destination), and per-channel
+//     sum / sum of squares of the bf16-rounded outputs for BatchNormalization, accumulated in registers over all tiles
+//     of the CTA and written once per warp (deterministic: no atomics).
+//   mode "wgrad" (weight gradient):
+//       dW[tap][c][n] = sum over pixels  x[pixel + offset(tap), c] * dy[pixel, n]
+//     Both operands are MN-major views of the very same pixel boxes; the pixel range is cut into slices that run as
+//     separate work units and add their fp32 partial tiles into dW with TMA reduce stores.
+//
+// Kernel structure as the persistent GEMM (gemm_sm100.cu): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 =
+// epilogue; 4 operand stages; two 256-column TMEM accumulators so an epilogue overlaps the next tile's main loop.
+// Every wait is bounded; on expiry an error code is stored and the CTA drains and leaves.
+#include "gemm_sm100.cuh"
+
+namespace {
+using namespace kbgemm;
+
+constexpr int CV_STAGES = 4;
+constexpr int CV_A_BYTES = 128 * 64 * 2;            // 16 KB: 128 pixels x 64 channels (igemm) / 64 pixels x 128 channels (wgrad)
+constexpr int CV_B_BYTES = 256 * 64 * 2;            // up to 32 KB
+constexpr int CV_STAGE_BYTES = CV_A_BYTES + CV_B_BYTES;
+constexpr int CV_OUT_BYTES = 4 * 2 * 4096;
+constexpr int CV_SMEM_BYTES = CV_STAGES * CV_STAGE_BYTES + CV_OUT_BYTES + 1024 + 256;
+constexpr uint32_t CV_TMEM_COLS = 512;
+
+struct ConvParams {
+  int mode;                 // 0: igemm, 1: wgrad
+  int lw, lh, lt;           // log2 of the pixel box (wt, ht) and of the pixels per box (7 or 6); nt = 2^(lt - lw - lh)
+  int tiles_w, tiles_h, tiles_n;
+  int Wo, Ho, No;           // extents of the tiled pixel space
+  int n_tiles, bn;          // tiles and tile width along the GEMM N dimension (bn = 64, 128 or 256)
+  int Ngemm;                // extent of the GEMM N dimension (channels of the result)
+  int kc_blocks;            // igemm: 64-channel blocks of the contraction per tap
+  int R, S, dh0, dh_step, dw0, dw_step;
+  int b_kmajor;             // igemm: 1 = B rows run along N (input gradient), 0 = along the contraction (forward)
+  int rows_per_tap;         // rows of the kernel matrix per tap (input channels)
+  const float* bias;
+  int act;
+  int accumulate;           // igemm: add the bf16 result into the destination
+  float* stats;             // igemm: [grid * 4][2][stats_ld] per-warp partial sums (or null)
+  int stats_ld;
+  int* err;
+  // wgrad
+  int m_tiles;              // 128-row tiles over the input channels
+  int split, pb_per, total_pb;
+  int Mrows;                // R * S * Cin
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+// Epilogue of one 32-row slice of an igemm accumulator tile: bf16 output through a swizzled staging buffer and a 4-D TMA
+// box store; optional per-channel statistics in `acc` (4 chunks x {sum0, sum1, sq0, sq1} for the two columns a lane owns).
+template <int CHUNKS>
+__device__ __forceinline__ void conv_store_rows(uint32_t tmem_row, int ng0, int q, int w0, int h0, int n0, uint32_t stage, uint32_t& stores,
+                                                const CUtensorMap* map_c, const ConvParams& p, int lane, float* acc) {
+  const int wt_mask = (1 << p.lw) - 1, ht_mask = (1 << p.lh) - 1;
+  const int r = q * 32 + lane;
+  const bool valid = (w0 + (r & wt_mask) < p.Wo) && (h0 + ((r >> p.lw) & ht_mask) < p.Ho) && (n0 + (r >> (p.lw + p.lh)) < p.No);
+  const int r0 = q * 32;
+  const int bw0 = w0 + (r0 & wt_mask), bh0 = h0 + ((r0 >> p.lw) & ht_mask), bn0 = n0 + (r0 >> (p.lw + p.lh));
+  const bool box_ok = bw0 < p.Wo && bh0 < p.Ho && bn0 < p.No;
+  const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col0 = ng0 + c * 64;
+    if (col0 < p.Ngemm) {
+      uint32_t rr[64];
+      tmem_ld32(tmem_row + (uint32_t)(c * 64), rr);
+      tmem_ld32(tmem_row + (uint32_t)(c * 64 + 32), rr + 32);
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      __syncwarp();
+      const uint32_t buf0 = stage + (stores & 1u) * 4096u;
+      const uint32_t buf = buf0 + (uint32_t)lane * 128u;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rr[h * 32 + j]);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += __ldg(p.bias + min(col0 + h * 32 + j, p.Ngemm - 1));
+        }
+        if (p.act != ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+        }
+        if (!valid) {  // pixels beyond the image: clipped by the store, and they must not enter the statistics
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const bf16x8 pk = pack8(v + u * 8);
+          const uint4 w = *reinterpret_cast<const uint4*>(&pk);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + (((uint32_t)(h * 4 + u) ^ sw) << 4)), "r"(w.x), "r"(w.y), "r"(w.z),
+                       "r"(w.w) : "memory");
+        }
+      }
+      if (p.stats != nullptr) {
+        // column sums over the 32 rows just staged: lane L owns columns 2L and 2L+1 of the chunk
+        __syncwarp();
+        float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+        const uint32_t cbase = buf0 + (uint32_t)(lane & 3) * 4u;
+        const uint32_t cch = (uint32_t)(lane >> 2);
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+          uint32_t w;
+          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w) : "r"(cbase + (uint32_t)i * 128u + ((cch ^ (uint32_t)(i & 7)) << 4)) : "memory");
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+          s0 += f.x; q0 = fmaf(f.x, f.x, q0);
+          s1 += f.y; q1 = fmaf(f.y, f.y, q1);
+        }
+        acc[c * 4 + 0] += s0; acc[c * 4 + 1] += s1; acc[c * 4 + 2] += q0; acc[c * 4 + 3] += q1;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0 && box_ok) {
+        if (p.accumulate) {
+          asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map_c), "r"(buf0),
+                       "r"(col0), "r"(bw0), "r"(bh0), "r"(bn0) : "memory");
+        } else {
+          asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map_c), "r"(buf0), "r"(col0),
+                       "r"(bw0), "r"(bh0), "r"(bn0) : "memory");
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+      ++stores;
+    }
+  }
+}
+
+__device__ __forceinline__ void pixel_tile_origin(const ConvParams& p, int ptile, int& w0, int& h0, int& n0) {
+  const int tw = ptile % p.tiles_w;
+  const int rest = ptile / p.tiles_w;
+  const int th = rest % p.tiles_h;
+  const int tn = rest / p.tiles_h;
+  w0 = tw << p.lw;
+  h0 = th << p.lh;
+  n0 = tn << (p.lt - p.lw - p.lh);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                    const ConvParams p) {
+  constexpr int STAGES = CV_STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t stage_out = base + STAGES * CV_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * CV_STAGE_BYTES + CV_OUT_BYTES);
+  const uint32_t bar_base = stage_out + CV_OUT_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.R * p.S;
+  const int pix_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+  const int tiles_out = p.mode == 0 ? pix_tiles * p.n_tiles : taps * p.m_tiles * p.n_tiles;
+  const int total_units = p.mode == 0 ? tiles_out : tiles_out * p.split;
+  const uint32_t stage_tx = (uint32_t)(CV_A_BYTES + p.bn * 128);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(CV_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0, issued = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        if (p.mode == 0) {
+          const int ng0 = (u % p.n_tiles) * p.bn;
+          int w0, h0, n0;
+          pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
+          for (int tap = 0; tap < taps && ok; ++tap) {
+            const int dh = p.dh0 + (tap / p.S) * p.dh_step, dw = p.dw0 + (tap % p.S) * p.dw_step;
+            const int brow = tap * p.rows_per_tap;
+            for (int kc = 0; kc < p.kc_blocks; ++kc, ++it) {
+              const int s = it % STAGES;
+              ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+              if (!ok) break;
+              const uint32_t sa = base + s * CV_STAGE_BYTES, sb = sa + CV_A_BYTES;
+              mbar_expect_tx(full_bar(s), stage_tx);
+              tma_load_4d(sa, &map_a, full_bar(s), kc * 64, w0 + dw, h0 + dh, n0);
+              if (p.b_kmajor) {
+                tma_load_2d(sb, &map_b, full_bar(s), kc * 64, brow + ng0);
+              } else {
+                for (int j = 0; j < (p.bn >> 6); ++j) tma_load_2d(sb + j * 8192, &map_b, full_bar(s), ng0 + j * 64, brow + kc * 64);
+              }
+              issued = it + 1;
+            }
+          }
+        } else {
+          const int tile = u % tiles_out, slice = u / tiles_out;
+          const int ng0 = (tile % p.n_tiles) * p.bn;
+          const int rest = tile / p.n_tiles;
+          const int c0 = (rest % p.m_tiles) * 128;
+          const int tap = rest / p.m_tiles;
+          const int dh = p.dh0 + (tap / p.S) * p.dh_step, dw = p.dw0 + (tap % p.S) * p.dw_step;
+          const int pb0 = slice * p.pb_per, pb1 = min(pb0 + p.pb_per, p.total_pb);
+          for (int pb = pb0; pb < pb1; ++pb, ++it) {
+            const int s = it % STAGES;
+            ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            int w0, h0, n0;
+            pixel_tile_origin(p, pb, w0, h0, n0);
+            const uint32_t sa = base + s * CV_STAGE_BYTES, sb = sa + CV_A_BYTES;
+            mbar_expect_tx(full_bar(s), stage_tx);
+            tma_load_4d(sa, &map_a, full_bar(s), c0, w0 + dw, h0 + dh, n0);
+            tma_load_4d(sa + 8192, &map_a, full_bar(s), c0 + 64, w0 + dw, h0 + dh, n0);
+            for (int j = 0; j < (p.bn >> 6); ++j) tma_load_4d(sb + j * 8192, &map_b, full_bar(s), ng0 + j * 64, w0, h0, n0);
+            issued = it + 1;
+          }
+        }
+      }
+      if (!ok) {
+        if (p.err) atomicExch(p.err, 21);
+        *abort_flag = 1;
+        const uint32_t first = issued > STAGES ? issued - STAGES : 0;
+        for (uint32_t i = first; i < issued; ++i) {
+          for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+            if (mbar_try_wait(full_bar(i % STAGES), (i / STAGES) & 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t a_mn = p.mode == 1 ? 1u : 0u;
+      const uint32_t b_mn = p.mode == 1 ? 1u : (p.b_kmajor ? 0u : 1u);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (a_mn << 15) | (b_mn << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t a_step = a_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t b_step = b_mn ? (2048u >> 4) : (32u >> 4);
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
+        const uint32_t acc = local & 1;
+        ok = mbar_wait(acc_empty_bar(acc), ((local >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + acc * 256u;
+        int steps;
+        if (p.mode == 0) {
+          steps = taps * p.kc_blocks;
+        } else {
+          const int slice = u / tiles_out;
+          const int pb0 = slice * p.pb_per;
+          steps = min(pb0 + p.pb_per, p.total_pb) - pb0;
+        }
+        for (int st = 0; st < steps; ++st, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = base + s * CV_STAGE_BYTES, sb = sa + CV_A_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, a_mn != 0), bdesc = make_smem_desc(sb, b_mn != 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (st > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(acc_full_bar(acc));
+      }
+      if (!ok) {
+        if (p.err) atomicExch(p.err, 22);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;
+    uint32_t local = 0, stores = 0;
+    bool ok = true;
+    float acc_stats[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc_stats[i] = 0.f;
+    GemmParams gp{};
+    if (p.mode == 1) {
+      gp.M = p.Mrows; gp.N = p.Ngemm; gp.out_fp32 = 1; gp.split_k = 2;  // every unit adds its partial tile
+    }
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
+      const uint32_t acc = local & 1;
+      ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1, abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_row = tmem_base + acc * 256u + ((uint32_t)(q * 32) << 16);
+      if (p.mode == 0) {
+        const int ng0 = (u % p.n_tiles) * p.bn;
+        int w0, h0, n0;
+        pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
+        if (p.bn == 256) conv_store_rows<4>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats);
+        else if (p.bn == 128) conv_store_rows<2>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats);
+        else conv_store_rows<1>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats);
+      } else {
+        const int tile = u % tiles_out;
+        const int ng0 = (tile % p.n_tiles) * p.bn;
+        const int rest = tile / p.n_tiles;
+        const int row0 = (rest / p.m_tiles) * p.rows_per_tap + (rest % p.m_tiles) * 128 + q * 32;
+        store_rows_tma(tmem_row, p.bn, ng0, row0, my_stage, stores, &map_c, gp, lane);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (p.mode == 0 && p.stats != nullptr) {
+      // every tile of this CTA has the same column origin (the grid is a multiple of n_tiles)
+      const int ng0 = (blockIdx.x % p.n_tiles) * p.bn;
+      float* dst = p.stats + (size_t)(blockIdx.x * 4 + q) * 2 * p.stats_ld + ng0 + 2 * lane;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (c * 64 < p.bn) {
+          dst[c * 64] = acc_stats[c * 4 + 0];
+          dst[c * 64 + 1] = acc_stats[c * 4 + 1];
+          dst[p.stats_ld + c * 64] = acc_stats[c * 4 + 2];
+          dst[p.stats_ld + c * 64 + 1] = acc_stats[c * 4 + 3];
+        }
+      }
+    }
+    if (!ok) {
+      if (lane == 0 && p.err) atomicExch(p.err, 23);
+      *abort_flag = 1;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(CV_TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+
+// 4-D bf16 tensor map over (channels, w, h, n) with element strides (sw, sh, sn); box = (64, bw, bh, bn).
+bool make_map_4d(CUtensorMap* map, const void* ptr, long long C, long long W, long long H, long long N, long long sw, long long sh, long long sn,
+                 int bw, int bh, int bnn) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)sw * 2, (cuuint64_t)sh * 2, (cuuint64_t)sn * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bnn};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int ilog2i(int v) {
+  int l = 0;
+  while ((1 << (l + 1)) <= v) ++l;
+  return l;
+}
+
+// Power-of-two box (wt, ht, nt) of `pixels` pixels that covers W x H x N with the least padding (ties: widest, then tallest).
+void pick_box(int pixels, int W, int H, int N, int& lw, int& lh) {
+  const int lt = ilog2i(pixels);
+  long long best = -1;
+  for (int a = lt; a >= 0; --a) {
+    for (int b = lt - a; b >= 0; --b) {
+      const int wt = 1 << a, ht = 1 << b, nt = 1 << (lt - a - b);
+      const long long vol = (long long)((W + wt - 1) / wt) * ((H + ht - 1) / ht) * ((N + nt - 1) / nt);
+      if (best < 0 || vol < best) {
+        best = vol;
+        lw = a;
+        lh = b;
+      }
+    }
+  }
+}
+
+int conv_sm_count() {
+  static int counts[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (counts[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    counts[dev] = n;
+  }
+  return counts[dev];
+}
+
+bool conv_set_attr() {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return false;
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM_BYTES) != cudaSuccess) return false;
+    done[dev] = true;
+  }
+  return true;
+}
+
+int pick_bn(int n) { return n <= 64 ? 64 : (n <= 128 ? 128 : 256); }
+
+bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+}  // namespace
+
+// Launch plan of kb200_conv_igemm for a result of N x Ho x Wo pixels and Cn channels: plan_out = {grid, n_tiles, bn}.
+// The statistics buffer of that call needs grid * 4 * 2 * (n_tiles * bn) floats.
+KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Cn, int* plan_out) {
+  int lw = 0, lh = 0;
+  pick_box(128, Wo, Ho, N, lw, lh);
+  const int wt = 1 << lw, ht = 1 << lh, nt = 1 << (7 - lw - lh);
+  const int bn = pick_bn(Cn);
+  const int n_tiles = (Cn + bn - 1) / bn;
+  const long long total = (long long)((Wo + wt - 1) / wt) * ((Ho + ht - 1) / ht) * ((N + nt - 1) / nt) * n_tiles;
+  const int sms = conv_sm_count();
+  int grid = total <= sms ? (int)total : sms - sms % n_tiles;
+  if (grid <= 0) grid = (int)(total < n_tiles ? total : n_tiles);
+  plan_out[0] = grid;
+  plan_out[1] = n_tiles;
+  plan_out[2] = bn;
+  return 0;
+}
+
+// Implicit-GEMM convolution, forward or input-gradient form.
+//
+//   a:   bf16 activations seen as (n, h, w, c) with element strides (a_sn, a_sh, a_sw, 1) and extents (N, H, W, Ca)
+//   wgt: bf16 kernel array [R][S][rows_per_tap][w_cols] (Keras layout: rows = input channels, columns = filters)
+//   out: bf16 result seen as (n, h, w, c) with element strides (c_sn, c_sh, c_sw, 1) and extents (N, Ho, Wo, Cn)
+//   out[n, h, w, :] = act(bias + sum over r, s:  a[n, h + dh0 + r*dh_step, w + dw0 + s*dw_step, :] x B[r][s])
+//   b_kmajor = 0: B[r][s] = wgt[r][s] (Ca = rows_per_tap contracted, Cn = w_cols)            -> forward
+//   b_kmajor = 1: B[r][s] = wgt[r][s] transposed (Ca = w_cols contracted, Cn = rows_per_tap) -> input gradient
+//   accumulate: add into `out` instead of overwriting it.
+//   stats (optional): fp32 [grid * 4][2][stats_ld] per-warp partial sums of out and out^2 per channel over all pixels;
+//   plan_out (optional) receives {grid, n_tiles, bn} so that the caller can reduce them (kb200_bn_finalize_partials).
+// All channel counts and strides must be multiples of 8 elements and all base pointers 16-byte aligned.
+KB_API int kb200_conv_igemm(const void* a, const void* wgt, void* out, const float* bias, float* stats, int stats_ld, int* plan_out, int N, int H, int W,
+                            int Ca, long long a_sw, long long a_sh, long long a_sn, int Ho, int Wo, int Cn, long long c_sw, long long c_sh,
+                            long long c_sn, int R, int S, int dh0, int dh_step, int dw0, int dw_step, int b_kmajor, int rows_per_tap, int w_cols,
+                            int act, int accumulate, int* err, cudaStream_t stream) {
+  if (N <= 0 || Ho <= 0 || Wo <= 0 || Cn <= 0 || Ca <= 0) return 0;
+  if ((Ca % 8) || (Cn % 8) || (w_cols % 8) || (a_sw % 8) || (a_sh % 8) || (a_sn % 8) || (c_sw % 8) || (c_sh % 8) || (c_sn % 8) || !aligned16(a) ||
+      !aligned16(wgt) || !aligned16(out)) {
+    kb200_set_error("conv_igemm: channel counts and strides must be multiples of 8 and pointers 16-byte aligned");
+    return -2;
+  }
+  if (!conv_set_attr()) {
+    kb200_set_error("conv_igemm: cannot raise the shared-memory limit");
+    return -5;
+  }
+  ConvParams p{};
+  p.mode = 0;
+  p.lt = 7;
+  pick_box(128, Wo, Ho, N, p.lw, p.lh);
+  const int wt = 1 << p.lw, ht = 1 << p.lh, nt = 1 << (p.lt - p.lw - p.lh);
+  p.tiles_w = (Wo + wt - 1) / wt;
+  p.tiles_h = (Ho + ht - 1) / ht;
+  p.tiles_n = (N + nt - 1) / nt;
+  p.Wo = Wo; p.Ho = Ho; p.No = N;
+  p.bn = pick_bn(Cn);
+  p.n_tiles = (Cn + p.bn - 1) / p.bn;
+  p.Ngemm = Cn;
+  p.kc_blocks = (Ca + 63) / 64;
+  p.R = R; p.S = S; p.dh0 = dh0; p.dh_step = dh_step; p.dw0 = dw0; p.dw_step = dw_step;
+  p.b_kmajor = b_kmajor;
+  p.rows_per_tap = rows_per_tap;
+  p.bias = bias; p.act = act; p.accumulate = accumulate;
+  p.stats = stats; p.stats_ld = stats_ld;
+  p.err = err;
+  const long long total = (long long)p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
+  if (total > 0x7fffffffLL) {
+    kb200_set_error("conv_igemm: too many tiles");
+    return -6;
+  }
+  const int sms = conv_sm_count();
+  int grid = total <= sms ? (int)total : sms - sms % p.n_tiles;
+  if (grid <= 0) grid = (int)(total < p.n_tiles ? total : p.n_tiles);
+  if (plan_out != nullptr) {
+    plan_out[0] = grid; plan_out[1] = p.n_tiles; plan_out[2] = p.bn;
+  }
+  if (stats != nullptr && stats_ld < p.n_tiles * p.bn) {
+    kb200_set_error("conv_igemm: stats_ld is smaller than the padded channel count");
+    return -7;
+  }
+  CUtensorMap map_a, map_b, map_c;
+  bool ok = make_map_4d(&map_a, a, Ca, W, H, N, a_sw, a_sh, a_sn, wt, ht, nt);
+  const long long wrows = (long long)R * S * rows_per_tap;
+  ok = ok && (b_kmajor ? make_map(&map_b, wgt, w_cols, wrows, w_cols, 64, p.bn) : make_map(&map_b, wgt, w_cols, wrows, w_cols, 64, 64));
+  const int sbw = wt < 32 ? wt : 32;
+  const int sbh = (32 / sbw) < ht ? (32 / sbw) : ht;
+  const int sbn = 32 / (sbw * sbh);
+  ok = ok && make_map_4d(&map_c, out, Cn, Wo, Ho, N, c_sw, c_sh, c_sn, sbw, sbh, sbn);
+  if (!ok) {
+    kb200_set_error("conv_igemm: cuTensorMapEncodeTiled failed");
+    return -3;
+  }
+  conv_tcgen05_kernel<<<(unsigned)grid, THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
+  KB_CHECK_LAUNCH("conv_igemm");
+  return 0;
+}
+
+// Weight gradient: dw[r][s][c][n] += sum over pixels x[n_, h + dh0 + r*dh_step, w + dw0 + s*dw_step, c] * dy[n_, h, w, n].
+//   x:  bf16 (N, H, W, Cin) with element strides (x_sn, x_sh, x_sw, 1);  dy: bf16 (N, Ho, Wo, Cout) with strides (d_sn, d_sh, d_sw, 1)
+//   dw: fp32 [R*S*Cin, Cout] contiguous, ADDED to (zero it for a plain gradient).
+KB_API int kb200_conv_wgrad(const void* x, const void* dy, float* dw, int N, int H, int W, int Cin, long long x_sw, long long x_sh, long long x_sn,
+                            int Ho, int Wo, int Cout, long long d_sw, long long d_sh, long long d_sn, int R, int S, int dh0, int dh_step, int dw0,
+                            int dw_step, int* err, cudaStream_t stream) {
+  if (N <= 0 || Ho <= 0 || Wo <= 0 || Cin <= 0 || Cout <= 0) return 0;
+  if ((Cin % 8) || (Cout % 8) || (x_sw % 8) || (x_sh % 8) || (x_sn % 8) || (d_sw % 8) || (d_sh % 8) || (d_sn % 8) || !aligned16(x) || !aligned16(dy) ||
+      !aligned16(dw)) {
+    kb200_set_error("conv_wgrad: channel counts and strides must be multiples of 8 and pointers 16-byte aligned");
+    return -2;
+  }
+  if (!conv_set_attr()) {
+    kb200_set_error("conv_wgrad: cannot raise the shared-memory limit");
+    return -5;
+  }
+  ConvParams p{};
+  p.mode = 1;
+  p.lt = 6;
+  pick_box(64, Wo, Ho, N, p.lw, p.lh);
+  const int wt = 1 << p.lw, ht = 1 << p.lh, nt = 1 << (p.lt - p.lw - p.lh);
+  p.tiles_w = (Wo + wt - 1) / wt;
+  p.tiles_h = (Ho + ht - 1) / ht;
+  p.tiles_n = (N + nt - 1) / nt;
+  p.Wo = Wo; p.Ho = Ho; p.No = N;
+  p.bn = pick_bn(Cout);
+  p.n_tiles = (Cout + p.bn - 1) / p.bn;
+  p.Ngemm = Cout;
+  p.R = R; p.S = S; p.dh0 = dh0; p.dh_step = dh_step; p.dw0 = dw0; p.dw_step = dw_step;
+  p.rows_per_tap = Cin;
+  p.m_tiles = (Cin + 127) / 128;
+  p.Mrows = R * S * Cin;
+  p.err = err;
+  const long long pbs = (long long)p.tiles_w * p.tiles_h * p.tiles_n;
+  if (pbs > 0x7fffffffLL) {
+    kb200_set_error("conv_wgrad: too many pixel blocks");
+    return -6;
+  }
+  p.total_pb = (int)pbs;
+  const int tiles = R * S * p.m_tiles * p.n_tiles;
+  const int sms = conv_sm_count();
+  // slices of the pixel range: enough work units for two waves, at least 8 pixel blocks each
+  int split = (2 * sms + tiles - 1) / tiles;
+  if (split > p.total_pb / 8) split = p.total_pb / 8;
+  if (split < 1) split = 1;
+  p.pb_per = (p.total_pb + split - 1) / split;
+  p.split = (p.total_pb + p.pb_per - 1) / p.pb_per;
+  const long long units = (long long)tiles * p.split;
+  CUtensorMap map_a, map_b, map_c;
+  bool ok = make_map_4d(&map_a, x, Cin, W, H, N, x_sw, x_sh, x_sn, wt, ht, nt);
+  ok = ok && make_map_4d(&map_b, dy, Cout, Wo, Ho, N, d_sw, d_sh, d_sn, wt, ht, nt);
+  ok = ok && make_map(&map_c, dw, Cout, p.Mrows, Cout, 32, 32, true);
+  if (!ok) {
+    kb200_set_error("conv_wgrad: cuTensorMapEncodeTiled failed");
+    return -3;
+  }
+  const unsigned grid = (unsigned)(units < sms ? units : sms);
+  conv_tcgen05_kernel<<<grid, THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
+  KB_CHECK_LAUNCH("conv_wgrad");
+  return 0;
+}
+
+namespace {
+// Patch matrix of a convolution with few input channels (the 7x7 stem on RGB): row = output pixel, columns = R groups of
+// `seg` elements, the first S*C of which are the contiguous input run x[n, ih, iw0 .. iw0+S-1, :] and the rest zeros.
+template <typename T>
+__global__ void __launch_bounds__(256) im2col_rows_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
+                                                          int R, int S, int sh, int sw, int pt, int pl, int seg, long long total) {
+  const int run = S * C;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(t % R);
+    long long pix = t / R;
+    const int ow = (int)(pix % Wo);
+    const long long rest = pix / Wo;
+    const int oh = (int)(rest % Ho);
+    const int n = (int)(rest / Ho);
+    const int ih = oh * sh - pt + r;
+    const int iw0 = ow * sw - pl;
+    __nv_bfloat16* dst = out + (pix * R + r) * seg;
+    const bool row_in = ih >= 0 && ih < H;
+    const T* src = x + ((long long)n * H + (row_in ? ih : 0)) * W * C;
+    for (int v = 0; v < seg; v += 8) {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = v + j;
+        const int iw = iw0 + e / C;
+        f[j] = (row_in && e < run && iw >= 0 && iw < W) ? to_f32<T>(src[(long long)iw0 * C + e]) : 0.f;
+      }
+      *reinterpret_cast<bf16x8*>(dst + v) = pack8(f);
+    }
+  }
+}
+}  // namespace
+
+// out[N*Ho*Wo, R*seg] (bf16) from x[N, H, W, C] (dtype 0: fp32, 1: bf16); seg >= S*C, a multiple of 8.
+KB_API int kb200_im2col_rows(const void* x, void* out, int N, int H, int W, int C, int Ho, int Wo, int R, int S, int sh, int sw, int pt, int pl, int seg,
+                             int dtype, cudaStream_t stream) {
+  if (seg % 8 || seg < S * C || !aligned16(out)) {
+    kb200_set_error("im2col_rows: seg must be a multiple of 8 and at least S*C");
+    return -2;
+  }
+  const long long total = (long long)N * Ho * Wo * R;
+  if (total <= 0) return 0;
+  const unsigned grid = (unsigned)((total + 255) / 256 < 148LL * 16 ? (total + 255) / 256 : 148LL * 16);
+  if (dtype == 1)
+    im2col_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, N, H, W, C, Ho, Wo, R, S, sh, sw, pt, pl, seg, total);
+  else
+    im2col_rows_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (__nv_bfloat16*)out, N, H, W, C, Ho, Wo, R, S, sh, sw, pt, pl, seg, total);
+  KB_CHECK_LAUNCH("im2col_rows");
+  return 0;
+}

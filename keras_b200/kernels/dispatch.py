@@ -86,7 +86,7 @@ def fp8_matmul(layer, inputs, kernel, equation, training):
 
 
 def conv(x, kernel, strides, padding, data_format, dilation):
-    if not (enabled(x) and enabled(kernel)):
+    if not (enabled(x) and enabled(kernel)) or x.ndim != 4:
         return None
     from keras_b200.kernels import conv as conv_mod
 
@@ -106,8 +106,11 @@ def rms_norm(x, scale, eps):
     return _ops().FusedNorm.apply(x, scale, None, float(eps), True)
 
 
-def batch_norm(layer, inputs, training, residual=None, relu=False, pre_bias=None):
-    """Fused channels-last BatchNorm (+residual)(+ReLU).  Returns ``None`` when not applicable."""
+def batch_norm(layer, inputs, training, residual=None, relu=False, pre_bias=None, conv_stats=None):
+    """Fused channels-last BatchNorm (+residual)(+ReLU).  Returns ``None`` when not applicable.
+
+    ``conv_stats``: partial sums of ``inputs`` left by the producing convolution kernel (training mode only); the
+    statistics pass over ``inputs`` is then skipped."""
     x = inputs
     if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim < 2:
         return None
@@ -129,7 +132,7 @@ def batch_norm(layer, inputs, training, residual=None, relu=False, pre_bias=None
     if training:
         if beta is None:
             beta = torch.zeros(C, dtype=torch.float32, device=x.device)
-        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu), pre_bias)
+        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu), pre_bias, conv_stats)
     if torch.is_grad_enabled() and (x.requires_grad or (gamma is not None and gamma.requires_grad and layer.trainable)):
         return None
     with torch.no_grad():

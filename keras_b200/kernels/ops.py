@@ -101,21 +101,28 @@ class FusedBatchNormAct(torch.autograd.Function):
     """y = relu?(batchnorm_train(x) (+ residual)) for channels-last x, with moving-stat update."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu, pre_bias=None):
+    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu, pre_bias=None, conv_stats=None):
         lib = _lib()
         C = x.shape[-1]
         M = x.numel() // C
         x = x.contiguous()
         dev = x.device
-        sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
         stats = torch.empty(4 * C, dtype=torch.float32, device=dev)
         mean, invstd, scale, shift = stats[:C], stats[C:2 * C], stats[2 * C:3 * C], stats[3 * C:]
         y = torch.empty_like(x)
         st = _stream()
         dt = _dt(x)
-        _check(lib.kb200_bn_stats(_p(x), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_stats")
-        _check(lib.kb200_bn_finalize(_p(sums), _p(gamma), _p(beta), _p(pre_bias), _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C),
-                                     _p(mean), _p(invstd), _p(scale), _p(shift), st), "bn_finalize")
+        if conv_stats is not None and conv_stats.count == M:
+            # the producing convolution's epilogue already summed x and x^2 per channel
+            cs = conv_stats
+            _check(lib.kb200_bn_finalize_partials(_p(cs.partials), _i(cs.grid), _i(cs.n_tiles), _i(cs.bn), _i(cs.ld), _p(gamma), _p(beta), _p(pre_bias),
+                                                  _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C), _p(mean), _p(invstd), _p(scale),
+                                                  _p(shift), st), "bn_finalize_partials")
+        else:
+            sums = torch.empty(2 * C, dtype=torch.float32, device=dev)
+            _check(lib.kb200_bn_stats(_p(x), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_stats")
+            _check(lib.kb200_bn_finalize(_p(sums), _p(gamma), _p(beta), _p(pre_bias), _p(moving_mean), _p(moving_var), _f(momentum), _f(eps), _ll(M), _i(C),
+                                         _p(mean), _p(invstd), _p(scale), _p(shift), st), "bn_finalize")
         res = residual.contiguous() if residual is not None else None
         bits = None
         if relu:
@@ -147,7 +154,7 @@ class FusedBatchNormAct(torch.autograd.Function):
         _check(lib.kb200_bn_bwd_apply_mask(_p(dy), _p(x), _p(bits), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(coef), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
         dgamma = sums[C:2 * C] if gamma is not None else None
         dbeta = sums[:C]
-        return dx, dgamma, dbeta, dres, None, None, None, None, None, None
+        return dx, dgamma, dbeta, dres, None, None, None, None, None, None, None
 
 
 def bn_inference(x, scale, shift, residual, relu):

@@ -30,10 +30,14 @@ class _ShadowRead(torch.autograd.Function):
     @staticmethod
     def forward(ctx, param, shadow):
         ctx.param = param
+        # a consumer that already added its gradient into the parameter's fp32 storage sends nothing back
+        ctx.set_materialize_grads(False)
         return shadow.view_as(shadow)
 
     @staticmethod
     def backward(ctx, grad):
+        if grad is None:
+            return None, None
         p = ctx.param
         g = p.grad
         if g is not None and g.dtype == torch.float32 and g.shape == grad.shape and not g.requires_grad:

@@ -20,10 +20,10 @@ from keras_b200.layers.normalization.normalization_layers import BatchNormalizat
 
 
 class Deferred:
-    __slots__ = ("layer", "x", "pre_bias", "shape", "dtype", "device", "ndim")
+    __slots__ = ("layer", "x", "pre_bias", "stats", "shape", "dtype", "device", "ndim")
 
-    def __init__(self, layer, x, pre_bias=None):
-        self.layer, self.x, self.pre_bias = layer, x, pre_bias
+    def __init__(self, layer, x, pre_bias=None, stats=None):
+        self.layer, self.x, self.pre_bias, self.stats = layer, x, pre_bias, stats
         self.shape, self.dtype, self.device, self.ndim = x.shape, x.dtype, x.device, x.ndim
 
 
@@ -39,10 +39,10 @@ class Padded:
 class NoBias:
     """Output of a convolution whose bias add was folded into the following BatchNormalization."""
 
-    __slots__ = ("x", "bias")
+    __slots__ = ("x", "bias", "stats")
 
-    def __init__(self, x, bias):
-        self.x, self.bias = x, bias
+    def __init__(self, x, bias, stats=None):
+        self.x, self.bias, self.stats = x, bias, stats
 
 
 def _is_relu(op):
@@ -111,7 +111,7 @@ def build_plan(function):
         if src is None or id(src) in plan:
             continue
         op = src.operation
-        if not isinstance(op, BaseConv) or not op.use_bias or op.lora_enabled or op.data_format != "channels_last":
+        if not isinstance(op, BaseConv) or op.lora_enabled or op.data_format != "channels_last":
             continue
         if getattr(op.activation, "__name__", "linear") != "linear" or op.activity_regularizer is not None:
             continue
@@ -155,34 +155,52 @@ def run_pool_padded(layer, x, pairs):
     return layer(ops.pad(x, pads))
 
 
-def run_conv_nobias(layer, x, pairs=None):
+def run_conv_nobias(layer, x, pairs=None, want_stats=False):
     """The convolution of ``layer`` without its bias add (autocast applied as ``Layer.__call__`` would).
 
-    ``pairs``: symmetric zero padding of a folded ZeroPadding2D, applied by the convolution itself."""
+    ``pairs``: symmetric zero padding of a folded ZeroPadding2D, applied by the convolution itself.
+    Returns ``(y, stats)``; ``stats`` holds the per-channel partial sums of ``y`` left by the convolution kernel's
+    epilogue when ``want_stats`` is set and that kernel ran (else ``None``)."""
     from keras_b200 import ops
     from keras_b200.core.variables import AutocastScope
+    from keras_b200.kernels import conv as kconv
 
     td = layer._compute_torch_dtype()
-    if x.dtype != td and x.dtype.is_floating_point:
-        x = x.to(td)
     with AutocastScope(layer.compute_dtype):
+        if layer.rank == 2 and layer.groups == 1 and type(layer).convolution_op is BaseConvOp():
+            padding = layer.padding if pairs is None else tuple(lo for lo, _ in pairs)
+            w = layer.kernel.value
+            xin = x
+            if xin.dtype != td and xin.dtype.is_floating_point and not (xin.dtype == torch.float32 and w.shape[-2] % 8):
+                xin = xin.to(td)  # an fp32 input with few channels is cast inside the patch kernel
+            out = kconv.conv(xin, w, layer.strides, padding, layer.data_format, layer.dilation_rate, grad_target=layer.kernel, want_stats=want_stats)
+            if out is not None:
+                return out if want_stats else (out, None)
+        if x.dtype != td and x.dtype.is_floating_point:
+            x = x.to(td)
         if pairs is None:
-            return layer.convolution_op(x, layer.kernel)
+            return layer.convolution_op(x, layer.kernel), None
         return ops.conv(x, layer.kernel, strides=list(layer.strides), padding=tuple(lo for lo, _ in pairs),
-                        dilation_rate=layer.dilation_rate, data_format=layer.data_format)
+                        dilation_rate=layer.dilation_rate, data_format=layer.data_format), None
+
+
+def BaseConvOp():
+    from keras_b200.layers.convolutional.base_conv import BaseConv
+
+    return BaseConv.convolution_op
 
 
 def applicable(x):
     return isinstance(x, torch.Tensor) and x.is_cuda
 
 
-def run_bn(layer, x, training, residual=None, relu=False, pre_bias=None):
+def run_bn(layer, x, training, residual=None, relu=False, pre_bias=None, stats=None):
     """Execute a (possibly fused) BatchNormalization outside of ``Layer.__call__``."""
     from keras_b200.kernels import dispatch
 
     train = bool(training) and layer.trainable
     bias_value = pre_bias._value if pre_bias is not None else None
-    out = dispatch.batch_norm(layer, x, train, residual=residual, relu=relu, pre_bias=bias_value)
+    out = dispatch.batch_norm(layer, x, train, residual=residual, relu=relu, pre_bias=bias_value, conv_stats=stats)
     if out is not None:
         return out
     if pre_bias is not None:

@@ -139,7 +139,7 @@ class Function(Operation):
             if role == "pad_fold":
                 x = env[id(ins[0])]
                 if isinstance(x, fusion.Deferred):
-                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
+                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias, stats=x.stats)
                 env[id(outs[0])] = fusion.Padded(x, node.operation.padding)
                 continue
             if role == "pool_padded":
@@ -152,30 +152,31 @@ class Function(Operation):
                 if isinstance(x, fusion.Padded):
                     x, pairs = x.x, x.pairs
                 elif isinstance(x, fusion.Deferred):
-                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
-                env[id(outs[0])] = fusion.NoBias(fusion.run_conv_nobias(node.operation, x, pairs), node.operation.bias)
+                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias, stats=x.stats)
+                y, stats = fusion.run_conv_nobias(node.operation, x, pairs, want_stats=bool(training))
+                env[id(outs[0])] = fusion.NoBias(y, node.operation.bias if node.operation.use_bias else None, stats)
                 continue
             if role == "defer_bn":
                 x = env[id(ins[0])]
-                pre_bias = None
+                pre_bias = stats = None
                 if isinstance(x, fusion.NoBias):
-                    x, pre_bias = x.x, x.bias
+                    x, pre_bias, stats = x.x, x.bias, x.stats
                 elif isinstance(x, fusion.Deferred):
-                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias)
-                env[id(outs[0])] = fusion.Deferred(node.operation, x, pre_bias)
+                    x = fusion.run_bn(x.layer, x.x, training, pre_bias=x.pre_bias, stats=x.stats)
+                env[id(outs[0])] = fusion.Deferred(node.operation, x, pre_bias, stats)
                 continue
             if role == "consume_relu":
                 d = env[id(ins[0])]
-                env[id(outs[0])] = fusion.run_bn(d.layer, d.x, training, relu=True, pre_bias=d.pre_bias) if isinstance(d, fusion.Deferred) else node.operation(d)
+                env[id(outs[0])] = fusion.run_bn(d.layer, d.x, training, relu=True, pre_bias=d.pre_bias, stats=d.stats) if isinstance(d, fusion.Deferred) else node.operation(d)
                 continue
             if role in ("consume_add", "consume_add_relu"):
                 a, b = env[id(ins[0])], env[id(ins[1])]
                 if isinstance(a, fusion.Deferred) and isinstance(b, fusion.Deferred):
-                    b = fusion.run_bn(b.layer, b.x, training, pre_bias=b.pre_bias)
+                    b = fusion.run_bn(b.layer, b.x, training, pre_bias=b.pre_bias, stats=b.stats)
                 if isinstance(b, fusion.Deferred):
                     a, b = b, a
                 if isinstance(a, fusion.Deferred):
-                    env[id(outs[0])] = fusion.run_bn(a.layer, a.x, training, residual=b, relu=role == "consume_add_relu", pre_bias=a.pre_bias)
+                    env[id(outs[0])] = fusion.run_bn(a.layer, a.x, training, residual=b, relu=role == "consume_add_relu", pre_bias=a.pre_bias, stats=a.stats)
                 else:
                     r = node.operation([a, b])
                     env[id(outs[0])] = torch_relu(r) if role == "consume_add_relu" else r
@@ -195,7 +196,7 @@ class Function(Operation):
         for ref in self._outputs:
             v = env[id(ref)]
             if isinstance(v, fusion.Deferred):
-                v = fusion.run_bn(v.layer, v.x, training, pre_bias=v.pre_bias)
+                v = fusion.run_bn(v.layer, v.x, training, pre_bias=v.pre_bias, stats=v.stats)
             flat_out.append(v if sp is None else sp.finish(v))
         return tree.pack_sequence_as(self._outputs_struct, flat_out)
 
