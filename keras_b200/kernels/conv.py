@@ -29,7 +29,7 @@ _MAX_PATCH = 1024  # widest patch-matrix row (elements) for the few-channel path
 
 
 class ConvStats:
-    """Partial sums left by the convolution epilogue: ``partials`` [grid*4, 2, ld] fp32 and the launch plan."""
+    """Partial sums left by the convolution epilogue: ``partials`` [grid, 2, ld] fp32 and the launch plan."""
 
     __slots__ = ("partials", "grid", "n_tiles", "bn", "ld", "count")
 
@@ -265,7 +265,7 @@ def conv(x, kernel, strides, padding, data_format, dilation, grad_target=None, w
         lib.kb200_conv_igemm_plan(_i(dims[0]), _i(dims[1]), _i(dims[2]), _i(g.Cout), plan)
         grid, n_tiles, bn = plan[0], plan[1], plan[2]
         ld = n_tiles * bn
-        partials = torch.empty((grid * 4, 2, ld), dtype=torch.float32, device=x.device)
+        partials = torch.empty((grid, 2, ld), dtype=torch.float32, device=x.device)
         stats = ConvStats(partials, grid, n_tiles, bn, ld, g.N * g.Ho * g.Wo)
     target = _target_param(grad_target, w) if grad_target is not None and w is kernel else None
     y = ConvFn.apply(x, w, g, target, partials, plan)

@@ -199,7 +199,7 @@ __global__ void bn_finalize_kernel(const float* __restrict__ sums, const float* 
 }
 
 // As bn_finalize_kernel, with the per-channel sums gathered from the per-warp partials that the convolution epilogue
-// (conv_sm100.cu) leaves behind: partials[(cta * 4 + warp)][2][ld]; CTA `cta` covers channels [(cta % n_tiles) * bn, + bn).
+// (conv_sm100.cu) leaves behind: partials[cta][2][ld]; CTA `cta` covers channels [(cta % n_tiles) * bn, + bn).
 // One warp per channel; the order of the additions is fixed, so the result is reproducible bit for bit.
 __global__ void bn_finalize_partials_kernel(const float* __restrict__ partials, int grid, int n_tiles, int bn, int ld,
                                             const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ pre_bias,
@@ -210,11 +210,11 @@ __global__ void bn_finalize_partials_kernel(const float* __restrict__ partials, 
   const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (c >= C) return;
   const int ntile = c / bn;
-  const int count = ntile < grid ? ((grid - 1 - ntile) / n_tiles + 1) * 4 : 0;
+  const int count = ntile < grid ? (grid - 1 - ntile) / n_tiles + 1 : 0;
   float s = 0.f, q = 0.f;
   for (int i = lane; i < count; i += 32) {
-    const int b = ntile + (i >> 2) * n_tiles;
-    const float* src = partials + (size_t)(b * 4 + (i & 3)) * 2 * ld + c;
+    const int b = ntile + i * n_tiles;
+    const float* src = partials + (size_t)b * 2 * ld + c;
     s += src[0];
     q += src[ld];
   }

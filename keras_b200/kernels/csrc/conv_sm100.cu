@@ -31,12 +31,14 @@
 namespace {
 using namespace kbgemm;
 
-constexpr int CV_STAGES = 4;
 constexpr int CV_A_BYTES = 128 * 64 * 2;            // 16 KB: 128 pixels x 64 channels (igemm) / 64 pixels x 128 channels (wgrad)
-constexpr int CV_B_BYTES = 256 * 64 * 2;            // up to 32 KB
-constexpr int CV_STAGE_BYTES = CV_A_BYTES + CV_B_BYTES;
-constexpr int CV_OUT_BYTES = 4 * 2 * 4096;
-constexpr int CV_SMEM_BYTES = CV_STAGES * CV_STAGE_BYTES + CV_OUT_BYTES + 1024 + 256;
+constexpr int CV_BAR_BYTES = 512;
+constexpr int CV_MAX_STAGES = 12;
+constexpr int CV_SMEM_BYTES = 227 * 1024;           // everything a CTA may have
+constexpr int CV_IGEMM_THREADS = 320;               // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two sets of four lane quarters)
+// operand bytes (resident kernel slice / dY ring + operand ring) left beside the staging buffers of `epi_sets` sets of four
+// epilogue warps (two 4 KB buffers per warp)
+constexpr int cv_oper_bytes(int epi_sets) { return (CV_SMEM_BYTES - 1024 /*alignment slack*/ - CV_BAR_BYTES - epi_sets * 4 * 8192) / 1024 * 1024; }
 constexpr uint32_t CV_TMEM_COLS = 512;
 
 struct ConvParams {
@@ -53,13 +55,21 @@ struct ConvParams {
   const float* bias;
   int act;
   int accumulate;           // igemm: add the bf16 result into the destination
-  float* stats;             // igemm: [grid * 4][2][stats_ld] per-warp partial sums (or null)
+  float* stats;             // igemm: [grid][2][stats_ld] per-CTA partial sums (or null)
   int stats_ld;
   int* err;
+  // shared-memory plan: [resident region or dY ring: res_bytes][operand ring: stages x stage_bytes][staging][barriers]
+  int stages, stage_bytes, res_bytes;
+  int rank2;                // pixels are one flat dimension (1x1 filter, stride 1): 2-D tensor maps, which the TMA unit walks faster
+  int oper_bytes, epi_sets; // operand region size; sets of four epilogue warps that share a tile's columns (1 or 2)
+  int resident_b;           // igemm: this CTA's column slice of the kernel array stays in shared memory for all tiles
   // wgrad
   int m_tiles;              // 128-row tiles over the input channels
   int split, pb_per, total_pb;
   int Mrows;                // R * S * Cin
+  int items, group;         // accumulators (128 rows of dW each) in total / per work unit
+  int pair_taps;            // Cin == 64: one accumulator holds the rows of two taps
+  int b_slots;              // depth of the dY ring
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -72,7 +82,7 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
 // box store; optional per-channel statistics in `acc` (4 chunks x {sum0, sum1, sq0, sq1} for the two columns a lane owns).
 template <int CHUNKS>
 __device__ __forceinline__ void conv_store_rows(uint32_t tmem_row, int ng0, int q, int w0, int h0, int n0, uint32_t stage, uint32_t& stores,
-                                                const CUtensorMap* map_c, const ConvParams& p, int lane, float* acc) {
+                                                const CUtensorMap* map_c, const ConvParams& p, int lane, float* acc, int c_begin) {
   const int wt_mask = (1 << p.lw) - 1, ht_mask = (1 << p.lh) - 1;
   const int r = q * 32 + lane;
   const bool valid = (w0 + (r & wt_mask) < p.Wo) && (h0 + ((r >> p.lw) & ht_mask) < p.Ho) && (n0 + (r >> (p.lw + p.lh)) < p.No);
@@ -80,15 +90,25 @@ __device__ __forceinline__ void conv_store_rows(uint32_t tmem_row, int ng0, int 
   const int bw0 = w0 + (r0 & wt_mask), bh0 = h0 + ((r0 >> p.lw) & ht_mask), bn0 = n0 + (r0 >> (p.lw + p.lh));
   const bool box_ok = bw0 < p.Wo && bh0 < p.Ho && bn0 < p.No;
   const uint32_t sw = (uint32_t)(lane & 7);
+  // two register sets: the tensor-memory load of chunk c+1 is in flight while chunk c is converted and staged
+  uint32_t ra[64], rb[64];
+  tmem_row += (uint32_t)(c_begin * 64);
+  ng0 += c_begin * 64;
+  tmem_ld32(tmem_row, ra);
+  tmem_ld32(tmem_row + 32u, ra + 32);
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
     const int col0 = ng0 + c * 64;
+    uint32_t* rr = (c & 1) ? rb : ra;
+    uint32_t* rn = (c & 1) ? ra : rb;
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (c + 1 < CHUNKS) {
+      tmem_ld32(tmem_row + (uint32_t)((c + 1) * 64), rn);
+      tmem_ld32(tmem_row + (uint32_t)((c + 1) * 64 + 32), rn + 32);
+    }
     if (col0 < p.Ngemm) {
-      uint32_t rr[64];
-      tmem_ld32(tmem_row + (uint32_t)(c * 64), rr);
-      tmem_ld32(tmem_row + (uint32_t)(c * 64 + 32), rr + 32);
+      // the staging buffer about to be reused must have been read out by the TMA engine
       if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       __syncwarp();
       const uint32_t buf0 = stage + (stores & 1u) * 4096u;
       const uint32_t buf = buf0 + (uint32_t)lane * 128u;
@@ -136,7 +156,15 @@ __device__ __forceinline__ void conv_store_rows(uint32_t tmem_row, int ng0, int 
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0 && box_ok) {
-        if (p.accumulate) {
+        if (p.rank2) {
+          if (p.accumulate) {
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c), "r"(buf0),
+                         "r"(col0), "r"(bw0) : "memory");
+          } else {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map_c), "r"(buf0), "r"(col0), "r"(bw0)
+                         : "memory");
+          }
+        } else if (p.accumulate) {
           asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map_c), "r"(buf0),
                        "r"(col0), "r"(bw0), "r"(bh0), "r"(bn0) : "memory");
         } else {
@@ -145,7 +173,7 @@ __device__ __forceinline__ void conv_store_rows(uint32_t tmem_row, int ng0, int 
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
-      ++stores;
+      if (box_ok) ++stores;  // buffers alternate per committed store group (see store_rows_tma)
     }
   }
 }
@@ -160,98 +188,128 @@ __device__ __forceinline__ void pixel_tile_origin(const ConvParams& p, int ptile
   n0 = tn << (p.lt - p.lw - p.lh);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
-conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
-                    const ConvParams p) {
-  constexpr int STAGES = CV_STAGES;
-  extern __shared__ uint8_t smem_raw[];
+
+// Shared-memory carve-up common to both kernels.
+struct ConvSmem {
+  uint32_t res, ring, out, bar;
+  uint8_t* bar_ptr;
+};
+__device__ __forceinline__ ConvSmem conv_smem(uint8_t* smem_raw, const ConvParams& p) {
+  ConvSmem s;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t stage_out = base + STAGES * CV_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base_ptr + STAGES * CV_STAGE_BYTES + CV_OUT_BYTES);
-  const uint32_t bar_base = stage_out + CV_OUT_BYTES;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);
+  s.res = base;
+  s.ring = base + (uint32_t)p.res_bytes;
+  s.out = base + (uint32_t)p.oper_bytes;
+  s.bar = s.out + (uint32_t)(p.epi_sets * 4 * 8192);
+  s.bar_ptr = smem_raw + (s.bar - smem_u32(smem_raw));
+  return s;
+}
+// barrier slots (8 bytes each): full[12] empty[12] acc_full[2] acc_empty[2] b_full[4] b_empty[4] | tmem slot | abort flag
+__device__ __forceinline__ uint32_t bar_full(const ConvSmem& s, int i) { return s.bar + 8u * (uint32_t)i; }
+__device__ __forceinline__ uint32_t bar_empty(const ConvSmem& s, int i) { return s.bar + 8u * (uint32_t)(CV_MAX_STAGES + i); }
+__device__ __forceinline__ uint32_t bar_acc_full(const ConvSmem& s, int i) { return s.bar + 8u * (uint32_t)(2 * CV_MAX_STAGES + i); }
+__device__ __forceinline__ uint32_t bar_acc_empty(const ConvSmem& s, int i) { return s.bar + 8u * (uint32_t)(2 * CV_MAX_STAGES + 2 + i); }
+__device__ __forceinline__ uint32_t bar_b_full(const ConvSmem& s, int i) { return s.bar + 8u * (uint32_t)(2 * CV_MAX_STAGES + 4 + i); }
+__device__ __forceinline__ uint32_t bar_b_empty(const ConvSmem& s, int i) { return s.bar + 8u * (uint32_t)(2 * CV_MAX_STAGES + 8 + i); }
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int taps = p.R * p.S;
-  const int pix_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
-  const int tiles_out = p.mode == 0 ? pix_tiles * p.n_tiles : taps * p.m_tiles * p.n_tiles;
-  const int total_units = p.mode == 0 ? tiles_out : tiles_out * p.split;
-  const uint32_t stage_tx = (uint32_t)(CV_A_BYTES + p.bn * 128);
-
+__device__ __forceinline__ void conv_prologue(const ConvSmem& s, const ConvParams& p, int acc_empty_count, volatile uint32_t*& tmem_slot,
+                                              volatile int*& abort_flag) {
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s.bar_ptr);
+  tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * CV_MAX_STAGES + 12);
+  abort_flag = reinterpret_cast<volatile int*>(bars + 2 * CV_MAX_STAGES + 13);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(bar_full(s, i), 1);
+      mbar_init(bar_empty(s, i), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), 4);
+      mbar_init(bar_acc_full(s, a), 1);
+      mbar_init(bar_acc_empty(s, a), acc_empty_count);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar_b_full(s, i), 1);
+      mbar_init(bar_b_empty(s, i), 1);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if ((threadIdx.x >> 5) == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(CV_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// Give copies that were issued before an abort a bounded time to land (the CTA must not exit under them).
+__device__ __forceinline__ void conv_drain(const ConvSmem& s, const ConvParams& p, uint32_t issued) {
+  const uint32_t first = issued > (uint32_t)p.stages ? issued - (uint32_t)p.stages : 0;
+  for (uint32_t i = first; i < issued; ++i) {
+    for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+      if (mbar_try_wait(bar_full(s, (int)(i % (uint32_t)p.stages)), (i / (uint32_t)p.stages) & 1)) break;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ forward / input gradient
+__global__ void __launch_bounds__(CV_IGEMM_THREADS, 1)
+conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                          const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const ConvSmem s = conv_smem(smem_raw, p);
+  volatile uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  conv_prologue(s, p, 8, tmem_slot, abort_flag);
   const uint32_t tmem_base = *tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.R * p.S;
+  const int STAGES = p.stages;
+  const int total_units = p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
+  const int ng0 = (blockIdx.x % p.n_tiles) * p.bn;  // the grid is a multiple of n_tiles: one column tile per CTA
+  const uint32_t b_block = (uint32_t)p.bn * 128u;   // bytes of one 64-deep slice of the kernel tile
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0, issued = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        if (p.mode == 0) {
-          const int ng0 = (u % p.n_tiles) * p.bn;
-          int w0, h0, n0;
-          pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
-          for (int tap = 0; tap < taps && ok; ++tap) {
-            const int dh = p.dh0 + (tap / p.S) * p.dh_step, dw = p.dw0 + (tap % p.S) * p.dw_step;
-            const int brow = tap * p.rows_per_tap;
-            for (int kc = 0; kc < p.kc_blocks; ++kc, ++it) {
-              const int s = it % STAGES;
-              ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
-              if (!ok) break;
-              const uint32_t sa = base + s * CV_STAGE_BYTES, sb = sa + CV_A_BYTES;
-              mbar_expect_tx(full_bar(s), stage_tx);
-              tma_load_4d(sa, &map_a, full_bar(s), kc * 64, w0 + dw, h0 + dh, n0);
-              if (p.b_kmajor) {
-                tma_load_2d(sb, &map_b, full_bar(s), kc * 64, brow + ng0);
-              } else {
-                for (int j = 0; j < (p.bn >> 6); ++j) tma_load_2d(sb + j * 8192, &map_b, full_bar(s), ng0 + j * 64, brow + kc * 64);
-              }
-              issued = it + 1;
+      if (p.resident_b) {
+        mbar_expect_tx(bar_b_full(s, 0), (uint32_t)p.res_bytes);
+        for (int tap = 0; tap < taps; ++tap) {
+          const int brow = tap * p.rows_per_tap;
+          for (int kc = 0; kc < p.kc_blocks; ++kc) {
+            const uint32_t sb = s.res + (uint32_t)(tap * p.kc_blocks + kc) * b_block;
+            if (p.b_kmajor) {
+              tma_load_2d(sb, &map_b, bar_b_full(s, 0), kc * 64, brow + ng0);
+            } else {
+              for (int j = 0; j < (p.bn >> 6); ++j) tma_load_2d(sb + j * 8192, &map_b, bar_b_full(s, 0), ng0 + j * 64, brow + kc * 64);
             }
           }
-        } else {
-          const int tile = u % tiles_out, slice = u / tiles_out;
-          const int ng0 = (tile % p.n_tiles) * p.bn;
-          const int rest = tile / p.n_tiles;
-          const int c0 = (rest % p.m_tiles) * 128;
-          const int tap = rest / p.m_tiles;
+        }
+      }
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int w0, h0, n0;
+        pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
+        for (int tap = 0; tap < taps && ok; ++tap) {
           const int dh = p.dh0 + (tap / p.S) * p.dh_step, dw = p.dw0 + (tap % p.S) * p.dw_step;
-          const int pb0 = slice * p.pb_per, pb1 = min(pb0 + p.pb_per, p.total_pb);
-          for (int pb = pb0; pb < pb1; ++pb, ++it) {
-            const int s = it % STAGES;
-            ok = mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1, abort_flag);
+          const int brow = tap * p.rows_per_tap;
+          for (int kc = 0; kc < p.kc_blocks; ++kc, ++it) {
+            const int st = it % STAGES;
+            ok = mbar_wait(bar_empty(s, st), ((it / STAGES) & 1) ^ 1, abort_flag);
             if (!ok) break;
-            int w0, h0, n0;
-            pixel_tile_origin(p, pb, w0, h0, n0);
-            const uint32_t sa = base + s * CV_STAGE_BYTES, sb = sa + CV_A_BYTES;
-            mbar_expect_tx(full_bar(s), stage_tx);
-            tma_load_4d(sa, &map_a, full_bar(s), c0, w0 + dw, h0 + dh, n0);
-            tma_load_4d(sa + 8192, &map_a, full_bar(s), c0 + 64, w0 + dw, h0 + dh, n0);
-            for (int j = 0; j < (p.bn >> 6); ++j) tma_load_4d(sb + j * 8192, &map_b, full_bar(s), ng0 + j * 64, w0, h0, n0);
+            const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
+            mbar_expect_tx(bar_full(s, st), (uint32_t)p.stage_bytes);
+            if (p.rank2) tma_load_2d(sa, &map_a, bar_full(s, st), kc * 64, w0 + dw);
+            else tma_load_4d(sa, &map_a, bar_full(s, st), kc * 64, w0 + dw, h0 + dh, n0);
+            if (!p.resident_b) {
+              const uint32_t sb = sa + CV_A_BYTES;
+              if (p.b_kmajor) {
+                tma_load_2d(sb, &map_b, bar_full(s, st), kc * 64, brow + ng0);
+              } else {
+                for (int j = 0; j < (p.bn >> 6); ++j) tma_load_2d(sb + j * 8192, &map_b, bar_full(s, st), ng0 + j * 64, brow + kc * 64);
+              }
+            }
             issued = it + 1;
           }
         }
@@ -259,50 +317,47 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!ok) {
         if (p.err) atomicExch(p.err, 21);
         *abort_flag = 1;
-        const uint32_t first = issued > STAGES ? issued - STAGES : 0;
-        for (uint32_t i = first; i < issued; ++i) {
-          for (uint32_t spin = 0; spin < (1u << 16); ++spin)
-            if (mbar_try_wait(full_bar(i % STAGES), (i / STAGES) & 1)) break;
-        }
+        conv_drain(s, p, issued);
+      }
+      if (p.resident_b) {  // the kernel slice must have landed before the CTA may exit
+        for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+          if (mbar_try_wait(bar_b_full(s, 0), 0)) break;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t a_mn = p.mode == 1 ? 1u : 0u;
-      const uint32_t b_mn = p.mode == 1 ? 1u : (p.b_kmajor ? 0u : 1u);
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (a_mn << 15) | (b_mn << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      const uint32_t a_step = a_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t b_mn = p.b_kmajor ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (b_mn << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t a_step = 32u >> 4;
       const uint32_t b_step = b_mn ? (2048u >> 4) : (32u >> 4);
       uint32_t it = 0, local = 0;
       bool ok = true;
+      if (p.resident_b) {
+        ok = mbar_wait(bar_b_full(s, 0), 0, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      const int steps = taps * p.kc_blocks;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
         const uint32_t acc = local & 1;
-        ok = mbar_wait(acc_empty_bar(acc), ((local >> 1) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(bar_acc_empty(s, acc), ((local >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + acc * 256u;
-        int steps;
-        if (p.mode == 0) {
-          steps = taps * p.kc_blocks;
-        } else {
-          const int slice = u / tiles_out;
-          const int pb0 = slice * p.pb_per;
-          steps = min(pb0 + p.pb_per, p.total_pb) - pb0;
-        }
-        for (int st = 0; st < steps; ++st, ++it) {
-          const int s = it % STAGES;
-          ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag);
+        for (int k = 0; k < steps; ++k, ++it) {
+          const int st = it % STAGES;
+          ok = mbar_wait(bar_full(s, st), (it / STAGES) & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t sa = base + s * CV_STAGE_BYTES, sb = sa + CV_A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa, a_mn != 0), bdesc = make_smem_desc(sb, b_mn != 0);
+          const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
+          const uint32_t sb = p.resident_b ? s.res + (uint32_t)k * b_block : sa + CV_A_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, false), bdesc = make_smem_desc(sb, b_mn != 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * k), bdesc + (uint64_t)(b_step * k), idesc, (st > 0 || k > 0) ? 1u : 0u);
-          umma_commit(empty_bar(s));
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * kk), bdesc + (uint64_t)(b_step * kk), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar_empty(s, st));
         }
-        if (ok) umma_commit(acc_full_bar(acc));
+        if (ok) umma_commit(bar_acc_full(s, acc));
       }
       if (!ok) {
         if (p.err) atomicExch(p.err, 22);
@@ -310,59 +365,241 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // Two sets of four warps (one warp per tensor-memory lane quarter in each set).  With epi_sets == 2 the sets split the
+    // tile's 64-column chunks between them; with epi_sets == 1 the second set only takes part in the barriers.
     const int q = warp & 3;
-    const uint32_t my_stage = stage_out + (uint32_t)(warp - 2) * 8192u;
+    const int ew = warp - 2, set = ew >> 2;
+    const bool active = set < p.epi_sets;
+    const int cps = (p.bn >> 6) / p.epi_sets;  // chunks per set
+    const int c_begin = set * cps;
+    const uint32_t my_stage = s.out + (uint32_t)ew * 8192u;
     uint32_t local = 0, stores = 0;
     bool ok = true;
     float acc_stats[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc_stats[i] = 0.f;
-    GemmParams gp{};
-    if (p.mode == 1) {
-      gp.M = p.Mrows; gp.N = p.Ngemm; gp.out_fp32 = 1; gp.split_k = 2;  // every unit adds its partial tile
-    }
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
       const uint32_t acc = local & 1;
-      ok = mbar_wait(acc_full_bar(acc), (local >> 1) & 1, abort_flag);
+      ok = mbar_wait(bar_acc_full(s, acc), (local >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t tmem_row = tmem_base + acc * 256u + ((uint32_t)(q * 32) << 16);
-      if (p.mode == 0) {
-        const int ng0 = (u % p.n_tiles) * p.bn;
+      if (active) {
+        const uint32_t tmem_row = tmem_base + acc * 256u + ((uint32_t)(q * 32) << 16);
         int w0, h0, n0;
         pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
-        if (p.bn == 256) conv_store_rows<4>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats);
-        else if (p.bn == 128) conv_store_rows<2>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats);
-        else conv_store_rows<1>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats);
-      } else {
-        const int tile = u % tiles_out;
-        const int ng0 = (tile % p.n_tiles) * p.bn;
-        const int rest = tile / p.n_tiles;
-        const int row0 = (rest / p.m_tiles) * p.rows_per_tap + (rest % p.m_tiles) * 128 + q * 32;
-        store_rows_tma(tmem_row, p.bn, ng0, row0, my_stage, stores, &map_c, gp, lane);
+        if (cps == 4) conv_store_rows<4>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats, c_begin);
+        else if (cps == 2) conv_store_rows<2>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats, c_begin);
+        else conv_store_rows<1>(tmem_row, ng0, q, w0, h0, n0, my_stage, stores, &map_c, p, lane, acc_stats, c_begin);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      if (lane == 0) mbar_arrive(bar_acc_empty(s, acc));
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    if (p.mode == 0 && p.stats != nullptr) {
-      // every tile of this CTA has the same column origin (the grid is a multiple of n_tiles)
-      const int ng0 = (blockIdx.x % p.n_tiles) * p.bn;
-      float* dst = p.stats + (size_t)(blockIdx.x * 4 + q) * 2 * p.stats_ld + ng0 + 2 * lane;
+    if (p.stats != nullptr) {
+      // combine the warps' column sums in a fixed order (reproducible) and write one row pair per CTA
+      __syncwarp();  // lane 0 has waited for this warp's stores: the staging buffers are free
+      if (active) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        if (c * 64 < p.bn) {
-          dst[c * 64] = acc_stats[c * 4 + 0];
-          dst[c * 64 + 1] = acc_stats[c * 4 + 1];
-          dst[p.stats_ld + c * 64] = acc_stats[c * 4 + 2];
-          dst[p.stats_ld + c * 64 + 1] = acc_stats[c * 4 + 3];
+        for (int c = 0; c < 4; ++c) {
+          if (c < cps) {
+            const uint32_t o = my_stage + (uint32_t)((c_begin + c) * 64 + 2 * lane) * 4u;
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(o), "f"(acc_stats[c * 4 + 0]), "f"(acc_stats[c * 4 + 1]) : "memory");
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(o + 1024u), "f"(acc_stats[c * 4 + 2]), "f"(acc_stats[c * 4 + 3]) : "memory");
+          }
         }
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps
+      const int tid = threadIdx.x - 64;
+      float* dst = p.stats + (size_t)blockIdx.x * 2 * p.stats_ld + ng0;
+      for (int col = tid; col < p.bn; col += 256) {
+        const uint32_t owner = s.out + (uint32_t)(((col >> 6) / cps) * 4) * 8192u + (uint32_t)col * 4u;
+        float sum = 0.f, sq = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float a, b;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a) : "r"(owner + (uint32_t)w * 8192u) : "memory");
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(b) : "r"(owner + (uint32_t)w * 8192u + 1024u) : "memory");
+          sum += a;
+          sq += b;
+        }
+        dst[col] = sum;
+        dst[p.stats_ld + col] = sq;
       }
     }
     if (!ok) {
       if (lane == 0 && p.err) atomicExch(p.err, 23);
+      *abort_flag = 1;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(CV_TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ weight gradient
+// Work unit = (group of up to `group` accumulators, column tile, slice of the pixel range).  An accumulator holds 128 rows
+// of dW: one (tap, 128-channel tile) pair, or two taps when Cin == 64.  For every 64-pixel block of its slice the unit
+// loads the dY box once (dY ring) and one shifted x box per accumulator (operand ring), so dY crosses L2 -> shared memory
+// once per group instead of once per tap.  All accumulators of the unit live in tensor memory until the slice is done.
+__device__ __forceinline__ void wgrad_unit(const ConvParams& p, int u, int& item0, int& cnt, int& ng0, int& pb0, int& pb1) {
+  const int groups = (p.items + p.group - 1) / p.group;
+  const int grp = u % groups;
+  const int rest = u / groups;
+  ng0 = (rest % p.n_tiles) * p.bn;
+  const int slice = rest / p.n_tiles;
+  item0 = grp * p.group;
+  cnt = min(p.group, p.items - item0);
+  pb0 = slice * p.pb_per;
+  pb1 = min(pb0 + p.pb_per, p.total_pb);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                          const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const ConvSmem s = conv_smem(smem_raw, p);
+  volatile uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  conv_prologue(s, p, 4, tmem_slot, abort_flag);
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int taps = p.R * p.S;
+  const int STAGES = p.stages, BSLOTS = p.b_slots;
+  const int groups = (p.items + p.group - 1) / p.group;
+  const int total_units = groups * p.n_tiles * p.split;
+  const uint32_t b_bytes = (uint32_t)p.bn * 128u;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0, bit = 0, issued = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int item0, cnt, ng0, pb0, pb1;
+        wgrad_unit(p, u, item0, cnt, ng0, pb0, pb1);
+        for (int pb = pb0; pb < pb1 && ok; ++pb, ++bit) {
+          int w0, h0, n0;
+          pixel_tile_origin(p, pb, w0, h0, n0);
+          const int bs = bit % BSLOTS;
+          ok = mbar_wait(bar_b_empty(s, bs), ((bit / BSLOTS) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint32_t sb = s.res + (uint32_t)bs * b_bytes;
+          mbar_expect_tx(bar_b_full(s, bs), b_bytes);
+          if (p.rank2) {
+            for (int j = 0; j < (p.bn >> 6); ++j) tma_load_2d(sb + j * 8192, &map_b, bar_b_full(s, bs), ng0 + j * 64, w0);
+          } else {
+            for (int j = 0; j < (p.bn >> 6); ++j) tma_load_4d(sb + j * 8192, &map_b, bar_b_full(s, bs), ng0 + j * 64, w0, h0, n0);
+          }
+          for (int i = 0; i < cnt; ++i, ++it) {
+            const int st = it % STAGES;
+            ok = mbar_wait(bar_empty(s, st), ((it / STAGES) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
+            mbar_expect_tx(bar_full(s, st), (uint32_t)CV_A_BYTES);
+            const int item = item0 + i;
+            if (p.pair_taps) {
+              const int ta = 2 * item, tb = 2 * item + 1;
+              tma_load_4d(sa, &map_a, bar_full(s, st), 0, w0 + p.dw0 + (ta % p.S) * p.dw_step, h0 + p.dh0 + (ta / p.S) * p.dh_step, n0);
+              if (tb < taps) {
+                tma_load_4d(sa + 8192, &map_a, bar_full(s, st), 0, w0 + p.dw0 + (tb % p.S) * p.dw_step, h0 + p.dh0 + (tb / p.S) * p.dh_step, n0);
+              } else {
+                tma_load_4d(sa + 8192, &map_a, bar_full(s, st), 64, w0, h0, n0);  // channels 64.. do not exist: zero fill
+              }
+            } else {
+              const int tap = item / p.m_tiles, c0 = (item % p.m_tiles) * 128;
+              const int dh = p.dh0 + (tap / p.S) * p.dh_step, dw = p.dw0 + (tap % p.S) * p.dw_step;
+              if (p.rank2) {
+                tma_load_2d(sa, &map_a, bar_full(s, st), c0, w0 + dw);
+                tma_load_2d(sa + 8192, &map_a, bar_full(s, st), c0 + 64, w0 + dw);
+              } else {
+                tma_load_4d(sa, &map_a, bar_full(s, st), c0, w0 + dw, h0 + dh, n0);
+                tma_load_4d(sa + 8192, &map_a, bar_full(s, st), c0 + 64, w0 + dw, h0 + dh, n0);
+              }
+            }
+            issued = it + 1;
+          }
+        }
+      }
+      if (!ok) {
+        if (p.err) atomicExch(p.err, 31);
+        *abort_flag = 1;
+        conv_drain(s, p, issued);
+        for (int i = 0; i < BSLOTS; ++i)
+          for (uint32_t spin = 0; spin < (1u << 14); ++spin)
+            if (mbar_try_wait(bar_b_full(s, i), 0) || mbar_try_wait(bar_b_full(s, i), 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t step = 2048u >> 4;
+      uint32_t it = 0, bit = 0, local = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
+        int item0, cnt, ng0, pb0, pb1;
+        wgrad_unit(p, u, item0, cnt, ng0, pb0, pb1);
+        ok = mbar_wait(bar_acc_empty(s, 0), (local & 1) ^ 1, abort_flag);  // the epilogue has drained the previous unit
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int pb = pb0; pb < pb1 && ok; ++pb, ++bit) {
+          const int bs = bit % BSLOTS;
+          ok = mbar_wait(bar_b_full(s, bs), (bit / BSLOTS) & 1, abort_flag);
+          if (!ok) break;
+          const uint64_t bdesc = make_smem_desc(s.res + (uint32_t)bs * b_bytes, true);
+          for (int i = 0; i < cnt; ++i, ++it) {
+            const int st = it % STAGES;
+            ok = mbar_wait(bar_full(s, st), (it / STAGES) & 1, abort_flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t adesc = make_smem_desc(s.ring + (uint32_t)(st * p.stage_bytes), true);
+            const uint32_t tmem_d = tmem_base + (uint32_t)(i * p.bn);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_bf16(tmem_d, adesc + (uint64_t)(step * kk), bdesc + (uint64_t)(step * kk), idesc, (pb > pb0 || kk > 0) ? 1u : 0u);
+            umma_commit(bar_empty(s, st));
+          }
+          if (ok) umma_commit(bar_b_empty(s, bs));
+        }
+        if (ok) umma_commit(bar_acc_full(s, 0));
+      }
+      if (!ok) {
+        if (p.err) atomicExch(p.err, 32);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    const uint32_t my_stage = s.out + (uint32_t)(warp - 2) * 8192u;
+    uint32_t local = 0, stores = 0;
+    bool ok = true;
+    GemmParams gp{};
+    gp.M = p.Mrows; gp.N = p.Ngemm; gp.out_fp32 = 1; gp.split_k = 2;  // every unit adds its partial tiles (TMA reduce stores)
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
+      int item0, cnt, ng0, pb0, pb1;
+      wgrad_unit(p, u, item0, cnt, ng0, pb0, pb1);
+      ok = mbar_wait(bar_acc_full(s, 0), local & 1, abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int i = 0; i < cnt; ++i) {
+        const int item = item0 + i;
+        const int row0 = (p.pair_taps ? item * 128 : (item / p.m_tiles) * p.rows_per_tap + (item % p.m_tiles) * 128) + q * 32;
+        const uint32_t tmem_row = tmem_base + (uint32_t)(i * p.bn) + ((uint32_t)(q * 32) << 16);
+        store_rows_tma(tmem_row, p.bn, ng0, row0, my_stage, stores, &map_c, gp, lane);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(s, 0));
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (!ok) {
+      if (lane == 0 && p.err) atomicExch(p.err, 33);
       *abort_flag = 1;
     }
   }
@@ -431,7 +668,8 @@ bool conv_set_attr() {
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return false;
   if (!done[dev]) {
-    if (cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM_BYTES) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(conv_igemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM_BYTES) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(conv_wgrad_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM_BYTES) != cudaSuccess) return false;
     done[dev] = true;
   }
   return true;
@@ -444,7 +682,7 @@ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 }  // namespace
 
 // Launch plan of kb200_conv_igemm for a result of N x Ho x Wo pixels and Cn channels: plan_out = {grid, n_tiles, bn}.
-// The statistics buffer of that call needs grid * 4 * 2 * (n_tiles * bn) floats.
+// The statistics buffer of that call needs grid * 2 * (n_tiles * bn) floats.
 KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Cn, int* plan_out) {
   int lw = 0, lh = 0;
   pick_box(128, Wo, Ho, N, lw, lh);
@@ -470,7 +708,7 @@ KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Cn, int* plan_out) {
 //   b_kmajor = 0: B[r][s] = wgt[r][s] (Ca = rows_per_tap contracted, Cn = w_cols)            -> forward
 //   b_kmajor = 1: B[r][s] = wgt[r][s] transposed (Ca = w_cols contracted, Cn = rows_per_tap) -> input gradient
 //   accumulate: add into `out` instead of overwriting it.
-//   stats (optional): fp32 [grid * 4][2][stats_ld] per-warp partial sums of out and out^2 per channel over all pixels;
+//   stats (optional): fp32 [grid][2][stats_ld] per-CTA partial sums of out and out^2 per channel over all pixels;
 //   plan_out (optional) receives {grid, n_tiles, bn} so that the caller can reduce them (kb200_bn_finalize_partials).
 // All channel counts and strides must be multiples of 8 elements and all base pointers 16-byte aligned.
 KB_API int kb200_conv_igemm(const void* a, const void* wgt, void* out, const float* bias, float* stats, int stats_ld, int* plan_out, int N, int H, int W,
@@ -521,19 +759,38 @@ KB_API int kb200_conv_igemm(const void* a, const void* wgt, void* out, const flo
     kb200_set_error("conv_igemm: stats_ld is smaller than the padded channel count");
     return -7;
   }
+  // shared-memory plan.  With few MMAs per tile the epilogue (about 1500 cycles per 64-column chunk and warp) is the
+  // bottleneck: both sets of epilogue warps then work on a tile.  The kernel slice of this CTA's column tile stays resident
+  // in shared memory when that leaves a ring of at least six 16 KB stages.
+  const long long bbytes = (long long)R * S * p.kc_blocks * p.bn * 128;
+  const int steps = R * S * p.kc_blocks;
+  p.epi_sets = (p.bn >= 128 && steps <= 12) ? 2 : 1;
+  p.oper_bytes = cv_oper_bytes(p.epi_sets);
+  if (bbytes <= p.oper_bytes - 6 * CV_A_BYTES) {
+    p.resident_b = 1;
+    p.res_bytes = (int)bbytes;
+    p.stage_bytes = CV_A_BYTES;
+  } else {
+    p.resident_b = 0;
+    p.res_bytes = 0;
+    p.stage_bytes = CV_A_BYTES + p.bn * 128;
+  }
+  p.stages = (p.oper_bytes - p.res_bytes) / p.stage_bytes;
+  if (p.stages > CV_MAX_STAGES) p.stages = CV_MAX_STAGES;
+  p.rank2 = (R == 1 && S == 1 && H == 1 && N == 1 && Ho == 1) ? 1 : 0;
   CUtensorMap map_a, map_b, map_c;
-  bool ok = make_map_4d(&map_a, a, Ca, W, H, N, a_sw, a_sh, a_sn, wt, ht, nt);
+  bool ok = p.rank2 ? make_map(&map_a, a, Ca, W, a_sw, 64, 128) : make_map_4d(&map_a, a, Ca, W, H, N, a_sw, a_sh, a_sn, wt, ht, nt);
   const long long wrows = (long long)R * S * rows_per_tap;
   ok = ok && (b_kmajor ? make_map(&map_b, wgt, w_cols, wrows, w_cols, 64, p.bn) : make_map(&map_b, wgt, w_cols, wrows, w_cols, 64, 64));
   const int sbw = wt < 32 ? wt : 32;
   const int sbh = (32 / sbw) < ht ? (32 / sbw) : ht;
   const int sbn = 32 / (sbw * sbh);
-  ok = ok && make_map_4d(&map_c, out, Cn, Wo, Ho, N, c_sw, c_sh, c_sn, sbw, sbh, sbn);
+  ok = ok && (p.rank2 ? make_map(&map_c, out, Cn, Wo, c_sw, 64, 32) : make_map_4d(&map_c, out, Cn, Wo, Ho, N, c_sw, c_sh, c_sn, sbw, sbh, sbn));
   if (!ok) {
     kb200_set_error("conv_igemm: cuTensorMapEncodeTiled failed");
     return -3;
   }
-  conv_tcgen05_kernel<<<(unsigned)grid, THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
+  conv_igemm_tcgen05_kernel<<<(unsigned)grid, CV_IGEMM_THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   KB_CHECK_LAUNCH("conv_igemm");
   return 0;
 }
@@ -577,25 +834,37 @@ KB_API int kb200_conv_wgrad(const void* x, const void* dy, float* dw, int N, int
     return -6;
   }
   p.total_pb = (int)pbs;
-  const int tiles = R * S * p.m_tiles * p.n_tiles;
+  const int taps = R * S;
+  p.pair_taps = (Cin == 64 && taps > 1) ? 1 : 0;
+  p.items = p.pair_taps ? (taps + 1) / 2 : taps * p.m_tiles;
+  p.group = 512 / p.bn < p.items ? 512 / p.bn : p.items;
+  p.b_slots = p.bn == 256 ? 2 : 3;
+  p.res_bytes = p.b_slots * p.bn * 128;
+  p.stage_bytes = CV_A_BYTES;
+  p.epi_sets = 1;
+  p.oper_bytes = cv_oper_bytes(1);
+  p.stages = (p.oper_bytes - p.res_bytes) / p.stage_bytes;
+  if (p.stages > CV_MAX_STAGES) p.stages = CV_MAX_STAGES;
+  const int tiles = ((p.items + p.group - 1) / p.group) * p.n_tiles;
   const int sms = conv_sm_count();
-  // slices of the pixel range: enough work units for two waves, at least 8 pixel blocks each
-  int split = (2 * sms + tiles - 1) / tiles;
-  if (split > p.total_pb / 8) split = p.total_pb / 8;
+  // slices of the pixel range: one wave of work units, at least 4 pixel blocks each
+  int split = tiles >= sms ? 1 : sms / tiles;
+  if (split > p.total_pb / 4) split = p.total_pb / 4;
   if (split < 1) split = 1;
   p.pb_per = (p.total_pb + split - 1) / split;
   p.split = (p.total_pb + p.pb_per - 1) / p.pb_per;
   const long long units = (long long)tiles * p.split;
   CUtensorMap map_a, map_b, map_c;
-  bool ok = make_map_4d(&map_a, x, Cin, W, H, N, x_sw, x_sh, x_sn, wt, ht, nt);
-  ok = ok && make_map_4d(&map_b, dy, Cout, Wo, Ho, N, d_sw, d_sh, d_sn, wt, ht, nt);
+  p.rank2 = (R == 1 && S == 1 && H == 1 && N == 1 && Ho == 1) ? 1 : 0;
+  bool ok = p.rank2 ? make_map(&map_a, x, Cin, W, x_sw, 64, 64) : make_map_4d(&map_a, x, Cin, W, H, N, x_sw, x_sh, x_sn, wt, ht, nt);
+  ok = ok && (p.rank2 ? make_map(&map_b, dy, Cout, Wo, d_sw, 64, 64) : make_map_4d(&map_b, dy, Cout, Wo, Ho, N, d_sw, d_sh, d_sn, wt, ht, nt));
   ok = ok && make_map(&map_c, dw, Cout, p.Mrows, Cout, 32, 32, true);
   if (!ok) {
     kb200_set_error("conv_wgrad: cuTensorMapEncodeTiled failed");
     return -3;
   }
   const unsigned grid = (unsigned)(units < sms ? units : sms);
-  conv_tcgen05_kernel<<<grid, THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
+  conv_wgrad_tcgen05_kernel<<<grid, THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   KB_CHECK_LAUNCH("conv_wgrad");
   return 0;
 }
@@ -606,29 +875,34 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(256) im2col_rows_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
                                                           int R, int S, int sh, int sw, int pt, int pl, int seg, long long total) {
-  const int run = S * C;
+  // one thread per 16-byte vector of the patch matrix: consecutive threads write consecutive vectors and read
+  // consecutive runs of the same input row
+  const int run = S * C, vecs = seg >> 3, row_len = W * C;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(t % R);
-    long long pix = t / R;
+    const int v = (int)(t % vecs);
+    long long rest = t / vecs;
+    const int r = (int)(rest % R);
+    const long long pix = rest / R;
     const int ow = (int)(pix % Wo);
-    const long long rest = pix / Wo;
+    rest = pix / Wo;
     const int oh = (int)(rest % Ho);
     const int n = (int)(rest / Ho);
     const int ih = oh * sh - pt + r;
-    const int iw0 = ow * sw - pl;
-    __nv_bfloat16* dst = out + (pix * R + r) * seg;
-    const bool row_in = ih >= 0 && ih < H;
-    const T* src = x + ((long long)n * H + (row_in ? ih : 0)) * W * C;
-    for (int v = 0; v < seg; v += 8) {
-      float f[8];
+    const int e0 = v << 3;
+    const int off0 = (ow * sw - pl) * C + e0;  // element offset inside the input row
+    float f[8];
+    if (ih >= 0 && ih < H) {
+      const T* src = x + ((long long)n * H + ih) * row_len;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int e = v + j;
-        const int iw = iw0 + e / C;
-        f[j] = (row_in && e < run && iw >= 0 && iw < W) ? to_f32<T>(src[(long long)iw0 * C + e]) : 0.f;
+        const int off = off0 + j;
+        f[j] = (e0 + j < run && off >= 0 && off < row_len) ? to_f32<T>(src[off]) : 0.f;
       }
-      *reinterpret_cast<bf16x8*>(dst + v) = pack8(f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
     }
+    *reinterpret_cast<bf16x8*>(out + t * 8) = pack8(f);
   }
 }
 }  // namespace
@@ -640,9 +914,9 @@ KB_API int kb200_im2col_rows(const void* x, void* out, int N, int H, int W, int 
     kb200_set_error("im2col_rows: seg must be a multiple of 8 and at least S*C");
     return -2;
   }
-  const long long total = (long long)N * Ho * Wo * R;
+  const long long total = (long long)N * Ho * Wo * R * (seg / 8);
   if (total <= 0) return 0;
-  const unsigned grid = (unsigned)((total + 255) / 256 < 148LL * 16 ? (total + 255) / 256 : 148LL * 16);
+  const unsigned grid = (unsigned)((total + 255) / 256 < 148LL * 32 ? (total + 255) / 256 : 148LL * 32);
   if (dtype == 1)
     im2col_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, N, H, W, C, Ho, Wo, R, S, sh, sw, pt, pl, seg, total);
   else

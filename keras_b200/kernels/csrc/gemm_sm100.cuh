@@ -236,7 +236,9 @@ __device__ __forceinline__ void store_rows_tma(uint32_t tmem_row, int ncols, int
       }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
-    ++stores;
+    // the staging buffers alternate per committed store group: `wait_group.read 1` above only protects the buffer of
+    // the group before last, so a chunk that issued no store must not advance the buffer index
+    if (row0 < p.M) ++stores;
   }
 }
 

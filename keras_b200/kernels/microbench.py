@@ -8,6 +8,8 @@
     python -m keras_b200.kernels.microbench pool --batch 256
     python -m keras_b200.kernels.microbench norm --rows 16384 --channels 768
     python -m keras_b200.kernels.microbench xent --rows 16384 --channels 50257
+    python -m keras_b200.kernels.microbench conv --batch 256            (every ResNet-50 convolution shape)
+    python -m keras_b200.kernels.microbench conv --batch 32 --case 5    (one shape)
 
 Each prints one JSON line per case: time (median of ``--iters`` after ``--warmup``), achieved TFLOP/s or GB/s and the
 fraction of the measured peak (``MEASURED_PEAKS.json`` beside the package's parent directory when present, else the
@@ -245,9 +247,75 @@ def bench_xent(args, flush):
              "frac_of_peak": (fb + bb) / t_fb / 1e6 / bw, "peak": src}]
 
 
+# ResNet-50 v1 convolution shapes at 224x224 (keras/src/applications/resnet.py:219-273): (H, Cin, Cout, k, stride, count per step)
+RESNET50_CONVS = [
+    (224, 3, 64, 7, 2, 1),
+    (56, 64, 64, 1, 1, 1), (56, 64, 64, 3, 1, 3), (56, 64, 256, 1, 1, 4), (56, 256, 64, 1, 1, 2),
+    (56, 256, 128, 1, 2, 1), (28, 128, 128, 3, 1, 4), (28, 128, 512, 1, 1, 4), (56, 256, 512, 1, 2, 1), (28, 512, 128, 1, 1, 3),
+    (28, 512, 256, 1, 2, 1), (14, 256, 256, 3, 1, 6), (14, 256, 1024, 1, 1, 6), (28, 512, 1024, 1, 2, 1), (14, 1024, 256, 1, 1, 5),
+    (14, 1024, 512, 1, 2, 1), (7, 512, 512, 3, 1, 3), (7, 512, 2048, 1, 1, 3), (14, 1024, 2048, 1, 2, 1), (7, 2048, 512, 1, 1, 2),
+]
+
+
+def bench_conv(args, flush):
+    """Forward / input-gradient / weight-gradient time of each shape on the tcgen05 kernel and on the library (cuDNN)."""
+    import torch.nn.functional as F
+
+    from keras_b200.kernels import conv as kconv
+
+    peak, _, src = _peaks()
+    N = args.batch
+    cases = RESNET50_CONVS if args.case < 0 else [RESNET50_CONVS[args.case]]
+    totals = {"ours": 0.0, "library": 0.0}
+    for (H, Cin, Cout, k, s, count) in cases:
+        stem = Cin < 8
+        x = torch.randn(N, H, H, Cin, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(k, k, Cin, Cout, device="cuda") / (k * k * Cin) ** 0.5).to(torch.bfloat16)
+        padding = (3, 3) if stem else "same"
+        xg = x.clone().requires_grad_(not stem)
+        wg = w.clone().requires_grad_(True)
+        y = kconv.conv(xg, wg, (s, s), padding, "channels_last", (1, 1))
+        assert y is not None
+        dy = torch.randn_like(y)
+        xc = x.permute(0, 3, 1, 2).requires_grad_(not stem)  # channels-last memory format view for the library
+        wc = w.permute(3, 2, 0, 1).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        pad = 3 if stem else (k // 2 if s == 1 else 0)
+        yl = F.conv2d(xc, wc, stride=s, padding=pad)
+        dyl = dy.permute(0, 3, 1, 2)
+        if args.once:
+            kconv.conv(x, w, (s, s), padding, "channels_last", (1, 1))
+            y.backward(dy)
+            torch.cuda.synchronize()
+            return
+
+        def ours_fwd():
+            kconv.conv(x, w, (s, s), padding, "channels_last", (1, 1))
+
+        def ours_bwd():
+            y.backward(dy, retain_graph=True)
+
+        def lib_fwd():
+            F.conv2d(xc.detach(), wc.detach(), stride=s, padding=pad)
+
+        def lib_bwd():
+            yl.backward(dyl, retain_graph=True)
+
+        t_of, t_ob = _time(ours_fwd, args.iters, args.warmup, flush), _time(ours_bwd, args.iters, args.warmup, flush)
+        t_lf, t_lb = _time(lib_fwd, args.iters, args.warmup, flush), _time(lib_bwd, args.iters, args.warmup, flush)
+        Ho = y.shape[1]
+        flops = 2.0 * N * Ho * Ho * Cout * k * k * Cin
+        nb = 1 if stem else 2
+        totals["ours"] += count * (t_of + t_ob)
+        totals["library"] += count * (t_lf + t_lb)
+        yield {"kernel": "conv_tcgen05", "shape": f"{N}x{H}x{H}x{Cin}->{Cout} k{k} s{s}", "count": count, "fwd_ms": round(t_of, 4), "bwd_ms": round(t_ob, 4),
+               "library_fwd_ms": round(t_lf, 4), "library_bwd_ms": round(t_lb, 4), "fwd_tflops": round(flops / t_of / 1e9, 1),
+               "bwd_tflops": round(nb * flops / t_ob / 1e9, 1), "fwd_frac_of_%s_peak" % src: round(flops / t_of / 1e9 / peak, 3)}
+    yield {"kernel": "conv_tcgen05", "sum_over_step_ms": {k_: round(v, 3) for k_, v in totals.items()}}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "optim", "bn", "pool", "norm", "xent"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "optim", "bn", "pool", "norm", "xent", "conv"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -260,10 +328,11 @@ def main():
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--case", type=int, default=-1)
     ap.add_argument("--once", action="store_true")
     args = ap.parse_args()
     flush = torch.zeros(96 * 1024 * 1024, device="cuda")  # 384 MB > 126 MB L2
-    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "optim": bench_optim, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent}[args.what](args, flush):
+    for row in {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "optim": bench_optim, "bn": bench_bn, "pool": bench_pool, "norm": bench_norm, "xent": bench_xent, "conv": bench_conv}[args.what](args, flush):
         print(json.dumps(row))
 
 
