@@ -47,7 +47,11 @@ class _ShadowRead(torch.autograd.Function):
 
 
 def attach(variables):
-    """Create shadows for fp32 CUDA variables that are read with autocast."""
+    """Create shadows for fp32 CUDA variables that are read with autocast.
+
+    A shadow remembers the version counter of its parameter: any in-place torch update of the parameter (an unfused
+    optimizer, ``assign``, weight loading) is noticed at the next read and the shadow is refreshed with one cast; the
+    fused optimizer kernels write parameter and shadow together through raw pointers and leave the counter alone."""
     from keras_b200.kernels import ops
 
     for v in variables:
@@ -57,20 +61,42 @@ def attach(variables):
         sh = torch.empty_like(p, dtype=torch.bfloat16)
         ops.cast_f32_to_bf16(p.detach().reshape(-1), sh.reshape(-1))
         v._shadow_tensor = sh
-        state = {"dirty": False}
+        state = {"version": p._version, "ptr": p.data_ptr()}
 
         def read(value, _v=v, _sh=sh, _state=state):
-            if _state["dirty"]:
-                ops.cast_f32_to_bf16(_v._value.detach().reshape(-1), _sh.reshape(-1))
-                _state["dirty"] = False
+            p_now = _v._value
+            if p_now._version != _state["version"] or p_now.data_ptr() != _state["ptr"]:
+                if p_now.shape != _sh.shape or not p_now.is_cuda:
+                    return value.to(torch.bfloat16)
+                ops.cast_f32_to_bf16(p_now.detach().reshape(-1), _sh.reshape(-1))
+                _state["version"], _state["ptr"] = p_now._version, p_now.data_ptr()
             if value.requires_grad and torch.is_grad_enabled():
                 return _ShadowRead.apply(value, _sh)
             return _sh
 
         def invalidate(_state=state):
-            _state["dirty"] = True
+            _state["version"] = -1
 
         v._shadow = (torch.bfloat16, read, invalidate)
+
+
+def attach_for_model(model, variables):
+    """Attach shadows when ``model`` computes in bfloat16 on fp32 variables (``mixed_bfloat16``); switch off with
+    ``KERAS_B200_SHADOW_WEIGHTS=0``."""
+    import os
+
+    if os.environ.get("KERAS_B200_SHADOW_WEIGHTS", "1") == "0" or not variables:
+        return
+    if getattr(model, "_shadows_checked", None) == tuple(id(v) for v in variables):
+        return
+    model._shadows_checked = tuple(id(v) for v in variables)
+    try:
+        mixed = any(getattr(layer, "compute_dtype", None) == "bfloat16" and getattr(layer, "variable_dtype", None) == "float32"
+                    for layer in model._flatten_layers())
+    except Exception:
+        mixed = False
+    if mixed:
+        attach(variables)
 
 
 def detach(variables):

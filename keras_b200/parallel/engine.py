@@ -103,6 +103,10 @@ class DataParallelEngine:
             self.sync_variables(model)
         arena = self._gradient_arena(trainable_weights)
         arena.bind()
+        if arena.flat.is_cuda:
+            from keras_b200.kernels import shadow
+
+            shadow.attach_for_model(model, trainable_weights)
         loss.backward()
         self._after_backward(trainable_weights)
         if self.world > 1:

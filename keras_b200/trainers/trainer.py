@@ -309,6 +309,9 @@ class Trainer:
 
             arena = GradArena(trainable_weights)
             self._grad_arena = arena
+            from keras_b200.kernels import shadow
+
+            shadow.attach_for_model(self, trainable_weights)
         arena.bind()
         return arena
 
@@ -421,135 +424,154 @@ class Trainer:
 
             self._parallel_engine = parallel_engine.make_engine(dist, self)
 
-    # -- fit -----------------------------------------------------------------------------
+    # -- step loops ----------------------------------------------------------------------
+    def _stager(self):
+        from keras_b200.trainers.device_stager import DeviceStager
+
+        stager = getattr(self, "_device_stager", None)
+        if stager is None or stager.device != get_device():
+            stager = self._device_stager = DeviceStager()
+        return stager
+
+    def _drive(self, epoch_iterator, run_group, on_begin, on_end, stop_flag):
+        """Run one epoch of step groups with one group of look-ahead.
+
+        The kernels of group i are launched first; only then group i+1 is pulled from the data adapter, which also issues
+        its host-to-device copies on the stager's stream, so data loading and the copy overlap the compute of group i.
+        ``on_end`` (callbacks, which may read metrics back and thereby wait for the device) runs after that."""
+        stager = self._stager()
+        groups = iter(epoch_iterator)
+        pending = next(groups, None)
+        logs = {}
+        while pending is not None:
+            first, last, staged = pending
+            on_begin(first)
+            logs = run_group([stager.acquire(b) for b in staged])
+            pending = next(groups, None)
+            on_end(last, logs)
+            if getattr(self, stop_flag):
+                break
+        return logs
+
+    def _epoch_source(self, x, y, sample_weight, batch_size, steps, shuffle, class_weight=None):
+        return EpochIterator(x=x, y=y, sample_weight=sample_weight, batch_size=batch_size, steps_per_epoch=steps, shuffle=shuffle,
+                             class_weight=class_weight, steps_per_execution=self.steps_per_execution, transform=self._stager().stage)
+
+    def _callback_list(self, callbacks, verbose, epochs, steps, history=False):
+        from keras_b200 import callbacks as callbacks_module
+
+        if isinstance(callbacks, callbacks_module.CallbackList):
+            return callbacks
+        return callbacks_module.CallbackList(callbacks, add_history=history, add_progbar=verbose != 0, verbose=verbose, epochs=epochs, steps=steps,
+                                             model=self)
+
     def fit(self, x=None, y=None, batch_size=None, epochs=1, verbose="auto", callbacks=None, validation_split=0.0, validation_data=None,
             shuffle=True, class_weight=None, sample_weight=None, initial_epoch=0, steps_per_epoch=None, validation_steps=None,
             validation_batch_size=None, validation_freq=1):
         self._assert_compile_called("fit")
-        from keras_b200 import callbacks as callbacks_module
-
-        max_epochs = config.max_epochs()
-        if max_epochs and max_epochs < epochs:
-            warnings.warn("Limiting epochs to %d" % max_epochs)
-            epochs = max_epochs
-        self._eval_epoch_iterator = None
+        cap = config.max_epochs()
+        if cap and cap < epochs:
+            warnings.warn("Limiting epochs to %d" % cap)
+            epochs = cap
         if validation_split and validation_data is None:
             from keras_b200.trainers.data_adapters import array_slicing
 
             (x, y, sample_weight), validation_data = array_slicing.train_validation_split((x, y, sample_weight), validation_split=validation_split)
+        validation = None
         if validation_data is not None:
-            val_x, val_y, val_sample_weight = data_adapter_utils.unpack_x_y_sample_weight(validation_data)
-        epoch_iterator = EpochIterator(x=x, y=y, sample_weight=sample_weight, batch_size=batch_size, steps_per_epoch=steps_per_epoch,
-                                       shuffle=shuffle, class_weight=class_weight, steps_per_execution=self.steps_per_execution)
-        self._symbolic_build(iterator=epoch_iterator)
-        epoch_iterator.reset()
-        if not isinstance(callbacks, callbacks_module.CallbackList):
-            callbacks = callbacks_module.CallbackList(callbacks, add_history=True, add_progbar=verbose != 0, verbose=verbose, epochs=epochs,
-                                                      steps=epoch_iterator.num_batches, model=self)
+            validation = data_adapter_utils.unpack_x_y_sample_weight(validation_data)
+        source = self._epoch_source(x, y, sample_weight, batch_size, steps_per_epoch, shuffle, class_weight)
+        self._symbolic_build(iterator=source)
+        source.reset()
+        callbacks = self._callback_list(callbacks, verbose, epochs, source.num_batches, history=True)
         self.stop_training = False
-        training_logs = {}
+        self._eval_epoch_iterator = None
         self.make_train_function()
         callbacks.on_train_begin()
-        initial_epoch = self._initial_epoch or initial_epoch
-        for epoch in range(initial_epoch, epochs):
+        last_logs = {}
+        for epoch in range(self._initial_epoch or initial_epoch, epochs):
             self.reset_metrics()
             callbacks.on_epoch_begin(epoch)
-            logs = {}
-            for begin_step, end_step, data in epoch_iterator:
-                callbacks.on_train_batch_begin(begin_step)
-                logs = self.train_function(data)
-                callbacks.on_train_batch_end(end_step, logs)
-                if self.stop_training:
-                    break
-            epoch_logs = dict(self._get_metrics_result_or_logs(logs))
-            if validation_data is not None and self._should_eval(epoch, validation_freq):
-                if getattr(self, "_eval_epoch_iterator", None) is None:
-                    self._eval_epoch_iterator = EpochIterator(x=val_x, y=val_y, sample_weight=val_sample_weight,
-                                                              batch_size=validation_batch_size or batch_size,
-                                                              steps_per_execution=self.steps_per_execution, steps_per_epoch=validation_steps, shuffle=False)
-                val_logs = self.evaluate(x=val_x, y=val_y, sample_weight=val_sample_weight, batch_size=validation_batch_size or batch_size,
-                                         steps=validation_steps, callbacks=callbacks, return_dict=True, _use_cached_eval_dataset=True)
-                val_logs = {f"val_{name}": val for name, val in val_logs.items()}
-                epoch_logs.update(val_logs)
-            callbacks.on_epoch_end(epoch, epoch_logs)
-            training_logs = epoch_logs
+            step_logs = self._drive(source, self.train_function, callbacks.on_train_batch_begin, callbacks.on_train_batch_end, "stop_training")
+            self._check_kernel_status()
+            last_logs = dict(self._get_metrics_result_or_logs(step_logs))
+            if validation is not None and self._should_eval(epoch, validation_freq):
+                vx, vy, vw = validation
+                if self._eval_epoch_iterator is None:
+                    self._eval_epoch_iterator = self._epoch_source(vx, vy, vw, validation_batch_size or batch_size, validation_steps, False)
+                scores = self.evaluate(x=vx, y=vy, sample_weight=vw, batch_size=validation_batch_size or batch_size, steps=validation_steps,
+                                       callbacks=callbacks, return_dict=True, _use_cached_eval_dataset=True)
+                last_logs.update({"val_" + name: value for name, value in scores.items()})
+            callbacks.on_epoch_end(epoch, last_logs)
             if self.stop_training:
                 break
         if isinstance(self.optimizer, optimizers.Optimizer) and epochs > 0:
             self.optimizer.finalize_variable_values(self.trainable_weights)
-        if getattr(self, "_eval_epoch_iterator", None) is not None:
-            del self._eval_epoch_iterator
-        callbacks.on_train_end(logs=training_logs)
+        self._eval_epoch_iterator = None
+        callbacks.on_train_end(logs=last_logs)
         return self.history
 
     def evaluate(self, x=None, y=None, batch_size=None, verbose="auto", sample_weight=None, steps=None, callbacks=None, return_dict=False, **kwargs):
         self._assert_compile_called("evaluate")
-        from keras_b200 import callbacks as callbacks_module
-
-        use_cached_eval_dataset = kwargs.pop("_use_cached_eval_dataset", False)
+        cached = kwargs.pop("_use_cached_eval_dataset", False)
         if kwargs:
             raise ValueError(f"Arguments not recognized: {kwargs}")
-        if use_cached_eval_dataset:
-            epoch_iterator = self._eval_epoch_iterator
-        else:
-            epoch_iterator = EpochIterator(x=x, y=y, sample_weight=sample_weight, batch_size=batch_size, steps_per_epoch=steps, shuffle=False,
-                                           steps_per_execution=self.steps_per_execution)
-        self._symbolic_build(iterator=epoch_iterator)
-        epoch_iterator.reset()
-        if not isinstance(callbacks, callbacks_module.CallbackList):
-            callbacks = callbacks_module.CallbackList(callbacks, add_progbar=verbose != 0, verbose=verbose, epochs=1,
-                                                      steps=epoch_iterator.num_batches, model=self)
+        source = self._eval_epoch_iterator if cached else self._epoch_source(x, y, sample_weight, batch_size, steps, False)
+        self._symbolic_build(iterator=source)
+        source.reset()
+        callbacks = self._callback_list(callbacks, verbose, 1, source.num_batches)
         self.make_test_function()
         self.stop_evaluating = False
         callbacks.on_test_begin()
-        logs = {}
         self.reset_metrics()
-        for begin_step, end_step, data in epoch_iterator:
-            callbacks.on_test_batch_begin(begin_step)
-            logs = self.test_function(data)
-            callbacks.on_test_batch_end(end_step, logs)
-            if self.stop_evaluating:
-                break
-        logs = pythonify_logs(self._get_metrics_result_or_logs(logs))
+        step_logs = self._drive(source, self.test_function, callbacks.on_test_batch_begin, callbacks.on_test_batch_end, "stop_evaluating")
+        self._check_kernel_status()
+        logs = pythonify_logs(self._get_metrics_result_or_logs(step_logs))
         callbacks.on_test_end(logs)
-        if return_dict:
-            return logs
-        return self._flatten_metrics_in_order(logs)
+        return logs if return_dict else self._flatten_metrics_in_order(logs)
 
     def predict(self, x, batch_size=None, verbose="auto", steps=None, callbacks=None):
-        from keras_b200 import callbacks as callbacks_module
+        from keras_b200.core.tensor import convert_to_numpy
 
-        epoch_iterator = EpochIterator(x=x, batch_size=batch_size, steps_per_epoch=steps, shuffle=False, steps_per_execution=self.steps_per_execution)
+        source = self._epoch_source(x, None, None, batch_size, steps, False)
         if not all(layer.built for layer in self._flatten_layers()):
-            for _, _, data in epoch_iterator:
-                data_batch = data[0]
-                self._symbolic_build(data_batch=data_batch)
+            for _, _, staged in source:
+                self._symbolic_build(data_batch=self._stager().acquire(staged[0]))
                 break
-            epoch_iterator.reset()
-        if not isinstance(callbacks, callbacks_module.CallbackList):
-            callbacks = callbacks_module.CallbackList(callbacks, add_progbar=verbose != 0, verbose=verbose, epochs=1,
-                                                      steps=epoch_iterator.num_batches, model=self)
+            source.reset()
+        callbacks = self._callback_list(callbacks, verbose, 1, source.num_batches)
         self.make_predict_function()
         self.stop_predicting = False
         callbacks.on_predict_begin()
-        outputs = None
-        for begin_step, end_step, data in epoch_iterator:
-            callbacks.on_predict_batch_begin(begin_step)
-            batch_outputs = self.predict_function(data)
-            host = tree.map_structure(lambda t: t.detach().to("cpu", non_blocking=False) if isinstance(t, torch.Tensor) else t, batch_outputs)
-            if outputs is None:
-                outputs = tree.map_structure(lambda t: [t], host)
-            else:
-                tree.map_structure_up_to(host, lambda acc, t: acc.append(t), outputs, host)
-            callbacks.on_predict_batch_end(end_step, {"outputs": batch_outputs})
-            if self.stop_predicting:
-                break
-        callbacks.on_predict_end()
-        if outputs is None:
-            return None
-        from keras_b200.core.tensor import convert_to_numpy
+        collected = []  # one host copy of the outputs per step group, concatenated at the end
 
-        return tree.map_structure_up_to(host, lambda parts: convert_to_numpy(torch.cat(parts, dim=0)) if isinstance(parts[0], torch.Tensor) else parts, outputs)
+        def run(batches):
+            outputs = self.predict_function(batches)
+            collected.append(tree.map_structure(lambda t: t.detach().to("cpu") if isinstance(t, torch.Tensor) else t, outputs))
+            return {"outputs": outputs}
+
+        self._drive(source, run, callbacks.on_predict_batch_begin, callbacks.on_predict_batch_end, "stop_predicting")
+        self._check_kernel_status()
+        callbacks.on_predict_end()
+        if not collected:
+            return None
+
+        def join(*parts):
+            return convert_to_numpy(torch.cat(parts, dim=0)) if isinstance(parts[0], torch.Tensor) else list(parts)
+
+        return tree.map_structure(join, *collected)
+
+    def _check_kernel_status(self):
+        """Surface device-side time-outs (bounded waits that ran out in a collective or a tensor-core pipeline) before any
+        callback can checkpoint weights that were updated from incomplete results."""
+        engine = getattr(self, "_parallel_engine", None)
+        if engine is not None and hasattr(engine, "check"):
+            engine.check(wait=True)
+        if get_device().type == "cuda":
+            from keras_b200.kernels import attention as kattention, gemm as kgemm
+
+            kgemm.check_errors()
+            kattention.check_errors()
 
     def train_on_batch(self, x, y=None, sample_weight=None, class_weight=None, return_dict=False):
         self._assert_compile_called("train_on_batch")
@@ -560,6 +582,7 @@ class Trainer:
         data = (x, y, sample_weight)
         self._symbolic_build(data_batch=data)
         self.make_train_function()
+        self.reset_metrics()
         logs = self.train_function([data])
         logs = pythonify_logs(logs)
         if return_dict:
@@ -571,6 +594,7 @@ class Trainer:
         data = (x, y, sample_weight)
         self._symbolic_build(data_batch=data)
         self.make_test_function()
+        self.reset_metrics()
         logs = pythonify_logs(self.test_function([data]))
         if return_dict:
             return logs
@@ -645,6 +669,10 @@ class Trainer:
                     return KerasTensor(tuple(v.shape), dtype=d)
                 return v
 
+            from keras_b200.trainers.device_stager import Staged
+
+            if isinstance(data_batch, Staged):
+                data_batch = data_batch.data
             data_batch = tree.map_structure(to_spec, data_batch)
             x, y, sample_weight = data_adapter_utils.unpack_x_y_sample_weight(data_batch)
             try:
