@@ -5,6 +5,7 @@ flow runs as Python loops (eager execution); hot training loops are captured in 
 the trainer instead of by a tracing compiler.
 """
 
+import ml_dtypes
 import numpy as np
 import torch
 
@@ -27,20 +28,35 @@ def cast(x, dtype):
 
 @op()
 def saturate_cast(x, dtype):
+    """Cast after clipping to the value range both dtypes share.  A limit that the input dtype cannot represent exactly
+    (float32 -> int32: 2147483647) is moved one step towards zero, other limits are used as they are
+    (keras/src/ops/core.py:950-990)."""
     x = _t(x)
     td = to_torch_dtype(dtype)
-    if td.is_floating_point or td == torch.bool:
-        return x.to(td)
-    info = torch.iinfo(td)
-    if x.dtype.is_floating_point:
-        lo = float(info.min)
-        hi = float(np.nextafter(np.float64(info.max), 0)) if x.dtype == torch.float64 else float(np.nextafter(np.float32(info.max), np.float32(0)))
-        return torch.clip(x, lo, hi).to(td)
+    out_name, in_name = standardize_dtype(dtype), standardize_dtype(x.dtype)
+
+    def limits(name):
+        if name == "bool":
+            return 0, 1
+        if "int" in name:
+            info = ml_dtypes.iinfo(name)
+            return int(info.min), int(info.max)
+        info = ml_dtypes.finfo(name)
+        return float(info.min), float(info.max)
+
+    (in_lo, in_hi), (out_lo, out_hi) = limits(in_name), limits(out_name)
+    np_in = np.dtype(in_name) if in_name != "bfloat16" else ml_dtypes.bfloat16
+    lo = np.maximum(in_lo, out_lo).astype(np_in)
+    if lo < out_lo:
+        lo = np.nextafter(lo, 0, dtype=np_in)
+    hi = np.minimum(in_hi, out_hi).astype(np_in)
+    if hi > out_hi:
+        hi = np.nextafter(hi, 0, dtype=np_in)
     if x.dtype == torch.bool:
         return x.to(td)
-    xinfo = torch.iinfo(x.dtype)
-    lo, hi = max(info.min, xinfo.min), min(info.max, xinfo.max)
-    return torch.clip(x, lo, hi).to(td)
+    lo_v = float(lo) if x.dtype.is_floating_point else int(lo)
+    hi_v = float(hi) if x.dtype.is_floating_point else int(hi)
+    return torch.clip(x, lo_v, hi_v).to(td)
 
 
 @keras_export("keras.ops.convert_to_tensor")

@@ -455,10 +455,12 @@ def gaussian_blur(images, kernel_size=(3, 3), sigma=(1.0, 1.0), data_format=None
     C = xf.shape[1]
     ks = (kernel_size, kernel_size) if isinstance(kernel_size, int) else tuple(kernel_size)
     sg = (sigma, sigma) if isinstance(sigma, (int, float)) else tuple(float(s) for s in (sigma.tolist() if isinstance(sigma, torch.Tensor) else sigma))
-    ky = _gauss_kernel1d(ks[0], sg[0], xf.dtype, xf.device)
-    kx = _gauss_kernel1d(ks[1], sg[1], xf.dtype, xf.device)
+    # entry 0 of `kernel_size` / `sigma` runs along the width, entry 1 along the height
+    # (keras/src/backend/torch/image.py:859-862 builds outer(g(size[1], sigma[1]), g(size[0], sigma[0])))
+    ky = _gauss_kernel1d(ks[1], sg[1], xf.dtype, xf.device)
+    kx = _gauss_kernel1d(ks[0], sg[0], xf.dtype, xf.device)
     k2 = torch.outer(ky, kx).expand(C, 1, -1, -1)
-    pads = ((ks[1] - 1) // 2, ks[1] - 1 - (ks[1] - 1) // 2, (ks[0] - 1) // 2, ks[0] - 1 - (ks[0] - 1) // 2)
+    pads = ((ks[0] - 1) // 2, ks[0] - 1 - (ks[0] - 1) // 2, (ks[1] - 1) // 2, ks[1] - 1 - (ks[1] - 1) // 2)
     y = F.conv2d(F.pad(xf, pads), k2, groups=C)
     return restore(y.to(ori))
 
@@ -533,9 +535,9 @@ def sobel_edges(images, data_format=None):
     C = x.shape[1]
     kh = torch.tensor([[-1, -2, -1], [0, 0, 0], [1, 2, 1]], dtype=x.dtype, device=x.device)
     kw = kh.t()
-    xp = F.pad(x, (1, 1, 1, 1), mode="reflect")
-    gy = F.conv2d(xp, kh.expand(C, 1, 3, 3), groups=C)
-    gx = F.conv2d(xp, kw.expand(C, 1, 3, 3), groups=C)
+    # zero padding at the border, as keras/src/backend/torch/image.py:1196-1236
+    gy = F.conv2d(x, kh.expand(C, 1, 3, 3), padding=1, groups=C)
+    gx = F.conv2d(x, kw.expand(C, 1, 3, 3), padding=1, groups=C)
     out = torch.stack([restore(gy), restore(gx)], dim=-1)
     return out
 

@@ -144,7 +144,7 @@ def matrix_power(x, n):
 
 @op("linalg")
 def matrix_rank(x, tol=None):
-    return torch.linalg.matrix_rank(_floatize(x), tol=tol).to(torch.int32)
+    return torch.linalg.matrix_rank(_floatize(x), atol=tol).to(torch.int32)
 
 
 def jvp(fun, primals, tangents, has_aux=False):

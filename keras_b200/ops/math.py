@@ -61,8 +61,8 @@ def top_k(x, k, sorted=True):
     x = _t(x)
     if x.dtype == torch.bool:
         x = x.to(torch.uint8)
-    r = torch.topk(x, k, sorted=True)
-    return r.values, r.indices.to(torch.int32)
+    values, indices = torch.sort(x, dim=-1, descending=True, stable=True)
+    return values[..., :k], indices[..., :k]
 
 
 @op()

@@ -87,6 +87,8 @@ swish = silu
 @op("nn")
 def squareplus(x, b=4):
     x = _floatize(x)
+    if not isinstance(b, (int, float)):
+        b = _t(b).to(x.dtype)
     return (x + torch.sqrt(x * x + b)) / 2
 
 
@@ -140,7 +142,10 @@ def glu(x, axis=-1):
 
 @op("nn")
 def hard_tanh(x):
-    return F.hardtanh(_floatize(x), min_val=-1.0, max_val=1.0)
+    x = _t(x)
+    if not x.dtype.is_floating_point:
+        return torch.clamp(x, min=-1, max=1)  # integer inputs keep their dtype
+    return F.hardtanh(x, min_val=-1.0, max_val=1.0)
 
 
 @op("nn")
@@ -186,16 +191,18 @@ def log_softmax(x, axis=-1):
 
 @op("nn")
 def sparsemax(x, axis=-1):
+    # The threshold follows keras/src/backend/torch/nn.py:199-218 term by term: it is built from the sum of the running
+    # sums over the support (not from the running sum at the support's size), and checkpoints trained against that
+    # activation expect exactly this function.
     x = _floatize(x)
     z, _ = torch.sort(x, dim=axis, descending=True)
-    k = torch.arange(1, x.shape[axis] + 1, device=x.device, dtype=x.dtype)
+    running = torch.cumsum(z, dim=axis)
     shape = [1] * x.ndim
     shape[axis] = -1
-    k = k.reshape(shape)
-    cs = torch.cumsum(z, dim=axis)
-    support = (1 + k * z) > cs
-    k_z = torch.sum(support.to(x.dtype), dim=axis, keepdim=True)
-    tau = (torch.sum(torch.where(support, z, torch.zeros_like(z)), dim=axis, keepdim=True) - 1) / k_z
+    rank = torch.arange(1, x.shape[axis] + 1, device=x.device, dtype=x.dtype).reshape(shape)
+    support = z - (running - 1) / rank > 0
+    size = torch.sum(support, dim=axis, keepdim=True)
+    tau = (torch.sum(torch.where(support, running, torch.zeros_like(running)), dim=axis, keepdim=True) - 1) / size
     return torch.clamp(x - tau, min=0)
 
 
@@ -378,44 +385,37 @@ def conv_transpose(inputs, kernel, strides=1, padding="valid", output_padding=No
     # Keras transposed kernel: (*spatial, out, in) → torch (in, out, *spatial)
     kt = k.permute(k.ndim - 1, k.ndim - 2, *range(nsp))
     opad = None if output_padding is None else _tuple(output_padding, nsp)
-    tpads, topads = [], []
+    # The full transposed convolution (no padding) has (in - 1) * stride + eff samples per axis.  Keras semantics
+    # (keras/src/backend/common/backend_utils.py:8-50, 215-268) select a window of it that is in general not centred:
+    #   valid: everything, plus `output_padding` zeros on the right (default: up to (in - 1) * stride + max(eff, stride));
+    #   same:  `total = stride + eff - 2` samples are dropped (with output_padding: eff + eff % 2 - 2 + output_padding are
+    #          kept back), the larger half on the left but never more than eff - 1.
+    fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[nsp]
+    out = fn(xc, kt, stride=strides, padding=0, output_padding=0, dilation=dilation)
+    mode = padding.lower()
+    if mode not in ("valid", "same"):
+        raise ValueError(f"The `padding` argument must be one of 'valid', 'same'. Received: padding={padding}")
+    grow = []  # zeros to append per axis (left, right), innermost axis first as F.pad wants them
     for i in range(nsp):
         eff = (ksize[i] - 1) * dilation[i] + 1
-        s = strides[i]
-        if padding.lower() == "valid":
-            op_i = (max(s - eff, 0) if opad is None else opad[i])
-            # Keras valid: out = (in-1)*s + max(eff, s) (or with explicit output_padding: (in-1)*s+eff+op)
-            if opad is None:
-                tpads.append(0)
-                topads.append(max(s - eff, 0))
-            else:
-                tpads.append(0)
-                topads.append(opad[i])
+        s_i = strides[i]
+        if mode == "valid":
+            extra = (max(eff, s_i) - eff) if opad is None else opad[i]
+            keep_left, keep_right = eff - 1, eff - 1 + extra
         else:
-            if opad is None:
-                total = max(eff - s, 0)   # out = in*s
-                lo = total // 2 + total % 2 if False else (eff - s + 1) // 2 if eff > s else 0
-                # choose pad so that (in-1)*s - 2p + eff + op = in*s
-                p = max(eff - s, 0) // 2 + (max(eff - s, 0) % 2)
-                o = (s - eff + 2 * p)
-                tpads.append(p)
-                topads.append(o)
-            else:
-                p = eff // 2
-                tpads.append(p)
-                topads.append(opad[i])
-    fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[nsp]
-    extra = [max(o - (max(strides[i], dilation[i]) - 1), 0) for i, o in enumerate(topads)]
-    if any(e > 0 for e in extra):
-        # torch requires output_padding < max(stride, dilation); pad the result instead
-        base = [o - e for o, e in zip(topads, extra)]
-        out = fn(xc, kt, stride=strides, padding=tuple(tpads), output_padding=tuple(base), dilation=dilation)
+            kept = (s_i + eff - 2) if opad is None else (eff + eff % 2 - 2 + opad[i])
+            keep_left = min(kept // 2 + kept % 2, eff - 1)
+            keep_right = kept - keep_left
+        drop_left, drop_right = (eff - 1) - keep_left, (eff - 1) - keep_right
+        axis = 2 + i
+        length = out.shape[axis]
+        out = out.narrow(axis, max(drop_left, 0), length - max(drop_left, 0) - max(drop_right, 0))
+        grow.append((max(-drop_left, 0), max(-drop_right, 0)))
+    if any(l or r for l, r in grow):
         flat = []
-        for e in reversed(extra):
-            flat.extend([0, e])
+        for l, r in reversed(grow):
+            flat.extend([l, r])
         out = F.pad(out, flat)
-    else:
-        out = fn(xc, kt, stride=strides, padding=tuple(tpads), output_padding=tuple(topads), dilation=dilation)
     return _from_cf(out, data_format)
 
 

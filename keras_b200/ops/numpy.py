@@ -1064,7 +1064,7 @@ def full(shape, fill_value, dtype=None):
         fv = _t(fill_value)
         d = to_torch_dtype(dtype) if dtype is not None else fv.dtype
         return torch.broadcast_to(fv.to(d), shape).clone()
-    d = to_torch_dtype(dtype) if dtype is not None else to_torch_dtype(result_type(_dt(fill_value)))
+    d = to_torch_dtype(dtype if dtype is not None else config.floatx())  # no dtype: floatx, whatever the scalar's type
     return torch.full(shape, fill_value, dtype=d, device=get_device())
 
 
@@ -1264,10 +1264,7 @@ def squeeze(x, axis=None):
     if axis is None:
         return torch.squeeze(x)
     axes = (axis,) if isinstance(axis, int) else tuple(axis)
-    for a in axes:
-        if x.shape[a] != 1:
-            raise ValueError(f"Cannot squeeze axis={a}, because the dimension is not 1. Received: x.shape={tuple(x.shape)}")
-    return torch.squeeze(x, dim=axes)
+    return torch.squeeze(x, dim=axes)  # an axis whose extent is not 1 is left alone (eager torch semantics)
 
 
 @op("numpy")
@@ -1581,18 +1578,22 @@ def argsort(x, axis=-1):
 
 @op("numpy")
 def argpartition(x, kth, axis=-1):
-    x = _t(x)
-    if x.dtype == torch.bool:
-        x = x.to(torch.uint8)
-    x = torch.movedim(x, axis, -1)
+    # Same selection steps as keras/src/backend/torch/numpy.py:2421-2452 (values are compared as int32, the remaining
+    # indices come from a top-k over a 0/1 marker), so that ties and the order inside both halves agree with it.
+    x = _t(x).to(torch.int32)
+    if axis is None:
+        x, axis, flat = x.flatten(), 0, True
+    else:
+        flat = False
+    x = torch.transpose(x, axis, -1)
     n = x.shape[-1]
-    kth = kth % n
-    top = torch.topk(-x if x.dtype != torch.uint8 else -(x.to(torch.int32)), kth + 1, dim=-1).indices
-    mask = torch.ones_like(x, dtype=torch.bool).scatter_(-1, top, False)
-    rest = torch.argsort(mask.to(torch.uint8), dim=-1, stable=True)[..., kth + 1:]
-    # order inside `top` is ascending by value: last element is the kth smallest
-    out = torch.cat([top, rest], dim=-1)
-    return torch.movedim(out, -1, axis).to(torch.int32)
+    lowest = torch.topk(-x, kth + 1).indices
+    marker = torch.ones_like(x, dtype=torch.int32).scatter_(-1, lowest, 0)
+    others = torch.topk(marker, n - kth - 1).indices
+    out = torch.cat([lowest, others], dim=-1)
+    if flat:
+        return out.to(torch.int32)
+    return torch.transpose(out, -1, axis).to(torch.int32)
 
 
 @op("numpy")
@@ -1626,7 +1627,7 @@ def bincount(x, weights=None, minlength=0, sparse=False):
         out = torch.stack(rows)
     else:
         out = torch.bincount(x.long(), weights=w, minlength=minlength)
-    return out.to(torch.int32) if w is None else out
+    return out.to(torch.int32) if w is None else out.to(w.dtype)
 
 
 @op("numpy")
@@ -1713,7 +1714,7 @@ def histogram(x, bins=10, range=None):
         lo, hi = range
     xc = x.cpu().to(torch.float32)
     hist, edges = torch.histogram(xc, bins=bins, range=(float(lo), float(hi)))
-    return hist.to(torch.int32).to(x.device), edges.to(x.dtype).to(x.device)
+    return hist.to(x.dtype).to(x.device), edges.to(x.dtype).to(x.device)
 
 
 @op("numpy")
@@ -1725,7 +1726,7 @@ def unravel_index(indices, shape):
 @op("numpy")
 def view(x, dtype=None):
     x = _t(x)
-    return x.view(to_torch_dtype(dtype)) if dtype is not None else x
+    return x.view(to_torch_dtype(dtype if dtype is not None else config.floatx()))
 
 
 @op("numpy")
