@@ -60,7 +60,7 @@ class DTypePolicy:
                 from keras_b200.core.dtypes import to_torch_dtype
 
                 td = to_torch_dtype(dtype)
-                if x.dtype != td:
+                if x.dtype != td and td.is_floating_point:
                     x = x.to(td)
             from keras_b200.core.tensor import get_device
 

@@ -150,9 +150,16 @@ def _wrap_build(build_fn):
     def build(self, *args, **kwargs):
         if self.built and getattr(self, "_build_lock_shapes", None) is not None and not getattr(self, "_allow_rebuild", False):
             return
-        with _StateUnlock(self), self._open_name_scope():
-            self._path = current_path()
-            build_fn(self, *args, **kwargs)
+        depth = self.__dict__.get("_build_depth", 0)
+        object.__setattr__(self, "_build_depth", depth + 1)
+        try:
+            with _StateUnlock(self), self._open_name_scope():
+                self._path = current_path()
+                build_fn(self, *args, **kwargs)
+        finally:
+            object.__setattr__(self, "_build_depth", depth)
+        if depth > 0:
+            return  # a parent class's build called through super(): the outermost build finishes and locks the state
         names = _plan_for(type(self)).build_names
         shapes = dict(zip(names, args))
         shapes.update(kwargs)
@@ -513,7 +520,22 @@ class Layer(Operation):
 
     @property
     def weights(self):
-        return self.trainable_weights + self.non_trainable_weights
+        """Weight variables in layer order: a layer's own trainable then non-trainable variables, followed by those of its
+        sub-layers, depth first (keras/src/layers/layer.py:713-731).  ``get_weights`` / ``set_weights`` use this order, so
+        BatchNormalization contributes gamma, beta, moving_mean, moving_variance in one run."""
+        skip = {id(v) for v in self._all_aux_variables()}
+        out, seen = [], set()
+
+        def walk(layer):
+            for v in layer._trainable_variables + layer._non_trainable_variables:
+                if id(v) not in seen and id(v) not in skip:
+                    seen.add(id(v))
+                    out.append(v)
+            for sub in layer._layers:
+                walk(sub)
+
+        walk(self)
+        return out
 
     @property
     def trainable_weights(self):
@@ -669,7 +691,7 @@ class Layer(Operation):
                 if type(first) is torch.Tensor:
                     if self.autocast and first.dtype.is_floating_point:
                         compute_td = self._compute_torch_dtype()
-                        if first.dtype != compute_td:
+                        if first.dtype != compute_td and compute_td.is_floating_point:
                             args = (first.to(compute_td),) + args[1:]
                 elif not isinstance(first, KerasTensor):
                     args = (self._convert_structure(first),) + args[1:]
@@ -826,7 +848,7 @@ class Layer(Operation):
         if type(x) is torch.Tensor or isinstance(x, KerasTensor):
             if self.autocast and type(x) is torch.Tensor and x.dtype.is_floating_point:
                 td = self._compute_torch_dtype()
-                return x if x.dtype == td else x.to(td)
+                return x if x.dtype == td or not td.is_floating_point else x.to(td)  # never truncate floats to an integer policy
             return x
         policy = self._resolved_policy()
         autocast, dtype = self.autocast, self.input_dtype

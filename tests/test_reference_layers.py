@@ -1,0 +1,150 @@
+"""Layers against the reference: same constructor arguments, the reference's weights transferred with
+``get_weights`` / ``set_weights`` (which also pins the weight order), then forward outputs and the gradient of a
+scalar with respect to the input are compared (CPU, float32)."""
+
+import numpy as np
+import pytest
+import torch
+
+import keras_b200 as keras
+from tests import oracle
+
+
+def _x(shape, seed=0, integer=None):
+    rng = np.random.default_rng(seed)
+    if integer is not None:
+        return rng.integers(0, integer, shape).astype("int32")
+    return rng.normal(size=shape).astype("float32")
+
+
+# (layer class, constructor kwargs, input shapes, call kwargs, integer vocabulary or None)
+LAYERS = [
+    ("Dense", dict(units=5, activation="gelu"), [(3, 7)], {}, None),
+    ("EinsumDense", dict(equation="abc,cde->abde", output_shape=(None, 2, 3), bias_axes="de"), [(2, 4, 6)], {}, None),
+    ("Embedding", dict(input_dim=11, output_dim=4, mask_zero=True), [(3, 5)], {}, 11),
+    ("Conv1D", dict(filters=4, kernel_size=3, padding="causal", dilation_rate=2), [(2, 9, 3)], {}, None),
+    ("Conv2D", dict(filters=4, kernel_size=3, strides=2, padding="same", activation="relu"), [(2, 9, 8, 3)], {}, None),
+    ("Conv3D", dict(filters=2, kernel_size=2, padding="valid"), [(1, 4, 5, 4, 3)], {}, None),
+    ("Conv2D", dict(filters=6, kernel_size=3, groups=3, padding="same"), [(2, 6, 6, 3)], {}, None),
+    ("DepthwiseConv2D", dict(kernel_size=3, depth_multiplier=2, padding="same"), [(2, 6, 7, 3)], {}, None),
+    ("SeparableConv2D", dict(filters=5, kernel_size=3, strides=2, padding="same"), [(2, 8, 8, 3)], {}, None),
+    ("Conv1DTranspose", dict(filters=3, kernel_size=3, strides=2, padding="same"), [(2, 7, 4)], {}, None),
+    ("Conv2DTranspose", dict(filters=3, kernel_size=(3, 2), strides=(2, 3), padding="same"), [(2, 5, 4, 4)], {}, None),
+    ("Conv2DTranspose", dict(filters=3, kernel_size=3, strides=2, padding="valid", output_padding=1), [(2, 5, 4, 4)], {}, None),
+    ("Conv3DTranspose", dict(filters=2, kernel_size=2, strides=2, padding="same"), [(1, 3, 3, 3, 2)], {}, None),
+    ("BatchNormalization", dict(momentum=0.9, epsilon=1e-4), [(4, 5, 5, 3)], dict(training=True), None),
+    ("BatchNormalization", dict(axis=1), [(4, 3, 6)], dict(training=False), None),
+    ("LayerNormalization", dict(axis=(-2, -1)), [(2, 4, 6)], {}, None),
+    ("RMSNormalization", dict(), [(2, 4, 6)], {}, None),
+    ("GroupNormalization", dict(groups=2), [(2, 5, 5, 4)], {}, None),
+    ("UnitNormalization", dict(axis=-1), [(3, 6)], {}, None),
+    ("SpectralNormalization", dict(layer=("Dense", dict(units=5))), [(3, 7)], dict(training=False), None),
+    ("MultiHeadAttention", dict(num_heads=2, key_dim=3, value_dim=4, output_shape=5), [(2, 5, 6), (2, 7, 6)], dict(use_causal_mask=False), None),
+    ("MultiHeadAttention", dict(num_heads=2, key_dim=3), [(2, 6, 6), (2, 6, 6)], dict(use_causal_mask=True), None),
+    ("GroupQueryAttention", dict(head_dim=4, num_query_heads=4, num_key_value_heads=2), [(2, 5, 8), (2, 5, 8)], dict(use_causal_mask=True), None),
+    ("Attention", dict(use_scale=True, score_mode="dot"), [(2, 4, 6), (2, 5, 6)], {}, None),
+    ("AdditiveAttention", dict(), [(2, 4, 6), (2, 5, 6)], {}, None),
+    ("LSTM", dict(units=5, return_sequences=True), [(2, 6, 4)], {}, None),
+    ("GRU", dict(units=5, reset_after=False, return_state=True), [(2, 6, 4)], {}, None),
+    ("SimpleRNN", dict(units=4, go_backwards=True), [(2, 6, 4)], {}, None),
+    ("Bidirectional", dict(layer=("LSTM", dict(units=3, return_sequences=True)), merge_mode="sum"), [(2, 5, 4)], {}, None),
+    ("TimeDistributed", dict(layer=("Dense", dict(units=3))), [(2, 5, 4)], {}, None),
+    ("ConvLSTM2D", dict(filters=2, kernel_size=3, padding="same"), [(1, 3, 5, 5, 2)], {}, None),
+    ("PReLU", dict(shared_axes=[1]), [(2, 4, 5)], {}, None),
+    ("ELU", dict(alpha=0.7), [(3, 5)], {}, None),
+    ("LeakyReLU", dict(negative_slope=0.2), [(3, 5)], {}, None),
+    ("Softmax", dict(axis=(1, 2)), [(2, 3, 4)], {}, None),
+    ("ReLU", dict(max_value=1.0, negative_slope=0.1, threshold=0.2), [(3, 5)], {}, None),
+    ("MaxPooling2D", dict(pool_size=3, strides=2, padding="same"), [(2, 7, 8, 3)], {}, None),
+    ("AveragePooling2D", dict(pool_size=2, strides=1, padding="same"), [(2, 5, 6, 3)], {}, None),
+    ("AveragePooling1D", dict(pool_size=3, strides=2, padding="valid"), [(2, 9, 3)], {}, None),
+    ("MaxPooling3D", dict(pool_size=2), [(1, 4, 4, 4, 2)], {}, None),
+    ("GlobalAveragePooling2D", dict(keepdims=True), [(2, 5, 6, 3)], {}, None),
+    ("GlobalMaxPooling1D", dict(), [(2, 5, 3)], {}, None),
+    ("AdaptiveAveragePooling2D", dict(output_size=(2, 3)), [(2, 7, 8, 3)], {}, None),
+    ("AdaptiveMaxPooling1D", dict(output_size=3), [(2, 8, 3)], {}, None),
+    ("UpSampling2D", dict(size=(2, 3), interpolation="bilinear"), [(2, 3, 4, 2)], {}, None),
+    ("ZeroPadding2D", dict(padding=((1, 2), (0, 3))), [(2, 3, 4, 2)], {}, None),
+    ("Cropping2D", dict(cropping=((1, 0), (1, 1))), [(2, 5, 5, 2)], {}, None),
+    ("Permute", dict(dims=(2, 1, 3)), [(2, 3, 4, 5)], {}, None),
+    ("RepeatVector", dict(n=3), [(2, 5)], {}, None),
+    ("Reshape", dict(target_shape=(-1, 2)), [(3, 4, 5)], {}, None),
+    ("Flatten", dict(), [(2, 3, 4)], {}, None),
+    ("Add", dict(), [(2, 3), (2, 3)], {}, None),
+    ("Concatenate", dict(axis=1), [(2, 3), (2, 4)], {}, None),
+    ("Dot", dict(axes=1, normalize=True), [(2, 4), (2, 4)], {}, None),
+    ("Maximum", dict(), [(2, 3), (2, 3)], {}, None),
+    ("Normalization", dict(mean=[1.0, 2.0, 3.0], variance=[1.0, 4.0, 9.0]), [(4, 3)], {}, None),
+    ("Rescaling", dict(scale=1 / 127.5, offset=-1), [(2, 3)], {}, None),
+    ("CategoryEncoding", dict(num_tokens=6, output_mode="multi_hot"), [(3, 4)], {}, 6),
+    ("Discretization", dict(bin_boundaries=[-0.5, 0.0, 0.5]), [(3, 4)], {}, None),
+    ("Resizing", dict(height=5, width=7, interpolation="bilinear"), [(2, 8, 6, 3)], {}, None),
+    ("CenterCrop", dict(height=4, width=3), [(2, 8, 6, 3)], {}, None),
+    ("Masking", dict(mask_value=0.0), [(2, 4, 3)], {}, None),
+    ("ActivityRegularization", dict(l1=0.1), [(2, 4)], {}, None),
+    ("MelSpectrogram", dict(fft_length=32, sequence_stride=16, num_mel_bins=8, sampling_rate=800), [(2, 128)], {}, None),
+]
+
+
+def _make(k, name, kwargs):
+    kwargs = dict(kwargs)
+    if "layer" in kwargs and isinstance(kwargs["layer"], tuple):
+        inner_name, inner_kwargs = kwargs["layer"]
+        kwargs["layer"] = getattr(k.layers, inner_name)(**inner_kwargs)
+    return getattr(k.layers, name)(**kwargs)
+
+
+def _ids():
+    seen, out = {}, []
+    for name, *_ in LAYERS:
+        seen[name] = seen.get(name, 0) + 1
+        out.append(f"{name}_{seen[name]}")
+    return out
+
+
+@pytest.mark.parametrize("spec", LAYERS, ids=_ids())
+def test_layer_matches_reference(spec):
+    rk = oracle.ref()
+    name, kwargs, shapes, call_kwargs, vocab = spec
+    if not hasattr(rk.layers, name):
+        pytest.skip("layer absent from this reference version")
+    inputs = [_x(s, seed=i, integer=vocab) for i, s in enumerate(shapes)]
+    theirs, ours = _make(rk, name, kwargs), _make(keras, name, kwargs)
+    merging = name in ("Add", "Concatenate", "Dot", "Maximum", "Attention", "AdditiveAttention")
+
+    def run(layer, tensors):
+        if merging:
+            return layer(tensors, **call_kwargs)
+        return layer(*tensors, **call_kwargs)
+
+    expected = run(theirs, [torch.tensor(a) for a in inputs])
+    run(ours, [torch.tensor(a) for a in inputs])  # builds
+    weights = theirs.get_weights()
+    assert [tuple(w.shape) for w in ours.get_weights()] == [tuple(w.shape) for w in weights], "weight order or shapes differ"
+    ours.set_weights(weights)
+    mine = [torch.tensor(a, requires_grad=vocab is None) for a in inputs]
+    got = run(ours, mine)
+    # Discretization: the reference's integer width depends on which of its backends ends up running the layer
+    oracle.assert_same(got, expected, name, rtol=2e-4, atol=2e-5, check_dtype=name != "Discretization")
+    if vocab is None and isinstance(got, torch.Tensor) and got.requires_grad:
+        ref_in = [torch.tensor(a, requires_grad=True) for a in inputs]
+        out_ref = run(theirs, ref_in)
+        probe = torch.tensor(np.random.default_rng(9).normal(size=tuple(got.shape)).astype("float32"))
+        (got * probe).sum().backward()
+        (out_ref * probe).sum().backward()
+        for g_ours, g_ref in zip(mine, ref_in):
+            if g_ref.grad is not None:
+                oracle.assert_same(g_ours.grad, g_ref.grad, name + " input gradient", rtol=5e-4, atol=5e-5)
+
+
+def test_get_weights_order_of_a_model_with_batchnorm():
+    rk = oracle.ref()
+
+    def build(k):
+        return k.Sequential([k.Input((6, 6, 3)), k.layers.Conv2D(4, 3), k.layers.BatchNormalization(), k.layers.ReLU(), k.layers.Flatten(), k.layers.Dense(2)])
+
+    theirs, ours = build(rk), build(keras)
+    assert [w.name for w in ours.weights] == [w.name for w in theirs.weights]
+    ours.set_weights(theirs.get_weights())
+    x = _x((3, 6, 6, 3))
+    oracle.assert_same(ours.predict(x, verbose=0), theirs.predict(x, verbose=0), "predict", rtol=1e-4, atol=1e-5)
