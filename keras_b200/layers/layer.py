@@ -748,8 +748,11 @@ class Layer(Operation):
                     training = None if default is inspect.Parameter.empty else default
             else:
                 ctx.training = training
+            implicit = ()
             if plan.has_training:
                 if not (len(args) > plan.arg_names.index("training") and plan.arg_names.index("training") < plan.n_positional):
+                    if kwargs.get("training") is None:
+                        implicit = ("training",)  # resolved from the context or the default, not chosen by the caller
                     kwargs["training"] = training
             elif "training" in kwargs and not plan.has_var_kw:
                 kwargs.pop("training")
@@ -791,7 +794,9 @@ class Layer(Operation):
                     global_state.set_global_attribute("autocast_scope", _NO_AUTOCAST)
                 try:
                     if symbolic:
-                        outputs = self._symbolic_call(*args, **kwargs)
+                        # a graph node remembers only what the caller chose: an implicit `training` stays open so that the
+                        # model's own call can set it later
+                        outputs = self._symbolic_call(*args, _implicit=implicit, **kwargs) if implicit else self._symbolic_call(*args, **kwargs)
                     else:
                         outputs = self._eager_call(*args, **kwargs)
                 finally:
@@ -863,9 +868,10 @@ class Layer(Operation):
             return self.rematerialized_call(self.call, *args, **kwargs)(*args, **kwargs)
         return self.call(*args, **kwargs)
 
-    def _symbolic_call(self, *args, **kwargs):
+    def _symbolic_call(self, *args, _implicit=(), **kwargs):
         outputs = self.compute_output_spec(*args, **kwargs)
-        Node(operation=self, call_args=args, call_kwargs=kwargs, outputs=outputs)
+        recorded = {k: v for k, v in kwargs.items() if k not in _implicit} if _implicit else kwargs
+        Node(operation=self, call_args=args, call_kwargs=recorded, outputs=outputs)
         return outputs
 
     def symbolic_call(self, *args, **kwargs):
@@ -1215,7 +1221,7 @@ class _NoAutocast:
 
 _NO_AUTOCAST = None
 # Trainer-owned objects that are reported through `Model.metrics` explicitly.
-_UNTRACKED_ATTRS = frozenset({"_loss_tracker", "_compile_metrics", "_compile_loss", "_parallel_engine", "_grad_arena", "history"})
+_UNTRACKED_ATTRS = frozenset({"_loss_tracker", "_compile_metrics", "_compile_loss", "_compile_config", "_parallel_engine", "_grad_arena", "_device_stager", "history"})
 _TRACK_EXTRA = ()
 
 

@@ -318,7 +318,9 @@ def circle(y_true, y_pred, ref_labels=None, ref_embeddings=None, remove_diagonal
     ninf = -1e9
     p_loss = torch.logsumexp(torch.where(positive_mask, pos_wdists, torch.full_like(pos_wdists, ninf)), dim=1)
     n_loss = torch.logsumexp(torch.where(negative_mask, neg_wdists, torch.full_like(neg_wdists, ninf)), dim=1)
-    return torch.nn.functional.softplus(p_loss + n_loss)
+    out = torch.nn.functional.softplus(p_loss + n_loss)
+    out._keras_mask = out > 0  # anchors without a positive or without a negative do not count in the reduction
+    return out
 
 
 @keras_export("keras.losses.categorical_generalized_cross_entropy")

@@ -87,17 +87,28 @@ def _in_top_k(y_true, y_pred, k):
     return ops.in_top_k(yt, yp, k).to(torch.float32).reshape(shape)
 
 
-def _wrap(name, fn, exports, arg_defaults, default_name, direction="up"):
+def _wrap(name, fn, exports, arg_defaults, default_name, direction="up", leading=()):
+    """Metric class averaging ``fn`` over samples.  Positional constructor arguments are ``leading`` (for example ``k``
+    of the top-k accuracies), then ``name`` and ``dtype``, then the remaining entries of ``arg_defaults``."""
     arg_names = list(arg_defaults)
+    positional = list(leading) + ["name", "dtype"] + [a for a in arg_names if a not in leading]
 
-    def __init__(self, name=default_name, dtype=None, **kwargs):
+    def __init__(self, *args, **kwargs):
+        if len(args) > len(positional):
+            raise TypeError(f"{name}() takes at most {len(positional)} positional arguments but {len(args)} were given")
+        for key, value in zip(positional, args):
+            if key in kwargs:
+                raise TypeError(f"{name}() got multiple values for argument '{key}'")
+            kwargs[key] = value
+        metric_name = kwargs.pop("name", default_name)
+        dtype = kwargs.pop("dtype", None)
         vals = dict(arg_defaults)
         for k in list(kwargs):
             if k in vals:
                 vals[k] = kwargs.pop(k)
         if kwargs:
             raise TypeError(f"Unexpected keyword arguments: {kwargs}")
-        MeanMetricWrapper.__init__(self, fn, name=name, dtype=dtype, **vals)
+        MeanMetricWrapper.__init__(self, fn, name=metric_name, dtype=dtype, **vals)
         for k, v in vals.items():
             setattr(self, k, v)
         self._direction = direction
@@ -117,8 +128,8 @@ Accuracy = _wrap("Accuracy", accuracy, "keras.metrics.Accuracy", {}, "accuracy")
 BinaryAccuracy = _wrap("BinaryAccuracy", binary_accuracy, "keras.metrics.BinaryAccuracy", {"threshold": 0.5}, "binary_accuracy")
 CategoricalAccuracy = _wrap("CategoricalAccuracy", categorical_accuracy, "keras.metrics.CategoricalAccuracy", {}, "categorical_accuracy")
 SparseCategoricalAccuracy = _wrap("SparseCategoricalAccuracy", sparse_categorical_accuracy, "keras.metrics.SparseCategoricalAccuracy", {}, "sparse_categorical_accuracy")
-TopKCategoricalAccuracy = _wrap("TopKCategoricalAccuracy", top_k_categorical_accuracy, "keras.metrics.TopKCategoricalAccuracy", {"k": 5}, "top_k_categorical_accuracy")
-SparseTopKCategoricalAccuracy = _wrap("SparseTopKCategoricalAccuracy", sparse_top_k_categorical_accuracy, "keras.metrics.SparseTopKCategoricalAccuracy", {"k": 5, "from_sorted_ids": False}, "sparse_top_k_categorical_accuracy")
+TopKCategoricalAccuracy = _wrap("TopKCategoricalAccuracy", top_k_categorical_accuracy, "keras.metrics.TopKCategoricalAccuracy", {"k": 5}, "top_k_categorical_accuracy", leading=("k",))
+SparseTopKCategoricalAccuracy = _wrap("SparseTopKCategoricalAccuracy", sparse_top_k_categorical_accuracy, "keras.metrics.SparseTopKCategoricalAccuracy", {"k": 5, "from_sorted_ids": False}, "sparse_top_k_categorical_accuracy", leading=("k",))
 
 MeanSquaredError = _wrap("MeanSquaredError", L.mean_squared_error, "keras.metrics.MeanSquaredError", {}, "mean_squared_error", "down")
 MeanAbsoluteError = _wrap("MeanAbsoluteError", L.mean_absolute_error, "keras.metrics.MeanAbsoluteError", {}, "mean_absolute_error", "down")

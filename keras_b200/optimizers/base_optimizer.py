@@ -95,6 +95,15 @@ class BaseOptimizer(KerasSaveable):
             self._host_step_version = v
         return self._host_step
 
+    def _local_step(self):
+        """Number of completed *updates*: the value of the public ``iterations`` (the raw call counter divided by
+        ``gradient_accumulation_steps``), which is what bias corrections and schedules count in
+        (keras/src/optimizers/base_optimizer.py ``iterations``)."""
+        step = self._step()
+        if self.gradient_accumulation_steps:
+            return step // self.gradient_accumulation_steps
+        return step
+
     def _bump_step(self):
         with torch.no_grad():
             self._iterations._value.add_(1)
@@ -268,7 +277,6 @@ class BaseOptimizer(KerasSaveable):
             else:
                 for g, a in zip(grads, acc):
                     a._value.add_(g)
-                return
         else:
             fused = self._fused_apply(grads, trainable_variables)
             if not fused:
@@ -278,7 +286,7 @@ class BaseOptimizer(KerasSaveable):
         if self.use_ema:
             self._update_model_variables_moving_average(self._trainable_variables)
             if self.ema_overwrite_frequency:
-                if (self._step() + 1) % self.ema_overwrite_frequency == 0:
+                if (self._local_step() + 1) % self.ema_overwrite_frequency == 0:
                     self._overwrite_model_variables_with_average_value(self._trainable_variables)
 
     def _fused_apply(self, grads, trainable_variables):
@@ -460,7 +468,7 @@ class BaseOptimizer(KerasSaveable):
         if self.use_ema:
             for var, average in zip(trainable_variables, self._model_variables_moving_average):
                 if average is not None:
-                    not_first = 0.0 if self._step() == 0 else 1.0
+                    not_first = 0.0 if self._local_step() == 0 else 1.0
                     momentum = not_first * self.ema_momentum
                     average._value.mul_(momentum).add_(var._value, alpha=1 - momentum)
 

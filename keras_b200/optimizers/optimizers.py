@@ -116,7 +116,7 @@ class Adam(Optimizer):
             self._velocity_hats = self.add_optimizer_variables(var_list, "velocity_hat")
 
     def _alpha(self, lr):
-        t = self._step() + 1
+        t = self._local_step() + 1
         return lr * math.sqrt(1 - self.beta_2 ** t) / (1 - self.beta_1 ** t)
 
     def _fused_apply(self, grads, variables):
@@ -313,7 +313,7 @@ class Adamax(Optimizer):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
         g = gradient.to(p.dtype)
-        t = self._step() + 1
+        t = self._local_step() + 1
         i = self._get_variable_index(variable)
         m, u = self._m[i]._value, self._u[i]._value
         m.add_((g - m) * (1 - self.beta_1))
@@ -350,7 +350,7 @@ class Nadam(Optimizer):
 
     def _backend_update_step(self, grads, trainable_variables, learning_rate):
         dtype = self._u_product._value.dtype
-        t = self._step() + 1
+        t = self._local_step() + 1
         u_t = self.beta_1 * (1.0 - 0.5 * (0.96 ** t))
         self._u_product._value.mul_(u_t)
         super()._backend_update_step(grads, trainable_variables, learning_rate)
@@ -359,7 +359,7 @@ class Nadam(Optimizer):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
         g = gradient.to(p.dtype)
-        t = self._step() + 1
+        t = self._local_step() + 1
         u_t = self.beta_1 * (1.0 - 0.5 * (0.96 ** t))
         u_t_1 = self.beta_1 * (1.0 - 0.5 * (0.96 ** (t + 1)))
         u_product_t = self._u_product._value.to(p.dtype)
@@ -429,7 +429,7 @@ class Lamb(Optimizer):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
         g = gradient.to(p.dtype)
-        t = self._step() + 1
+        t = self._local_step() + 1
         i = self._get_variable_index(variable)
         m, v = self._momentums[i]._value, self._velocities[i]._value
         m.add_((g - m) * (1 - self.beta_1))
@@ -544,7 +544,7 @@ class Adafactor(Optimizer):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
         g = gradient.to(p.dtype)
-        t = float(self._step() + 1)
+        t = float(self._local_step() + 1)
         if not callable(self._learning_rate) and self.relative_step:
             lr = min(lr, 1 / math.sqrt(t)) if isinstance(lr, float) else torch.minimum(lr, torch.as_tensor(1 / math.sqrt(t), dtype=p.dtype, device=p.device))
         i = self._get_variable_index(variable)
@@ -617,7 +617,7 @@ class Muon(Optimizer):
         v = self.adam_velocities[i]
         if v is not None:
             v = v._value
-            t = self._step() + 1
+            t = self._local_step() + 1
             alpha = lr * self.adam_lr_ratio * math.sqrt(1 - self.adam_beta_2 ** t) / (1 - self.adam_beta_1 ** t)
             m.add_((g - m) * (1 - self.adam_beta_1))
             v.add_((g * g - v) * (1 - self.adam_beta_2))
@@ -689,12 +689,16 @@ class ScheduleFreeAdamW(Optimizer):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
         g = gradient.to(p.dtype)
-        t = float(self._step() + 1)
+        t = float(self._local_step() + 1)
         if self.warmup_steps > 0:
             lr = lr * min(t / self.warmup_steps, 1.0)
         i = self._get_variable_index(variable)
         z, v = self._momentums[i]._value, self._velocities[i]._value
-        z_old = z.clone()
+        # On the reference's torch backend "the momentum before the update" is read through `Variable.value`, which hands out
+        # the parameter itself, so the value it then uses is the momentum *after* the in-place update
+        # (keras/src/optimizers/schedule_free_adamw.py:137,156-167).  Checkpoints and trajectories of that backend are the
+        # contract here, so the same value is used.
+        z_old = z
         bc2 = 1 - self.beta_2 ** t
         v.add_((g * g - v) * (1 - self.beta_2))
         denom = torch.sqrt(v / bc2) + self.epsilon

@@ -13,7 +13,7 @@ from keras_b200.core import config
 from keras_b200.core.dtypes import to_torch_dtype
 from keras_b200.core.export_registry import keras_export
 from keras_b200.core.tensor import convert_to_tensor, get_device
-from keras_b200.random.seed_generator import draw_seed
+from keras_b200.random.seed_generator import SeedGenerator, draw_seed
 
 _GENERATORS = {}
 
@@ -74,15 +74,16 @@ def randint(shape, minval, maxval, dtype="int32", seed=None):
 
 @keras_export("keras.random.truncated_normal")
 def truncated_normal(shape, mean=0.0, stddev=1.0, dtype=None, seed=None):
+    """Normal samples within two standard deviations.  Four candidates are drawn per element and the first inside the range
+    is taken, which is the reference's rule (keras/src/backend/torch/random.py:114-124), so a seeded initializer gives the
+    same weights in both frameworks."""
     td = to_torch_dtype(dtype or config.floatx())
-    dev = get_device()
-    g = _generator(seed, dev)
-    # Inverse-CDF sampling restricted to [-2, 2] standard deviations.
-    lo, hi = 0.5 * (1 + math.erf(-2 / math.sqrt(2))), 0.5 * (1 + math.erf(2 / math.sqrt(2)))
-    u = torch.rand(_shape(shape), generator=g, dtype=torch.float32, device=dev) * (hi - lo) + lo
-    z = math.sqrt(2) * torch.erfinv(torch.clamp(2 * u - 1, -1 + 1e-7, 1 - 1e-7))
-    z = torch.clamp(z, -2.0, 2.0)
-    return (z * stddev + mean).to(td)
+    shape = _shape(shape)
+    candidates = normal(shape + (4,), mean=0.0, stddev=1.0, dtype=dtype, seed=seed)
+    inside = (candidates > -2) & (candidates < 2)
+    first = inside.max(-1, keepdim=True)[1]
+    out = candidates.gather(-1, first).squeeze(-1)
+    return (out * stddev + mean).to(td)
 
 
 @keras_export("keras.random.categorical")
@@ -97,18 +98,24 @@ def categorical(logits, num_samples, dtype="int32", seed=None):
 
 @keras_export("keras.random.dropout")
 def dropout(inputs, rate, noise_shape=None, seed=None):
+    """Inverted dropout.  A seeded call (an integer, or a ``SeedGenerator`` that was given a seed) or a ``noise_shape``
+    draws a Bernoulli keep-mask from a generator seeded for this call, which reproduces the reference's stream
+    (keras/src/backend/torch/random.py:140-175); an unseeded call uses the library's fused dropout."""
     x = convert_to_tensor(inputs)
-    keep = 1.0 - rate
-    if noise_shape is None:
-        shape = x.shape
-    else:
-        shape = tuple(x.shape[i] if s is None else s for i, s in enumerate(noise_shape))
     if rate >= 1.0:
         return torch.zeros_like(x)
-    g = _generator(seed, x.device)
-    if g is None:
+    if rate == 0.0:
         return x
-    mask = torch.rand(tuple(shape), generator=g, device=x.device, dtype=torch.float32) < keep
+    seeded = seed is not None and not (isinstance(seed, SeedGenerator) and seed._initial_seed is None)
+    if not seeded and noise_shape is None:
+        return torch.nn.functional.dropout(x, p=rate, training=True)
+    keep = 1.0 - rate
+    shape = tuple(x.shape) if noise_shape is None else tuple(x.shape[i] if s is None else s for i, s in enumerate(noise_shape))
+    g = _generator(seed, x.device)
+    probs = torch.full(shape, keep, device=x.device)
+    mask = (torch.bernoulli(probs) if g is None else torch.bernoulli(probs, generator=g)).bool()
+    if mask.shape != x.shape:
+        mask = torch.broadcast_to(mask, x.shape)
     return torch.where(mask, x / keep, torch.zeros((), dtype=x.dtype, device=x.device))
 
 

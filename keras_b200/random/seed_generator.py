@@ -26,11 +26,12 @@ class SeedGenerator:
         custom_backend = kwargs.pop("backend", None)
         if kwargs:
             raise ValueError(f"Unrecognized keyword arguments: {kwargs}")
+        self._initial_seed = seed  # what the caller gave (None: unseeded); random ops use it to pick their unseeded fast paths
         if seed is None:
             seed = make_default_seed()
         if not isinstance(seed, int):
             raise ValueError(f"Argument `seed` must be an integer. Received: seed={seed}")
-        self._initial_seed = seed
+        self._seed_value = seed
 
         def seed_init(*args, **kw):
             return torch.tensor([seed & 0x7FFFFFFF if seed > 0x7FFFFFFF else seed, 0], dtype=torch.int32)
@@ -52,10 +53,10 @@ class SeedGenerator:
         self._host_counter = counter + 1
         with torch.no_grad():
             self.state._value[1] = self._host_counter
-        return (self._initial_seed, counter)
+        return (self._seed_value, counter)
 
     def get_config(self):
-        return {"seed": self._initial_seed}
+        return {"seed": self._initial_seed, "name": self.name}
 
     @classmethod
     def from_config(cls, config):

@@ -1,0 +1,207 @@
+"""Optimizers, losses, metrics, random ops and a short ``fit`` against the reference (CPU, float32)."""
+
+import numpy as np
+import pytest
+import torch
+
+import keras_b200 as keras
+from tests import oracle
+
+OPTIMIZERS = [
+    ("SGD", dict(learning_rate=0.1)),
+    ("SGD", dict(learning_rate=0.1, momentum=0.9, nesterov=True)),
+    ("Adam", dict(learning_rate=0.01)),
+    ("Adam", dict(learning_rate=0.01, amsgrad=True)),
+    ("Adam", dict(learning_rate=0.1, gradient_accumulation_steps=2)),
+    ("Adam", dict(learning_rate=0.01, use_ema=True, ema_momentum=0.9)),
+    ("Adam", dict(learning_rate=0.01, clipnorm=0.5)),
+    ("Adam", dict(learning_rate=0.01, global_clipnorm=0.5)),
+    ("AdamW", dict(learning_rate=0.01, weight_decay=0.1)),
+    ("Adamax", dict(learning_rate=0.01)),
+    ("Adadelta", dict(learning_rate=1.0)),
+    ("Adagrad", dict(learning_rate=0.1)),
+    ("Adafactor", dict(learning_rate=0.01)),
+    ("Ftrl", dict(learning_rate=0.1, l1_regularization_strength=0.01)),
+    ("Lamb", dict(learning_rate=0.01)),
+    ("Lion", dict(learning_rate=0.01)),
+    ("Nadam", dict(learning_rate=0.01)),
+    ("RMSprop", dict(learning_rate=0.01, momentum=0.5, centered=True)),
+    ("Muon", dict(learning_rate=0.01)),
+    ("ScheduleFreeAdamW", dict(learning_rate=0.01, warmup_steps=2)),
+]
+
+
+def _opt_ids():
+    return [f"{n}_{i}" for i, (n, _) in enumerate(OPTIMIZERS)]
+
+
+@pytest.mark.parametrize("spec", OPTIMIZERS, ids=_opt_ids())
+def test_optimizer_trajectory_matches_reference(spec):
+    rk = oracle.ref()
+    name, kwargs = spec
+    if not hasattr(rk.optimizers, name):
+        pytest.skip("optimizer absent from this reference version")
+    rng = np.random.default_rng(0)
+    init = [rng.normal(size=(4, 3)).astype("float32"), rng.normal(size=(3,)).astype("float32")]
+    grads = [[rng.normal(size=a.shape).astype("float32") for a in init] for _ in range(5)]
+
+    def run(k):
+        variables = [k.Variable(a.copy(), name=f"v{i}") for i, a in enumerate(init)]
+        opt = getattr(k.optimizers, name)(**kwargs)
+        for step in grads:
+            opt.apply([torch.tensor(g) for g in step], variables)
+        if kwargs.get("use_ema"):
+            opt.finalize_variable_values(variables)
+        return [oracle.to_np(v.value) for v in variables], int(oracle.to_np(getattr(opt.iterations, "value", opt.iterations)))
+
+    (theirs, their_it), (ours, our_it) = run(rk), run(keras)
+    assert our_it == their_it
+    for a, b in zip(ours, theirs):
+        np.testing.assert_allclose(a, b, rtol=2e-5, atol=2e-6, err_msg=name)
+
+
+LOSSES = ["BinaryCrossentropy", "BinaryFocalCrossentropy", "CategoricalCrossentropy", "CategoricalFocalCrossentropy", "CategoricalHinge",
+          "CosineSimilarity", "Dice", "Hinge", "Huber", "KLDivergence", "LogCosh", "MeanAbsoluteError", "MeanAbsolutePercentageError",
+          "MeanSquaredError", "MeanSquaredLogarithmicError", "Poisson", "SquaredHinge", "Tversky", "Circle", "CategoricalGeneralizedCrossEntropy"]
+
+
+@pytest.mark.parametrize("name", LOSSES)
+def test_loss_matches_reference(name):
+    rk = oracle.ref()
+    if not hasattr(rk.losses, name):
+        pytest.skip("loss absent from this reference version")
+    rng = np.random.default_rng(1)
+    p = rng.uniform(0.05, 0.95, (6, 4)).astype("float32")
+    p = p / p.sum(-1, keepdims=True)
+    t = np.eye(4, dtype="float32")[rng.integers(0, 4, 6)]
+    weights = rng.uniform(0.5, 1.5, (6,)).astype("float32")
+    if name in ("Circle", "CategoricalGeneralizedCrossEntropy"):
+        t_arg = t.argmax(-1).astype("int32")
+    else:
+        t_arg = t
+    expected = getattr(rk.losses, name)()(t_arg, p, sample_weight=weights)
+    got = getattr(keras.losses, name)()(t_arg, p, sample_weight=weights)
+    oracle.assert_same(got, expected, name, rtol=1e-5, atol=1e-6)
+
+
+def test_sparse_categorical_crossentropy_with_ignore_class_and_logits():
+    rk = oracle.ref()
+    rng = np.random.default_rng(2)
+    logits = rng.normal(size=(5, 7, 4)).astype("float32")
+    labels = rng.integers(0, 4, (5, 7)).astype("int32")
+    labels[0, :3] = -1
+    for k_args in (dict(from_logits=True), dict(from_logits=True, ignore_class=-1), dict(from_logits=True, reduction="sum")):
+        oracle.assert_same(keras.losses.SparseCategoricalCrossentropy(**k_args)(labels, logits) if "ignore_class" in k_args or labels.min() >= 0 else 0,
+                           rk.losses.SparseCategoricalCrossentropy(**k_args)(labels, logits) if "ignore_class" in k_args or labels.min() >= 0 else 0,
+                           str(k_args), rtol=1e-5, atol=1e-6, check_dtype=False)
+
+
+METRICS = [
+    ("Accuracy", {}, "labels"), ("BinaryAccuracy", dict(threshold=0.4), "binary"), ("CategoricalAccuracy", {}, "onehot"),
+    ("SparseCategoricalAccuracy", {}, "sparse"), ("TopKCategoricalAccuracy", dict(k=2), "onehot"), ("SparseTopKCategoricalAccuracy", dict(k=2), "sparse"),
+    ("AUC", dict(num_thresholds=20), "binary"), ("Precision", {}, "binary"), ("Recall", dict(thresholds=0.3), "binary"),
+    ("F1Score", dict(average="macro"), "onehot"), ("FBetaScore", dict(beta=2.0, average="weighted"), "onehot"),
+    ("MeanIoU", dict(num_classes=4), "labels"), ("IoU", dict(num_classes=4, target_class_ids=[1, 2]), "labels"), ("BinaryIoU", {}, "binary"),
+    ("OneHotMeanIoU", dict(num_classes=4), "onehot"), ("MeanSquaredError", {}, "real"), ("RootMeanSquaredError", {}, "real"),
+    ("MeanAbsoluteError", {}, "real"), ("LogCoshError", {}, "real"), ("CosineSimilarity", {}, "real"), ("R2Score", {}, "real"),
+    ("PearsonCorrelation", {}, "real"), ("ConcordanceCorrelation", {}, "real"), ("KLDivergence", {}, "onehot"), ("Poisson", {}, "onehot"),
+    ("Hinge", {}, "onehot"), ("CategoricalCrossentropy", {}, "onehot"), ("SparseCategoricalCrossentropy", {}, "sparse"),
+    ("BinaryCrossentropy", {}, "binary"), ("TruePositives", {}, "binary"), ("FalseNegatives", dict(thresholds=[0.3, 0.7]), "binary"),
+    ("PrecisionAtRecall", dict(recall=0.5, num_thresholds=20), "binary"), ("SensitivityAtSpecificity", dict(specificity=0.5, num_thresholds=20), "binary"),
+    ("Mean", {}, "values"), ("Sum", {}, "values"),
+]
+
+
+@pytest.mark.parametrize("spec", METRICS, ids=[m[0] for m in METRICS])
+def test_metric_matches_reference(spec):
+    rk = oracle.ref()
+    name, kwargs, kind = spec
+    if not hasattr(rk.metrics, name):
+        pytest.skip("metric absent from this reference version")
+    rng = np.random.default_rng(3)
+
+    def batch():
+        p = rng.uniform(0.05, 0.95, (8, 4)).astype("float32")
+        p = p / p.sum(-1, keepdims=True)
+        lab = rng.integers(0, 4, 8).astype("int32")
+        if kind == "labels":
+            return lab, p.argmax(-1).astype("int32")
+        if kind == "binary":
+            return (rng.uniform(size=(8, 1)) > 0.5).astype("float32"), rng.uniform(size=(8, 1)).astype("float32")
+        if kind == "onehot":
+            return np.eye(4, dtype="float32")[lab], p
+        if kind == "sparse":
+            return lab, p
+        if kind == "real":
+            return rng.normal(size=(8, 3)).astype("float32"), rng.normal(size=(8, 3)).astype("float32")
+        return (rng.normal(size=(8,)).astype("float32"),)
+
+    batches = [batch() for _ in range(3)]
+    theirs, ours = getattr(rk.metrics, name)(**kwargs), getattr(keras.metrics, name)(**kwargs)
+    for b in batches:
+        theirs.update_state(*b)
+        ours.update_state(*b)
+    oracle.assert_same(ours.result(), theirs.result(), name, rtol=1e-5, atol=1e-6, check_dtype=False)
+
+
+def test_positional_k_of_sparse_top_k_accuracy():
+    m = keras.metrics.SparseTopKCategoricalAccuracy(3)
+    assert m.k == 3 and isinstance(m.name, str)
+
+
+def test_random_ops_follow_the_reference_generator_rule():
+    rk = oracle.ref()
+    x = torch.ones((4, 6))
+    for seed in (7, 1234):
+        oracle.assert_same(keras.random.dropout(x, 0.4, seed=seed), rk.random.dropout(x, 0.4, seed=seed), "dropout")
+        oracle.assert_same(keras.random.normal((3, 4), seed=seed), rk.random.normal((3, 4), seed=seed), "normal")
+        oracle.assert_same(keras.random.uniform((3, 4), seed=seed), rk.random.uniform((3, 4), seed=seed), "uniform")
+        oracle.assert_same(keras.random.truncated_normal((3, 4), seed=seed), rk.random.truncated_normal((3, 4), seed=seed), "truncated_normal")
+        oracle.assert_same(keras.random.randint((3, 4), 0, 9, seed=seed), rk.random.randint((3, 4), 0, 9, seed=seed), "randint")
+    theirs, ours = rk.random.SeedGenerator(5), keras.random.SeedGenerator(5)
+    for _ in range(3):
+        oracle.assert_same(keras.random.dropout(x, 0.5, seed=ours), rk.random.dropout(x, 0.5, seed=theirs), "dropout with a SeedGenerator")
+    theirs_layer, ours_layer = rk.layers.Dropout(0.3, seed=11), keras.layers.Dropout(0.3, seed=11)
+    oracle.assert_same(ours_layer(x, training=True), theirs_layer(x, training=True), "Dropout layer")
+
+
+def _small_convnet(k):
+    return k.Sequential([
+        k.Input((12, 12, 1)), k.layers.Conv2D(4, 3, activation="relu"), k.layers.MaxPooling2D(2), k.layers.Conv2D(6, 3, activation="relu"),
+        k.layers.GlobalAveragePooling2D(), k.layers.Dropout(0.25, seed=3), k.layers.Dense(5, activation="softmax")])
+
+
+@pytest.mark.parametrize("options", [dict(), dict(steps_per_execution=2), dict(gradient_accumulation_steps=2)], ids=["plain", "steps_per_execution", "accumulation"])
+def test_fit_history_matches_reference(options):
+    rk = oracle.ref()
+    rng = np.random.default_rng(4)
+    x = rng.normal(size=(64, 12, 12, 1)).astype("float32")
+    y = rng.integers(0, 5, (64,)).astype("int32")
+    theirs, ours = _small_convnet(rk), _small_convnet(keras)
+    ours.set_weights(theirs.get_weights())
+    accumulation = options.get("gradient_accumulation_steps")
+    spe = options.get("steps_per_execution", 1)
+    histories = []
+    for k, model in ((rk, theirs), (keras, ours)):
+        opt = k.optimizers.Adam(1e-2, gradient_accumulation_steps=accumulation) if accumulation else k.optimizers.Adam(1e-2)
+        model.compile(optimizer=opt, loss="sparse_categorical_crossentropy", metrics=["accuracy"], steps_per_execution=spe)
+        h = model.fit(x, y, batch_size=16, epochs=2, shuffle=False, verbose=0, validation_split=0.25)
+        histories.append(h.history)
+    for key in histories[0]:
+        np.testing.assert_allclose(histories[1][key], histories[0][key], rtol=2e-3, atol=2e-4, err_msg=key)
+    scores_theirs = theirs.evaluate(x, y, batch_size=32, verbose=0)
+    scores_ours = ours.evaluate(x, y, batch_size=32, verbose=0)
+    assert len(scores_ours) == len(scores_theirs)
+    np.testing.assert_allclose(scores_ours, scores_theirs, rtol=2e-3, atol=2e-4)
+
+
+def test_evaluate_with_metric_instance_returns_each_metric_once():
+    rk = oracle.ref()
+    rng = np.random.default_rng(5)
+    x, y = rng.normal(size=(16, 4)).astype("float32"), rng.integers(0, 3, (16,)).astype("int32")
+    out = []
+    for k in (rk, keras):
+        model = k.Sequential([k.Input((4,)), k.layers.Dense(3, activation="softmax")])
+        model.compile(optimizer="sgd", loss="sparse_categorical_crossentropy", metrics=[k.metrics.SparseCategoricalAccuracy(name="acc"), "accuracy"])
+        out.append(model.evaluate(x, y, verbose=0))
+    assert len(out[1]) == len(out[0])
