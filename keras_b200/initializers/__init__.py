@@ -161,7 +161,7 @@ def compute_fans(shape, input_axes=None, output_axes=None):
 
 @keras_export(["keras.initializers.VarianceScaling", "keras.initializers.variance_scaling"])
 class VarianceScaling(RandomInitializer):
-    def __init__(self, scale=1.0, mode="fan_in", distribution="truncated_normal", seed=None):
+    def __init__(self, scale=1.0, mode="fan_in", distribution="truncated_normal", seed=None, input_axes=None, output_axes=None):
         if scale <= 0.0:
             raise ValueError(f"Argument `scale` must be positive float. Received: scale={scale}")
         if mode not in {"fan_in", "fan_out", "fan_avg"}:
@@ -172,10 +172,14 @@ class VarianceScaling(RandomInitializer):
         if distribution not in {"uniform", "truncated_normal", "untruncated_normal"}:
             raise ValueError(f"Invalid `distribution` argument: {distribution}.Please use one of {{'uniform', 'truncated_normal', 'untruncated_normal'}}")
         self.scale, self.mode, self.distribution = scale, mode, distribution
+        # which axes of the weight count as inputs / outputs when fans are computed (EinsumDense kernels); None: the
+        # usual convention (last axis out, the one before in, leading axes a receptive field)
+        self.input_axes, self.output_axes = input_axes, output_axes
         super().__init__(seed=seed)
 
     def __call__(self, shape, dtype=None, input_axes=None, output_axes=None):
-        fan_in, fan_out = compute_fans(shape, input_axes, output_axes)
+        fan_in, fan_out = compute_fans(shape, input_axes if input_axes is not None else self.input_axes,
+                                       output_axes if output_axes is not None else self.output_axes)
         scale = self.scale
         if self.mode == "fan_in":
             scale /= max(1.0, fan_in)
@@ -192,15 +196,16 @@ class VarianceScaling(RandomInitializer):
         return _random.uniform(shape, minval=-limit, maxval=limit, dtype=dtype, seed=self.seed)
 
     def get_config(self):
-        return {"scale": self.scale, "mode": self.mode, "distribution": self.distribution, **super().get_config()}
+        return {"scale": self.scale, "mode": self.mode, "distribution": self.distribution, **super().get_config(), "input_axes": self.input_axes,
+                "output_axes": self.output_axes}
 
 
 def _vs_subclass(name, exports, scale, mode, distribution):
-    def __init__(self, seed=None):
-        VarianceScaling.__init__(self, scale=scale, mode=mode, distribution=distribution, seed=seed)
+    def __init__(self, seed=None, input_axes=None, output_axes=None):
+        VarianceScaling.__init__(self, scale=scale, mode=mode, distribution=distribution, seed=seed, input_axes=input_axes, output_axes=output_axes)
 
     def get_config(self):
-        return {"seed": RandomInitializer.get_config(self)["seed"]}
+        return {"seed": RandomInitializer.get_config(self)["seed"], "input_axes": self.input_axes, "output_axes": self.output_axes}
 
     cls = type(name, (VarianceScaling,), {"__init__": __init__, "get_config": get_config})
     cls.__module__ = __name__

@@ -645,8 +645,13 @@ class File(Group):
         reader = _Reader(buf)
         super().__init__(reader, reader.root_header, "/")
 
+    def __bool__(self):
+        """True while the file is open (h5py's convention; a Group would otherwise be falsy when it has no members)."""
+        return not getattr(self, "_closed", False)
+
     def close(self):
         self._links = None
+        self._closed = True
         if self._mmap is not None:
             try:
                 self._r.buf.release()

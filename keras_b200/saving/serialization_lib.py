@@ -22,6 +22,7 @@ from keras_b200.core import global_state
 from keras_b200.core.dtypes import standardize_dtype
 from keras_b200.core.export_registry import get_name_from_symbol, get_symbol_from_name, keras_export
 from keras_b200.core.keras_tensor import KerasTensor
+from keras_b200.ops.operation import KerasSaveable
 from keras_b200.saving import object_registration
 
 PLAIN_TYPES = (str, int, float, bool)
@@ -217,6 +218,10 @@ def _class_config(obj):
 
 
 def _public_class_config(cls, inner_config):
+    if cls.__name__ == "Functional" and cls.__module__.endswith("models.functional"):
+        # a model built as `keras.Model(inputs, outputs)`: the reference names its (unexported) class by module path, and
+        # that is the only spelling it accepts back (keras/src/models/functional.py, keras/src/saving/serialization_lib.py:157-313)
+        return {"module": "keras.src.models.functional", "class_name": "Functional", "config": inner_config, "registered_name": "Functional"}
     api_name = get_name_from_symbol(cls)
     if api_name is None:
         registered = object_registration.GLOBAL_CUSTOM_NAMES.get(cls)
@@ -353,53 +358,51 @@ def deserialize_keras_object(config, custom_objects=None, safe_mode=True, **kwar
     return instance
 
 
+# Packages whose modules may be imported while resolving a config.  Anything else has to be registered
+# (`register_keras_serializable`) or passed in `custom_objects`: a model file must never be able to make the loader import
+# a module of its choosing (the reference draws the same line, keras/src/saving/serialization_lib.py:880-891).
+_IMPORTABLE_PACKAGES = frozenset({"keras_b200", "keras_hub", "keras_cv", "keras_nlp"})
+
+
+def _lookup_public(module, name):
+    """Symbol behind a `keras...` module path, public (`keras.layers`) or private to the reference (`keras.src...`)."""
+    obj = get_symbol_from_name(f"{module}.{name}")
+    if obj is None and module.startswith("keras.src."):
+        obj = _resolve_private(module, name)
+    return obj
+
+
 def _retrieve(name, registered_name, module, obj_type, full_config, custom_objects):
+    # 1. objects the caller vouches for: `custom_objects`, the custom-object scope, the global registry
     key = name if obj_type == "function" else registered_name
-    if key in custom_objects:
+    if key is not None and key in custom_objects:
         return custom_objects[key]
-    if name in custom_objects and obj_type == "class" and (registered_name is None or registered_name == name):
+    if obj_type == "class" and name in custom_objects and registered_name in (None, name):
         return custom_objects[name]
-    if module:
-        if module == "keras" or module.startswith("keras."):
-            obj = get_symbol_from_name(f"{module}.{name}")
-            if obj is not None:
-                return obj
-            # private module paths written by reference Keras (e.g. its per-backend optimizers
-            # or op classes): resolve by class name in the matching public namespace
-            if module.startswith("keras.src."):
-                obj = _resolve_private(module, name)
-                if obj is not None:
-                    return obj
-        if obj_type == "function" and module == "builtins":
-            for mod in BUILTIN_MODULES:
-                obj = get_symbol_from_name(f"keras.{mod}.{name}")
-                if obj is not None:
-                    return obj
-            sep = f">{name}"
-            for custom_name, custom_object in custom_objects.items():
-                if custom_name.endswith(sep):
-                    return custom_object
-        if module.startswith("keras_b200"):
-            try:
-                mod = importlib.import_module(module)
-                obj = vars(mod).get(name)
-                if obj is not None:
-                    return obj
-            except ModuleNotFoundError:
-                pass
-        try:
-            mod = importlib.import_module(module)
-            obj = vars(mod).get(name, None)
-            if obj is not None and (inspect.isclass(obj) or callable(obj)) and module.split(".")[0] not in ("os", "sys", "subprocess", "builtins"):
-                if hasattr(obj, "from_config") or obj_type == "function" and name in object_registration.GLOBAL_CUSTOM_OBJECTS:
-                    return obj
-        except Exception:
-            pass
+    # 2. this framework's own symbols, addressed by their Keras names
+    if module and (module == "keras" or module.startswith("keras.")):
+        obj = _lookup_public(module, name)
+        if obj is not None:
+            return obj
     if obj_type == "function":
-        for mod in BUILTIN_MODULES:
-            obj = get_symbol_from_name(f"keras.{mod}.{name}")
-            if obj is not None:
-                return obj
+        if module in (None, "builtins"):
+            for area in BUILTIN_MODULES:
+                obj = get_symbol_from_name(f"keras.{area}.{name}")
+                if obj is not None:
+                    return obj
+        # files written before registered names were stored for functions carry the bare name only
+        for custom_name, custom_object in custom_objects.items():
+            if custom_name.endswith(f">{name}"):
+                return custom_object
+    # 3. classes inside allow-listed packages, and only savable ones
+    if module and obj_type == "class" and module.split(".", 1)[0] in _IMPORTABLE_PACKAGES:
+        try:
+            candidate = vars(importlib.import_module(module)).get(name)
+        except ModuleNotFoundError:
+            raise TypeError(f"Could not deserialize {obj_type} '{name}' because its parent module {module} cannot be imported. Full object config: {full_config}")
+        if isinstance(candidate, type) and issubclass(candidate, KerasSaveable):
+            return candidate
+        raise TypeError(f"Could not deserialize '{module}.{name}' because it is not a KerasSaveable subclass")
     raise TypeError(
         f"Could not locate {obj_type} '{name}'. Make sure custom classes and functions are decorated with "
         "`@keras.saving.register_keras_serializable()`. If they are already decorated, make sure they are all imported so that "
@@ -408,6 +411,10 @@ def _retrieve(name, registered_name, module, obj_type, full_config, custom_objec
 
 
 def _resolve_private(module, name):
+    if name == "Functional" and module.endswith("models.functional"):
+        from keras_b200.models.functional import Functional
+
+        return Functional
     parts = module.split(".")
     if len(parts) >= 3:
         area = parts[2]
