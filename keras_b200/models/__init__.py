@@ -2,6 +2,7 @@ from keras_b200.models.functional import Functional  # noqa: F401
 from keras_b200.models.model import Model  # noqa: F401
 from keras_b200.models.sequential import Sequential  # noqa: F401
 from keras_b200.models.cloning import clone_model  # noqa: F401
+from keras_b200.saving.saving_api import load_model, save_model  # noqa: F401
 from keras_b200.core.export_registry import keras_export as _keras_export  # noqa: E402
 
 

@@ -24,6 +24,10 @@ def __getattr__(name):
         return importlib.import_module("keras_b200.utils.bounding_boxes")
     if name == "legacy":
         return importlib.import_module("keras_b200.legacy.saving.legacy_serialization_api")
+    if name == "clear_session":
+        from keras_b200.core.global_state import clear_session
+
+        return clear_session
     if name == "get_source_inputs":
         from keras_b200.ops.operation_utils import get_source_inputs
 
