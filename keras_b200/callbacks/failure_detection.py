@@ -1,7 +1,7 @@
 """``FailureDetection``: aborts ``fit`` on every rank when a rank of the job is lost (no counterpart in the reference,
 whose jobs wait inside the collective until the library's time-out)."""
 
-from keras_b200.callbacks.callbacks import Callback
+from keras_b200.callbacks.base import Callback
 from keras_b200.core.export_registry import keras_export
 
 

@@ -14,7 +14,7 @@ import threading
 
 import numpy as np
 
-from keras_b200.callbacks.callbacks import MonitorCallback, _is_chief
+from keras_b200.callbacks.watch import MonitorCallback, is_chief as _is_chief
 from keras_b200.core.export_registry import keras_export
 
 

@@ -13,7 +13,7 @@ import warnings
 import numpy as np
 import torch
 
-from keras_b200.callbacks.callbacks import Callback
+from keras_b200.callbacks.base import Callback
 from keras_b200.core.export_registry import keras_export
 
 
