@@ -9,10 +9,6 @@ import numpy as np
 
 from keras_b200.callbacks.base import Callback
 
-# metric-name fragments that mean "larger is better" when neither the mode nor the metric object says so
-_HIGHER_IS_BETTER = ("acc", "auc")
-
-
 def _model_metric(model, name):
     """The metric object called ``name`` among the model's metrics (compile metrics unpacked), or None."""
     from keras_b200.trainers.compile_utils import CompileMetrics
@@ -45,13 +41,11 @@ class MetricWatch:
         if direction is not None:
             self.larger_is_better = direction == "up"
         if self.larger_is_better is None:
-            if any(tag in self.monitor for tag in _HIGHER_IS_BETTER) or self.monitor.endswith("fmeasure"):
-                self.larger_is_better = True
-            else:
-                raise ValueError(
-                    f"{owner} callback received monitor={self.monitor}, but Keras isn't able to automatically determine whether that metric "
-                    "should be maximized or minimized. Pass `mode='max'` in order to monitor based on the highest metric value, or pass "
-                    "`mode='min'` in order to use the lowest value.")
+            # no guessing from the metric's name: only "loss" and metrics that declare a direction are known
+            raise ValueError(
+                f"{owner} callback received monitor={self.monitor}, but Keras isn't able to automatically determine whether that metric "
+                "should be maximized or minimized. Pass `mode='max'` in order to monitor based on the highest metric value, or pass "
+                "`mode='min'` in order to use the lowest value.")
 
     @property
     def resolved(self):
