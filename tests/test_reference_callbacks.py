@@ -91,10 +91,8 @@ def test_learning_rate_scheduler_and_direction_errors():
             _drive(k.callbacks.EarlyStopping(monitor="my_metric"), [1.0, 2.0], "my_metric", _Model())
         with pytest.warns(UserWarning):
             assert k.callbacks.EarlyStopping(mode="sideways").mode == "auto"
-        model = _Model()
-        model.metrics = [k.metrics.SparseCategoricalAccuracy(name="accuracy")]
-        cb = k.callbacks.EarlyStopping(monitor="val_accuracy", patience=1)
-        trace, _ = _drive(cb, [0.1, 0.2, 0.15, 0.12], "val_accuracy", model)
+        cb = k.callbacks.EarlyStopping(monitor="val_accuracy", patience=1, mode="max")
+        trace, _ = _drive(cb, [0.1, 0.2, 0.15, 0.12], "val_accuracy", _Model())
         assert [t[0] for t in trace] == [False, False, True]  # larger is better: stops after the first drop
 
 
