@@ -1,5 +1,11 @@
-"""``OptimizerMap`` / ``MultiOptimizer``: different optimizers for different variables, chosen by regex on the
-variable path (keras/src/optimizers/multi_optimizer.py:10-413)."""
+"""Different optimizers for different variables (``keras.optimizers.OptimizerMap`` / ``MultiOptimizer``;
+behaviour of keras/src/optimizers/multi_optimizer.py:10-413).
+
+``OptimizerMap`` resolves a variable path to an optimizer: an exact key wins, otherwise the single key that matches the
+whole path as a regular expression, otherwise the default.  ``MultiOptimizer`` turns any such selector (a map or a
+callable) into a routing table built once: ``route[i]`` is the slot of the inner optimizer that owns variable ``i`` of
+the list the optimizer was built on, so ``apply`` is one pass that fills per-optimizer buckets by index.
+"""
 
 import re
 from collections.abc import MutableMapping
@@ -10,6 +16,16 @@ from keras_b200.optimizers.optimizers import Optimizer
 from keras_b200.saving import serialization_lib
 
 
+def _check_inner(optimizer, where):
+    """An inner optimizer is a plain optimizer: wrappers that rescale or re-route gradients cannot nest."""
+    if not isinstance(optimizer, Optimizer):
+        raise ValueError(f"optimizer must be a Keras Optimizer instance. Received: {optimizer}")
+    if isinstance(optimizer, LossScaleOptimizer):
+        raise ValueError("optimizer cannot be LossScaleOptimizer." if where == "map" else "LossScaleOptimizer cannot be used inside an MultiOptimizer.")
+    if isinstance(optimizer, MultiOptimizer):
+        raise ValueError("optimizer cannot be MultiOptimizer." if where == "map" else "MultiOptimizer cannot be used inside an MultiOptimizer.")
+
+
 @keras_export("keras.optimizers.OptimizerMap")
 class OptimizerMap(MutableMapping):
     def __init__(self, default_optimizer, optimizer_map=None):
@@ -18,35 +34,42 @@ class OptimizerMap(MutableMapping):
         if optimizer_map is not None and not isinstance(optimizer_map, dict):
             raise TypeError(f"optimizer_map must be a dictionary. Received: {optimizer_map}")
         self._default_optimizer = default_optimizer
-        self._optimizer_map = optimizer_map or dict()
+        self._optimizer_map = {}
+        self._patterns = {}  # key -> compiled pattern, filled lazily
+        for key, optimizer in (optimizer_map or {}).items():
+            self._optimizer_map[key] = optimizer
 
-    default_optimizer = property(lambda self: self._default_optimizer)
+    @property
+    def default_optimizer(self):
+        return self._default_optimizer
 
-    def __getitem__(self, key):
-        if key in self._optimizer_map:
-            return self._optimizer_map[key]
-        matching = [p for p in self._optimizer_map.keys() if re.fullmatch(p, key)]
-        if len(matching) > 1:
-            raise ValueError(f"Multiple optimizers assigned to variable {key}.")
-        if len(matching) == 1:
-            return self._optimizer_map[matching[0]]
-        return self.default_optimizer
+    def _pattern(self, key):
+        compiled = self._patterns.get(key)
+        if compiled is None:
+            compiled = self._patterns[key] = re.compile(key)
+        return compiled
+
+    def __getitem__(self, path):
+        exact = self._optimizer_map.get(path)
+        if exact is not None:
+            return exact
+        hits = [key for key in self._optimizer_map if self._pattern(key).fullmatch(path)]
+        if len(hits) > 1:
+            raise ValueError(f"Multiple optimizers assigned to variable {path}.")
+        return self._optimizer_map[hits[0]] if hits else self._default_optimizer
 
     def __setitem__(self, key, optimizer):
         if key in self._optimizer_map:
-            raise ValueError(f"'{key}' already exists in the OptimizerMap with value {self._optimizer_map[key]}. Please make sure to not use duplicated keys.")
+            raise ValueError(f"'{key}' already exists in the OptimizerMap with value {self._optimizer_map[key]}. "
+                             "Please make sure to not use duplicated keys.")
         if not isinstance(key, str):
             raise ValueError(f"key must be a string. Received: {key}")
-        if not isinstance(optimizer, Optimizer):
-            raise ValueError(f"optimizer must be a Keras Optimizer instance. Received: {optimizer}")
-        if isinstance(optimizer, LossScaleOptimizer):
-            raise ValueError("optimizer cannot be LossScaleOptimizer.")
-        if isinstance(optimizer, MultiOptimizer):
-            raise ValueError("optimizer cannot be MultiOptimizer.")
+        _check_inner(optimizer, "map")
         self._optimizer_map[key] = optimizer
 
     def __delitem__(self, key):
         del self._optimizer_map[key]
+        self._patterns.pop(key, None)
 
     def __len__(self):
         return len(self._optimizer_map)
@@ -63,61 +86,71 @@ class OptimizerMap(MutableMapping):
 
     @classmethod
     def from_config(cls, config, custom_objects=None):
-        return cls(serialization_lib.deserialize_keras_object(config["default_optimizer"], custom_objects=custom_objects),
-                   serialization_lib.deserialize_keras_object(config["optimizer_map"], custom_objects=custom_objects))
+        load = lambda part: serialization_lib.deserialize_keras_object(part, custom_objects=custom_objects)  # noqa: E731
+        return cls(load(config["default_optimizer"]), load(config["optimizer_map"]))
 
 
 @keras_export("keras.optimizers.MultiOptimizer")
 class MultiOptimizer(Optimizer):
+    """``optimizer_map``: an ``OptimizerMap`` or any ``variable -> Optimizer`` callable."""
+
     def __init__(self, optimizer_map, loss_scale_factor=None, name=None):
         self._inner_optimizers = []
         super().__init__(learning_rate=0.0, loss_scale_factor=loss_scale_factor, name=name)
         self._optimizer_map = optimizer_map
-        if hasattr(optimizer_map, "values"):
-            for opt in optimizer_map.values():
-                if opt not in self._inner_optimizers:
-                    opt.loss_scale_factor = loss_scale_factor
-                    self._inner_optimizers.append(opt)
-        default_opt = getattr(optimizer_map, "default_optimizer", None)
-        if default_opt is not None and default_opt not in self._inner_optimizers:
-            default_opt.loss_scale_factor = loss_scale_factor
-            self._inner_optimizers.append(default_opt)
+        self._route = {}  # variable key -> slot in _inner_optimizers
+        # optimizers that are known before any variable is seen get their slots now, in map order, the default last
+        known = list(optimizer_map.values()) if hasattr(optimizer_map, "values") else []
+        default = getattr(optimizer_map, "default_optimizer", None)
+        if default is not None:
+            known.append(default)
+        for optimizer in known:
+            self._slot_of(optimizer)
+
+    def _slot_of(self, optimizer):
+        for slot, existing in enumerate(self._inner_optimizers):
+            if existing is optimizer:
+                return slot
+        optimizer.loss_scale_factor = self.loss_scale_factor
+        self._inner_optimizers.append(optimizer)
+        return len(self._inner_optimizers) - 1
+
+    def _buckets(self, variables, payload=None):
+        """Per-slot lists of ``variables`` (or of ``(payload[i], variables[i])`` pairs) according to the routing table."""
+        buckets = [[] for _ in self._inner_optimizers]
+        for i, variable in enumerate(variables):
+            slot = self._route[self._var_key(variable)]
+            buckets[slot].append(variable if payload is None else (payload[i], variable))
+        return buckets
 
     def build(self, var_list):
         if self.built:
             return
-        self._var_to_optimizer_idx = {}
+        self._route = {}
         self._trainable_variables_indices = {}
-        per_opt = [[] for _ in self._inner_optimizers]
-        for i, var in enumerate(var_list):
-            opt = self._optimizer_map(var)
-            if not isinstance(opt, Optimizer):
-                raise ValueError(f"Optimizer for variable {var} is not an Optimizer instance.")
-            if isinstance(opt, LossScaleOptimizer):
-                raise ValueError("LossScaleOptimizer cannot be used inside an MultiOptimizer.")
-            if isinstance(opt, MultiOptimizer):
-                raise ValueError("MultiOptimizer cannot be used inside an MultiOptimizer.")
-            if opt not in self._inner_optimizers:
-                opt.loss_scale_factor = self.loss_scale_factor
-                self._inner_optimizers.append(opt)
-                per_opt.append([])
-            idx = self._inner_optimizers.index(opt)
-            self._var_to_optimizer_idx[self._var_key(var)] = idx
-            self._trainable_variables_indices[self._var_key(var)] = i
-            per_opt[idx].append(var)
-        for opt, variables in zip(self._inner_optimizers, per_opt):
-            if variables:
-                opt.build(variables)
+        for position, variable in enumerate(var_list):
+            optimizer = self._optimizer_map(variable)
+            if not isinstance(optimizer, Optimizer):
+                raise ValueError(f"Optimizer for variable {variable} is not an Optimizer instance.")
+            _check_inner(optimizer, "build")
+            key = self._var_key(variable)
+            self._route[key] = self._slot_of(optimizer)
+            self._trainable_variables_indices[key] = position
+        for optimizer, owned in zip(self._inner_optimizers, self._buckets(var_list)):
+            if owned:
+                optimizer.build(owned)
         super().build(var_list)
 
-    optimizers = property(lambda self: self._inner_optimizers)
+    @property
+    def optimizers(self):
+        return self._inner_optimizers
 
     @property
     def variables(self):
-        out = self._variables[:]
-        for opt in self._inner_optimizers:
-            out.extend(opt.variables)
-        return out
+        collected = list(self._variables)
+        for optimizer in self._inner_optimizers:
+            collected.extend(optimizer.variables)
+        return collected
 
     @property
     def learning_rate(self):
@@ -134,56 +167,53 @@ class MultiOptimizer(Optimizer):
     @loss_scale_factor.setter
     def loss_scale_factor(self, value):
         self._loss_scale_factor = value
-        for opt in getattr(self, "_inner_optimizers", []):
-            opt.loss_scale_factor = value
+        for optimizer in getattr(self, "_inner_optimizers", ()):
+            optimizer.loss_scale_factor = value
 
     def apply(self, grads, trainable_variables=None):
         if len(grads) == 0:
             return
         if trainable_variables is None:
             if not self.built:
-                raise ValueError("When passing `grads` without `variables`, the optimizer must already be built on a list of variables. Call `optimizer.build(trainable_variables)` first.")
+                raise ValueError("When passing `grads` without `variables`, the optimizer must already be built on a list of variables. "
+                                 "Call `optimizer.build(trainable_variables)` first.")
             trainable_variables = self._trainable_variables
         if not self.built:
             self.build(trainable_variables)
             self.built = True
-        if len(grads) != len(self._trainable_variables_indices):
-            raise ValueError(f"Gradients must match trainable variables one-to-one. Received {len(grads)} gradients and {len(self._trainable_variables_indices)} variables.")
-        per_opt = [[] for _ in self._inner_optimizers]
-        for g, v in zip(grads, trainable_variables):
-            per_opt[self._var_to_optimizer_idx[self._var_key(v)]].append((g, v))
-        for opt, gv in zip(self._inner_optimizers, per_opt):
-            if gv:
-                sub_grads, sub_vars = zip(*gv)
-                opt.apply(list(sub_grads), list(sub_vars))
+        if len(grads) != len(self._route):
+            raise ValueError(f"Gradients must match trainable variables one-to-one. Received {len(grads)} gradients and {len(self._route)} variables.")
+        for optimizer, pairs in zip(self._inner_optimizers, self._buckets(trainable_variables, payload=grads)):
+            if pairs:
+                optimizer.apply([g for g, _ in pairs], [v for _, v in pairs])
         self._iterations.assign_add(1)
 
     def finalize_variable_values(self, var_list):
-        per_opt = [[] for _ in self._inner_optimizers]
-        for var in var_list:
-            per_opt[self._var_to_optimizer_idx[self._var_key(var)]].append(var)
-        for opt, variables in zip(self._inner_optimizers, per_opt):
-            if variables:
-                opt.finalize_variable_values(variables)
+        for optimizer, owned in zip(self._inner_optimizers, self._buckets(var_list)):
+            if owned:
+                optimizer.finalize_variable_values(owned)
 
     def set_weights(self, weights):
         if not self.built:
-            raise ValueError("You are calling `set_weights()` on an optimizer that has not yet been built. Please call `optimizer.build(trainable_variables)` to create the optimizer weights before calling `set_weights()`.")
-        own = len(self._variables)
-        for i in range(own):
-            self._variables[i].assign(weights[i])
-        idx = own
-        for opt in self._inner_optimizers:
-            n = len(opt.variables)
-            if n > 0:
-                opt.set_weights(weights[idx: idx + n])
-                idx += n
+            raise ValueError("You are calling `set_weights()` on an optimizer that has not yet been built. Please call "
+                             "`optimizer.build(trainable_variables)` to create the optimizer weights before calling `set_weights()`.")
+        # layout of `weights`: this optimizer's own variables, then each inner optimizer's block in slot order
+        cursor = 0
+        for variable in self._variables:
+            variable.assign(weights[cursor])
+            cursor += 1
+        for optimizer in self._inner_optimizers:
+            count = len(optimizer.variables)
+            if count:
+                optimizer.set_weights(weights[cursor:cursor + count])
+                cursor += count
 
     def get_config(self):
-        return {"optimizer_map": serialization_lib.serialize_keras_object(self._optimizer_map), "loss_scale_factor": self.loss_scale_factor, "name": self.name}
+        return {"optimizer_map": serialization_lib.serialize_keras_object(self._optimizer_map), "loss_scale_factor": self.loss_scale_factor,
+                "name": self.name}
 
     @classmethod
     def from_config(cls, config, custom_objects=None):
-        config = config.copy()
+        config = dict(config)
         config["optimizer_map"] = serialization_lib.deserialize_keras_object(config["optimizer_map"], custom_objects=custom_objects)
         return cls(**config)

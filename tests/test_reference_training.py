@@ -205,3 +205,34 @@ def test_evaluate_with_metric_instance_returns_each_metric_once():
         model.compile(optimizer="sgd", loss="sparse_categorical_crossentropy", metrics=[k.metrics.SparseCategoricalAccuracy(name="acc"), "accuracy"])
         out.append(model.evaluate(x, y, verbose=0))
     assert len(out[1]) == len(out[0])
+
+
+def test_multi_optimizer_routing_matches_reference():
+    rk = oracle.ref()
+    if not hasattr(rk.optimizers, "MultiOptimizer"):
+        pytest.skip("MultiOptimizer absent from this reference version")
+    rng = np.random.default_rng(6)
+    init = {"enc/kernel": rng.normal(size=(3, 2)), "enc/bias": rng.normal(size=(2,)), "head/kernel": rng.normal(size=(2, 2))}
+    grads = [[rng.normal(size=a.shape).astype("float32") for a in init.values()] for _ in range(4)]
+
+    def run(k):
+        variables = [k.Variable(a.astype("float32"), name=n.split("/")[1]) for n, a in init.items()]
+        for v, n in zip(variables, init):
+            v._path = n if hasattr(v, "_path") else None
+            try:
+                v.path = n
+            except Exception:
+                pass
+        omap = k.optimizers.OptimizerMap(k.optimizers.SGD(0.1), {"enc/.*": k.optimizers.Adam(0.01)})
+        omap["head/kernel"] = k.optimizers.SGD(0.5, momentum=0.9)
+        opt = k.optimizers.MultiOptimizer(omap)
+        for step in grads:
+            opt.apply([torch.tensor(g) for g in step], variables)
+        return [oracle.to_np(v.value) for v in variables], [type(o).__name__ for o in opt.optimizers], len(opt.variables)
+
+    theirs, ours = run(rk), run(keras)
+    assert ours[1:] == theirs[1:]
+    for a, b in zip(ours[0], theirs[0]):
+        np.testing.assert_allclose(a, b, rtol=2e-5, atol=2e-6)
+    with pytest.raises(ValueError):
+        keras.optimizers.OptimizerMap(keras.optimizers.SGD(0.1), {"a.*": keras.optimizers.SGD(0.1), "ab.*": keras.optimizers.SGD(0.2)})["abc"]
