@@ -21,6 +21,8 @@ def _x(shape, seed=0, integer=None):
 LAYERS = [
     ("Dense", dict(units=5, activation="gelu"), [(3, 7)], {}, None),
     ("EinsumDense", dict(equation="abc,cde->abde", output_shape=(None, 2, 3), bias_axes="de"), [(2, 4, 6)], {}, None),
+    ("TernaryDense", dict(units=5, activation="relu"), [(3, 7)], {}, None),
+    ("TernaryDense", dict(units=4, threshold=0.2, use_bias=False), [(3, 7)], {}, None),
     ("Embedding", dict(input_dim=11, output_dim=4, mask_zero=True), [(3, 5)], {}, 11),
     ("Conv1D", dict(filters=4, kernel_size=3, padding="causal", dilation_rate=2), [(2, 9, 3)], {}, None),
     ("Conv2D", dict(filters=4, kernel_size=3, strides=2, padding="same", activation="relu"), [(2, 9, 8, 3)], {}, None),
