@@ -297,92 +297,111 @@ class _FusionCtx:
         self.run_conv_nobias, self.run_pool_padded, self.Padded = mod.run_conv_nobias, mod.run_pool_padded, mod.Padded
 
 
-def functional_from_config(cls, config, custom_objects=None):
-    from keras_b200.saving import serialization_lib
+class _NotReady(Exception):
+    """A recorded call refers to an output that has not been produced yet."""
 
-    created_layers = {}
-    unprocessed_nodes = {}
 
-    def add_unprocessed_node(layer, node_data):
-        unprocessed_nodes.setdefault(layer, []).append(node_data)
+class _GraphReplayer:
+    """Rebuilds a functional graph from its config by replaying the recorded layer calls.
 
-    def process_node(layer, node_data):
-        args, kwargs = deserialize_node(node_data, created_layers)
-        layer(*args, **kwargs)
+    Every layer of the config is created first.  Its recorded calls ("inbound nodes") wait in a queue, in config order, and
+    a call runs as soon as all tensors it names exist, i.e. as soon as the producing layers have been called often enough.
+    The queue is swept until it is empty; a sweep that runs nothing means the config names a tensor nobody produces.
+    Calls of one layer keep their recorded order, because node indices are positions in that order."""
 
-    def process_layer(layer_data):
-        layer_name = layer_data["name"]
-        if "module" not in layer_data:
-            layer = serialization_lib.deserialize_keras_object(layer_data, custom_objects=custom_objects) if False else _legacy_layer(layer_data, custom_objects)
-        else:
-            layer = serialization_lib.deserialize_keras_object(layer_data, custom_objects=custom_objects)
+    def __init__(self, custom_objects):
+        self.custom_objects = custom_objects
+        self.layers = {}          # name -> layer
+        self.pending = []         # [layer, [recorded call, ...]] in config order
+
+    def add_layer(self, layer_config):
+        from keras_b200.saving import serialization_lib
+
+        if "module" in layer_config:
+            layer = serialization_lib.deserialize_keras_object(layer_config, custom_objects=self.custom_objects)
+        else:  # a Keras 2 config: only class_name / config
+            layer = _legacy_layer(layer_config, self.custom_objects)
         if not isinstance(layer, Operation):
             raise ValueError(f"Unexpected object from deserialization, expected a layer or operation, got a {type(layer)}")
-        created_layers[layer_name] = layer
-        for node_data in layer_data["inbound_nodes"]:
-            add_unprocessed_node(layer, node_data)
+        self.layers[layer_config["name"]] = layer
+        calls = list(layer_config["inbound_nodes"])
+        if calls:
+            self.pending.append([layer, calls])
 
-    functional_config = {}
-    for key in ["layers", "input_layers", "output_layers"]:
-        functional_config[key] = config.pop(key)
-    for key in ["name", "trainable"]:
-        if key in config:
-            functional_config[key] = config.pop(key)
-        else:
-            functional_config[key] = None
+    def output_of(self, layer_name, node_index, tensor_index):
+        layer = self.layers.get(layer_name)
+        if layer is None:
+            raise ValueError(f"Unknown layer: {layer_name}")
+        if node_index >= len(layer._inbound_nodes):
+            raise _NotReady(layer_name)
+        return layer._inbound_nodes[node_index].output_tensors[tensor_index]
 
-    for layer_data in functional_config["layers"]:
-        process_layer(layer_data)
+    def _arguments(self, call):
+        """(args, kwargs) of a recorded call with tensor references replaced by the live tensors."""
+        from keras_b200.saving import serialization_lib
 
-    while unprocessed_nodes:
-        progressed = False
-        for layer_data in functional_config["layers"]:
-            layer = created_layers[layer_data["name"]]
-            if layer in unprocessed_nodes:
-                node_data_list = unprocessed_nodes[layer]
-                node_index = 0
-                while node_index < len(node_data_list):
-                    node_data = node_data_list[node_index]
+        if not call:
+            return [], {}
+        if isinstance(call, list):
+            # Keras 2: [[layer_name, node_index, tensor_index, kwargs?], ...]
+            tensors, kwargs = [], {}
+            for entry in call:
+                tensors.append(self.output_of(entry[0], entry[1], entry[2]))
+                if len(entry) == 4:
+                    kwargs = entry[3]
+            return [unpack_singleton(tensors)], kwargs
+
+        def revive(x):
+            history = getattr(x, "_pre_serialization_keras_history", None) if isinstance(x, KerasTensor) else None
+            return x if history is None else self.output_of(history[0], history[1], history[2])
+
+        args = tree.map_structure(revive, serialization_lib.deserialize_keras_object(call["args"]))
+        kwargs = tree.map_structure(revive, serialization_lib.deserialize_keras_object(call["kwargs"]))
+        return args, kwargs
+
+    def replay(self):
+        while self.pending:
+            ran_any = False
+            for entry in self.pending:
+                layer, calls = entry
+                while calls:
                     try:
-                        process_node(layer, node_data)
-                        progressed = True
-                    except IndexError:
+                        args, kwargs = self._arguments(calls[0])
+                    except _NotReady:
                         break
-                    node_index += 1
-                if node_index < len(node_data_list):
-                    unprocessed_nodes[layer] = node_data_list[node_index:]
-                else:
-                    del unprocessed_nodes[layer]
-        if not progressed and unprocessed_nodes:
-            raise ValueError("Could not rebuild the model graph from its config: some nodes depend on tensors that are never produced.")
+                    layer(*args, **kwargs)
+                    calls.pop(0)
+                    ran_any = True
+            self.pending = [entry for entry in self.pending if entry[1]]
+            if self.pending and not ran_any:
+                raise ValueError("Could not rebuild the model graph from its config: some nodes depend on tensors that are never produced.")
 
-    name = functional_config["name"]
-    trainable = functional_config["trainable"]
+    def endpoints(self, spec):
+        """Tensors named by an ``input_layers`` / ``output_layers`` entry: ``[name, node, tensor]`` triples in any nesting."""
+        if isinstance(spec, list) and len(spec) == 3 and isinstance(spec[0], str):
+            name, node_index, tensor_index = spec
+            if isinstance(self.layers.get(name), Functional):
+                node_index -= 1  # a nested model was called once more when it was built
+            return self.output_of(name, node_index, tensor_index)
+        if isinstance(spec, dict):
+            return {key: self.endpoints(value) for key, value in spec.items()}
+        if isinstance(spec, tuple):
+            return tuple(self.endpoints(value) for value in spec)
+        return [self.endpoints(value) for value in spec]
 
-    def get_tensor(layer_name, node_index, tensor_index):
-        assert layer_name in created_layers
-        layer = created_layers[layer_name]
-        if isinstance(layer, Functional):
-            node_index -= 1
-        layer_output_tensors = layer._inbound_nodes[node_index].output_tensors
-        return layer_output_tensors[tensor_index]
 
-    def map_tensors(tensors):
-        if isinstance(tensors, list) and len(tensors) == 3 and isinstance(tensors[0], str):
-            return get_tensor(*tensors)
-        if isinstance(tensors, dict):
-            return {k: map_tensors(v) for k, v in tensors.items()}
-        if isinstance(tensors, tuple):
-            return tuple(map_tensors(v) for v in tensors)
-        return [map_tensors(v) for v in tensors]
-
-    input_tensors = map_tensors(functional_config["input_layers"])
-    output_tensors = map_tensors(functional_config["output_layers"])
-    if isinstance(input_tensors, list) and len(input_tensors) == 1:
-        input_tensors = input_tensors[0]
-    if isinstance(output_tensors, list) and len(output_tensors) == 1:
-        output_tensors = output_tensors[0]
-    return cls(inputs=input_tensors, outputs=output_tensors, name=name, trainable=trainable, **config)
+def functional_from_config(cls, config, custom_objects=None):
+    """``cls`` instance rebuilt from ``Functional.get_config()`` output (schema of keras/src/models/functional.py:430-504)."""
+    layer_configs = config.pop("layers")
+    inputs_spec, outputs_spec = config.pop("input_layers"), config.pop("output_layers")
+    name, trainable = config.pop("name", None), config.pop("trainable", None)
+    replayer = _GraphReplayer(custom_objects)
+    for layer_config in layer_configs:
+        replayer.add_layer(layer_config)
+    replayer.replay()
+    inputs = unpack_singleton(replayer.endpoints(inputs_spec)) if isinstance(inputs_spec, list) else replayer.endpoints(inputs_spec)
+    outputs = unpack_singleton(replayer.endpoints(outputs_spec)) if isinstance(outputs_spec, list) else replayer.endpoints(outputs_spec)
+    return cls(inputs=inputs, outputs=outputs, name=name, trainable=trainable, **config)
 
 
 def _legacy_layer(layer_data, custom_objects):
@@ -438,48 +457,6 @@ def serialize_node(node, own_nodes=()):
     args = tree.map_structure(serialize_keras_tensor, node.arguments.args)
     kwargs = tree.map_structure(serialize_keras_tensor, node.arguments.kwargs)
     return {"args": serialization_lib.serialize_keras_object(args), "kwargs": serialization_lib.serialize_keras_object(kwargs)}
-
-
-def deserialize_node(node_data, created_layers):
-    from keras_b200.saving import serialization_lib
-
-    if not node_data:
-        return [], {}
-    if isinstance(node_data, list):
-        # Keras 2 format: [[layer_name, node_index, tensor_index, kwargs], ...]
-        input_tensors = []
-        for input_data in node_data:
-            inbound_layer_name, inbound_node_index, inbound_tensor_index = input_data[0], input_data[1], input_data[2]
-            kwargs = input_data[3] if len(input_data) == 4 else {}
-            inbound_layer = created_layers[inbound_layer_name]
-            if len(inbound_layer._inbound_nodes) <= inbound_node_index:
-                raise IndexError("Layer node index out of bounds.")
-            inbound_node = inbound_layer._inbound_nodes[inbound_node_index]
-            input_tensors.append(inbound_node.output_tensors[inbound_tensor_index])
-        return [unpack_singleton(input_tensors)], kwargs
-
-    args = serialization_lib.deserialize_keras_object(node_data["args"])
-    kwargs = serialization_lib.deserialize_keras_object(node_data["kwargs"])
-
-    def convert_revived_tensor(x):
-        if isinstance(x, KerasTensor):
-            history = x._pre_serialization_keras_history
-            if history is None:
-                return x
-            layer = created_layers.get(history[0], None)
-            if layer is None:
-                raise ValueError(f"Unknown layer: {history[0]}")
-            inbound_node_index = history[1]
-            inbound_tensor_index = history[2]
-            if len(layer._inbound_nodes) <= inbound_node_index:
-                raise IndexError(f"Layer node index out of bounds.\ninbound_layer = {layer}\ninbound_layer._inbound_nodes = {layer._inbound_nodes}\ninbound_node_index = {inbound_node_index}")
-            inbound_node = layer._inbound_nodes[inbound_node_index]
-            return inbound_node.output_tensors[inbound_tensor_index]
-        return x
-
-    args = tree.map_structure(convert_revived_tensor, args)
-    kwargs = tree.map_structure(convert_revived_tensor, kwargs)
-    return args, kwargs
 
 
 def is_input_keras_tensor(x):
