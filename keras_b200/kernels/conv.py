@@ -21,6 +21,7 @@ import os
 import torch
 
 from keras_b200.kernels import ops as kops
+from keras_b200.kernels import shadow
 from keras_b200.kernels.gemm import _err_flag
 
 _MIN_WORK = int(os.environ.get("KERAS_B200_CONV_MIN_FLOPS", str(1 << 24)))
@@ -146,10 +147,8 @@ class ConvFn(torch.autograd.Function):
                 _igemm(dy, (N, Ho, Wo, Cout), _nhwc_strides(Ho, Wo, Cout), w, dx, (H, W, Cin), _nhwc_strides(H, W, Cin),
                        (g.R, g.S, g.pt, -g.dh, g.pl, -g.dw), 1, Cin, Cout)
         if ctx.needs_input_grad[1]:
-            tgt = ctx.grad_target
-            acc = tgt.grad if tgt is not None else None
-            in_place = (not g.patch and acc is not None and acc.dtype == torch.float32 and acc.numel() == w.numel() and acc.is_contiguous()
-                        and not acc.requires_grad and acc.data_ptr() % 16 == 0)
+            acc = None if g.patch else shadow.grad_slot(ctx.grad_target, w.shape)
+            in_place = acc is not None
             if g.patch:
                 K = g.R * g.seg
                 M = N * Ho * Wo

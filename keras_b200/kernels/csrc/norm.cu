@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(NT) norm_bwd_warp_kernel(const T* __restrict__
 
 // Sums `nblocks` partial rows of D columns: 32 columns x 32 row groups per block, four loads in flight per thread.
 __global__ void __launch_bounds__(1024) norm_partial_reduce2_kernel(const float* __restrict__ pa, float* __restrict__ oa, const float* __restrict__ pb,
-                                                                    float* __restrict__ ob, int nblocks, int D) {
+                                                                    float* __restrict__ ob, int nblocks, int D, int accumulate) {
   __shared__ float tile[32][33];
   const float* partial = blockIdx.y == 0 ? pa : pb;
   float* out = blockIdx.y == 0 ? oa : ob;
@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(1024) norm_partial_reduce2_kernel(const float*
     float s = 0.f;
 #pragma unroll
     for (int r = 0; r < 32; ++r) s += tile[r][cx];
-    out[c] = s;
+    out[c] = accumulate ? out[c] + s : s;
   }
 }
 
@@ -374,12 +374,12 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restr
   }
 }
 
-__global__ void norm_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int D) {
+__global__ void norm_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int D, int accumulate) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= D) return;
   float s = 0.f;
   for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * D + i];
-  out[i] = s;
+  out[i] = accumulate ? out[i] + s : s;
 }
 
 KB_API int kb200_norm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, long long rows, int D, float eps,
@@ -428,9 +428,10 @@ KB_API int kb200_norm_bwd_blocks(long long rows) {
   return (int)(rows < b ? rows : b);
 }
 
-// partial_dgamma / partial_dbeta: scratch [kb200_norm_bwd_blocks(rows), D] fp32
+// partial_dgamma / partial_dbeta: scratch [kb200_norm_bwd_blocks(rows), D] fp32; accumulate != 0: dgamma and dbeta are added to
 KB_API int kb200_norm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx, float* partial_dgamma,
-                          float* partial_dbeta, float* dgamma, float* dbeta, long long rows, int D, int rms, int dtype, cudaStream_t stream) {
+                          float* partial_dbeta, float* dgamma, float* dbeta, long long rows, int D, int rms, int dtype, int accumulate,
+                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D > NORM_THREADS * 32) { kb200_set_error("norm_bwd: D too large (max 8192)"); return -2; }
   const int blocks = kb200_norm_bwd_blocks(rows);
@@ -471,7 +472,7 @@ KB_API int kb200_norm_bwd(const void* dy, const void* x, const float* gamma, con
       KB_CHECK_LAUNCH("norm_bwd");
       if (dgamma || (dbeta && partial_dbeta)) {
         dim3 grid((D + 31) / 32, 2);
-        norm_partial_reduce2_kernel<<<grid, 1024, 0, stream>>>(dgamma ? partial_dgamma : nullptr, dgamma, partial_dbeta, dbeta, blocks, D);
+        norm_partial_reduce2_kernel<<<grid, 1024, 0, stream>>>(dgamma ? partial_dgamma : nullptr, dgamma, partial_dbeta, dbeta, blocks, D, accumulate);
         KB_CHECK_LAUNCH("norm_partial_reduce");
       }
       return 0;
@@ -494,8 +495,8 @@ KB_API int kb200_norm_bwd(const void* dy, const void* x, const float* gamma, con
   }
 #undef LAUNCH
   KB_CHECK_LAUNCH("norm_bwd");
-  if (dgamma) norm_partial_reduce_kernel<<<(D + 127) / 128, 128, 0, stream>>>(partial_dgamma, dgamma, blocks, D);
-  if (dbeta && partial_dbeta) norm_partial_reduce_kernel<<<(D + 127) / 128, 128, 0, stream>>>(partial_dbeta, dbeta, blocks, D);
+  if (dgamma) norm_partial_reduce_kernel<<<(D + 127) / 128, 128, 0, stream>>>(partial_dgamma, dgamma, blocks, D, accumulate);
+  if (dbeta && partial_dbeta) norm_partial_reduce_kernel<<<(D + 127) / 128, 128, 0, stream>>>(partial_dbeta, dbeta, blocks, D, accumulate);
   KB_CHECK_LAUNCH("norm_partial_reduce");
   return 0;
 }
@@ -549,7 +550,9 @@ KB_API int kb200_colsum_slabs(long long rows, int cols, int dtype) {
 
 // x: [rows, cols] with row pitch ld (elements), cols a multiple of the 16-byte vector and rows 16-byte aligned;
 // partial: scratch [kb200_colsum_slabs(rows, cols, dtype), cols] fp32; out: [cols] fp32.
-KB_API int kb200_colsum(const void* x, long long ld, long long rows, int cols, float* partial, float* out, int dtype, cudaStream_t stream) {
+// accumulate != 0: out += the sums (a bias gradient added into persistent storage).
+KB_API int kb200_colsum(const void* x, long long ld, long long rows, int cols, float* partial, float* out, int dtype, int accumulate,
+                        cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   const int vn = dtype == 1 ? 8 : 4;
   if (cols % vn || ld % vn || ((uintptr_t)x & 15)) {
@@ -564,7 +567,7 @@ KB_API int kb200_colsum(const void* x, long long ld, long long rows, int cols, f
     colsum_partial_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ld, rows, cols, partial);
   KB_CHECK_LAUNCH("colsum");
   dim3 grid2((cols + 31) / 32, 1);
-  norm_partial_reduce2_kernel<<<grid2, 1024, 0, stream>>>(partial, out, nullptr, nullptr, slabs, cols);
+  norm_partial_reduce2_kernel<<<grid2, 1024, 0, stream>>>(partial, out, nullptr, nullptr, slabs, cols, accumulate);
   KB_CHECK_LAUNCH("colsum_reduce");
   return 0;
 }

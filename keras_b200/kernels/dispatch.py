@@ -216,16 +216,28 @@ def _plan_for(opt, grads, variables, slot_lists):
     from keras_b200.kernels import shadow
 
     shadows = shadow.shadows_for(variables)
-    plan = _ops().OptimizerPlan(params, list(grads), slots[0], slots[1] if len(slots) > 1 else None, shadows, [1.0] * len(params))
+    plan = _ops().OptimizerPlan(params, list(grads), slots[0], slots[1] if len(slots) > 1 else None, shadows, [0.0] * len(params))
     opt._fused_plan = (key, plan)
     return plan
 
 
-def _decays(opt, variables, lr):
+def _decays(opt, variables):
+    """Per-variable decoupled weight-decay coefficient (0 where the variable is excluded), or ``None`` without decay."""
     wd = opt.weight_decay
     if wd is None:
         return None
-    return [(1.0 - wd * lr) if opt._use_weight_decay(v) else 1.0 for v in variables]
+    return [float(wd) if opt._use_weight_decay(v) else 0.0 for v in variables]
+
+
+def _device_scalars(opt):
+    """(learning-rate tensor, iteration tensor) when both live on the device in the types the kernels read: the update
+    then takes its step scalars from device memory and a captured replay of it stays correct as they change."""
+    lr = getattr(opt._learning_rate, "_value", None)
+    it = getattr(opt._iterations, "_value", None)
+    if (isinstance(lr, torch.Tensor) and isinstance(it, torch.Tensor) and lr.is_cuda and it.is_cuda and lr.dtype == torch.float32
+            and it.dtype == torch.int32 and lr.numel() == 1 and it.numel() == 1):
+        return lr, it
+    return None, None
 
 
 def fused_sgd(opt, grads, variables, lr):
@@ -235,12 +247,14 @@ def fused_sgd(opt, grads, variables, lr):
     plan = _plan_for(opt, grads, variables, [slot0])
     if plan is None:
         return False
-    d = _decays(opt, variables, lr)
+    d = _decays(opt, variables)
     if d is not None:
         plan.set_decays(d)
     scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
-    plan.sgd(lr, opt.momentum, opt.nesterov, grad_scale=scale, zero_grad=True)
+    lr_t, _ = _device_scalars(opt)
+    plan.sgd(lr, opt.momentum, opt.nesterov, grad_scale=scale, zero_grad=True, lr_tensor=lr_t)
     opt._fused_zeroed_grads = True
+    opt._step_scalars_on_device = lr_t is not None
     return True
 
 
@@ -250,10 +264,15 @@ def fused_adam(opt, grads, variables, lr):
     plan = _plan_for(opt, grads, variables, [opt._momentums, opt._velocities])
     if plan is None:
         return False
-    d = _decays(opt, variables, lr)
+    d = _decays(opt, variables)
     if d is not None:
         plan.set_decays(d)
     scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
-    plan.adam(opt._alpha(lr), opt.beta_1, opt.beta_2, opt.epsilon, grad_scale=scale, zero_grad=True)
+    lr_t, step_t = _device_scalars(opt)
+    if lr_t is not None:
+        plan.adam(0.0, opt.beta_1, opt.beta_2, opt.epsilon, grad_scale=scale, zero_grad=True, lr_tensor=lr_t, step_tensor=step_t)
+    else:
+        plan.adam(opt._alpha(lr), opt.beta_1, opt.beta_2, opt.epsilon, lr=lr, grad_scale=scale, zero_grad=True)
     opt._fused_zeroed_grads = True
+    opt._step_scalars_on_device = lr_t is not None
     return True

@@ -15,12 +15,13 @@ import os
 import torch
 
 from keras_b200.kernels import ops as kops
+from keras_b200.kernels import shadow
 
 _ACT = {None: 0, "linear": 0, "relu": 1, "gelu_tanh": 2, "silu": 3, "swish": 3, "gelu_erf": 4}
 _ERR = {}
 _MIN_WORK = int(os.environ.get("KERAS_B200_GEMM_MIN_FLOPS", str(1 << 22)))
 # measured on GPT-2 (launch-bound step): 2 % slower than the bf16 gradient + one add, so off unless asked for
-_WGRAD_IN_PLACE = os.environ.get("KERAS_B200_WGRAD_IN_PLACE", "0") == "1"
+_WGRAD_IN_PLACE = os.environ.get("KERAS_B200_WGRAD_IN_PLACE", "1") == "1"
 
 
 def _err_flag(device):
@@ -102,12 +103,13 @@ class GemmFn(torch.autograd.Function):
     the padded output keeps its 16-byte row pitch and the caller sees its first ``N`` columns as a view."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, grad_target=None):
+    def forward(ctx, x, w, bias, grad_target=None, bias_target=None):
         """``grad_target``: the fp32 parameter behind ``w`` (its bf16 shadow) when its ``.grad`` is persistent fp32 storage: the
         weight gradient is then accumulated there by the GEMM itself and no bf16 gradient tensor is produced."""
         M, K = x.shape
         N = w.shape[1]
         ctx.grad_target = grad_target
+        ctx.bias_target = bias_target
         Np = (N + 7) // 8 * 8
         b32 = bias.float().contiguous() if bias is not None else None
         if Np != N:
@@ -143,18 +145,20 @@ class GemmFn(torch.autograd.Function):
             dx = gemm(dy, w, 0, 0, M, K, Np)
         if ctx.needs_input_grad[1]:
             split = split_k_for(K, Np, M, x.device)
-            tgt = ctx.grad_target
-            g = tgt.grad if tgt is not None else None
-            if (g is not None and Np == N and g.dtype == torch.float32 and g.numel() == K * N and g.is_contiguous() and not g.requires_grad
-                    and g.data_ptr() % 16 == 0 and N % 4 == 0):
+            g = shadow.grad_slot(ctx.grad_target, (K, N)) if Np == N and N % 4 == 0 else None
+            if g is not None:
                 gemm(x, dy, 1, 1, K, N, M, split_k=split, accumulate_into=g.view(K, N))  # dw stays None: already accumulated
             else:
                 dw = gemm(x, dy, 1, 1, K, Np, M, split_k=split)
                 if Np != N:
                     dw = dw[:, :N]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = kops.column_sum(dy)[:N].to(ctx.bias_dtype)
-        return (dx, dw, db, None)[: len(ctx.needs_input_grad)]
+            g = shadow.grad_slot(ctx.bias_target, (N,)) if Np == N else None
+            if g is not None:
+                kops.column_sum(dy, accumulate_into=g.view(N))  # db stays None: already accumulated
+            else:
+                db = kops.column_sum(dy)[:N].to(ctx.bias_dtype)
+        return (dx, dw, db, None, None)[: len(ctx.needs_input_grad)]
 
 
 def _qualifies(x2, w):
@@ -174,14 +178,14 @@ def matmul(a, b):
     a2 = a.reshape(-1, a.shape[-1])
     if not _qualifies(a2, b):
         return None
-    out = GemmFn.apply(a2, b, None, None)
+    out = GemmFn.apply(a2, b, None, None, None)
     return out.reshape(tuple(lead) + (b.shape[1],))
 
 
 def _grad_target(variable, w):
     """The fp32 parameter to accumulate the weight gradient into: only when ``w`` is the variable's bf16 shadow read."""
     p = getattr(variable, "_value", None)
-    if not _WGRAD_IN_PLACE or p is None or getattr(variable, "_shadow", None) is None or not p.requires_grad or p.dtype != torch.float32 or w.dtype != torch.bfloat16:
+    if not _WGRAD_IN_PLACE or variable is None or p is None or getattr(variable, "_shadow", None) is None or not p.requires_grad or p.dtype != torch.float32 or w.dtype != torch.bfloat16:
         return None
     if getattr(variable, "_shard_slices", None) is not None or p.numel() != w.numel():
         return None
@@ -218,5 +222,6 @@ def dense(x, kernel, bias, activation_name, kernel_shape=None):
             out = out[:, :N]
         return out.reshape(tuple(lead) + (N,)), fused_act
     target = _grad_target(kernel, w) if isinstance(kernel, Variable) else None
-    out = GemmFn.apply(x2, w, b, target)
+    bias_target = _grad_target(bias, b) if isinstance(bias, Variable) else None
+    out = GemmFn.apply(x2, w, b, target, bias_target)
     return out.reshape(tuple(lead) + (w.shape[1],)), activation_name in (None, "linear")

@@ -136,8 +136,8 @@ def bench_optim(args, flush):
     m = [torch.zeros(numel, device="cuda") for _ in range(n)]
     v = [torch.zeros(numel, device="cuda") for _ in range(n)]
     shadows = [torch.empty(numel, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
-    plan = kops.OptimizerPlan(params, grads, m, v, shadows, [1.0 - 3e-5] * n)
-    ours = lambda: plan.adam(3e-4, 0.9, 0.999, 1e-8, grad_scale=1.0, zero_grad=True)
+    plan = kops.OptimizerPlan(params, grads, m, v, shadows, [0.1] * n)
+    ours = lambda: plan.adam(3e-4, 0.9, 0.999, 1e-8, lr=3e-4, grad_scale=1.0, zero_grad=True)
     if args.once:
         ours()
         torch.cuda.synchronize()

@@ -10,6 +10,7 @@ _vp = ctypes.c_void_p
 _ll = ctypes.c_longlong
 _i = ctypes.c_int
 _f = ctypes.c_float
+_d = ctypes.c_double
 
 
 def _p(t):
@@ -51,6 +52,11 @@ _LAUNCHES = [0]
 def launch_count():
     """Number of kernel-launcher calls made by this process so far."""
     return _LAUNCHES[0]
+
+
+def add_launches(n):
+    """Account for launcher calls that ran without passing through Python (a replayed CUDA graph of them)."""
+    _LAUNCHES[0] += n
 
 
 def _check(code, what):
@@ -186,6 +192,9 @@ class FusedNorm(torch.autograd.Function):
         ctx.save_for_backward(x, g, stats)
         ctx.rms = rms
         ctx.has_beta = beta is not None
+        # fp32 leaf parameters handed in directly: their gradients can be added into persistent storage by the reduction
+        ctx.leaves = (gamma if gamma is not None and gamma.is_leaf and gamma.requires_grad else None,
+                      beta if beta is not None and beta.is_leaf and beta.requires_grad else None)
         ctx.gamma_dtype = gamma.dtype if gamma is not None else None
         ctx.beta_dtype = beta.dtype if beta is not None else None
         return y
@@ -203,10 +212,18 @@ class FusedNorm(torch.autograd.Function):
         nb = lib.kb200_norm_bwd_blocks(_ll(rows))
         pdg = torch.empty((nb, D), dtype=torch.float32, device=x.device)
         pdb = torch.empty((nb, D), dtype=torch.float32, device=x.device) if ctx.has_beta else None
+        from keras_b200.kernels import shadow
+
+        slot_g = shadow.grad_slot(ctx.leaves[0], (D,)) if g is not None else None
+        slot_b = shadow.grad_slot(ctx.leaves[1], (D,)) if ctx.has_beta else None
+        if g is not None and slot_g is not None and (slot_b is not None or not ctx.has_beta):
+            _check(lib.kb200_norm_bwd(_p(dy), _p(x), _p(g), _p(mean), _p(rstd), _p(dx), _p(pdg), _p(pdb), _p(slot_g), _p(slot_b), _ll(rows), _i(D),
+                                      _i(1 if ctx.rms else 0), _i(_dt(x)), _i(1), _stream()), "norm_bwd")
+            return dx, None, None, None, None
         dgamma = torch.empty(D, dtype=torch.float32, device=x.device) if g is not None else None
         dbeta = torch.empty(D, dtype=torch.float32, device=x.device) if ctx.has_beta else None
         _check(lib.kb200_norm_bwd(_p(dy), _p(x), _p(g), _p(mean), _p(rstd), _p(dx), _p(pdg), _p(pdb), _p(dgamma), _p(dbeta), _ll(rows), _i(D),
-                                  _i(1 if ctx.rms else 0), _i(_dt(x)), _stream()), "norm_bwd")
+                                  _i(1 if ctx.rms else 0), _i(_dt(x)), _i(0), _stream()), "norm_bwd")
         if dgamma is not None and ctx.gamma_dtype != torch.float32:
             dgamma = dgamma.to(ctx.gamma_dtype)
         if dbeta is not None and ctx.beta_dtype != torch.float32:
@@ -214,19 +231,22 @@ class FusedNorm(torch.autograd.Function):
         return dx, dgamma, dbeta, None, None
 
 
-def column_sum(x):
-    """fp32 sums over the rows of a 2-D bf16/fp32 CUDA tensor (bias gradients); falls back to torch for other layouts."""
+def column_sum(x, accumulate_into=None):
+    """fp32 sums over the rows of a 2-D bf16/fp32 CUDA tensor (bias gradients); falls back to torch for other layouts.
+    ``accumulate_into``: an fp32 vector the sums are added to (returned) instead of a fresh result."""
     vn = 8 if x.dtype == torch.bfloat16 else 4
     if (x.ndim != 2 or not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float32) or x.stride(1) != 1 or x.shape[1] % vn or x.stride(0) % vn
             or x.data_ptr() % 16 or x.shape[0] < 256):
-        return x.sum(0, dtype=torch.float32)
+        sums = x.sum(0, dtype=torch.float32)
+        return sums if accumulate_into is None else accumulate_into.add_(sums)
     lib = _lib()
     rows, cols = x.shape
     lib.kb200_colsum_slabs.restype = ctypes.c_int
     slabs = lib.kb200_colsum_slabs(_ll(rows), _i(cols), _i(_dt(x)))
     partial = torch.empty((slabs, cols), dtype=torch.float32, device=x.device)
-    out = torch.empty(cols, dtype=torch.float32, device=x.device)
-    _check(lib.kb200_colsum(_p(x), _ll(x.stride(0)), _ll(rows), _i(cols), _p(partial), _p(out), _i(_dt(x)), _stream()), "colsum")
+    out = torch.empty(cols, dtype=torch.float32, device=x.device) if accumulate_into is None else accumulate_into
+    _check(lib.kb200_colsum(_p(x), _ll(x.stride(0)), _ll(rows), _i(cols), _p(partial), _p(out), _i(_dt(x)), _i(0 if accumulate_into is None else 1),
+                            _stream()), "colsum")
     return out
 
 
@@ -303,7 +323,7 @@ class OptimizerPlan:
         self.keep = (params, grads, slot0, slot1, shadows)
 
     def set_decays(self, decays):
-        """Refresh per-tensor decay factors (they depend on the learning rate)."""
+        """Refresh the per-tensor weight-decay coefficients (0 for tensors excluded from decay)."""
         import numpy as np
 
         changed = False
@@ -314,15 +334,18 @@ class OptimizerPlan:
         if changed:
             self.desc.copy_(torch.from_numpy(self.desc_host.view(np.uint8).copy()), non_blocking=True)
 
-    def adam(self, alpha, beta1, beta2, eps, grad_scale=1.0, zero_grad=True, check_inf=False):
+    def adam(self, alpha, beta1, beta2, eps, lr=0.0, grad_scale=1.0, zero_grad=True, check_inf=False, lr_tensor=None, step_tensor=None):
+        """``lr_tensor`` (fp32 scalar) and ``step_tensor`` (int32 count of completed updates), both on the device: the kernel
+        reads them and derives the bias-corrected step size itself; ``alpha`` and ``lr`` are then ignored."""
         lib = _lib()
-        _check(lib.kb200_fused_adam(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _f(alpha), _f(beta1), _f(beta2), _f(eps), _f(grad_scale),
-                                    _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _stream()), "fused_adam")
+        _check(lib.kb200_fused_adam(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _f(alpha), _f(lr), _d(beta1), _d(beta2), _f(eps),
+                                    _f(grad_scale), _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _p(lr_tensor),
+                                    _p(step_tensor), _stream()), "fused_adam")
 
-    def sgd(self, lr, momentum, nesterov, grad_scale=1.0, zero_grad=True, check_inf=False):
+    def sgd(self, lr, momentum, nesterov, grad_scale=1.0, zero_grad=True, check_inf=False, lr_tensor=None):
         lib = _lib()
         _check(lib.kb200_fused_sgd(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _f(lr), _f(momentum), _i(1 if nesterov else 0), _f(grad_scale),
-                                   _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _stream()), "fused_sgd")
+                                   _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _p(lr_tensor), _stream()), "fused_sgd")
 
 
 def cast_f32_to_bf16(src, dst):

@@ -8,7 +8,46 @@ the fp32 parameter.
 
 import torch
 
-_ENABLED = False
+_arena_backward_depth = 0
+
+
+class arena_backward:
+    """Scope of a backward pass whose parameter gradients live in persistent fp32 storage bound to ``.grad`` (the
+    gradient arena).  Inside it, kernels that produce a weight gradient may add it into ``param.grad`` themselves and
+    send nothing back through autograd; outside it (``torch.autograd.grad`` in user code, say) they return gradients."""
+
+    def __enter__(self):
+        global _arena_backward_depth
+        _arena_backward_depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        global _arena_backward_depth
+        _arena_backward_depth -= 1
+        return False
+
+
+def in_arena_backward():
+    return _arena_backward_depth > 0
+
+
+def grad_slot(param, shape=None):
+    """``param.grad`` when a kernel may accumulate into it: inside ``arena_backward``, fp32, contiguous, 16-byte aligned."""
+    if _arena_backward_depth <= 0 or param is None:
+        return None
+    g = param.grad
+    if g is None or g.dtype != torch.float32 or g.requires_grad or not g.is_contiguous() or g.data_ptr() % 16:
+        return None
+    if shape is not None and g.numel() != _numel(shape):
+        return None
+    return g
+
+
+def _numel(shape):
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
 
 
 def shadows_for(variables):
@@ -38,10 +77,9 @@ class _ShadowRead(torch.autograd.Function):
     def backward(ctx, grad):
         if grad is None:
             return None, None
-        p = ctx.param
-        g = p.grad
-        if g is not None and g.dtype == torch.float32 and g.shape == grad.shape and not g.requires_grad:
-            g.add_(grad)
+        g = grad_slot(ctx.param, grad.shape)
+        if g is not None:
+            g.view(grad.shape).add_(grad)
             return None, None
         return grad.float(), None
 

@@ -1221,7 +1221,7 @@ class _NoAutocast:
 
 _NO_AUTOCAST = None
 # Trainer-owned objects that are reported through `Model.metrics` explicitly.
-_UNTRACKED_ATTRS = frozenset({"_loss_tracker", "_compile_metrics", "_compile_loss", "_compile_config", "_parallel_engine", "_grad_arena", "_device_stager", "history"})
+_UNTRACKED_ATTRS = frozenset({"_loss_tracker", "_compile_metrics", "_compile_loss", "_compile_config", "_parallel_engine", "_grad_arena", "_device_stager", "_graphed_step", "history"})
 _TRACK_EXTRA = ()
 
 

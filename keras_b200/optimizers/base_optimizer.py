@@ -111,6 +111,12 @@ class BaseOptimizer(KerasSaveable):
             self._host_step += 1
             self._host_step_version += 1
 
+    def _note_replayed_step(self):
+        """A captured replay of the update advanced ``iterations`` on the device (no Python-visible write): advance the
+        host mirror with it."""
+        self._step()
+        self._host_step += 1
+
     def _lr_float(self):
         """Learning rate as a Python float when it is a plain variable (else ``None``)."""
         lr = self._learning_rate
@@ -223,6 +229,7 @@ class BaseOptimizer(KerasSaveable):
     def apply(self, grads, trainable_variables=None):
         if len(grads) == 0:
             return
+        self._step_scalars_on_device = False  # set by a fused update that read its step scalars from device memory
         if trainable_variables is None:
             if not self.built:
                 raise ValueError("When passing `grads` without `variables`, the optimizer must already be built on a list of variables. Call `optimizer.build(trainable_variables)` first. ")

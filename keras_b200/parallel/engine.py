@@ -107,7 +107,10 @@ class DataParallelEngine:
             from keras_b200.kernels import shadow
 
             shadow.attach_for_model(model, trainable_weights)
-        loss.backward()
+            with shadow.arena_backward():
+                loss.backward()
+        else:
+            loss.backward()
         self._after_backward(trainable_weights)
         if self.world > 1:
             if self._reducer is not None:

@@ -78,8 +78,28 @@ def make_default_seed():
     return _py_random.randint(1, int(1e9))
 
 
+class CaptureUnsafe(RuntimeError):
+    """Raised when a seed is drawn while a training step is being recorded for replay: the seed is host state, and a
+    replay would repeat the recorded one."""
+
+
+_capture_depth = 0
+
+
+def begin_capture():
+    global _capture_depth
+    _capture_depth += 1
+
+
+def end_capture():
+    global _capture_depth
+    _capture_depth = max(0, _capture_depth - 1)
+
+
 def draw_seed(seed):
     """User-facing ``seed`` argument → integer seed for a ``torch.Generator``."""
+    if _capture_depth:
+        raise CaptureUnsafe("a random seed was drawn while the step was being recorded")
     if isinstance(seed, SeedGenerator):
         s = seed.next()
     elif isinstance(seed, int):

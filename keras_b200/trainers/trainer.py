@@ -117,6 +117,7 @@ class Trainer:
             self._compile_metrics = None
         # torch-style eager execution: a tracing compiler is never on the hot path
         self.jit_compile = False if jit_compile == "auto" else jit_compile
+        self._jit_request = jit_compile  # "auto" and True allow the step to be captured for replay; False forbids it
         self.run_eagerly = run_eagerly
         self.stop_training = False
         self.compiled = True
@@ -280,7 +281,13 @@ class Trainer:
                 if arena is None:
                     for p in params:
                         p.grad = None
-                loss.backward()
+                if arena is None:
+                    loss.backward()
+                else:
+                    from keras_b200.kernels import shadow
+
+                    with shadow.arena_backward():
+                        loss.backward()
                 grads = [p.grad for p in params]
                 opt = self.optimizer
                 opt._fused_zeroed_grads = False
@@ -368,14 +375,17 @@ class Trainer:
             return self.train_function
         self._ensure_parallel_engine()
 
-        def one_step_on_data(data):
-            data = data[0] if isinstance(data, list) and len(data) == 1 else data
-            return self.train_step(self._to_device(data))
+        step = self.train_step
+        self._graphed_step = None
+        if get_device().type == "cuda" and self._parallel_engine is None:
+            from keras_b200.trainers.graph_step import GraphedTrainStep
+
+            step = self._graphed_step = GraphedTrainStep(self)
 
         def multi_step(data_list):
             logs = None
             for data in data_list:
-                logs = self.train_step(self._to_device(data))
+                logs = step(self._to_device(data))
             return logs
 
         self.train_function = multi_step
