@@ -115,7 +115,11 @@ def convert_to_tensor(x, dtype=None, sparse=None, ragged=None):
     if isinstance(x, (bool, int, float, complex)):
         if td is None:
             td = TORCH_DTYPES[_python_dtype(x)]
-        return torch.as_tensor(x, dtype=td, device=get_device())
+        dev = get_device()
+        if dev.type == "cuda":
+            # a fill kernel instead of a copy from pageable host memory: asynchronous, and legal while a CUDA graph is recorded
+            return torch.full((), x, dtype=td, device=dev)
+        return torch.as_tensor(x, dtype=td, device=dev)
     if isinstance(x, np.ndarray) or isinstance(x, np.generic):
         if x.dtype == np.uint16:
             x = x.astype(np.int32)

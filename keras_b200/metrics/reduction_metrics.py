@@ -72,7 +72,9 @@ class Mean(Metric):
             num_samples = values.shape[0]
         else:
             num_samples = 1
-        self.count.assign_add(torch.as_tensor(num_samples, dtype=self.count._torch_dtype, device=self.count._value.device))
+        if not isinstance(num_samples, torch.Tensor):
+            num_samples = torch.full((), num_samples, dtype=self.count._torch_dtype, device=self.count._value.device)  # a fill: no host copy
+        self.count.assign_add(num_samples)
 
     def reset_state(self):
         self.total.assign(0)

@@ -21,6 +21,7 @@ capture off; ``jit_compile="auto"`` (the default) and ``True`` allow it.
 """
 
 import os
+import traceback
 import warnings
 
 import torch
@@ -28,6 +29,7 @@ import torch
 from keras_b200 import tree
 from keras_b200.kernels import ops as kops
 from keras_b200.random import seed_generator
+from keras_b200.trainers.data_adapters import data_adapter_utils
 
 _EAGER_STEPS_BEFORE_CAPTURE = 3
 
@@ -61,6 +63,8 @@ class GraphedTrainStep:
         self.out_packed = None       # one tensor holding every 0-dim floating output (snapshotted per replay)
         self.out_packed_index = None
         self.replays = 0
+        self.failure_traceback = None
+        self._stream = None
         self.launches_per_replay = 0
 
     # -- eligibility ---------------------------------------------------------------------
@@ -87,6 +91,7 @@ class GraphedTrainStep:
     def __call__(self, data):
         if self.disabled is not None:
             return self.model.train_step(data)
+        data = data_adapter_utils.unpack_x_y_sample_weight(data)  # (x, y) and (x, y, None) are the same batch
         leaves = tree.flatten(data)
         if not any(isinstance(leaf, torch.Tensor) and leaf.is_cuda for leaf in leaves):
             self.disabled = "inputs are not on a CUDA device"
@@ -100,13 +105,28 @@ class GraphedTrainStep:
             self._candidate, self._seen = sig, 0
         if self._seen < _EAGER_STEPS_BEFORE_CAPTURE:
             self._seen += 1
-            logs = self.model.train_step(data)
+            logs = self._eager_on_side_stream(data)
             if self._seen == _EAGER_STEPS_BEFORE_CAPTURE:
                 reason = self._why_not()
                 if reason is not None:
                     self.disabled = reason
             return logs
         return self._capture(data, leaves, sig)
+
+    def _eager_on_side_stream(self, data):
+        """The eager steps that precede capture run on the stream the capture will use: autograd's gradient-accumulation
+        nodes remember the stream they were made on, and one made on the default stream would tie the capture to it."""
+        if self._stream is None:
+            self._stream = torch.cuda.Stream()
+        main = torch.cuda.current_stream()
+        self._stream.wait_stream(main)
+        with torch.cuda.stream(self._stream):
+            logs = self.model.train_step(data)
+        main.wait_stream(self._stream)
+        for leaf in tree.flatten(data):
+            if isinstance(leaf, torch.Tensor) and leaf.is_cuda:
+                leaf.record_stream(self._stream)
+        return logs
 
     def _capture(self, data, leaves, sig):
         model = self.model
@@ -118,7 +138,7 @@ class GraphedTrainStep:
         launches_before = kops.launch_count()
         seed_generator.begin_capture()
         try:
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, stream=self._stream):
                 logs = model.train_step(static_data)
                 raw = dict(dict.items(logs)) if isinstance(logs, dict) else logs  # device scalars as they are: no read-back here
                 out_leaves = tree.flatten(raw)
@@ -128,6 +148,7 @@ class GraphedTrainStep:
         except Exception as e:  # capture ruled out: the step that was being captured has not run, so run it eagerly
             seed_generator.end_capture()
             self.disabled = f"capture failed: {type(e).__name__}: {e}"
+            self.failure_traceback = traceback.format_exc()
             del graph
             torch.cuda.synchronize()
             if not isinstance(e, seed_generator.CaptureUnsafe):

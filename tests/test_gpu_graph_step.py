@@ -47,7 +47,7 @@ def test_captured_step_matches_eager(policy, optimizer):
             losses["eager"].append(eager.train_on_batch(xb, yb))
             losses["graphed"].append(graphed.train_on_batch(xb, yb))
         assert eager._graphed_step.replays == 0
-        assert graphed._graphed_step.disabled is None, graphed._graphed_step.disabled
+        assert graphed._graphed_step.disabled is None, graphed._graphed_step.failure_traceback
         assert graphed._graphed_step.replays == 7
         np.testing.assert_allclose(np.array(losses["graphed"]), np.array(losses["eager"]), rtol=1e-5, atol=1e-6)
         for a, b in zip(graphed.get_weights(), eager.get_weights()):
@@ -64,7 +64,7 @@ def test_fit_with_short_last_batch_and_metrics():
     x, y = _data(128 * 5 + 48)
     history = model.fit(x, y, batch_size=128, epochs=3, verbose=0, shuffle=False)
     stepper = model._graphed_step
-    assert stepper.disabled is None, stepper.disabled
+    assert stepper.disabled is None, stepper.failure_traceback
     assert stepper.replays == 3 * 5 - 3          # three eager steps first; the short batches run eagerly as well
     assert int(model.optimizer.iterations.numpy()) == 3 * 6
     loss = history.history["loss"]
