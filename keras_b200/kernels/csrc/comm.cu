@@ -72,17 +72,23 @@ __device__ __forceinline__ float4 ld_peer(const float* p) { return __ldcv(reinte
 //   mode 3  broadcast        every arena := arena of rank `root`
 enum { COMM_ALLREDUCE = 0, COMM_REDUCE_SCATTER = 1, COMM_ALLGATHER = 2, COMM_BROADCAST = 3 };
 
+// The epoch of a collective is `epoch` plus, when `epoch_ctr` is given, the value of that device-side counter: the counter
+// holds the epoch of the last completed collective of this communicator and allreduce_wait_kernel advances it.  With the
+// counter in device memory the launch arguments are the same for every call, so a recorded (CUDA graph) step can be
+// replayed.
 __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(KbPeers peers, int rank, int world, long long n, float scale, unsigned epoch,
-                                                               unsigned long long timeout_ns, unsigned* status, int mode, int root) {
+                                                               const unsigned* epoch_ctr, unsigned long long timeout_ns, unsigned* status, int mode,
+                                                               int root) {
   unsigned* my_sig = peers.signal[rank];
+  if (epoch_ctr != nullptr) epoch += *epoch_ctr;
   // entry: tell every rank that this arena is complete, wait until every arena is
   if (blockIdx.x == 0 && (int)threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(peers.signal[threadIdx.x] + SIG_ENTRY + rank, epoch);
   }
-  if (!wait_flags(my_sig + SIG_ENTRY, world, epoch, timeout_ns, status, 1)) return;
+  const bool entered = wait_flags(my_sig + SIG_ENTRY, world, epoch, timeout_ns, status, 1);
 
-  const long long vecs = n / 4;
+  const long long vecs = entered ? n / 4 : 0;  // a rank that gave up moves no data but still keeps its block counter consistent
   const long long per = (vecs + world - 1) / world;
   long long lo = per * rank, hi = min(vecs, lo + per);
   if (mode == COMM_BROADCAST) {
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(KbPeers peers, i
   __syncthreads();
   if (last) {
     if (threadIdx.x == 0) my_sig[SIG_COUNTER] = 0u;
-    if ((int)threadIdx.x < world) {
+    if ((int)threadIdx.x < world && *(volatile unsigned*)status == 0u) {
       __threadfence_system();
       st_release_sys(peers.signal[threadIdx.x] + SIG_EXIT + rank, epoch);
     }
@@ -130,8 +136,12 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(KbPeers peers, i
 }
 
 // Waits until every rank has stored its slice (follows allreduce_twoshot_kernel on the same stream).
-__global__ void allreduce_wait_kernel(KbPeers peers, int rank, int world, unsigned epoch, unsigned long long timeout_ns, unsigned* status) {
-  wait_flags(peers.signal[rank] + SIG_EXIT, world, epoch, timeout_ns, status, 2);
+__global__ void allreduce_wait_kernel(KbPeers peers, int rank, int world, unsigned epoch, unsigned* epoch_ctr, unsigned long long timeout_ns,
+                                      unsigned* status) {
+  if (epoch_ctr != nullptr) epoch += *epoch_ctr;
+  if (*(volatile unsigned*)status == 0u) wait_flags(peers.signal[rank] + SIG_EXIT, world, epoch, timeout_ns, status, 2);
+  __syncthreads();
+  if (epoch_ctr != nullptr && threadIdx.x == 0) *epoch_ctr = epoch;  // also after a time-out: later calls must not reuse an epoch
 }
 
 }  // namespace
@@ -179,16 +189,18 @@ KB_API int kb200_ipc_free(void* ptr) {
 // of the arenas (same in every rank), `n` its length in floats; both multiples of 4.  status: one unsigned word
 // that the host can read (0 = fine).  The reduction is complete on `stream` when both kernels have run.
 KB_API int kb200_collective_p2p(void* const* bases, void* const* signals, int rank, int world, long long offset_floats, long long n, float scale,
-                                unsigned epoch, long long timeout_ms, unsigned* status, int mode, int root, cudaStream_t stream);
+                                unsigned epoch, unsigned* epoch_ctr, long long timeout_ms, unsigned* status, int mode, int root, cudaStream_t stream);
 
 KB_API int kb200_allreduce_p2p(void* const* bases, void* const* signals, int rank, int world, long long offset_floats, long long n, float scale,
                                unsigned epoch, long long timeout_ms, unsigned* status, cudaStream_t stream) {
-  return kb200_collective_p2p(bases, signals, rank, world, offset_floats, n, scale, epoch, timeout_ms, status, COMM_ALLREDUCE, 0, stream);
+  return kb200_collective_p2p(bases, signals, rank, world, offset_floats, n, scale, epoch, nullptr, timeout_ms, status, COMM_ALLREDUCE, 0, stream);
 }
 
 // mode: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 broadcast from `root` (see allreduce_twoshot_kernel).
+// epoch_ctr: optional device word owned by this rank's communicator; the call's epoch is then `epoch + *epoch_ctr` (pass
+// epoch = 1) and the counter is advanced on the device when the call completes.
 KB_API int kb200_collective_p2p(void* const* bases, void* const* signals, int rank, int world, long long offset_floats, long long n, float scale,
-                                unsigned epoch, long long timeout_ms, unsigned* status, int mode, int root, cudaStream_t stream) {
+                                unsigned epoch, unsigned* epoch_ctr, long long timeout_ms, unsigned* status, int mode, int root, cudaStream_t stream) {
   if (mode < 0 || mode > 3 || root < 0 || root >= world) { kb200_set_error("collective_p2p: bad mode or root"); return -2; }
   if (world < 1 || world > KB_MAX_RANKS) { kb200_set_error("allreduce_p2p: world size must be in [1, 16]"); return -2; }
   if ((n & 3) != 0 || (offset_floats & 3) != 0) { kb200_set_error("allreduce_p2p: offset and length must be multiples of 4 floats"); return -2; }
@@ -203,9 +215,9 @@ KB_API int kb200_collective_p2p(void* const* bases, void* const* signals, int ra
   if (blocks > 148 * 2) blocks = 148 * 2;
   if (blocks < 1) blocks = 1;
   const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
-  allreduce_twoshot_kernel<<<(int)blocks, 512, 0, stream>>>(peers, rank, world, n, scale, epoch, timeout_ns, status, mode, root);
+  allreduce_twoshot_kernel<<<(int)blocks, 512, 0, stream>>>(peers, rank, world, n, scale, epoch, epoch_ctr, timeout_ns, status, mode, root);
   KB_CHECK_LAUNCH("allreduce_twoshot");
-  allreduce_wait_kernel<<<1, 32, 0, stream>>>(peers, rank, world, epoch, timeout_ns, status);
+  allreduce_wait_kernel<<<1, 32, 0, stream>>>(peers, rank, world, epoch, epoch_ctr, timeout_ns, status);
   KB_CHECK_LAUNCH("allreduce_wait");
   return 0;
 }
@@ -216,7 +228,7 @@ KB_API int kb200_wait_selftest(unsigned* flag, unsigned* status, long long timeo
   KbPeers peers;
   for (int p = 0; p < KB_MAX_RANKS; ++p) { peers.base[p] = nullptr; peers.signal[p] = nullptr; }
   peers.signal[0] = flag - SIG_EXIT;
-  allreduce_wait_kernel<<<1, 32, 0, stream>>>(peers, 0, 1, 1u, (unsigned long long)timeout_ms * 1000000ull, status);
+  allreduce_wait_kernel<<<1, 32, 0, stream>>>(peers, 0, 1, 1u, nullptr, (unsigned long long)timeout_ms * 1000000ull, status);
   KB_CHECK_LAUNCH("wait_selftest");
   return 0;
 }

@@ -42,7 +42,8 @@ class P2PAllReducer:
         self.signals = SymmetricBuffer(256, group, ranks)
         self.flat = self.buffer.tensor(torch.float32)
         self.rank, self.world = self.buffer.rank, self.buffer.world
-        self.epoch = 0
+        self.epoch = 0  # host-side count of calls issued (bookkeeping); the epoch the kernels use lives in `epoch_ctr`
+        self.epoch_ctr = torch.zeros(1, dtype=torch.int32, device=self.flat.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.flat.device)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._status_event = None
@@ -52,13 +53,22 @@ class P2PAllReducer:
 
         lib = kops._lib()
         n = self.numel - offset if numel is None else int(numel)
-        self.check()
+        recording = torch.cuda.is_current_stream_capturing()
+        if not recording:
+            self.check()
         self.epoch += 1
+        # epoch argument 1 + device counter: identical launch arguments for every call, so a recorded step can be replayed
         kops._check(lib.kb200_collective_p2p(self.buffer.ptr_array, self.signals.ptr_array, ctypes.c_int(self.rank), ctypes.c_int(self.world),
-                                             ctypes.c_longlong(offset), ctypes.c_longlong(n), ctypes.c_float(scale), ctypes.c_uint(self.epoch),
-                                             ctypes.c_longlong(comm_timeout_ms()), ctypes.c_void_p(self.status.data_ptr()), ctypes.c_int(mode),
-                                             ctypes.c_int(root), kops._stream()),
+                                             ctypes.c_longlong(offset), ctypes.c_longlong(n), ctypes.c_float(scale), ctypes.c_uint(1),
+                                             ctypes.c_void_p(self.epoch_ctr.data_ptr()), ctypes.c_longlong(comm_timeout_ms()),
+                                             ctypes.c_void_p(self.status.data_ptr()), ctypes.c_int(mode), ctypes.c_int(root), kops._stream()),
                     "collective_p2p")
+        if not recording:
+            self.post_status()
+
+    def post_status(self):
+        """Queue a copy of the device status word to the host (read by ``check`` once it has landed).  A replayed recording
+        of collectives calls this after each replay: events cannot be recorded for later queries inside a recording."""
         self._status_host.copy_(self.status, non_blocking=True)
         self._status_event = torch.cuda.Event()
         self._status_event.record()

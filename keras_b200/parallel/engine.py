@@ -39,6 +39,7 @@ class DataParallelEngine:
         self.world = len(self.members) if process_groups.is_initialized() else 1
         self._arena = None
         self._reducer = None
+        self._metric_reducer = None
         self._steps = 0
         self._synced_ids = set()
         self.sync_variables(model)
@@ -138,8 +139,10 @@ class DataParallelEngine:
         if self.world <= 1 or not vs:
             return []
         with torch.no_grad():
-            flat = torch.cat([v._value.detach().reshape(-1).to(torch.float64) for v in vs])
-            collectives.all_reduce(flat, group=self.group)
+            flat = self._reduce_metric_state_p2p(vs)
+            if flat is None:
+                flat = torch.cat([v._value.detach().reshape(-1).to(torch.float64) for v in vs])
+                collectives.all_reduce(flat, group=self.group)
             out, off = [], 0
             for v in vs:
                 n = v._value.numel()
@@ -147,14 +150,47 @@ class DataParallelEngine:
                 off += n
         return out
 
+    def _reduce_metric_state_p2p(self, vs):
+        """Metric state summed over replicas by this package's all-reduce kernel on a small symmetric buffer (fp32), or
+        ``None`` when gradients do not use that path either.  No library collective, so the step stays recordable."""
+        if self._reducer is None or not all(v._value.is_cuda for v in vs):
+            return None
+        n = sum(v._value.numel() for v in vs)
+        mr = self._metric_reducer
+        if mr is None or mr.numel < n:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("metric state grew while the step was being recorded")
+            if mr is not None:
+                mr.close()
+            mr = self._metric_reducer = collectives.P2PAllReducer(max(1024, 2 * n), self.group, self.members)
+            mr.flat.zero_()
+        padded = (n + 3) // 4 * 4
+        torch.cat([v._value.detach().reshape(-1).float() for v in vs], out=mr.flat[:n])
+        mr.all_reduce(0, padded)
+        return mr.flat[:n]
+
+    def recordable(self):
+        """True when every collective of a training step is one of this package's kernels with device-side epochs."""
+        return self.world <= 1 or self._reducer is not None
+
+    def after_replay(self):
+        """A recorded step was replayed: queue the status read-backs that the recorded collectives could not."""
+        for r in (self._reducer, self._metric_reducer):
+            if r is not None:
+                r.post_status()
+
     def sync_metrics(self, model):
         return self.reduced_metric_state(model)
 
     def check(self, wait=False):
-        if self._reducer is not None:
-            self._reducer.check(wait=wait)
+        for r in (self._reducer, self._metric_reducer):
+            if r is not None:
+                r.check(wait=wait)
 
     def close(self):
+        if self._metric_reducer is not None:
+            self._metric_reducer.close()
+            self._metric_reducer = None
         if self._reducer is not None:
             self._reducer.close()
             self._reducer = None

@@ -12,7 +12,11 @@ What makes the step replayable:
   new learning rate or advancing the counter needs no re-capture;
 * metric state lives in device variables that are updated in place.
 
-A step is captured only when all of this holds: the model runs on one CUDA device without a parallel engine,
+Data-parallel steps are recordable too: the gradient and metric all-reduces are this package's peer-memory kernels,
+whose epoch lives in a device counter, so their launch arguments never change; their status words are read back after
+each replay.
+
+A step is captured only when all of this holds: the model runs on CUDA devices (alone, or data parallel on those kernels),
 ``train_step`` is the stock one, the optimizer took its fused path with device-resident step scalars, and the batch
 signature (shapes, dtypes) repeats.  A batch with another signature (the short last batch of an epoch) runs eagerly on
 the same variables.  Drawing from a seeded random generator during capture aborts it (the seed is host state that a
@@ -76,14 +80,15 @@ class GraphedTrainStep:
             return "switched off by KERAS_B200_CUDA_GRAPHS=0"
         if getattr(model, "_jit_request", "auto") is False or model.run_eagerly:
             return "jit_compile=False or run_eagerly=True"
-        if getattr(model, "_parallel_engine", None) is not None:
-            return "a parallel engine owns the step"
+        engine = getattr(model, "_parallel_engine", None)
+        if engine is not None and not (type(engine).__name__ == "DataParallelEngine" and engine.recordable()):
+            return "the parallel engine's collectives cannot be recorded (library collectives, or model parallelism)"
         if type(model).train_step is not Trainer.train_step:
             return "train_step is overridden"
         opt = model.optimizer
         if opt is None or not getattr(opt, "_step_scalars_on_device", False) or not getattr(opt, "_fused_zeroed_grads", False):
             return "the optimizer update is not the fused one with device-resident step scalars"
-        if getattr(model, "_grad_arena", None) is None:
+        if getattr(model, "_grad_arena", None) is None and engine is None:
             return "no persistent gradient storage"
         return None
 
@@ -178,7 +183,12 @@ class GraphedTrainStep:
             for dst, src in zip(self.static_leaves, leaves):
                 if isinstance(dst, torch.Tensor):
                     dst.copy_(src, non_blocking=True)
+        engine = getattr(self.model, "_parallel_engine", None)
+        if engine is not None:
+            engine.check()
         self.graph.replay()
+        if engine is not None:
+            engine.after_replay()
         self.replays += 1
         kops.add_launches(self.launches_per_replay)
         self.model.optimizer._note_replayed_step()

@@ -377,7 +377,7 @@ class Trainer:
 
         step = self.train_step
         self._graphed_step = None
-        if get_device().type == "cuda" and self._parallel_engine is None:
+        if get_device().type == "cuda":
             from keras_b200.trainers.graph_step import GraphedTrainStep
 
             step = self._graphed_step = GraphedTrainStep(self)

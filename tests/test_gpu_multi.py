@@ -149,6 +149,53 @@ def test_data_parallel_replicas_stay_identical():
     np.testing.assert_allclose(out[0]["losses"], out[1]["losses"], rtol=1e-5)
 
 
+def _dp_graph_worker(rank, world):
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    keras.distribution.set_distribution(keras.distribution.DataParallel())
+
+    def make(jit):
+        keras.utils.set_random_seed(11)
+        m = keras.Sequential([keras.layers.Input((32,)), keras.layers.Dense(64, activation="relu"), keras.layers.LayerNormalization(),
+                              keras.layers.Dense(5)])
+        m.compile(optimizer=keras.optimizers.Adam(1e-2), loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True), metrics=["accuracy"],
+                  jit_compile=jit)
+        return m
+
+    eager, graphed = make(False), make("auto")
+    rng = np.random.RandomState(rank)
+    xs, ys = rng.randn(4, 16, 32).astype("float32"), rng.randint(0, 5, (4, 16))
+    rows = {"eager": [], "graphed": []}
+    for step in range(8):
+        rows["eager"].append(eager.train_on_batch(xs[step % 4], ys[step % 4]))
+        rows["graphed"].append(graphed.train_on_batch(xs[step % 4], ys[step % 4]))
+    for m in (eager, graphed):
+        m._parallel_engine.check(wait=True)
+    out = {"eager": np.array(rows["eager"]), "graphed": np.array(rows["graphed"]), "replays": np.array(graphed._graphed_step.replays),
+           "disabled": np.array(str(graphed._graphed_step.failure_traceback or graphed._graphed_step.disabled)),
+           "eager_replays": np.array(eager._graphed_step.replays)}
+    for i, (a, b) in enumerate(zip(eager.get_weights(), graphed.get_weights())):
+        out[f"e{i}"], out[f"g{i}"] = a, b
+    for m in (eager, graphed):
+        m._parallel_engine.close()
+    return out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_data_parallel_step_replays_as_cuda_graph():
+    codes, out = _spawn("_dp_graph_worker", 2)
+    assert codes == [0, 0], codes
+    for r in (0, 1):
+        assert str(out[r]["disabled"]) == "None", str(out[r]["disabled"])
+        assert int(out[r]["replays"]) == 5 and int(out[r]["eager_replays"]) == 0
+        np.testing.assert_allclose(out[r]["graphed"], out[r]["eager"], rtol=1e-5, atol=1e-6)
+        for k in [k for k in out[r] if k.startswith("e") and k[1:].isdigit()]:
+            np.testing.assert_allclose(out[r]["g" + k[1:]], out[r][k], rtol=1e-5, atol=1e-6)
+    # loss and accuracy are the replica means: both ranks log the same numbers
+    np.testing.assert_allclose(out[0]["graphed"], out[1]["graphed"], rtol=1e-6)
+
+
 def test_bounded_wait_reports_timeout_and_context_survives():
     from keras_b200.kernels import ops as kops
 
