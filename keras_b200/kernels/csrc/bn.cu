@@ -31,6 +31,15 @@ struct Vec<float> {
   __device__ static void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
 };
 
+// bn_stream.cu: the two-input passes on a shared-memory ring fed by bulk copies (bf16); returns 1 when it does not apply
+int kb200_bn_stream_launch(int mode, const void* in0, const void* in1, const unsigned char* bits_in, void* out0, void* out1, unsigned char* bits_out,
+                           const float* p0, const float* p1, const float* p2, float* sums, long long M, int C, int relu, cudaStream_t stream);
+
+template <typename T>
+struct IsBf16 { static constexpr bool value = false; };
+template <>
+struct IsBf16<__nv_bfloat16> { static constexpr bool value = true; };
+
 constexpr int BN_THREADS = 256;
 constexpr int BN_U = 4;  // rows in flight per thread (apply and backward-reduce kernels)
 
@@ -341,6 +350,10 @@ static int bn_reduce_launch(int mode, const void* x, const void* dy, const void*
     bn_reduce_kernel<T, 0, U0><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, M, C,
                                                                            ilog2(g.cx), sums);
   } else {
+    if (IsBf16<T>::value && y == nullptr) {
+      const int rc = kb200_bn_stream_launch(1, dy, x, bits, nullptr, nullptr, nullptr, mean, invstd, nullptr, sums, M, C, 0, stream);
+      if (rc <= 0) return rc;
+    }
     static const int resident = bn_resident_blocks(bn_reduce_kernel<T, 1, BN_U>);
     const BnGeom g = bn_geom(M, C / V, resident, BN_U);
     bn_reduce_kernel<T, 1, BN_U><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, (const T*)dy, (const T*)y, bits, mean, invstd, M, C,
@@ -393,6 +406,10 @@ static int bn_apply_launch(const void* x, const void* res, void* y, unsigned cha
     KB_CHECK_LAUNCH("bn_apply");
     return 0;
   }
+  if (IsBf16<T>::value) {
+    const int rc = kb200_bn_stream_launch(0, x, res, nullptr, y, nullptr, bits, scale, shift, nullptr, nullptr, M, C, relu, stream);
+    if (rc <= 0) return rc;
+  }
   static const int resident = bn_resident_blocks(bn_apply_kernel<T, 0>);
   const BnGeom g = bn_geom(M, C / V, resident, BN_U);
   bn_apply_kernel<T, 0><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)x, (const T*)res, nullptr, bits, (T*)y, nullptr, scale, shift,
@@ -425,6 +442,10 @@ template <typename T>
 static int bn_bwd_apply_launch(const void* dy, const void* x, const void* y, const unsigned char* bits, const float* coef, void* dx, void* dres,
                                long long M, int C, cudaStream_t stream) {
   constexpr int V = Vec<T>::N;
+  if (IsBf16<T>::value && y == nullptr) {
+    const int rc = kb200_bn_stream_launch(2, dy, x, bits, dx, dres, nullptr, coef, coef + C, coef + 2 * C, nullptr, M, C, 0, stream);
+    if (rc <= 0) return rc;
+  }
   static const int resident = bn_resident_blocks(bn_apply_kernel<T, 1>);
   const BnGeom g = bn_geom(M, C / V, resident, BN_U);
   bn_apply_kernel<T, 1><<<dim3(g.gx, g.gy), BN_THREADS, 0, stream>>>((const T*)dy, (const T*)x, (const T*)y, const_cast<unsigned char*>(bits),

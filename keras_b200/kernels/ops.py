@@ -54,6 +54,18 @@ def launch_count():
     return _LAUNCHES[0]
 
 
+def check_stream_kernels():
+    """Raise if a bounded wait ran out inside a bulk-copy ring kernel (BatchNorm streaming passes) since the last check.
+    Synchronises the device."""
+    lib = loader.get()
+    if lib is None or not hasattr(lib, "kb200_bn_stream_status"):
+        return
+    lib.kb200_bn_stream_status.restype = ctypes.c_int
+    code = lib.kb200_bn_stream_status()
+    if code > 0:
+        raise RuntimeError(f"a BatchNorm streaming kernel gave up waiting on its copy pipeline (wait {code}); results of that pass are incomplete")
+
+
 def add_launches(n):
     """Account for launcher calls that ran without passing through Python (a replayed CUDA graph of them)."""
     _LAUNCHES[0] += n

@@ -582,6 +582,9 @@ class Trainer:
 
             kgemm.check_errors()
             kattention.check_errors()
+            from keras_b200.kernels import ops as kops
+
+            kops.check_stream_kernels()
 
     def train_on_batch(self, x, y=None, sample_weight=None, class_weight=None, return_dict=False):
         self._assert_compile_called("train_on_batch")

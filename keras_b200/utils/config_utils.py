@@ -1,41 +1,59 @@
-"""``keras.utils.Config``: attribute-style, JSON-serialisable, freezable configuration record
-(keras/src/utils/config.py:12-190)."""
+"""``keras.utils.Config``: a record of named settings that reads like an object (``cfg.lr``) and like a mapping
+(``cfg["lr"]``), serialises to JSON and can be frozen against changes (behaviour of keras/src/utils/config.py:12-190).
 
-import copy
+The entries live in one dict kept under a private slot of the instance; everything that is not one of the instance's own
+two slots is an entry, so no table of reserved attribute names is needed.
+"""
+
 import difflib
 import json
+from collections.abc import MutableMapping
 
 from keras_b200.core.export_registry import keras_export
 
+_SLOTS = ("_config", "_frozen")
+
 
 @keras_export("keras.utils.Config")
-class Config:
-    __attrs__ = None
+class Config(MutableMapping):
+    def __init__(self, **entries):
+        vars(self)["_config"] = dict(entries)
+        vars(self)["_frozen"] = False
 
-    def __init__(self, **kwargs):
-        self._config = kwargs
-        self._frozen = False
-        self.__attrs__ = set(dir(self))
-
+    # -- freezing ------------------------------------------------------------------------
     @property
     def frozen(self):
         return self._frozen
 
     def freeze(self):
-        self._frozen = True
+        vars(self)["_frozen"] = True
 
     def unfreeze(self):
-        self._frozen = False
+        vars(self)["_frozen"] = False
 
-    def _raise_if_frozen(self):
+    def _writable(self):
         if self._frozen:
             raise ValueError("Cannot mutate attribute(s) because the config is frozen.")
+        return self._config
 
-    def as_dict(self):
-        return copy.copy(self._config)
+    # -- mapping protocol (MutableMapping derives pop, update, get, keys, values, items, __contains__ from these) ---
+    def __getitem__(self, key):
+        return self._config[key]
 
-    def to_json(self):
-        return json.dumps(self._config)
+    def __setitem__(self, key, value):
+        self._writable()[key] = value
+
+    def __delitem__(self, key):
+        del self._writable()[key]
+
+    def __iter__(self):
+        return iter(sorted(self._config))
+
+    def __len__(self):
+        return len(self._config)
+
+    def __contains__(self, key):
+        return key in self._config
 
     def keys(self):
         return self._config.keys()
@@ -46,57 +64,36 @@ class Config:
     def items(self):
         return self._config.items()
 
-    def pop(self, *args):
-        self._raise_if_frozen()
-        return self._config.pop(*args)
-
-    def update(self, *args, **kwargs):
-        self._raise_if_frozen()
-        return self._config.update(*args, **kwargs)
-
     def get(self, keyname, value=None):
         return self._config.get(keyname, value)
 
-    def __setattr__(self, name, value):
-        attrs = object.__getattribute__(self, "__attrs__")
-        if attrs is None or name in attrs:
-            return object.__setattr__(self, name, value)
-        self._raise_if_frozen()
-        self._config[name] = value
+    def pop(self, *args):
+        return self._writable().pop(*args)
 
+    def update(self, *args, **kwargs):
+        return self._writable().update(*args, **kwargs)
+
+    # -- attribute protocol --------------------------------------------------------------
     def __getattr__(self, name):
-        attrs = object.__getattribute__(self, "__attrs__")
-        if attrs is None or name in attrs:
-            return object.__getattribute__(self, name)
-        if name in self._config:
-            return self._config[name]
-        msg = f"Unknown attribute: '{name}'."
-        matches = difflib.get_close_matches(name, self._config.keys(), n=1, cutoff=0.7)
-        if matches:
-            msg += f" Did you mean '{matches[0]}'?"
-        raise AttributeError(msg)
+        # reached only when normal lookup failed: the name is an entry or a mistake
+        entries = vars(self).get("_config", {})
+        if name in entries:
+            return entries[name]
+        hint = difflib.get_close_matches(name, list(entries), n=1, cutoff=0.7)
+        raise AttributeError(f"Unknown attribute: '{name}'." + (f" Did you mean '{hint[0]}'?" if hint else ""))
 
-    def __setitem__(self, key, item):
-        self._raise_if_frozen()
-        self._config[key] = item
+    def __setattr__(self, name, value):
+        if name in _SLOTS or isinstance(getattr(type(self), name, None), property):
+            object.__setattr__(self, name, value)
+        else:
+            self._writable()[name] = value
 
-    def __getitem__(self, key):
-        return self._config[key]
+    # -- export --------------------------------------------------------------------------
+    def as_dict(self):
+        return dict(self._config)
+
+    def to_json(self):
+        return json.dumps(self._config)
 
     def __repr__(self):
         return f"<Config {self._config}>"
-
-    def __iter__(self):
-        keys = sorted(self._config.keys())
-        for k in keys:
-            yield k
-
-    def __len__(self):
-        return len(self._config)
-
-    def __delitem__(self, key):
-        self._raise_if_frozen()
-        del self._config[key]
-
-    def __contains__(self, item):
-        return item in self._config

@@ -50,6 +50,43 @@ def test_fused_batchnorm_forward_backward(dtype, tol, relu, res):
     assert torch.allclose(mv, 0.9 + 0.1 * var.detach(), atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("rows,C", [(40000 + 37, 64), (9000 + 5, 256), (1500 + 3, 2048), (300000 + 1, 8)])
+@pytest.mark.parametrize("relu,res", [(True, True), (True, False), (False, False)])
+def test_batchnorm_streaming_passes(rows, C, relu, res):
+    """Shapes large enough for the bulk-copy ring kernels (two-input passes), with a ragged last tile."""
+    from keras_b200.kernels import ops as kops
+
+    torch.manual_seed(3)
+    x = (torch.randn(rows, C, device="cuda") * 1.5 + 0.25).bfloat16().requires_grad_(True)
+    r = torch.randn(rows, C, device="cuda").bfloat16().requires_grad_(True) if res else None
+    gamma = (torch.rand(C, device="cuda") + 0.5).requires_grad_(True)
+    beta = torch.randn(C, device="cuda").requires_grad_(True)
+    mm, mv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    y = kops.FusedBatchNormAct.apply(x, gamma, beta, r, mm, mv, 0.9, 1e-3, relu)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_(True)
+    rf = r.detach().float().requires_grad_(True) if res else None
+    gf, bf = gamma.detach().clone().requires_grad_(True), beta.detach().clone().requires_grad_(True)
+    mean = xf.mean(0)
+    var = (xf * xf).mean(0) - mean * mean
+    ref = (xf - mean) * torch.rsqrt(var + 1e-3) * gf + bf
+    if res:
+        ref = ref + rf
+    if relu:
+        ref = torch.relu(ref)
+    ref.backward(dy.float())
+    assert kops._lib().kb200_bn_stream_status() == 0
+    torch.testing.assert_close(y.float(), ref, atol=6e-2, rtol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xf.grad, atol=6e-2, rtol=6e-2)
+    scale = float(rows) ** 0.5
+    torch.testing.assert_close(gamma.grad, gf.grad, atol=0.05 * scale, rtol=3e-2)
+    torch.testing.assert_close(beta.grad, bf.grad, atol=0.05 * scale, rtol=3e-2)
+    if res:
+        # the residual branch receives the masked gradient unchanged, bit for bit
+        assert torch.equal(r.grad, torch.where(y > 0, dy, torch.zeros_like(dy)) if relu else dy)
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("rms", [False, True])
 @pytest.mark.parametrize("D", [64, 768, 1000, 1001, 2048, 4096, 8192])
