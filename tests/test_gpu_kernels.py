@@ -73,12 +73,15 @@ def test_batchnorm_streaming_passes(rows, C, relu, res):
     ref = (xf - mean) * torch.rsqrt(var + 1e-3) * gf + bf
     if res:
         ref = ref + rf
+    # where the pre-activation is within rounding of zero the two sides may disagree about the ReLU mask: leave those out
+    sure = (ref.detach().abs() > 3e-2) if relu else torch.ones_like(ref, dtype=torch.bool)
     if relu:
         ref = torch.relu(ref)
     ref.backward(dy.float())
     assert kops._lib().kb200_bn_stream_status() == 0
     torch.testing.assert_close(y.float(), ref, atol=6e-2, rtol=2e-2)
-    torch.testing.assert_close(x.grad.float(), xf.grad, atol=6e-2, rtol=6e-2)
+    assert float(sure.float().mean()) > 0.95
+    torch.testing.assert_close(torch.where(sure, x.grad.float(), xf.grad), xf.grad, atol=6e-2, rtol=6e-2)
     scale = float(rows) ** 0.5
     torch.testing.assert_close(gamma.grad, gf.grad, atol=0.05 * scale, rtol=3e-2)
     torch.testing.assert_close(beta.grad, bf.grad, atol=0.05 * scale, rtol=3e-2)
