@@ -244,10 +244,14 @@ __global__ void bn_finalize_partials_kernel(const float* __restrict__ partials, 
 }
 
 // Backward coefficients: dx = A*dy' + B*x + Cc
+// dgamma_acc / dbeta_acc (optional): persistent gradient storage of gamma and beta; the sums are added there as well
 __global__ void bn_bwd_coeff_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
-                                    const float* __restrict__ invstd, float inv_m, int C, float* __restrict__ coef) {
+                                    const float* __restrict__ invstd, float inv_m, int C, float* __restrict__ coef, float* __restrict__ dgamma_acc,
+                                    float* __restrict__ dbeta_acc) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
+  if (dgamma_acc != nullptr) dgamma_acc[c] += sums[C + c];
+  if (dbeta_acc != nullptr) dbeta_acc[c] += sums[c];
   const float g = gamma ? gamma[c] : 1.f, is = invstd[c], mu = mean[c];
   const float s1 = sums[c] * inv_m, s2 = sums[C + c] * inv_m;
   const float a = g * is;
@@ -456,10 +460,10 @@ static int bn_bwd_apply_launch(const void* dy, const void* x, const void* y, con
 
 static int bn_bwd_apply_any(const void* dy, const void* x, const void* y, const unsigned char* bits, const float* mean, const float* invstd,
                             const float* gamma, const float* sums, float* coef, void* dx, void* dres, long long M, int C, int dtype,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, float* dgamma_acc = nullptr, float* dbeta_acc = nullptr) {
   const int V = dtype == 1 ? 8 : 4;
   if (C % V != 0) { kb200_set_error("bn: C must be a multiple of the vector width"); return -2; }
-  bn_bwd_coeff_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, mean, invstd, 1.f / (float)M, C, coef);
+  bn_bwd_coeff_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, gamma, mean, invstd, 1.f / (float)M, C, coef, dgamma_acc, dbeta_acc);
   KB_CHECK_LAUNCH("bn_bwd_coeff");
   return dtype == 1 ? bn_bwd_apply_launch<__nv_bfloat16>(dy, x, y, bits, coef, dx, dres, M, C, stream)
                     : bn_bwd_apply_launch<float>(dy, x, y, bits, coef, dx, dres, M, C, stream);
@@ -482,4 +486,12 @@ KB_API int kb200_bn_bwd_apply_mask(const void* dy, const void* x, const unsigned
                                    const float* gamma, const float* sums, float* coef, void* dx, void* dres, long long M, int C, int dtype,
                                    cudaStream_t stream) {
   return bn_bwd_apply_any(dy, x, nullptr, bits, mean, invstd, gamma, sums, coef, dx, dres, M, C, dtype, stream);
+}
+
+// As kb200_bn_bwd_apply_mask; in addition the gradients of gamma and beta are ADDED into dgamma_acc / dbeta_acc (fp32 [C],
+// either may be null): persistent gradient storage, so that no separate accumulation kernel runs.
+KB_API int kb200_bn_bwd_apply_mask_acc(const void* dy, const void* x, const unsigned char* bits, const float* mean, const float* invstd,
+                                       const float* gamma, const float* sums, float* coef, void* dx, void* dres, float* dgamma_acc,
+                                       float* dbeta_acc, long long M, int C, int dtype, cudaStream_t stream) {
+  return bn_bwd_apply_any(dy, x, nullptr, bits, mean, invstd, gamma, sums, coef, dx, dres, M, C, dtype, stream, dgamma_acc, dbeta_acc);
 }

@@ -149,6 +149,9 @@ class FusedBatchNormAct(torch.autograd.Function):
         else:
             _check(lib.kb200_bn_apply(_p(x), _p(res), _p(y), _p(scale), _p(shift), _ll(M), _i(C), _i(0), _i(dt), st), "bn_apply")
         ctx.save_for_backward(x, bits, gamma, stats)
+        # fp32 leaf parameters: their gradients can be added into persistent storage by the coefficient kernel
+        ctx.leaves = (gamma if gamma is not None and gamma.is_leaf and gamma.requires_grad else None,
+                      beta if beta is not None and beta.is_leaf and beta.requires_grad else None)
         ctx.relu = relu
         ctx.has_res = residual is not None
         ctx.dims = (M, C)
@@ -169,9 +172,13 @@ class FusedBatchNormAct(torch.autograd.Function):
         st = _stream()
         dt = _dt(x)
         _check(lib.kb200_bn_bwd_reduce_mask(_p(dy), _p(x), _p(bits), _p(mean), _p(invstd), _ll(M), _i(C), _i(dt), _p(sums), st), "bn_bwd_reduce")
-        _check(lib.kb200_bn_bwd_apply_mask(_p(dy), _p(x), _p(bits), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(coef), _p(dx), _p(dres), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
-        dgamma = sums[C:2 * C] if gamma is not None else None
-        dbeta = sums[:C]
+        from keras_b200.kernels import shadow
+
+        slot_g, slot_b = shadow.grad_slot(ctx.leaves[0], (C,)), shadow.grad_slot(ctx.leaves[1], (C,))
+        _check(lib.kb200_bn_bwd_apply_mask_acc(_p(dy), _p(x), _p(bits), _p(mean), _p(invstd), _p(gamma), _p(sums), _p(coef), _p(dx), _p(dres),
+                                               _p(slot_g), _p(slot_b), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
+        dgamma = sums[C:2 * C] if gamma is not None and slot_g is None else None
+        dbeta = sums[:C] if slot_b is None else None
         return dx, dgamma, dbeta, dres, None, None, None, None, None, None, None
 
 

@@ -248,7 +248,7 @@ def test_tcgen05_gemm_autograd_matches_torch():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("case", ["zero_pad", "same", "valid"])
+@pytest.mark.parametrize("case", ["zero_pad", "same", "valid", "two_by_two"])
 def test_fused_max_pool_matches_torch(dtype, case):
     import torch.nn.functional as F
 
@@ -263,6 +263,9 @@ def test_fused_max_pool_matches_torch(dtype, case):
     elif case == "same":
         y = dispatch.max_pool2d(x, (3, 3), (2, 2), "same")
         ref = F.max_pool2d(F.pad(xr.permute(0, 3, 1, 2), (1, 1, 1, 1), value=-float("inf")), 3, 2).permute(0, 2, 3, 1)
+    elif case == "two_by_two":
+        y = dispatch.max_pool2d(x, (2, 2), (2, 2), "valid")
+        ref = F.max_pool2d(xr.permute(0, 3, 1, 2), 2, 2).permute(0, 2, 3, 1)
     else:
         y = dispatch.max_pool2d(x, (2, 3), (2, 1), "valid")
         ref = F.max_pool2d(xr.permute(0, 3, 1, 2), (2, 3), (2, 1)).permute(0, 2, 3, 1)
