@@ -368,6 +368,11 @@ def run_secondary(keras, torch, dist, args, rank, world, local):
     library path (``KERAS_B200_TP_FUSED=0``) as its stated baseline: the reference has no torch-backend model parallelism
     to compare with."""
     cfg = CONFIGS[args.secondary_config]
+    # weak scaling over the data axis: each model-parallel group of `model_axis` GPUs keeps the per-replica batch of the
+    # 8-GPU layout (global batch 16 over 2 replicas), so N=4 (one replica) runs global batch 8
+    model_axis = min(cfg["model_axis"], world)
+    replicas = max(1, world // model_axis)
+    cfg = dict(cfg, global_batch=max(1, cfg["global_batch"] // 2) * replicas)
     rows = {}
     for label, fused in (("fused", "1"), ("library_collectives", "0")):
         os.environ["KERAS_B200_TP_FUSED"] = fused

@@ -14,11 +14,12 @@ from keras_b200.core.export_registry import keras_export
 from keras_b200.core.variables import Variable
 from keras_b200.kernels import dispatch
 from keras_b200.layers.input_spec import InputSpec
+from keras_b200.layers.core.calibrated_kernel import CalibratedKernel
 from keras_b200.layers.layer import Layer
 
 
 @keras_export("keras.layers.Dense")
-class Dense(Layer):
+class Dense(CalibratedKernel, Layer):
     def __init__(self, units, activation=None, use_bias=True, kernel_initializer="glorot_uniform", bias_initializer="zeros",
                  kernel_regularizer=None, bias_regularizer=None, activity_regularizer=None, kernel_constraint=None,
                  bias_constraint=None, lora_rank=None, lora_alpha=None, quantization_config=None, **kwargs):
@@ -46,7 +47,7 @@ class Dense(Layer):
         kernel_shape = (input_shape[-1], self.units)
         if self.quantization_mode:
             self.quantized_build(kernel_shape, mode=self.quantization_mode)
-        if self.quantization_mode not in ("int8", "int4"):
+        if self.quantization_mode not in ("int8", "int4", "gptq", "awq"):
             self._kernel = self.add_weight(name="kernel", shape=kernel_shape, initializer=self.kernel_initializer,
                                            regularizer=self.kernel_regularizer, constraint=self.kernel_constraint)
         if self.use_bias:
@@ -63,6 +64,8 @@ class Dense(Layer):
     def kernel(self):
         if not self.built:
             raise AttributeError("You must build the layer before accessing `kernel`.")
+        if self._calibrated:
+            return self._calibrated_matrix()
         k = self._kernel
         if self._is_quantized and self.quantization_mode == "int4":
             k = quantizers.unpack_int4(k.value, self._orig_input_dim)
@@ -72,7 +75,7 @@ class Dense(Layer):
         return k
 
     def call(self, inputs, training=None):
-        if getattr(self._kernel, "_shard_slices", None) is not None:
+        if getattr(getattr(self, "_kernel", None), "_shard_slices", None) is not None:
             from keras_b200.parallel import tensor_parallel
 
             out = tensor_parallel.dense(self, inputs)
@@ -126,6 +129,7 @@ class Dense(Layer):
             "int4": ["kernel", "bias", "kernel_scale"],
             "float8": ["kernel", "bias", "inputs_scale", "inputs_amax_history", "kernel_scale", "kernel_amax_history",
                        "outputs_grad_scale", "outputs_grad_amax_history"],
+            **CalibratedKernel.SPEC,
         }
 
     def _saved_names(self):
@@ -137,6 +141,8 @@ class Dense(Layer):
     def save_own_variables(self, store):
         if not self.built:
             return
+        if self._is_quantized and self.quantization_mode in ("gptq", "awq"):
+            return self._calibrated_save(store, self.quantization_mode)
         kernel_value, merged_scale = self._get_kernel_with_merged_lora()
         mode = self.quantization_mode if self._is_quantized else None
         for i, name in enumerate(self._saved_names()):
@@ -150,6 +156,8 @@ class Dense(Layer):
     def load_own_variables(self, store):
         if not self.built:
             return
+        if self._is_quantized and self.quantization_mode in ("gptq", "awq"):
+            return self._calibrated_load(store, self.quantization_mode)
         names = self._saved_names()
         if len(store.keys()) != len(names):
             raise ValueError(f"Layer '{self.name}' expected {len(names)} variables, but received {len(store.keys())} variables during loading. Expected: {names}")
@@ -214,9 +222,21 @@ class Dense(Layer):
             self._orig_input_dim = in_dim
         elif mode == "float8":
             quantizers.float8_build(self)
+        elif mode in ("gptq", "awq"):
+            self._calibrated_build(kernel_shape[0], kernel_shape[1], mode, config if config is not None else self.quantization_config)
         else:
             raise self._quantization_mode_error(mode)
         self._is_quantized = True
+
+    def _calibrated_call(self, inputs):
+        kernel = self._calibrated_matrix(inputs.dtype) if self._calibrated else self._kernel.value
+        return self._finish(ops.matmul(inputs, kernel), inputs)
+
+    def _gptq_call(self, inputs, training=None):
+        return self._calibrated_call(inputs)
+
+    def _awq_call(self, inputs, training=None):
+        return self._calibrated_call(inputs)
 
     def _finish(self, out, inputs):
         if self.lora_enabled:
@@ -261,6 +281,11 @@ class Dense(Layer):
             self.kernel_scale.assign(scale)
         elif mode == "float8":
             self.quantized_build(kernel_shape, mode)
+        elif mode in ("gptq", "awq"):
+            if self.lora_enabled:
+                raise NotImplementedError(f"lora is not currently supported with {mode.upper()} quantization.")
+            self.quantized_build(kernel_shape, mode, config)  # the float kernel stays until calibration replaces it
+            mode = config.dtype_policy_string()
         else:
             raise self._quantization_mode_error(mode)
         quantizers.set_quantized_policy(self, mode)

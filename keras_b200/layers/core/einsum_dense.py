@@ -14,6 +14,7 @@ import torch
 from keras_b200 import activations, constraints, initializers, ops, quantizers, regularizers
 from keras_b200.core.export_registry import keras_export
 from keras_b200.kernels import dispatch
+from keras_b200.layers.core.calibrated_kernel import CalibratedKernel
 from keras_b200.layers.layer import Layer
 
 
@@ -109,7 +110,7 @@ def _gemm_plan(equation):
 
 
 @keras_export("keras.layers.EinsumDense")
-class EinsumDense(Layer):
+class EinsumDense(CalibratedKernel, Layer):
     def __init__(self, equation, output_shape, activation=None, bias_axes=None, kernel_initializer="glorot_uniform",
                  bias_initializer="zeros", kernel_regularizer=None, bias_regularizer=None, kernel_constraint=None,
                  bias_constraint=None, lora_rank=None, lora_alpha=None, gptq_unpacked_column_size=None,
@@ -139,7 +140,7 @@ class EinsumDense(Layer):
         self._kernel_in_axes, self._kernel_out_axes = in_axes, out_axes
         if self.quantization_mode:
             self.quantized_build(self._kernel_shape, mode=self.quantization_mode)
-        if self.quantization_mode != "int8":
+        if self.quantization_mode not in ("int8", "gptq", "awq"):
             init = self.kernel_initializer
             if isinstance(init, initializers.VarianceScaling):
                 base = init
@@ -162,6 +163,8 @@ class EinsumDense(Layer):
     def kernel(self):
         if not self.built:
             raise AttributeError("You must build the layer before accessing `kernel`.")
+        if self._calibrated:
+            return self._calibrated_matrix().reshape(self._kernel_shape)
         if self.lora_enabled:
             return ops.add(self._kernel.value, (self.lora_alpha / self.lora_rank) * ops.matmul(self.lora_kernel_a.value, self.lora_kernel_b.value))
         return self._kernel
@@ -245,6 +248,7 @@ class EinsumDense(Layer):
             "int8": ["kernel", "bias", "kernel_scale"],
             "float8": ["kernel", "bias", "inputs_scale", "inputs_amax_history", "kernel_scale", "kernel_amax_history",
                        "outputs_grad_scale", "outputs_grad_amax_history"],
+            **CalibratedKernel.SPEC,
         }
 
     def _saved_names(self):
@@ -257,6 +261,8 @@ class EinsumDense(Layer):
         if not self.built:
             return
         mode = self.quantization_mode if self._is_quantized else None
+        if mode in ("gptq", "awq"):
+            return self._calibrated_save(store, mode)
         kernel, scale = self._kernel, getattr(self, "kernel_scale", None)
         if self.lora_enabled:
             delta = (self.lora_alpha / self.lora_rank) * torch.matmul(self.lora_kernel_a._value, self.lora_kernel_b._value)
@@ -276,6 +282,8 @@ class EinsumDense(Layer):
     def load_own_variables(self, store):
         if not self.built:
             return
+        if self._is_quantized and self.quantization_mode in ("gptq", "awq"):
+            return self._calibrated_load(store, self.quantization_mode)
         names = self._saved_names()
         if len(store.keys()) != len(names):
             raise ValueError(f"Layer '{self.name}' expected {len(names)} variables, but received {len(store.keys())} variables during loading. Expected: {names}")
@@ -310,9 +318,39 @@ class EinsumDense(Layer):
             self.kernel_scale = self.add_weight(name="kernel_scale", shape=scale_shape, initializer="ones", trainable=False)
         elif mode == "float8":
             quantizers.float8_build(self)
+        elif mode in ("gptq", "awq"):
+            rows, columns = self.calibrated_matrix_shape(kernel_shape)
+            self._calibrated_build(rows, columns, mode, config if config is not None else self.quantization_config)
         else:
             raise self._quantization_mode_error(mode)
         self._is_quantized = True
+
+    @staticmethod
+    def calibrated_matrix_shape(kernel_shape):
+        """``(input features, output features)`` of a 2-D or 3-D projection kernel.  A 3-D kernel is an attention projection:
+        ``[d_model, heads, head_dim]`` (query/key/value) when its largest axis comes first, else ``[heads, head_dim, d_model]``
+        (output); the same rule as keras/src/layers/core/einsum_dense.py:669-690."""
+        shape = list(kernel_shape)
+        if len(shape) == 2:
+            return shape[0], shape[1]
+        if len(shape) == 3:
+            if shape.index(max(shape)) == 0:
+                return shape[0], shape[1] * shape[2]
+            return shape[0] * shape[1], shape[2]
+        raise ValueError(f"Calibrated quantization supports 2-D and 3-D kernels, got shape {tuple(kernel_shape)}.")
+
+    def _calibrated_call(self, inputs):
+        if self._calibrated:
+            kernel = self._calibrated_matrix(inputs.dtype).reshape(self._kernel_shape)
+        else:
+            kernel = self._kernel.value
+        return self._finish(self._contract(inputs, kernel), inputs)
+
+    def _gptq_call(self, inputs, training=None):
+        return self._calibrated_call(inputs)
+
+    def _awq_call(self, inputs, training=None):
+        return self._calibrated_call(inputs)
 
     def _finish(self, x, inputs):
         if self.lora_enabled:
@@ -361,6 +399,11 @@ class EinsumDense(Layer):
             self.kernel_scale.assign(scale)
         elif mode == "float8":
             self.quantized_build(kernel_shape, mode)
+        elif mode in ("gptq", "awq"):
+            if self.lora_enabled:
+                raise NotImplementedError(f"lora is not currently supported with {mode.upper()} quantization.")
+            self.quantized_build(kernel_shape, mode, config)  # the float kernel stays until calibration replaces it
+            mode = config.dtype_policy_string()
         else:
             raise self._quantization_mode_error(mode)
         quantizers.set_quantized_policy(self, mode)

@@ -146,6 +146,12 @@ class Model(Trainer, Layer):
         (print_fn or io_utils.print_msg)(report.render())
         return report
 
+    def get_quantization_layer_structure(self, mode):
+        """Override to describe the model to the calibrated quantisation modes: ``{"pre_block_layers": [...],
+        "sequential_blocks": [...]}`` (see ``keras_b200.quantizers.calibration``).  ``None``: the structure must come
+        with the config."""
+        return None
+
     def _reset_step_functions(self):
         self.train_function = None
         self.test_function = None

@@ -114,13 +114,17 @@ class TernaryQuantizationConfig(QuantizationConfig):
 
 @keras_export("keras.quantizers.GPTQConfig")
 class GPTQConfig(QuantizationConfig):
-    def __init__(self, dataset=None, tokenizer=None, *, weight_bits=4, num_samples=128, per_channel=True, sequence_length=512,
-                 hessian_damping=0.01, group_size=128, symmetric=False, activation_order=False, quantization_layer_structure=None):
+    def __init__(self, dataset=None, tokenizer=None, *, weight_bits=4, num_samples=128, calibration_batch_size=8, per_channel=True,
+                 sequence_length=512, hessian_damping=0.01, group_size=128, symmetric=False, activation_order=False,
+                 quantization_layer_structure=None):
         super().__init__()
         if weight_bits not in (2, 3, 4, 8):
             raise ValueError(f"Unsupported weight_bits {weight_bits}. Supported values are 2, 3, 4, and 8.")
         if num_samples <= 0:
             raise ValueError("num_samples must be a positive integer.")
+        if calibration_batch_size <= 0:
+            raise ValueError("calibration_batch_size must be a positive integer.")
+        self.calibration_batch_size = calibration_batch_size
         if sequence_length <= 0:
             raise ValueError("sequence_length must be a positive integer.")
         if hessian_damping < 0 or hessian_damping > 1:
@@ -140,9 +144,9 @@ class GPTQConfig(QuantizationConfig):
 
     def get_config(self):
         return {"dataset": None, "tokenizer": None, "weight_bits": self.weight_bits, "num_samples": self.num_samples,
-                "per_channel": self.per_channel, "sequence_length": self.sequence_length, "hessian_damping": self.hessian_damping,
+                "calibration_batch_size": self.calibration_batch_size, "per_channel": self.per_channel, "sequence_length": self.sequence_length, "hessian_damping": self.hessian_damping,
                 "group_size": self.group_size, "symmetric": self.symmetric, "activation_order": self.activation_order,
-                "quantization_layer_structure": self.quantization_layer_structure}
+                "quantization_layer_structure": None}  # live layer objects: calibration-time only, never saved
 
     @classmethod
     def from_config(cls, config):
@@ -152,12 +156,15 @@ class GPTQConfig(QuantizationConfig):
 @keras_export("keras.quantizers.AWQConfig")
 class AWQConfig(QuantizationConfig):
     def __init__(self, dataset=None, tokenizer=None, *, weight_bits=4, num_samples=128, sequence_length=512, group_size=128,
-                 num_grid_points=20, quantization_layer_structure=None):
+                 num_grid_points=20, apply_clip=True, quantization_layer_structure=None):
         super().__init__()
         if weight_bits != 4:
             raise ValueError(f"AWQ only supports 4-bit quantization. Received weight_bits={weight_bits}.")
         if num_samples <= 0:
             raise ValueError("num_samples must be a positive integer.")
+        if sequence_length <= 0:
+            raise ValueError("sequence_length must be a positive integer.")
+        self.apply_clip = bool(apply_clip)
         if group_size < -1 or group_size == 0:
             raise ValueError(f"Invalid group_size. Supported values are -1 (per-channel) or a positive integer, but got {group_size}.")
         if num_grid_points <= 0:
@@ -175,7 +182,7 @@ class AWQConfig(QuantizationConfig):
     def get_config(self):
         return {"dataset": None, "tokenizer": None, "weight_bits": self.weight_bits, "num_samples": self.num_samples,
                 "sequence_length": self.sequence_length, "group_size": self.group_size, "num_grid_points": self.num_grid_points,
-                "quantization_layer_structure": self.quantization_layer_structure}
+                "apply_clip": self.apply_clip, "quantization_layer_structure": None}  # live layer objects: calibration-time only, never saved
 
     @classmethod
     def from_config(cls, config):
