@@ -322,9 +322,12 @@ def measure_ours(keras, torch, dist, args, cfg, rank, world, local, steps, warmu
     sampler = ClockSampler(local)
     sampler.start()
     launches0 = kops.launch_count()
+    replays0 = getattr(getattr(model, "_graphed_step", None), "replays", 0)
     ms = _timed(torch, dist, world, steps, dev_step)
     launches = kops.launch_count() - launches0
+    replays_value = getattr(getattr(model, "_graphed_step", None), "replays", 0) - replays0
     clocks = sampler.stop()
+    replays_before_e2e = getattr(getattr(model, "_graphed_step", None), "replays", 0)
     ms_e2e, e2e_api = run_e2e(keras, torch, dist, world, steps, warmup, model, host_x, host_y, last)
     total = per_step * world * steps
     value = total / (ms / 1e3)
@@ -341,6 +344,11 @@ def measure_ours(keras, torch, dist, args, cfg, rank, world, local, steps, warmu
         "gpu_launches": int(launches),
         "final_loss": float(last["loss"]) if not isinstance(last["loss"], (list, tuple)) else float(last["loss"][0]),
     }
+    stepper = getattr(model, "_graphed_step", None)
+    if stepper is not None:
+        # how the steps were issued: replays of the captured CUDA graph of the step, or eagerly (and why)
+        out["step_graph"] = {"replays": int(stepper.replays), "replays_in_value_region": int(replays_value), "replays_in_e2e_region": int(stepper.replays - replays_before_e2e),
+                             "eager_reason": stepper.disabled}
     return out, model
 
 
