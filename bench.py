@@ -353,7 +353,8 @@ def measure_ours(keras, torch, dist, args, cfg, rank, world, local, steps, warmu
 
 
 def _release(torch, model):
-    """Close the model's parallel engine (peer buffers) and give its memory back before the next model is built."""
+    """Close the model's parallel engine (peer buffers), drop what keeps its device memory alive (the captured step graph
+    and its pool, the gradient arena, optimizer state) and give the memory back before the next model is built."""
     import gc
 
     torch.cuda.synchronize()
@@ -362,6 +363,17 @@ def _release(torch, model):
         engine.check(wait=True)
         engine.close()
         model._parallel_engine = None
+    for attr in ("_graphed_step", "train_function", "test_function", "predict_function", "_grad_arena", "optimizer", "_device_stager"):
+        try:
+            setattr(model, attr, None)
+        except Exception:
+            pass
+    for v in list(getattr(model, "variables", [])):
+        for attr in ("_value", "_shadow", "_shadow_tensor"):
+            try:
+                object.__setattr__(v, attr, None)
+            except Exception:
+                pass
     gc.collect()
     torch.cuda.empty_cache()
 
@@ -386,10 +398,14 @@ def run_secondary(keras, torch, dist, args, rank, world, local):
         os.environ["KERAS_B200_TP_FUSED"] = fused
         distribution, _ = llama_layout(keras, cfg, world)
         keras.distribution.set_distribution(distribution)
+        free0 = torch.cuda.mem_get_info()[0] / 2**30
         row, model = measure_ours(keras, torch, dist, args, cfg, rank, world, local, SECONDARY_STEPS, 3)
+        row["free_gib_before_build"] = round(free0, 1)
+        row["peak_allocated_gib"] = round(torch.cuda.max_memory_allocated() / 2**30, 1)
         rows[label] = row
         _release(torch, model)
         del model
+        torch.cuda.reset_peak_memory_stats()
     os.environ["KERAS_B200_TP_FUSED"] = "1"
     out = dict(rows["fused"])
     base = rows["library_collectives"]
