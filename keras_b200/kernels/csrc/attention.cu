@@ -357,18 +357,12 @@ KB_API int kb200_flash_attention_fwd(const void* q, const void* k, const void* v
   }
   FlashParams p{B, H, Hkv, Tq, Tk, scale * 1.4426950408889634f, causal, lse, err};
   dim3 grid((Tq + 127) / 128, H, B);
-  static bool attr64 = false, attr128 = false;
+  static bool attr64[KB_MAX_DEVICES] = {false}, attr128[KB_MAX_DEVICES] = {false};
   if (D == 64) {
-    if (!attr64) {
-      cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<64>::SMEM);
-      attr64 = true;
-    }
+    if (!kb_allow_smem(flash_fwd_kernel<64>, FlashCfg<64>::SMEM, attr64)) { kb200_set_error("flash_attention: shared-memory limit"); return -3; }
     flash_fwd_kernel<64><<<grid, THREADS, FlashCfg<64>::SMEM, stream>>>(map_q, map_k, map_v, map_o, p);
   } else {
-    if (!attr128) {
-      cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<128>::SMEM);
-      attr128 = true;
-    }
+    if (!kb_allow_smem(flash_fwd_kernel<128>, FlashCfg<128>::SMEM, attr128)) { kb200_set_error("flash_attention: shared-memory limit"); return -3; }
     flash_fwd_kernel<128><<<grid, THREADS, FlashCfg<128>::SMEM, stream>>>(map_q, map_k, map_v, map_o, p);
   }
   KB_CHECK_LAUNCH("flash_attention_fwd");

@@ -50,16 +50,7 @@ struct BnGeom {
   int gx;       // blocks along rows
 };
 
-static int bn_sm_count() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-    sms = v;
-  }
-  return sms;
-}
+static int bn_sm_count() { return kb_sm_count(); }
 
 // Grid = one resident wave: `resident` blocks per SM (from the occupancy calculator), capped by the rows available.
 static BnGeom bn_geom(long long M, int cvecs, int resident, int rows_per_iter) {

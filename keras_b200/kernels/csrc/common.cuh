@@ -20,6 +20,41 @@ void kb200_set_error(const char* msg);
     }                                                           \
   } while (0)
 
+// Per-device launcher state.  Kernel attributes and SM counts belong to a device, and one process may drive several:
+// every "done once" flag in the launchers is an array indexed by the current device.
+constexpr int KB_MAX_DEVICES = 64;
+
+inline int kb_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= KB_MAX_DEVICES) dev = 0;
+  return dev;
+}
+
+inline int kb_sm_count() {
+  static int sms[KB_MAX_DEVICES] = {0};
+  const int slot = kb_device_slot();
+  if (sms[slot] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, slot) != cudaSuccess || v <= 0) v = 148;
+    sms[slot] = v;
+  }
+  return sms[slot];
+}
+
+// Raise a kernel's dynamic shared-memory limit once per device.  `flags` is a function-local `static bool [KB_MAX_DEVICES]`.
+template <typename Kernel>
+inline bool kb_allow_smem(Kernel kernel, int bytes, bool* flags) {
+  const int slot = kb_device_slot();
+  if (!flags[slot]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    flags[slot] = true;
+  }
+  return true;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

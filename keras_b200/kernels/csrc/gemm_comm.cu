@@ -474,23 +474,11 @@ gemm_bf16_tcgen05_comm(const __grid_constant__ CUtensorMap map_a, const __grid_c
   }
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
+int sm_count() { return kb_sm_count(); }
 
 bool prepare_kernel() {
-  static bool done = false;
-  if (!done) {
-    if (cudaFuncSetAttribute(gemm_bf16_tcgen05_comm, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES) != cudaSuccess) return false;
-    done = true;
-  }
-  return true;
+  static bool done[KB_MAX_DEVICES] = {false};
+  return kb_allow_smem(gemm_bf16_tcgen05_comm, v2::SMEM_BYTES, done);
 }
 
 }  // namespace

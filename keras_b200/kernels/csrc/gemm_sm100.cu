@@ -353,14 +353,12 @@ KB_API int kb200_gemm_bf16_splitk(const void* a, const void* b, void* c, const f
     return -2;
   }
   CUtensorMap map_a, map_b, map_c;
-  static int force_v1 = -1, sm_count = 0;
+  static int force_v1 = -1;
   if (force_v1 < 0) {
     const char* e = getenv("KB200_GEMM_V1");
     force_v1 = (e != nullptr && e[0] == '1') ? 1 : 0;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
+  const int sm_count = kb_sm_count();
   const long long tiles_v2 = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
   int kb_per_split = 0;
   if (split_k > 1) {
@@ -379,11 +377,10 @@ KB_API int kb200_gemm_bf16_splitk(const void* a, const void* b, void* c, const f
     kb200_set_error("gemm_bf16: cuTensorMapEncodeTiled failed");
     return -3;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
-    attr_set = true;
+  static bool attr_v1[KB_MAX_DEVICES] = {false}, attr_v2[KB_MAX_DEVICES] = {false};
+  if (!kb_allow_smem(gemm_bf16_tcgen05_kernel, SMEM_BYTES, attr_v1) || !kb_allow_smem(gemm_bf16_tcgen05_persistent, v2::SMEM_BYTES, attr_v2)) {
+    kb200_set_error("gemm_bf16: cannot raise the shared-memory limit of the kernels on this device");
+    return -3;
   }
   GemmParams p{c, bias, M, N, K, ldc, a_mn_major, b_mn_major, act, out_fp32, err, split_k, kb_per_split};
   p.accumulate = accumulate;
@@ -422,17 +419,12 @@ KB_API int kb200_gemm_fp8(const void* a, const void* b, void* c, const float* bi
     kb200_set_error("gemm_fp8: cuTensorMapEncodeTiled failed");
     return -3;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
-    attr_set = true;
+  static bool attr_v2[KB_MAX_DEVICES] = {false};
+  if (!kb_allow_smem(gemm_bf16_tcgen05_persistent, v2::SMEM_BYTES, attr_v2)) {
+    kb200_set_error("gemm: cannot raise the shared-memory limit of the kernel on this device");
+    return -3;
   }
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = kb_sm_count();
   GemmParams p{c, bias, M, N, K, ldc, 0, 0, act, out_fp32, err, 1, 0, 1 + a_format + 2 * b_format, alpha};
   const long long tiles = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
   gemm_bf16_tcgen05_persistent<<<(unsigned)(tiles < sm_count ? tiles : sm_count), THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
@@ -456,17 +448,12 @@ KB_API int kb200_gemm_i8(const void* a, const void* b, void* c, const float* bia
     kb200_set_error("gemm_i8: cuTensorMapEncodeTiled failed");
     return -3;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_tcgen05_persistent, cudaFuncAttributeMaxDynamicSharedMemorySize, v2::SMEM_BYTES);
-    attr_set = true;
+  static bool attr_v2[KB_MAX_DEVICES] = {false};
+  if (!kb_allow_smem(gemm_bf16_tcgen05_persistent, v2::SMEM_BYTES, attr_v2)) {
+    kb200_set_error("gemm: cannot raise the shared-memory limit of the kernel on this device");
+    return -3;
   }
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-  }
+  const int sm_count = kb_sm_count();
   GemmParams p{c, bias, M, N, K, ldc, 0, 0, act, out_fp32, err, 1, 0, 0, nullptr, 1, row_scale, col_scale};
   const long long tiles = (long long)((M + v2::BM - 1) / v2::BM) * ((N + v2::BN - 1) / v2::BN);
   gemm_bf16_tcgen05_persistent<<<(unsigned)(tiles < sm_count ? tiles : sm_count), THREADS, v2::SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);

@@ -108,14 +108,16 @@ class GraphedTrainStep:
             return self.model.train_step(data)  # an odd batch: eager, same variables
         if sig != self._candidate:
             self._candidate, self._seen = sig, 0
+        if self._seen == 0:
+            # the first step runs where any eager step would; once the optimizer has applied an update every condition is known.
+            # A model that will not be captured never touches the side stream (whose allocator pool would double its memory).
+            self._seen = 1
+            logs = self.model.train_step(data)
+            self.disabled = self._why_not()
+            return logs
         if self._seen < _EAGER_STEPS_BEFORE_CAPTURE:
             self._seen += 1
-            logs = self._eager_on_side_stream(data)
-            if self._seen == _EAGER_STEPS_BEFORE_CAPTURE:
-                reason = self._why_not()
-                if reason is not None:
-                    self.disabled = reason
-            return logs
+            return self._eager_on_side_stream(data)
         return self._capture(data, leaves, sig)
 
     def _eager_on_side_stream(self, data):
@@ -159,9 +161,11 @@ class GraphedTrainStep:
             if not isinstance(e, seed_generator.CaptureUnsafe):
                 warnings.warn(f"The training step could not be captured in a CUDA graph and runs eagerly ({self.disabled}).", stacklevel=2)
             self._resync_host_state()
+            torch.cuda.empty_cache()  # what the side-stream steps cached is of no use to the eager steps on the main stream
             return model.train_step(data)
         seed_generator.end_capture()
         self._resync_host_state()
+        torch.cuda.empty_cache()      # the graph owns its pool; the warm-up's cached blocks go back to the device
         # launcher calls recorded into the graph: nothing ran yet, each replay runs that many kernels' launchers
         self.launches_per_replay = kops.launch_count() - launches_before
         kops.add_launches(-self.launches_per_replay)
