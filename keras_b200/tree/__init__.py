@@ -102,64 +102,68 @@ def is_nested(structure):
     return _children(structure) is not None
 
 
+# The recursive helpers below are module-level functions on purpose: a nested function that calls itself refers to itself
+# through a closure cell, i.e. every call would leave a reference cycle that keeps whatever it captured (tensors with
+# their autograd graphs, in the training step) alive until the cyclic garbage collector runs.
+def _flatten_into(x, out):
+    ch = _children(x)
+    if ch is None:
+        out.append(x)
+    else:
+        for v in ch[1]:
+            _flatten_into(v, out)
+
+
 @keras_export("keras.tree.flatten")
 def flatten(structure):
     out = []
-
-    def rec(x):
-        ch = _children(x)
-        if ch is None:
-            out.append(x)
-        else:
-            for v in ch[1]:
-                rec(v)
-
-    rec(structure)
+    _flatten_into(structure, out)
     return out
+
+
+def _flatten_paths_into(x, path, out):
+    ch = _children(x)
+    if ch is None:
+        out.append((path, x))
+    else:
+        for k, v in zip(ch[0], ch[1]):
+            _flatten_paths_into(v, path + (k,), out)
 
 
 @keras_export("keras.tree.flatten_with_path")
 def flatten_with_path(structure):
     out = []
-
-    def rec(x, path):
-        ch = _children(x)
-        if ch is None:
-            out.append((path, x))
-        else:
-            for k, v in zip(ch[0], ch[1]):
-                rec(v, path + (k,))
-
-    rec(structure, ())
+    _flatten_paths_into(structure, (), out)
     return out
+
+
+def _traverse_top_down(func, x):
+    r = func(x)
+    if r is MAP_TO_NONE:
+        return None
+    if r is not None:
+        return r
+    ch = _children(x)
+    if ch is None:
+        return x
+    return ch[2]([_traverse_top_down(func, v) for v in ch[1]])
+
+
+def _traverse_bottom_up(func, x):
+    ch = _children(x)
+    if ch is not None:
+        x = ch[2]([_traverse_bottom_up(func, v) for v in ch[1]])
+    r = func(x)
+    if r is MAP_TO_NONE:
+        return None
+    return x if r is None else r
 
 
 @keras_export("keras.tree.traverse")
 def traverse(func, structure, top_down=True):
     if not callable(func):
         raise TypeError(f"`func` must be callable, got {func} of type {type(func)}")
-
-    def rec_top(x):
-        r = func(x)
-        if r is MAP_TO_NONE:
-            return None
-        if r is not None:
-            return r
-        ch = _children(x)
-        if ch is None:
-            return x
-        return ch[2]([rec_top(v) for v in ch[1]])
-
-    def rec_bottom(x):
-        ch = _children(x)
-        if ch is not None:
-            x = ch[2]([rec_bottom(v) for v in ch[1]])
-        r = func(x)
-        if r is MAP_TO_NONE:
-            return None
-        return x if r is None else r
-
-    return rec_top(structure) if top_down else rec_bottom(structure)
+    return _traverse_top_down(func, structure) if top_down else _traverse_bottom_up(func, structure)
 
 
 def _structure_mismatch(a, b, path="", check_types=True):
@@ -211,43 +215,45 @@ def map_structure(func, *structures, none_is_leaf=True):
         raise ValueError("Must provide at least one structure")
     first = structures[0]
     if len(structures) == 1:
-        def rec1(x):
-            ch = _children(x)
-            if ch is None:
-                return func(x)
-            return ch[2]([rec1(v) for v in ch[1]])
-
-        return rec1(first)
+        return _map_one(func, first)
     for other in structures[1:]:
         assert_same_structure(first, other, check_types=False)
+    return _map_many(func, structures)
 
-    def rec(*xs):
-        ch = _children(xs[0])
-        if ch is None:
-            return func(*xs)
-        others = [_children(x)[1] for x in xs[1:]]
-        return ch[2]([rec(v, *[o[i] for o in others]) for i, v in enumerate(ch[1])])
 
-    return rec(*structures)
+def _map_one(func, x):
+    ch = _children(x)
+    if ch is None:
+        return func(x)
+    return ch[2]([_map_one(func, v) for v in ch[1]])
+
+
+def _map_many(func, xs):
+    ch = _children(xs[0])
+    if ch is None:
+        return func(*xs)
+    others = [_children(x)[1] for x in xs[1:]]
+    return ch[2]([_map_many(func, (v, *[o[i] for o in others])) for i, v in enumerate(ch[1])])
+
+
+def _map_up_to(func, shallow, xs):
+    ch = _children(shallow)
+    if ch is None:
+        return func(*xs)
+    subs = []
+    for x in xs:
+        cx = _children(x)
+        if cx is None or len(cx[1]) != len(ch[1]):
+            raise ValueError(
+                f"Structure {x!r} does not match the shallow structure {shallow!r}."
+            )
+        subs.append(cx[1])
+    return ch[2]([_map_up_to(func, v, [s[i] for s in subs]) for i, v in enumerate(ch[1])])
 
 
 @keras_export("keras.tree.map_structure_up_to")
 def map_structure_up_to(shallow_structure, func, *structures):
-    def rec(shallow, *xs):
-        ch = _children(shallow)
-        if ch is None:
-            return func(*xs)
-        subs = []
-        for x in xs:
-            cx = _children(x)
-            if cx is None or len(cx[1]) != len(ch[1]):
-                raise ValueError(
-                    f"Structure {x!r} does not match the shallow structure {shallow!r}."
-                )
-            subs.append(cx[1])
-        return ch[2]([rec(v, *[s[i] for s in subs]) for i, v in enumerate(ch[1])])
-
-    return rec(shallow_structure, *structures)
+    return _map_up_to(func, shallow_structure, structures)
 
 
 @keras_export("keras.tree.pack_sequence_as")
@@ -261,20 +267,7 @@ def pack_sequence_as(structure, flat_sequence, sequence_fn=None):
             )
         return flat[0]
     pos = [0]
-
-    def rec(x):
-        ch = _children(x)
-        if ch is None:
-            if pos[0] >= len(flat):
-                raise ValueError(
-                    f"Could not pack sequence: structure has more leaves than {len(flat)} values."
-                )
-            v = flat[pos[0]]
-            pos[0] += 1
-            return v
-        return ch[2]([rec(v) for v in ch[1]])
-
-    out = rec(structure)
+    out = _pack(structure, flat, pos)
     if pos[0] != len(flat):
         raise ValueError(
             f"Could not pack sequence: structure had {pos[0]} leaves but flat_sequence had "
@@ -283,35 +276,42 @@ def pack_sequence_as(structure, flat_sequence, sequence_fn=None):
     return out
 
 
+def _pack(x, flat, pos):
+    ch = _children(x)
+    if ch is None:
+        if pos[0] >= len(flat):
+            raise ValueError(
+                f"Could not pack sequence: structure has more leaves than {len(flat)} values."
+            )
+        v = flat[pos[0]]
+        pos[0] += 1
+        return v
+    return ch[2]([_pack(v, flat, pos) for v in ch[1]])
+
+
 @keras_export("keras.tree.lists_to_tuples")
 def lists_to_tuples(structure):
-    def rec(x):
-        ch = _children(x)
-        if ch is None:
-            return x
-        vals = [rec(v) for v in ch[1]]
-        if type(x) is list:
-            return tuple(vals)
-        return ch[2](vals)
+    ch = _children(structure)
+    if ch is None:
+        return structure
+    vals = [lists_to_tuples(v) for v in ch[1]]
+    if type(structure) is list:
+        return tuple(vals)
+    return ch[2](vals)
 
-    return rec(structure)
+
+def _is_shape(x):
+    return isinstance(x, (list, tuple)) and all(isinstance(e, int) or e is None for e in x)
 
 
 @keras_export("keras.tree.map_shape_structure")
 def map_shape_structure(func, structure):
     """Like ``map_structure`` but tuples/lists made only of ints/None count as leaves."""
-
-    def is_shape(x):
-        return isinstance(x, (list, tuple)) and all(isinstance(e, int) or e is None for e in x)
-
-    def rec(x):
-        if is_shape(x):
-            return func(tuple(x))
-        ch = _children(x)
-        if ch is None:
-            if x is None:
-                return None
-            return func(x)
-        return ch[2]([rec(v) for v in ch[1]])
-
-    return rec(structure)
+    if _is_shape(structure):
+        return func(tuple(structure))
+    ch = _children(structure)
+    if ch is None:
+        if structure is None:
+            return None
+        return func(structure)
+    return ch[2]([map_shape_structure(func, v) for v in ch[1]])
