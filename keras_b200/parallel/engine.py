@@ -103,15 +103,22 @@ class DataParallelEngine:
                 opt.build(trainable_weights)
             self.sync_variables(model)
         arena = self._gradient_arena(trainable_weights)
-        arena.bind()
         if arena.flat.is_cuda:
             from keras_b200.kernels import shadow
 
             shadow.attach_for_model(model, trainable_weights)
-            with shadow.arena_backward():
-                loss.backward()
-        else:
+        if arena.unused is None:
+            # first pass over this set of variables: unbound, to see which variables the loss reaches (see GradArena.adopt)
+            arena.unbind()
             loss.backward()
+            arena.adopt()
+        else:
+            arena.bind()
+            if arena.flat.is_cuda:
+                with shadow.arena_backward():
+                    loss.backward()
+            else:
+                loss.backward()
         self._after_backward(trainable_weights)
         if self.world > 1:
             if self._reducer is not None:
@@ -121,8 +128,7 @@ class DataParallelEngine:
             else:
                 collectives.all_reduce(arena.flat, group=self.group)
                 arena.flat.div_(self.world)
-        params = [v._value for v in trainable_weights]
-        grads = [p.grad for p in params]
+        grads = arena.gradients()
         opt._fused_zeroed_grads = False
         opt.apply(grads, trainable_weights)
         if not opt._fused_zeroed_grads:

@@ -44,11 +44,38 @@ class GradArena:
             else:
                 self.views.append(None)
 
+        # indices of variables that the first backward pass did not reach (``None`` until ``adopt`` has looked): they get no
+        # gradient, so the optimizer skips them as it would skip a ``None`` gradient (no decay, no moment update)
+        self.unused = None
+
     def bind(self):
         for v, view in zip(self.variables, self.views):
             p = v._value
             if view is not None and p.grad is not view:
                 p.grad = view
+
+    def unbind(self):
+        """Detach every ``.grad`` so that the next backward pass shows which variables it reaches."""
+        for v in self.variables:
+            v._value.grad = None
+
+    def adopt(self):
+        """After a backward pass that ran unbound: note the variables without a gradient, move the gradients that exist into
+        the arena and bind."""
+        self.unused = set()
+        with torch.no_grad():
+            for idx, (v, view) in enumerate(zip(self.variables, self.views)):
+                g = v._value.grad
+                if g is None:
+                    self.unused.add(idx)
+                elif view is not None:
+                    view.copy_(g)
+        self.bind()
+
+    def gradients(self):
+        """Per variable: its gradient view, or ``None`` for a variable the model does not use."""
+        unused = self.unused or ()
+        return [None if idx in unused else v._value.grad for idx, v in enumerate(self.variables)]
 
     def zero(self):
         self.flat.zero_()

@@ -72,7 +72,7 @@ class GraphedTrainStep:
         self.launches_per_replay = 0
 
     # -- eligibility ---------------------------------------------------------------------
-    def _why_not(self):
+    def _why_not_static(self):
         from keras_b200.trainers.trainer import Trainer
 
         model = self.model
@@ -85,6 +85,15 @@ class GraphedTrainStep:
             return "the parallel engine's collectives cannot be recorded (library collectives, or model parallelism)"
         if type(model).train_step is not Trainer.train_step:
             return "train_step is overridden"
+        return None
+
+    def _why_not(self):
+        """Everything that decides eligibility, once the optimizer has applied updates."""
+        static = self._why_not_static()
+        if static is not None:
+            return static
+        model = self.model
+        engine = getattr(model, "_parallel_engine", None)
         opt = model.optimizer
         if opt is None or not getattr(opt, "_step_scalars_on_device", False) or not getattr(opt, "_fused_zeroed_grads", False):
             return "the optimizer update is not the fused one with device-resident step scalars"
@@ -109,15 +118,20 @@ class GraphedTrainStep:
         if sig != self._candidate:
             self._candidate, self._seen = sig, 0
         if self._seen == 0:
-            # the first step runs where any eager step would; once the optimizer has applied an update every condition is known.
-            # A model that will not be captured never touches the side stream (whose allocator pool would double its memory).
+            # What rules capture out for good is known before any step runs; such a model never touches the side stream
+            # (whose allocator pool would double its memory).  The first step also runs on the caller's stream: it is the one
+            # that discovers unused variables and builds caches.
+            self.disabled = self._why_not_static()
             self._seen = 1
-            logs = self.model.train_step(data)
-            self.disabled = self._why_not()
-            return logs
+            return self.model.train_step(data)
         if self._seen < _EAGER_STEPS_BEFORE_CAPTURE:
             self._seen += 1
-            return self._eager_on_side_stream(data)
+            logs = self._eager_on_side_stream(data)
+            if self._seen == _EAGER_STEPS_BEFORE_CAPTURE:
+                self.disabled = self._why_not()
+                if self.disabled is not None:
+                    torch.cuda.empty_cache()  # the side stream's cached blocks are of no use to eager steps on the main stream
+            return logs
         return self._capture(data, leaves, sig)
 
     def _eager_on_side_stream(self, data):

@@ -281,14 +281,20 @@ class Trainer:
                 if arena is None:
                     for p in params:
                         p.grad = None
-                if arena is None:
                     loss.backward()
+                    grads = [p.grad for p in params]
+                elif arena.unused is None:
+                    # first pass over this set of variables: run it unbound to see which variables the loss reaches at all
+                    arena.unbind()
+                    loss.backward()
+                    arena.adopt()
+                    grads = arena.gradients()
                 else:
                     from keras_b200.kernels import shadow
 
                     with shadow.arena_backward():
                         loss.backward()
-                grads = [p.grad for p in params]
+                    grads = arena.gradients()
                 opt = self.optimizer
                 opt._fused_zeroed_grads = False
                 opt.apply(grads, trainable_weights)
@@ -319,7 +325,8 @@ class Trainer:
             from keras_b200.kernels import shadow
 
             shadow.attach_for_model(self, trainable_weights)
-        arena.bind()
+        if arena.unused is not None:
+            arena.bind()
         return arena
 
     def test_step(self, data):

@@ -118,3 +118,28 @@ def test_adam_step_scalars_from_device_match_host_formula():
         torch.testing.assert_close(mm, want_m, rtol=2e-6, atol=2e-6)
         torch.testing.assert_close(vv, want_v, rtol=2e-6, atol=2e-6)
         assert float(gg.abs().max()) == 0.0
+
+
+def test_unused_variable_is_skipped_like_a_missing_gradient():
+    """A variable the loss never reaches gets no update (no weight decay either) although gradients live in the arena."""
+
+    class WithSpare(keras.layers.Layer):
+        def build(self, input_shape):
+            self.used = self.add_weight(shape=(input_shape[-1], 8), initializer="glorot_uniform", name="used")
+            self.spare = self.add_weight(shape=(4, 4), initializer="ones", name="spare")
+
+        def call(self, x):
+            return keras.ops.matmul(x, self.used)
+
+    model = keras.Sequential([keras.layers.Input((64,)), keras.layers.Dense(32, activation="relu"), WithSpare(), keras.layers.Dense(10)])
+    model.compile(optimizer=keras.optimizers.AdamW(1e-2, weight_decay=0.1), loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
+    x, y = _data(128)
+    spare = model.layers[1].spare
+    used_before = model.layers[1].used.numpy().copy()
+    with pytest.warns(UserWarning, match="Gradients do not exist"):
+        model.train_on_batch(x, y)
+    for _ in range(6):
+        model.train_on_batch(x, y)
+    assert model._graphed_step.replays == 4
+    np.testing.assert_array_equal(spare.numpy(), np.ones((4, 4), "float32"))
+    assert np.abs(model.layers[1].used.numpy() - used_before).max() > 1e-4
