@@ -399,7 +399,12 @@ def run_secondary(keras, torch, dist, args, rank, world, local):
         distribution, _ = llama_layout(keras, cfg, world)
         keras.distribution.set_distribution(distribution)
         free0 = torch.cuda.mem_get_info()[0] / 2**30
-        row, model = measure_ours(keras, torch, dist, args, cfg, rank, world, local, SECONDARY_STEPS, 3)
+        held0 = torch.cuda.memory_allocated() / 2**30
+        try:
+            row, model = measure_ours(keras, torch, dist, args, cfg, rank, world, local, SECONDARY_STEPS, 3)
+        except Exception as e:
+            raise RuntimeError(f"{label}: {type(e).__name__}: {str(e)[:160]} [free before build {free0:.1f} GiB, still allocated from the primary "
+                               f"{held0:.1f} GiB, peak {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB]") from None
         row["free_gib_before_build"] = round(free0, 1)
         row["peak_allocated_gib"] = round(torch.cuda.max_memory_allocated() / 2**30, 1)
         rows[label] = row
