@@ -179,15 +179,28 @@ def test_resnet_step_fused_matches_unfused(monkeypatch):
         monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "1" if disable else "0")
         model = keras.applications.ResNet50(weights=None, input_shape=(64, 64, 3), classes=10)
         model.compile(optimizer=keras.optimizers.SGD(0.01, momentum=0.9), loss="sparse_categorical_crossentropy")
-        return [model.train_on_batch(x, y) for _ in range(3)], model
+        first, last = model.get_layer("conv1_conv").kernel, model.get_layer("predictions").kernel
+        before = [first.numpy().copy(), last.numpy().copy()]
+        losses = [model.train_on_batch(x, y)]
+        # one SGD step from identical weights: the weight change is -lr * gradient, so it shows the first and the last layer's gradient
+        deltas = [first.numpy() - before[0], last.numpy() - before[1]]
+        losses += [model.train_on_batch(x, y) for _ in range(2)]
+        return losses, deltas
 
-    fused, mf = run(False)
-    plain, mp = run(True)
-    assert all(np.isfinite(fused)) and all(np.isfinite(plain))
-    assert abs(fused[0] - plain[0]) < 0.05 * abs(plain[0]) + 0.05
     from keras_b200.kernels import ops
 
-    assert ops.launch_count() > 0
+    launches_before = ops.launch_count()
+    fused, fused_deltas = run(False)
+    assert ops.launch_count() > launches_before
+    plain, plain_deltas = run(True)
+    assert all(np.isfinite(fused)) and all(np.isfinite(plain))
+    # the same initial weights and batch: every loss of the short run agrees (bf16 kernels against the library's bf16 kernels)
+    np.testing.assert_allclose(fused, plain, rtol=0.08, atol=0.08)
+    for name, a, b in zip(("first convolution", "classifier"), fused_deltas, plain_deltas):
+        a, b = a.ravel().astype("float64"), b.ravel().astype("float64")
+        cosine = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-30))
+        assert cosine > 0.97, (name, cosine)
+        assert abs(np.linalg.norm(a) / np.linalg.norm(b) - 1.0) < 0.15, (name, np.linalg.norm(a), np.linalg.norm(b))
 
 
 def test_training_on_gpu_transformer_block():

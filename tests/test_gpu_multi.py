@@ -70,6 +70,22 @@ def _allreduce_worker(rank, world):
         torch.cuda.synchronize()
         errs.append(float((red.flat - 0.5 * ref).abs().max()))
         dist.barrier()
+    # skewed starts: each rank in turn launches late (no barrier in between); the flag protocol has to absorb it
+    import time
+
+    for late in range(world):
+        src = torch.randn(red.numel, device="cuda", generator=g)
+        red.flat.copy_(src)
+        ref = src.clone()
+        dist.all_reduce(ref)
+        torch.cuda.synchronize()
+        if rank == late:
+            time.sleep(0.3)
+        red.all_reduce()
+        red.all_reduce(scale=0.5)  # back to back: the second call's entry flags must not be mistaken for the first's exit
+        torch.cuda.synchronize()
+        errs.append(float((red.flat - 0.5 * world * ref).abs().max() / world))
+    dist.barrier()
     # the other collectives of the same kernel: reduce-scatter, all-gather, broadcast
     per = ((red.numel // 4 + world - 1) // world) * 4
     lo, hi = per * rank, min(red.numel, per * (rank + 1))
@@ -280,12 +296,24 @@ def _fused_gemm_worker(rank, world):
     return {"errs": np.array(errs)}
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_allgather_gemm_and_gemm_reduce_scatter_match_nccl():
-    codes, out = _spawn("_fused_gemm_worker", 2)
-    assert codes == [0, 0], codes
-    for r in (0, 1):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_allgather_gemm_and_gemm_reduce_scatter_match_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    codes, out = _spawn("_fused_gemm_worker", world)
+    assert codes == [0] * world, codes
+    for r in range(world):
         assert (out[r]["errs"] < 3e-2).all(), out[r]["errs"]
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_p2p_collectives_match_nccl_on_more_ranks(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    codes, out = _spawn("_allreduce_worker", world)
+    assert codes == [0] * world, codes
+    for r in range(world):
+        assert out[r]["errs"].max() < 1e-5, out[r]["errs"]
 
 
 def _sp_gpu_worker(rank, world):
