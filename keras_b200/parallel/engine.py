@@ -176,8 +176,15 @@ class DataParallelEngine:
         return mr.flat[:n]
 
     def recordable(self):
-        """True when every collective of a training step is one of this package's kernels with device-side epochs."""
-        return self.world <= 1 or self._reducer is not None
+        """True when every collective of a training step is (or, before the first step has built the gradient arena, will
+        be) one of this package's kernels with device-side epochs."""
+        if self.world <= 1 or self._reducer is not None:
+            return True
+        if self._arena is not None:
+            return False  # the arena exists and is reduced by the library
+        from keras_b200.core.tensor import get_device
+
+        return collectives.use_p2p(get_device())
 
     def after_replay(self):
         """A recorded step was replayed: queue the status read-backs that the recorded collectives could not."""

@@ -212,6 +212,52 @@ def test_data_parallel_step_replays_as_cuda_graph():
     np.testing.assert_allclose(out[0]["graphed"], out[1]["graphed"], rtol=1e-6)
 
 
+def _equivalence_model(keras):
+    keras.utils.set_random_seed(23)
+    m = keras.Sequential([keras.layers.Input((32,)), keras.layers.Dense(64, activation="relu"), keras.layers.LayerNormalization(),
+                          keras.layers.Dense(64, activation="gelu"), keras.layers.Dense(5)])
+    m.compile(optimizer=keras.optimizers.SGD(0.05, momentum=0.9), loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
+    return m
+
+
+def _equivalence_data():
+    rng = np.random.RandomState(5)
+    return rng.randn(6, 64, 32).astype("float32"), rng.randint(0, 5, (6, 64))
+
+
+def _dp_equivalence_worker(rank, world):
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    keras.distribution.set_distribution(keras.distribution.DataParallel())
+    m = _equivalence_model(keras)
+    xs, ys = _equivalence_data()
+    per = xs.shape[1] // world
+    losses = [float(m.train_on_batch(xs[i][rank * per:(rank + 1) * per], ys[i][rank * per:(rank + 1) * per])) for i in range(6)]
+    m._parallel_engine.check(wait=True)
+    out = {"losses": np.array(losses)}
+    for i, w in enumerate(m.get_weights()):
+        out[f"w{i}"] = w
+    m._parallel_engine.close()
+    return out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_replicas_at_equal_global_batch_follow_the_single_gpu_run():
+    """Mean loss and mean gradient over two half batches are those of the whole batch: the curves agree to fp32 reordering."""
+    import keras_b200 as keras
+
+    codes, out = _spawn("_dp_equivalence_worker", 2)
+    assert codes == [0, 0], codes
+    single = _equivalence_model(keras)
+    xs, ys = _equivalence_data()
+    losses = [float(single.train_on_batch(xs[i], ys[i])) for i in range(6)]
+    np.testing.assert_allclose(out[0]["losses"], losses, rtol=2e-4, atol=2e-5)
+    for i, w in enumerate(single.get_weights()):
+        np.testing.assert_allclose(out[0][f"w{i}"], w, rtol=2e-3, atol=2e-5)
+        np.testing.assert_array_equal(out[0][f"w{i}"], out[1][f"w{i}"])
+
+
 def test_bounded_wait_reports_timeout_and_context_survives():
     from keras_b200.kernels import ops as kops
 
