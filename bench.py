@@ -138,6 +138,8 @@ def llama_layout(keras, cfg, world):
     lm["attn_.*/attention_output/kernel"] = ("model", None, None)
     lm["(gate|up)_.*/kernel"] = (None, "model")
     lm["down_.*/kernel"] = ("model", None)
+    if cfg.get("shard_head", True):
+        lm["lm_head/kernel"] = (None, "model")  # each rank computes its slice of the vocabulary; the logits are gathered
     return keras.distribution.ModelParallel(layout_map=lm, batch_dim_name="data"), data_axis
 
 
@@ -168,7 +170,7 @@ def describe(cfg, world):
         data_axis = world // model_axis
         return ("decoder training throughput (ModelParallel)", "tokens/sec", cfg["global_batch"] * cfg["seq"] / world,
                 {"model": cfg["model"], "global_batch": cfg["global_batch"], "seq_len": cfg["seq"], "parallelism": f"dp{data_axis}xtp{model_axis}",
-                 "sharding": "q/k/v/gate/up by columns, o/down by rows; batch-sharded activations between blocks (fused all-gather->GEMM, GEMM->reduce-scatter)",
+                 "sharding": "q/k/v/gate/up and the vocabulary projection by columns, o/down by rows; batch-sharded activations between blocks (fused all-gather->GEMM, GEMM->reduce-scatter)",
                  "optimizer": "AdamW(lr=3e-4, weight_decay=0.1)", "policy": "mixed_bfloat16",
                  "l2_hygiene": "inputs_larger_than_L2 (weights and activations of a step exceed 126 MB)"})
     return ("decoder training throughput", "tokens/sec", bs * cfg["seq"],
