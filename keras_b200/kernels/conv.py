@@ -20,6 +20,7 @@ import os
 
 import torch
 
+from keras_b200.kernels import grad_merge
 from keras_b200.kernels import ops as kops
 from keras_b200.kernels import shadow
 from keras_b200.kernels.gemm import _err_flag
@@ -88,7 +89,7 @@ class ConvFn(torch.autograd.Function):
     """y = conv2d(x, w) for channels-last bf16 tensors on the implicit-GEMM kernel; all three products run on it."""
 
     @staticmethod
-    def forward(ctx, x, w, g, grad_target, partials, plan):
+    def forward(ctx, x, w, g, grad_target, partials, plan, merge=None):
         N, H, W, Cin, Cout, Ho, Wo = g.N, g.H, g.W, g.Cin, g.Cout, g.Ho, g.Wo
         y = torch.empty((N, Ho, Wo, Cout), dtype=torch.bfloat16, device=x.device)
         ld = partials.shape[-1] if partials is not None else 0
@@ -120,6 +121,7 @@ class ConvFn(torch.autograd.Function):
         ctx.save_for_backward(saved_a, w)
         ctx.g = g
         ctx.grad_target = grad_target
+        ctx.merge = merge  # grad_merge.MergeSlot of the input activation, or None
         ctx.w_dtype = w.dtype
         return y
 
@@ -134,18 +136,26 @@ class ConvFn(torch.autograd.Function):
         dx = dw = None
         one = g.R == 1 and g.S == 1
         if ctx.needs_input_grad[0]:
+            # another consumer of the same activation may already have left its gradient: then this one is added into it
+            merged = None if g.patch else grad_merge.target(ctx.merge, (N, H, W, Cin), torch.bfloat16)
+            add = merged is not None
             if one and g.sh == 1 and g.sw == 1:
                 M = N * H * W
-                dx = torch.empty((N, H, W, Cin), dtype=torch.bfloat16, device=dy.device)
-                _igemm(dy, (1, 1, M, Cout), (Cout, M * Cout, M * Cout), w, dx, (1, M, Cin), (Cin, M * Cin, M * Cin), (1, 1, 0, 0, 0, 0), 1, Cin, Cout)
+                dx = merged if add else torch.empty((N, H, W, Cin), dtype=torch.bfloat16, device=dy.device)
+                _igemm(dy, (1, 1, M, Cout), (Cout, M * Cout, M * Cout), w, dx, (1, M, Cin), (Cin, M * Cin, M * Cin), (1, 1, 0, 0, 0, 0), 1, Cin, Cout,
+                       accumulate=add)
             elif one:
-                dx = torch.zeros((N, H, W, Cin), dtype=torch.bfloat16, device=dy.device)
+                dx = merged if add else torch.zeros((N, H, W, Cin), dtype=torch.bfloat16, device=dy.device)
                 _igemm(dy, (N, Ho, Wo, Cout), _nhwc_strides(Ho, Wo, Cout), w, dx, (Ho, Wo, Cin), (g.sw * Cin, g.sh * W * Cin, H * W * Cin),
-                       (1, 1, 0, 0, 0, 0), 1, Cin, Cout)
+                       (1, 1, 0, 0, 0, 0), 1, Cin, Cout, accumulate=add)
             else:
-                dx = torch.empty((N, H, W, Cin), dtype=torch.bfloat16, device=dy.device)
+                dx = merged if add else torch.empty((N, H, W, Cin), dtype=torch.bfloat16, device=dy.device)
                 _igemm(dy, (N, Ho, Wo, Cout), _nhwc_strides(Ho, Wo, Cout), w, dx, (H, W, Cin), _nhwc_strides(H, W, Cin),
-                       (g.R, g.S, g.pt, -g.dh, g.pl, -g.dw), 1, Cin, Cout)
+                       (g.R, g.S, g.pt, -g.dh, g.pl, -g.dw), 1, Cin, Cout, accumulate=add)
+            if add:
+                dx = None  # already inside the other consumer's gradient tensor
+            else:
+                grad_merge.offer(ctx.merge, dx)
         if ctx.needs_input_grad[1]:
             acc = None if g.patch else shadow.grad_slot(ctx.grad_target, w.shape)
             in_place = acc is not None
@@ -168,7 +178,7 @@ class ConvFn(torch.autograd.Function):
                            (g.R, g.S, -g.pt, g.dh, -g.pl, g.dw))
                 if not in_place:
                     dw = buf.reshape(g.R, g.S, Cin, Cout).to(ctx.w_dtype)
-        return dx, dw, None, None, None, None
+        return dx, dw, None, None, None, None, None
 
 
 def _geometry(x, kernel, strides, padding, dilation):
@@ -267,5 +277,5 @@ def conv(x, kernel, strides, padding, data_format, dilation, grad_target=None, w
         partials = torch.empty((grid, 2, ld), dtype=torch.float32, device=x.device)
         stats = ConvStats(partials, grid, n_tiles, bn, ld, g.N * g.Ho * g.Wo)
     target = _target_param(grad_target, w) if grad_target is not None and w is kernel else None
-    y = ConvFn.apply(x, w, g, target, partials, plan)
+    y = ConvFn.apply(x, w, g, target, partials, plan, grad_merge.slot_of(x))
     return (y, stats) if want_stats else y

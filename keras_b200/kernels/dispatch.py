@@ -132,7 +132,10 @@ def batch_norm(layer, inputs, training, residual=None, relu=False, pre_bias=None
     if training:
         if beta is None:
             beta = torch.zeros(C, dtype=torch.float32, device=x.device)
-        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu), pre_bias, conv_stats)
+        from keras_b200.kernels import grad_merge
+
+        return ops.FusedBatchNormAct.apply(x, gamma, beta, residual, mm, mv, float(layer.momentum), float(layer.epsilon), bool(relu), pre_bias, conv_stats,
+                                           grad_merge.slot_of(residual))
     if torch.is_grad_enabled() and (x.requires_grad or (gamma is not None and gamma.requires_grad and layer.trainable)):
         return None
     with torch.no_grad():

@@ -119,7 +119,7 @@ class FusedBatchNormAct(torch.autograd.Function):
     """y = relu?(batchnorm_train(x) (+ residual)) for channels-last x, with moving-stat update."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu, pre_bias=None, conv_stats=None):
+    def forward(ctx, x, gamma, beta, residual, moving_mean, moving_var, momentum, eps, relu, pre_bias=None, conv_stats=None, merge=None):
         lib = _lib()
         C = x.shape[-1]
         M = x.numel() // C
@@ -154,6 +154,8 @@ class FusedBatchNormAct(torch.autograd.Function):
                       beta if beta is not None and beta.is_leaf and beta.requires_grad else None)
         ctx.relu = relu
         ctx.has_res = residual is not None
+        ctx.merge = merge if residual is not None else None  # grad_merge.MergeSlot of the residual activation
+        ctx.res_shape = tuple(residual.shape) if residual is not None else None
         ctx.dims = (M, C)
         return y
 
@@ -179,7 +181,17 @@ class FusedBatchNormAct(torch.autograd.Function):
                                                _p(slot_g), _p(slot_b), _ll(M), _i(C), _i(dt), st), "bn_bwd_apply")
         dgamma = sums[C:2 * C] if gamma is not None and slot_g is None else None
         dbeta = sums[:C] if slot_b is None else None
-        return dx, dgamma, dbeta, dres, None, None, None, None, None, None, None
+        if dres is not None and ctx.merge is not None:
+            from keras_b200.kernels import grad_merge
+
+            dres = dres.view(ctx.res_shape)
+            other = grad_merge.target(ctx.merge, dres.shape, dres.dtype)
+            if other is not None:
+                other.add_(dres)  # the other consumer of the residual activation ran first: its tensor carries the sum
+                dres = None
+            else:
+                grad_merge.offer(ctx.merge, dres)
+        return dx, dgamma, dbeta, dres, None, None, None, None, None, None, None, None
 
 
 def bn_inference(x, scale, shift, residual, relu):

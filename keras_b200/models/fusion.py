@@ -141,6 +141,28 @@ def build_plan(function):
             plan[id(c)] = "pool_padded"
         elif plan.get(id(c)) == "conv_fold_bias" and cop.rank == 2 and cop.padding == "valid" and all(lo == hi for lo, hi in op.padding):
             plan[id(n)] = "pad_fold"
+    # Activations read by exactly two consumers that can share one gradient buffer (kernels/grad_merge.py): a bias-folded
+    # convolution reading the tensor itself, plus either a second such convolution (projection shortcut) or the fused
+    # BatchNorm+Add that takes the tensor as its residual operand (identity shortcut).
+    merge = set()
+    for n in nodes:
+        for out in n.outputs:
+            cons = consumers.get(id(out), [])
+            if id(out) in output_ids or len(cons) != 2 or cons[0] is cons[1]:
+                continue
+            kinds = []
+            for c in cons:
+                role = plan.get(id(c))
+                if role == "conv_fold_bias" and len(c.input_tensors) == 1:
+                    kinds.append("conv")
+                elif role in ("consume_add", "consume_add_relu"):
+                    # the residual operand is the one that does not come from a deferred BatchNormalization
+                    src = producers.get(id(out))
+                    if src is not None and plan.get(id(src)) != "defer_bn":
+                        kinds.append("add")
+            if sorted(kinds) in (["conv", "conv"], ["add", "conv"]):
+                merge.add(id(out))
+    plan["merge_tensors"] = merge
     return plan
 
 

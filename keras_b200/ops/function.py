@@ -130,10 +130,23 @@ class Function(Operation):
             plan = self._fusion_plan = fusion.build_plan(self)
         training = fusion.training
         sp = global_state.get_global_attribute("tp_sequence_parallel")
+        merge = plan.get("merge_tensors", ())
+        marked = set()
+        if merge:
+            import torch
+
+            from keras_b200.kernels import grad_merge
         for node in nodes:
             ins = node.input_tensors
             if any(id(t) not in env for t in ins):
                 continue
+            if merge:
+                # an activation with two gradient-sharing consumers gets its slot as soon as it exists as a tensor
+                for t in ins:
+                    if id(t) in merge and id(t) not in marked:
+                        marked.add(id(t))
+                        if isinstance(env[id(t)], torch.Tensor):
+                            grad_merge.mark(env[id(t)])
             role = plan.get(id(node))
             outs = node.outputs
             if role == "pad_fold":

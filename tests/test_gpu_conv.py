@@ -179,3 +179,42 @@ def test_conv_layer_with_batchnorm_uses_epilogue_statistics(monkeypatch):
     monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "1")
     p_plain = model.predict(x, verbose=0)
     assert np.allclose(p_fused, p_plain, atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("k1,s1,k2,s2", [(1, 1, 3, 1), (1, 2, 1, 2), (3, 1, 1, 1)])
+def test_two_consumers_share_one_gradient_buffer(k1, s1, k2, s2):
+    """An activation read by two convolutions: the second data-gradient kernel adds into the first one's tensor (TMA
+    reduce-add in bf16) and the input gradient equals the sum of both."""
+    import torch.nn.functional as F
+
+    from keras_b200.kernels import conv as kconv
+    from keras_b200.kernels import grad_merge, shadow
+
+    torch.manual_seed(0)
+    n, h, w, c = 4, 28, 28, 64
+    x = torch.randn(n, h, w, c, device="cuda").bfloat16().requires_grad_(True)
+    ka = (torch.randn(k1, k1, c, 128, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    kb = (torch.randn(k2, k2, c, 64, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    xm = grad_merge.mark(x.view_as(x))  # the marked tensor is an activation, not the leaf
+    slot = grad_merge.slot_of(xm)
+    assert slot is not None
+    ya = kconv.conv(xm, ka, (s1, s1), "same", "channels_last", (1, 1))
+    yb = kconv.conv(xm, kb, (s2, s2), "same", "channels_last", (1, 1))
+    ga, gb = torch.randn_like(ya), torch.randn_like(yb)
+    with shadow.arena_backward():
+        torch.autograd.backward([ya, yb], [ga, gb])
+    assert slot.buffer is not None  # one consumer offered its tensor, the other one added into it
+
+    xf = x.detach().float().permute(0, 3, 1, 2).requires_grad_(True)
+
+    def ref(kernel, stride, k):
+        wgt = kernel.detach().float().permute(3, 2, 0, 1)
+        if stride == 1:
+            return F.conv2d(xf, wgt, padding=k // 2)
+        # "same" with stride 2: pad so that the output has ceil(h / 2) rows
+        total = max((-(-h // stride) - 1) * stride + k - h, 0)
+        return F.conv2d(F.pad(xf, (total // 2, total - total // 2, total // 2, total - total // 2)), wgt, stride=stride)
+
+    ra, rb = ref(ka, s1, k1), ref(kb, s2, k2)
+    torch.autograd.backward([ra, rb], [ga.float().permute(0, 3, 1, 2), gb.float().permute(0, 3, 1, 2)])
+    torch.testing.assert_close(x.grad.float(), xf.grad.permute(0, 2, 3, 1), atol=0.15, rtol=5e-2)
