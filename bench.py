@@ -76,6 +76,9 @@ def build_model(keras, cfg):
     h = keras.layers.LayerNormalization(epsilon=1e-5, name="ln_f")(h)
     logits = keras.layers.Dense(cfg["vocab"], use_bias=False, name="lm_head")(h)
     model = keras.Model(tokens, logits)
+    if cfg.get("float8"):
+        # the float8 dtype policy on every Dense / EinsumDense (e4m3 operands, e5m2 output gradients, delayed scaling)
+        model.quantize("float8")
     model.compile(optimizer=keras.optimizers.AdamW(learning_rate=3e-4, weight_decay=0.1),
                   loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
     return model
