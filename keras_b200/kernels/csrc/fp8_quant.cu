@@ -155,7 +155,52 @@ __global__ void __launch_bounds__(256) fp8_quantize_vec_kernel(const T* __restri
   }
 }
 
+// Delayed-scaling bookkeeping of one tensor in one launch (the reference spends about nine elementwise kernels on it):
+//   new_scale   = 1 / (dtype_max / max(history))      kept at `scale` when that maximum is 0 or not finite
+//   new_history = history rolled by one towards the front, with the new max |x| in slot 0
+// (keras/src/quantizers/quantizers.py:585-606).  `amax` holds float bits (as written by the quantise kernel).
+__global__ void __launch_bounds__(256) fp8_delayed_scaling_kernel(const float* __restrict__ history, int length, const float* __restrict__ scale,
+                                                                  const unsigned* __restrict__ amax, float dtype_max,
+                                                                  float* __restrict__ new_scale, float* __restrict__ new_history) {
+  __shared__ float red[8];
+  float m = -INFINITY;
+  bool nan = false;
+  for (int i = threadIdx.x; i < length; i += 256) {
+    const float h = history[i];
+    nan |= h != h;
+    m = fmaxf(m, h);
+    new_history[i] = i == 0 ? __uint_as_float(*amax) : history[(i + 1 == length) ? 0 : i + 1];
+  }
+  // slot 0 of the rolled history is the old slot 1, then overwritten by the new amax: handled above; the last slot takes old slot 0
+  m = nan ? NAN : m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, m, o);
+    m = (m != m || other != other) ? NAN : fmaxf(m, other);
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = red[0];
+    for (int k = 1; k < 8; ++k) t = (t != t || red[k] != red[k]) ? NAN : fmaxf(t, red[k]);
+    const float old_sf = 1.f / *scale;
+    float sf = dtype_max / t;
+    if (!(t > 0.f)) sf = old_sf;     // zero (or NaN) maximum: keep the old scale factor
+    if (!isfinite(t)) sf = old_sf;
+    *new_scale = 1.f / sf;
+  }
+}
+
 }  // namespace
+
+// history: [length] fp32; scale: device scalar; amax: device word with float bits; outputs: new_scale [1], new_history [length].
+KB_API int kb200_fp8_delayed_scaling(const float* history, int length, const float* scale, const unsigned* amax, float dtype_max, float* new_scale,
+                                     float* new_history, cudaStream_t stream) {
+  if (length <= 0) return 0;
+  fp8_delayed_scaling_kernel<<<1, 256, 0, stream>>>(history, length, scale, amax, dtype_max, new_scale, new_history);
+  KB_CHECK_LAUNCH("fp8_delayed_scaling");
+  return 0;
+}
 
 // x: [rows, cols] bf16 (dtype 1) or fp32 (0) with row pitch ldx elements.  q: [rows, ldq] bytes or null; qt: [cols, ldqt] bytes or
 // null (pitches multiples of 4).  scale: device scalar.  amax: device word, zeroed by the caller, receives max |x| as float bits.

@@ -76,13 +76,14 @@ def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bf
     return out.reshape(tuple(q_inputs.shape[:-1]) + (N,))
 
 
-def fp8_matmul(layer, inputs, kernel, equation, training):
-    """float8-policy product on the fp8 tensor-core GEMM (plain matmul on the last axis only); ``None`` otherwise."""
+def fp8_matmul(layer, inputs, kernel, equation, training, bias=None):
+    """float8-policy product on the fp8 tensor-core GEMM (plain matmul on the last axis only); ``None`` otherwise.  ``bias``
+    (optional) is added by the GEMM's epilogue."""
     if equation is not None or not enabled(inputs):
         return None
     from keras_b200.kernels import fp8
 
-    return fp8.linear(layer, inputs, kernel, training)
+    return fp8.linear(layer, inputs, kernel, training, bias=bias)
 
 
 def conv(x, kernel, strides, padding, data_format, dilation):

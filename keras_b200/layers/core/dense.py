@@ -260,8 +260,12 @@ class Dense(CalibratedKernel, Layer):
     def _float8_call(self, inputs, training=None):
         if self.lora_enabled:
             raise NotImplementedError("Currently, `_float8_call` doesn't support LoRA")
-        out = quantizers.float8_matmul(self, inputs, self._kernel.value, None, training)
-        return self._finish(out, inputs)
+        if self.bias is None:
+            return self._finish(quantizers.float8_matmul(self, inputs, self._kernel.value, None, training), inputs)
+        out, bias_added = quantizers.float8_matmul(self, inputs, self._kernel.value, None, training, bias=self.bias)
+        if not bias_added:
+            return self._finish(out, inputs)
+        return out if self.activation is None else self.activation(out)
 
     def quantize(self, mode=None, type_check=True, config=None):
         if type_check and type(self) is not Dense:

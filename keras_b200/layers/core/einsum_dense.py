@@ -379,8 +379,17 @@ class EinsumDense(CalibratedKernel, Layer):
             for d in kv.shape[:nk]:
                 kdim *= d
             lead = inputs.shape[: inputs.ndim - nk]
-            out = quantizers.float8_matmul(self, inputs.reshape(tuple(lead) + (kdim,)), kv.reshape(kdim, -1), None, training)
-            out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+            x2 = inputs.reshape(tuple(lead) + (kdim,))
+            # a bias that spans exactly the kernel's output axes is one vector of the flattened width: the GEMM adds it
+            flat_bias = self.bias is not None and tuple(self.bias.shape) == tuple(kv.shape[nk:])
+            if flat_bias:
+                out, bias_added = quantizers.float8_matmul(self, x2, kv.reshape(kdim, -1), None, training, bias=self.bias)
+                out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+                if bias_added:
+                    return out if self.activation is None else self.activation(out)
+            else:
+                out = quantizers.float8_matmul(self, x2, kv.reshape(kdim, -1), None, training)
+                out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
         else:
             out = quantizers.float8_matmul(self, inputs, kv, self.equation, training)
         return self._finish(out, inputs)

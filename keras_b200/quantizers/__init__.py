@@ -340,23 +340,30 @@ class _QDQOutputGrad(torch.autograd.Function):
         return qdq, new_scale, new_history, None
 
 
-def float8_matmul(layer, inputs, kernel, equation, training):
+def float8_matmul(layer, inputs, kernel, equation, training, bias=None):
     """``inputs (x) kernel`` with e4m3 operands and e5m2 output gradient, delayed scaling.
 
-    ``equation`` None means a plain matmul on the last axis, else an einsum equation.
+    ``equation`` None means a plain matmul on the last axis, else an einsum equation.  With ``bias`` (a variable of the
+    output width) the result is ``(output, bias_added)``: the fp8 tensor-core path adds it in its epilogue, the emulated
+    path leaves it to the caller.
     """
     from keras_b200.kernels import dispatch
 
     inputs = convert_to_tensor(inputs)
     compute = layer.compute_dtype
     training = bool(training)
-    fused = dispatch.fp8_matmul(layer, inputs, kernel, equation, training)
+    fused = dispatch.fp8_matmul(layer, inputs, kernel, equation, training, bias=bias)
     if fused is not None:
-        return fused
+        return fused if bias is None else (fused, True)
     a = _QDQOperand.apply(inputs, layer.inputs_scale._value, layer.inputs_amax_history._value, training, compute)
     b = _QDQOperand.apply(kernel, layer.kernel_scale._value, layer.kernel_amax_history._value, training, compute)
-    out = torch.matmul(a, b.to(a.dtype)) if equation is None else torch.einsum(equation, a, b.to(a.dtype))
-    return _QDQOutputGrad.apply(out, layer.outputs_grad_scale._value, layer.outputs_grad_amax_history._value, compute)
+    out = None
+    if equation is None:
+        out = dispatch.matmul(a, b.to(a.dtype))  # own bf16 GEMM (handles widths that are not multiples of 8), else the library
+    if out is None:
+        out = torch.matmul(a, b.to(a.dtype)) if equation is None else torch.einsum(equation, a, b.to(a.dtype))
+    out = _QDQOutputGrad.apply(out, layer.outputs_grad_scale._value, layer.outputs_grad_amax_history._value, compute)
+    return out if bias is None else (out, False)
 
 
 def set_quantized_policy(layer, mode):

@@ -576,3 +576,50 @@ def test_flash_attention_training_path_gradients(monkeypatch):
     ref.backward(g.float())
     for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
         assert torch.allclose(a.float(), b, atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.gpu
+def test_fp8_delayed_scaling_kernel_matches_reference_formulas():
+    from keras_b200 import quantizers
+    from keras_b200.kernels import fp8
+
+    torch.manual_seed(0)
+    for length, fill in [(1024, "random"), (16, "random"), (1024, "zeros"), (7, "inf")]:
+        hist = torch.rand(length, device="cuda") * 3 if fill == "random" else torch.zeros(length, device="cuda")
+        if fill == "inf":
+            hist[3] = float("inf")
+        scale = torch.tensor(0.37, device="cuda")
+        amax = torch.tensor([2.5], device="cuda")
+        new_scale, new_hist = fp8.delayed_scaling(hist, scale, amax, 448.0)
+        want_scale = quantizers.compute_float8_scale(torch.amax(hist, dim=0), scale, 448.0)
+        want_hist = torch.roll(hist, shifts=-1).clone()
+        want_hist[0] = 2.5
+        torch.testing.assert_close(new_scale, want_scale, rtol=1e-6, atol=0)
+        assert torch.equal(new_hist, want_hist)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,with_bias", [(512, True), (1001, False), (1001, True)])
+def test_float8_dense_with_bias_and_odd_width_matches_emulation(n, with_bias):
+    """The fp8 tensor-core path (bias in the epilogue, zero-padded width) against quantise-dequantise around a float matmul."""
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    try:
+        keras.utils.set_random_seed(3)
+        layer = keras.layers.Dense(n, use_bias=with_bias, bias_initializer="random_normal")
+        layer.build((None, 256))
+        layer.quantize("float8")
+        x = torch.randn(64, 256, device="cuda").bfloat16().requires_grad_(True)
+        y = layer(x, training=True)
+        assert tuple(y.shape) == (64, n) and y.dtype == torch.bfloat16
+        g = torch.randn_like(y)
+        y.backward(g)
+        w = layer.kernel.value.float() if hasattr(layer.kernel, "value") else layer.kernel.float()
+        q = lambda t, m: torch.clip(t.float(), -m, m).to(torch.float8_e4m3fn if m == 448 else torch.float8_e5m2).float()  # noqa: E731
+        ref = q(x.detach(), 448) @ q(w, 448)
+        if with_bias:
+            ref = ref + layer.bias.value.float()
+        torch.testing.assert_close(y.float(), ref, atol=0.15, rtol=3e-2)
+        ref_dx = q(g, 57344) @ q(w, 448).t()
+        torch.testing.assert_close(x.grad.float(), ref_dx, atol=0.3, rtol=5e-2)
+    finally:
+        keras.config.set_dtype_policy("float32")
