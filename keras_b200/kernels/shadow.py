@@ -112,8 +112,15 @@ def attach(variables):
                 return _ShadowRead.apply(value, _sh)
             return _sh
 
-        def invalidate(_state=state):
-            _state["version"] = -1
+        def invalidate(_v=v, _sh=sh, _state=state):
+            """The parameter was assigned (``assign``, weight loading): refresh the shadow now.  A recorded training step reads
+            the shadow without coming back to Python, so "at the next read" would be one step too late."""
+            p_now = _v._value
+            if p_now is not None and p_now.is_cuda and p_now.shape == _sh.shape and p_now.dtype == torch.float32:
+                ops.cast_f32_to_bf16(p_now.detach().reshape(-1), _sh.reshape(-1))
+                _state["version"], _state["ptr"] = p_now._version, p_now.data_ptr()
+            else:
+                _state["version"] = -1
 
         v._shadow = (torch.bfloat16, read, invalidate)
 

@@ -143,3 +143,31 @@ def test_unused_variable_is_skipped_like_a_missing_gradient():
     assert model._graphed_step.replays == 4
     np.testing.assert_array_equal(spare.numpy(), np.ones((4, 4), "float32"))
     assert np.abs(model.layers[1].used.numpy() - used_before).max() > 1e-4
+
+
+def test_assigned_weights_reach_the_captured_step():
+    """``set_weights`` between replays: the recorded step reads the bf16 shadows, which must follow the assignment at once."""
+    keras.config.set_dtype_policy("mixed_bfloat16")
+    try:
+        def make(jit):
+            m = _mlp(9)
+            m.compile(optimizer=keras.optimizers.SGD(0.05), loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True), jit_compile=jit)
+            return m
+
+        eager, graphed = make(False), make("auto")
+        graphed.set_weights(eager.get_weights())
+        x, y = _data(128)
+        for _ in range(5):
+            eager.train_on_batch(x, y)
+            graphed.train_on_batch(x, y)
+        assert graphed._graphed_step.replays == 2
+        fresh = [w * 0.5 for w in eager.get_weights()]
+        eager.set_weights(fresh)
+        graphed.set_weights(fresh)
+        a, b = eager.train_on_batch(x, y), graphed.train_on_batch(x, y)
+        assert graphed._graphed_step.replays == 3
+        np.testing.assert_allclose(b, a, rtol=1e-5, atol=1e-6)
+        for u, v in zip(graphed.get_weights(), eager.get_weights()):
+            np.testing.assert_allclose(u, v, rtol=1e-5, atol=1e-6)
+    finally:
+        keras.config.set_dtype_policy("float32")
