@@ -268,10 +268,10 @@ def conv(x, kernel, strides, padding, data_format, dilation, grad_target=None, w
         lib = kops._lib()
         plan = (ctypes.c_int * 3)()
         if g.patch or (g.R == 1 and g.S == 1 and g.sh == 1 and g.sw == 1):
-            dims = (1, 1, g.N * g.Ho * g.Wo)
+            dims, taps, depth = (1, 1, g.N * g.Ho * g.Wo), (1, 1, 0), (g.R * g.seg if g.patch else g.Cin)
         else:
-            dims = (g.N, g.Ho, g.Wo)
-        lib.kb200_conv_igemm_plan(_i(dims[0]), _i(dims[1]), _i(dims[2]), _i(g.Cout), plan)
+            dims, taps, depth = (g.N, g.Ho, g.Wo), (g.R, g.S, g.dh), g.Cin
+        lib.kb200_conv_igemm_plan(_i(dims[0]), _i(dims[1]), _i(dims[2]), _i(depth), _i(g.Cout), _i(taps[0]), _i(taps[1]), _i(taps[2]), plan)
         grid, n_tiles, bn = plan[0], plan[1], plan[2]
         ld = n_tiles * bn
         partials = torch.empty((grid, 2, ld), dtype=torch.float32, device=x.device)

@@ -63,6 +63,13 @@ struct ConvParams {
   int rank2;                // pixels are one flat dimension (1x1 filter, stride 1): 2-D tensor maps, which the TMA unit walks faster
   int oper_bytes, epi_sets; // operand region size; sets of four epilogue warps that share a tile's columns (1 or 2)
   int resident_b;           // igemm: this CTA's column slice of the kernel array stays in shared memory for all tiles
+  // igemm, rows shared between vertical taps: one box of (ht + R - 1) image rows per (column offset s, channel block) serves
+  // the R taps of that column.  A tap's operand is the same shared-memory tile entered `row offset * wt` pixels further on:
+  // with wt a multiple of 8 that is a multiple of 1024 bytes, so the 128-byte swizzle pattern of the tile still applies.
+  int hshare;
+  int a_bytes;              // bytes of the activation box of one stage (16 KB without hshare)
+  int h_first;              // hshare: image-row offset of the box relative to the tile's first output row
+  int h_sign;               // hshare: +1 when tap r reads box row r, -1 when it reads box row R - 1 - r
   // wgrad
   int m_tiles;              // 128-row tiles over the input channels
   int split, pb_per, total_pb;
@@ -288,7 +295,34 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           }
         }
       }
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok && p.hshare; u += gridDim.x) {
+        int w0, h0, n0;
+        pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
+        for (int sc = 0; sc < p.S && ok; ++sc) {
+          const int dw = p.dw0 + sc * p.dw_step;
+          for (int kc = 0; kc < p.kc_blocks; ++kc, ++it) {
+            const int st = it % STAGES;
+            ok = mbar_wait(bar_empty(s, st), ((it / STAGES) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
+            mbar_expect_tx(bar_full(s, st), (uint32_t)p.stage_bytes);
+            tma_load_4d(sa, &map_a, bar_full(s, st), kc * 64, w0 + dw, h0 + p.h_first, n0);
+            if (!p.resident_b) {
+              for (int r = 0; r < p.R; ++r) {
+                const uint32_t sb = sa + (uint32_t)p.a_bytes + (uint32_t)r * b_block;
+                const int brow = (r * p.S + sc) * p.rows_per_tap;
+                if (p.b_kmajor) {
+                  tma_load_2d(sb, &map_b, bar_full(s, st), kc * 64, brow + ng0);
+                } else {
+                  for (int j = 0; j < (p.bn >> 6); ++j) tma_load_2d(sb + j * 8192, &map_b, bar_full(s, st), ng0 + j * 64, brow + kc * 64);
+                }
+              }
+            }
+            issued = it + 1;
+          }
+        }
+      }
+      for (int u = blockIdx.x; u < total_units && ok && !p.hshare; u += gridDim.x) {
         int w0, h0, n0;
         pixel_tile_origin(p, u / p.n_tiles, w0, h0, n0);
         for (int tap = 0; tap < taps && ok; ++tap) {
@@ -303,7 +337,7 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (p.rank2) tma_load_2d(sa, &map_a, bar_full(s, st), kc * 64, w0 + dw);
             else tma_load_4d(sa, &map_a, bar_full(s, st), kc * 64, w0 + dw, h0 + dh, n0);
             if (!p.resident_b) {
-              const uint32_t sb = sa + CV_A_BYTES;
+              const uint32_t sb = sa + (uint32_t)p.a_bytes;
               if (p.b_kmajor) {
                 tma_load_2d(sb, &map_b, bar_full(s, st), kc * 64, brow + ng0);
               } else {
@@ -337,7 +371,8 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         ok = mbar_wait(bar_b_full(s, 0), 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
-      const int steps = taps * p.kc_blocks;
+      const int steps = p.hshare ? p.S * p.kc_blocks : taps * p.kc_blocks;
+      const uint32_t row_bytes = (uint32_t)(128u << p.lw);  // one image row of the tile: wt pixels of 128 bytes
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
         const uint32_t acc = local & 1;
         ok = mbar_wait(bar_acc_empty(s, acc), ((local >> 1) & 1) ^ 1, abort_flag);
@@ -350,11 +385,24 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
-          const uint32_t sb = p.resident_b ? s.res + (uint32_t)k * b_block : sa + CV_A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa, false), bdesc = make_smem_desc(sb, b_mn != 0);
+          if (p.hshare) {
+            const int sc = k / p.kc_blocks, kc = k - sc * p.kc_blocks;
+            for (int r = 0; r < p.R; ++r) {
+              const int box_row = p.h_sign > 0 ? r : p.R - 1 - r;
+              const uint32_t sb = p.resident_b ? s.res + (uint32_t)((r * p.S + sc) * p.kc_blocks + kc) * b_block
+                                               : sa + (uint32_t)p.a_bytes + (uint32_t)r * b_block;
+              const uint64_t adesc = make_smem_desc(sa + (uint32_t)box_row * row_bytes, false), bdesc = make_smem_desc(sb, b_mn != 0);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_d, adesc + (uint64_t)(a_step * kk), bdesc + (uint64_t)(b_step * kk), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+              for (int kk = 0; kk < 4; ++kk)
+                umma_bf16(tmem_d, adesc + (uint64_t)(a_step * kk), bdesc + (uint64_t)(b_step * kk), idesc, (k > 0 || r > 0 || kk > 0) ? 1u : 0u);
+            }
+          } else {
+            const uint32_t sb = p.resident_b ? s.res + (uint32_t)k * b_block : sa + (uint32_t)p.a_bytes;
+            const uint64_t adesc = make_smem_desc(sa, false), bdesc = make_smem_desc(sb, b_mn != 0);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_bf16(tmem_d, adesc + (uint64_t)(a_step * kk), bdesc + (uint64_t)(b_step * kk), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
           umma_commit(bar_empty(s, st));
         }
         if (ok) umma_commit(bar_acc_full(s, acc));
@@ -681,11 +729,49 @@ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 }  // namespace
 
-// Launch plan of kb200_conv_igemm for a result of N x Ho x Wo pixels and Cn channels: plan_out = {grid, n_tiles, bn}.
-// The statistics buffer of that call needs grid * 2 * (n_tiles * bn) floats.
-KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Cn, int* plan_out) {
-  int lw = 0, lh = 0;
+namespace {
+// Pixel tile of the forward / input-gradient kernel.  Vertical taps can share one box of (ht + R - 1) rows when the tile lies
+// inside one image and is a multiple of 8 pixels wide: taken when it cuts the 128-byte rows the TMA unit has to fetch for the
+// whole problem by a quarter or more.  Measured cost of a 4-D box is about 6 cycles per 128-byte row, which is what bounds the
+// 3x3 layers with 64 and 128 channels.
+void igemm_box(int Wo, int Ho, int N, int R, int S, int dh_step, int Ca, int Cn, int& lw, int& lh, int& hshare) {
+  static const int allow = [] { const char* e = getenv("KERAS_B200_CONV_HSHARE"); return (e != nullptr && e[0] == '0') ? 0 : 1; }();
   pick_box(128, Wo, Ho, N, lw, lh);
+  hshare = 0;
+  if (!allow || R < 2 || R > 8 || (dh_step != 1 && dh_step != -1)) return;
+  const int wt0 = 1 << lw, ht0 = 1 << lh, nt0 = 1 << (7 - lw - lh);
+  const long long tiles_plain = (long long)((Wo + wt0 - 1) / wt0) * ((Ho + ht0 - 1) / ht0) * ((N + nt0 - 1) / nt0);
+  const long long rows_plain = tiles_plain * R * S * 128;
+  // KERAS_B200_CONV_HSHARE_LW=3..7 pins log2 of the tile width (for measurements)
+  static const int pinned = [] { const char* e = getenv("KERAS_B200_CONV_HSHARE_LW"); return (e != nullptr && e[0] >= '3' && e[0] <= '7') ? e[0] - '0' : 0; }();
+  long long best = -1;
+  int best_lw = 0;
+  for (int a = 3; a <= 7; ++a) {
+    if (pinned && a != pinned) continue;
+    const int wt1 = 1 << a, ht1 = 128 >> a;
+    const long long tiles = (long long)((Wo + wt1 - 1) / wt1) * ((Ho + ht1 - 1) / ht1) * N;
+    if (tiles * 4 > tiles_plain * 5) continue;  // at most a quarter more tiles (tensor-core and epilogue work) than the plain tiling
+    const long long rows = tiles * S * wt1 * (ht1 + R - 1);
+    if (best < 0 || rows < best) { best = rows; best_lw = a; }
+  }
+  if (best < 0 || best * 4 > rows_plain * 3) return;
+  // the operand ring must still hold two stages (four when the kernel slice is resident): same arithmetic as the launcher's
+  const int bn = pick_bn(Cn), kc_blocks = (Ca + 63) / 64;
+  const int a_bytes = (1 << best_lw) * ((128 >> best_lw) + R - 1) * 128;
+  const int oper = cv_oper_bytes((bn >= 128 && R * S * kc_blocks <= 12) ? 2 : 1);
+  const long long bbytes = (long long)R * S * kc_blocks * bn * 128;
+  if (bbytes > oper - 4 * a_bytes && 2 * (a_bytes + R * bn * 128) > oper) return;
+  hshare = 1;
+  lw = best_lw;
+  lh = 7 - best_lw;
+}
+}  // namespace
+
+// Launch plan of kb200_conv_igemm for a result of N x Ho x Wo pixels and Cn channels from Ca input channels and R x S taps: plan_out = {grid, n_tiles, bn}.
+// The statistics buffer of that call needs grid * 2 * (n_tiles * bn) floats.
+KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Ca, int Cn, int R, int S, int dh_step, int* plan_out) {
+  int lw = 0, lh = 0, hshare = 0;
+  igemm_box(Wo, Ho, N, R, S, dh_step, Ca, Cn, lw, lh, hshare);
   const int wt = 1 << lw, ht = 1 << lh, nt = 1 << (7 - lw - lh);
   const int bn = pick_bn(Cn);
   const int n_tiles = (Cn + bn - 1) / bn;
@@ -697,6 +783,13 @@ KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Cn, int* plan_out) {
   plan_out[1] = n_tiles;
   plan_out[2] = bn;
   return 0;
+}
+
+// 1 when kb200_conv_igemm would share image rows between the vertical taps for this problem.
+KB_API int kb200_conv_igemm_shares_rows(int N, int Ho, int Wo, int Ca, int Cn, int R, int S, int dh_step) {
+  int lw = 0, lh = 0, hshare = 0;
+  igemm_box(Wo, Ho, N, R, S, dh_step, Ca, Cn, lw, lh, hshare);
+  return hshare;
 }
 
 // Implicit-GEMM convolution, forward or input-gradient form.
@@ -728,7 +821,13 @@ KB_API int kb200_conv_igemm(const void* a, const void* wgt, void* out, const flo
   ConvParams p{};
   p.mode = 0;
   p.lt = 7;
-  pick_box(128, Wo, Ho, N, p.lw, p.lh);
+  igemm_box(Wo, Ho, N, R, S, dh_step, Ca, Cn, p.lw, p.lh, p.hshare);
+  p.a_bytes = CV_A_BYTES;
+  if (p.hshare) {
+    p.h_first = dh_step > 0 ? dh0 : dh0 + (R - 1) * dh_step;
+    p.h_sign = dh_step > 0 ? 1 : -1;
+    p.a_bytes = (1 << p.lw) * ((1 << p.lh) + R - 1) * 128;
+  }
   const int wt = 1 << p.lw, ht = 1 << p.lh, nt = 1 << (p.lt - p.lw - p.lh);
   p.tiles_w = (Wo + wt - 1) / wt;
   p.tiles_h = (Ho + ht - 1) / ht;
@@ -766,20 +865,26 @@ KB_API int kb200_conv_igemm(const void* a, const void* wgt, void* out, const flo
   const int steps = R * S * p.kc_blocks;
   p.epi_sets = (p.bn >= 128 && steps <= 12) ? 2 : 1;
   p.oper_bytes = cv_oper_bytes(p.epi_sets);
-  if (bbytes <= p.oper_bytes - 6 * CV_A_BYTES) {
+  const int b_per_stage = (p.hshare ? R : 1) * p.bn * 128;
+  if (bbytes <= p.oper_bytes - (p.hshare ? 4 : 6) * p.a_bytes) {
     p.resident_b = 1;
     p.res_bytes = (int)bbytes;
-    p.stage_bytes = CV_A_BYTES;
+    p.stage_bytes = p.a_bytes;
   } else {
     p.resident_b = 0;
     p.res_bytes = 0;
-    p.stage_bytes = CV_A_BYTES + p.bn * 128;
+    p.stage_bytes = p.a_bytes + b_per_stage;
   }
   p.stages = (p.oper_bytes - p.res_bytes) / p.stage_bytes;
   if (p.stages > CV_MAX_STAGES) p.stages = CV_MAX_STAGES;
+  if (p.stages < 2) {
+    kb200_set_error("conv_igemm: the operand ring does not fit two stages");
+    return -8;
+  }
   p.rank2 = (R == 1 && S == 1 && H == 1 && N == 1 && Ho == 1) ? 1 : 0;
   CUtensorMap map_a, map_b, map_c;
-  bool ok = p.rank2 ? make_map(&map_a, a, Ca, W, a_sw, 64, 128) : make_map_4d(&map_a, a, Ca, W, H, N, a_sw, a_sh, a_sn, wt, ht, nt);
+  bool ok = p.rank2 ? make_map(&map_a, a, Ca, W, a_sw, 64, 128)
+                    : make_map_4d(&map_a, a, Ca, W, H, N, a_sw, a_sh, a_sn, wt, p.hshare ? ht + R - 1 : ht, nt);
   const long long wrows = (long long)R * S * rows_per_tap;
   ok = ok && (b_kmajor ? make_map(&map_b, wgt, w_cols, wrows, w_cols, 64, p.bn) : make_map(&map_b, wgt, w_cols, wrows, w_cols, 64, 64));
   const int sbw = wt < 32 ? wt : 32;

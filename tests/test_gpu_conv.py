@@ -56,6 +56,10 @@ CASES = [
     (2, 20, 20, 64, 64, 3, 1, "same", 2),
     (2, 16, 16, 64, 64, 5, 1, "same", 1),
     (2, 18, 18, 64, 128, 3, 1, (1, 1), 1),
+    (3, 57, 57, 72, 64, 3, 1, "same", 1),
+    (2, 33, 40, 128, 128, 3, 1, "same", 1),
+    (2, 30, 30, 64, 64, 5, 1, "same", 1),
+    (2, 112, 112, 64, 64, 3, 1, "valid", 1),
 ]
 
 
@@ -218,3 +222,17 @@ def test_two_consumers_share_one_gradient_buffer(k1, s1, k2, s2):
     ra, rb = ref(ka, s1, k1), ref(kb, s2, k2)
     torch.autograd.backward([ra, rb], [ga.float().permute(0, 3, 1, 2), gb.float().permute(0, 3, 1, 2)])
     torch.testing.assert_close(x.grad.float(), xf.grad.permute(0, 2, 3, 1), atol=0.15, rtol=5e-2)
+
+
+def test_row_sharing_is_taken_for_the_resnet_3x3_layers():
+    """The wide 3x3 layers load one box with a halo of image rows per kernel column instead of one box per tap; the cases
+    above that this covers are only meaningful while the choice is made."""
+    from keras_b200.kernels import ops as kops
+
+    lib = kops._lib()
+    assert lib.kb200_conv_igemm_shares_rows(256, 56, 56, 64, 64, 3, 3, 1) == 1
+    assert lib.kb200_conv_igemm_shares_rows(256, 56, 56, 64, 64, 3, 3, -1) == 1
+    assert lib.kb200_conv_igemm_shares_rows(2, 56, 56, 64, 64, 3, 3, 1) == 1
+    assert lib.kb200_conv_igemm_shares_rows(4, 28, 28, 128, 128, 3, 3, 1) == 1
+    assert lib.kb200_conv_igemm_shares_rows(256, 56, 56, 64, 256, 1, 1, 0) == 0
+    assert lib.kb200_conv_igemm_shares_rows(2, 20, 20, 64, 64, 3, 3, 2) == 0
