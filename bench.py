@@ -39,6 +39,10 @@ CONFIGS = {
                 "per_gpu_batch": 8, "seq": 2048, "vocab": 50257, "layers": 24, "d": 2048, "heads": 16, "ffn": 8192, "float8": True},
     "gpt_bf16_1b3": {"kind": "decoder", "model": "1.3B decoder (24 x 2048, 16 heads, MLP 8192, vocab 50257), bf16", "per_gpu_batch": 8, "seq": 2048,
                      "vocab": 50257, "layers": 24, "d": 2048, "heads": 16, "ffn": 8192},
+    "gpt_int8_predict": {"kind": "decoder", "model": "1.3B decoder (24 x 2048, 16 heads, MLP 8192, vocab 50257), quantize('int8'), predict", "per_gpu_batch": 64,
+                         "seq": 128, "vocab": 50257, "layers": 24, "d": 2048, "heads": 16, "ffn": 8192, "predict": True, "int8": True},
+    "gpt_int8_predict_small": {"kind": "decoder", "model": "decoder (smoke size), quantize('int8'), predict", "per_gpu_batch": 8, "seq": 64, "vocab": 1024,
+                               "layers": 2, "d": 128, "heads": 4, "ffn": 512, "predict": True, "int8": True},
     "gpt2_small": {"kind": "decoder", "model": "GPT-2 shaped (smoke size)", "per_gpu_batch": 4, "seq": 128, "vocab": 1024, "layers": 2, "d": 128,
                    "heads": 4, "ffn": 512},
 }
@@ -76,6 +80,9 @@ def build_model(keras, cfg):
     h = keras.layers.LayerNormalization(epsilon=1e-5, name="ln_f")(h)
     logits = keras.layers.Dense(cfg["vocab"], use_bias=False, name="lm_head")(h)
     model = keras.Model(tokens, logits)
+    if cfg.get("int8"):
+        # post-training quantisation of every Dense / EinsumDense kernel to int8 (per-channel scales, activations quantised per row at run time)
+        model.quantize("int8")
     if cfg.get("float8"):
         # the float8 dtype policy on every Dense / EinsumDense (e4m3 operands, e5m2 output gradients, delayed scaling)
         model.quantize("float8")
@@ -312,6 +319,52 @@ def run_e2e(keras, torch, dist, world, steps, warmup, model, host_x, host_y, las
     return ms, api
 
 
+def measure_predict(keras, torch, args, cfg, local, impl, launch_count=None):
+    """Inference throughput of a quantised model on one GPU, through the public API only (both arms run this function):
+    ``value`` times ``model(tokens, training=False)`` on device-resident batches; ``e2e`` times ``model.predict_on_batch`` on
+    pinned host batches, which copies the tokens in and the logits out every step."""
+    model = build_model(keras, cfg)
+    n_buf = 3
+    host_x, _ = make_batches(torch, cfg, 0, n_buf)
+    dev_x = [t.cuda() for t in host_x]
+    bs, seq = cfg["per_gpu_batch"], cfg["seq"]
+    last = {}
+
+    def dev_step(i):
+        with torch.no_grad():
+            last["out"] = model(dev_x[i % n_buf], training=False)
+
+    def host_step(i):
+        last["np"] = model.predict_on_batch(host_x[i % n_buf])
+
+    for i in range(max(args.warmup, 3)):
+        dev_step(i)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = launch_count() if launch_count else 0
+    ms = _timed(torch, None, 1, args.steps, dev_step)
+    launches = (launch_count() - launches0) if launch_count else 0
+    clocks = sampler.stop()
+    for i in range(3):
+        host_step(i)
+    e2e_steps = max(3, args.steps // 4)
+    ms_e2e = _timed(torch, None, 1, e2e_steps, host_step)
+    out_bytes = int(last["np"].nbytes)
+    tokens = bs * seq
+    return {
+        "metric": "decoder int8 predict throughput", "value": tokens * args.steps / (ms / 1e3), "unit": "tokens/sec", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights and activations, bf16 elsewhere", "data": "synthetic", "impl": impl,
+        "config": {"model": cfg["model"], "global_batch": bs, "per_gpu_batch": bs, "seq_len": seq, "parallelism": "dp1", "policy": "mixed_bfloat16 + quantize('int8')",
+                   "l2_hygiene": "inputs_larger_than_L2 (1.3 GB of int8 weights and the logits of a step exceed 126 MB)"},
+        "clocks": clocks,
+        "e2e": {"value": tokens * e2e_steps / (ms_e2e / 1e3), "unit": "tokens/sec", "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
+                "h2d_bytes_per_step": int(host_x[0].numel() * host_x[0].element_size()), "d2h_bytes_per_step": out_bytes,
+                "api": "Model.predict_on_batch(pinned host tokens) -> numpy logits"},
+        "gpu_launches": int(launches),
+    }
+
+
 def measure_ours(keras, torch, dist, args, cfg, rank, world, local, steps, warmup):
     """Build the config's model under the distribution that is set, time ``steps`` training steps twice (device-resident
     inputs through ``train_on_batch``; pinned host batches through ``fit``) and return the result row (every rank returns
@@ -487,6 +540,13 @@ def run_ours(args, cfg):
         else:
             keras.distribution.set_distribution(keras.distribution.DataParallel())
     keras.config.set_dtype_policy("mixed_bfloat16")
+    if cfg.get("predict"):
+        from keras_b200.kernels import ops as kops
+
+        if world > 1:
+            raise SystemExit("the predict configs run on one GPU")
+        print(json.dumps(measure_predict(keras, torch, args, cfg, local, "ours", kops.launch_count)), flush=True)
+        return
     out, model = measure_ours(keras, torch, dist, args, cfg, rank, world, local, args.steps, args.warmup)
     if out is None:
         return
@@ -566,6 +626,11 @@ def run_reference(args, cfg):
 
         keras.distribution.set_distribution(keras.distribution.DataParallel())
     keras.config.set_dtype_policy("mixed_bfloat16")
+    if cfg.get("predict"):
+        out = measure_predict(keras, torch, args, cfg, local, "reference")
+        out["framework"] = f"keras {keras.__version__} (torch backend, stock code path)"
+        print(json.dumps(out))
+        return
     model = build_model(keras, cfg)
     n_buf = 3
     host_x, host_y = make_batches(torch, cfg, rank, n_buf)

@@ -179,6 +179,69 @@ def max_pool2d(x, pool_size, strides, padding, zero_pad=None):
     return _ops().FusedMaxPool2D.apply(x, tuple(pool_size), tuple(strides), (pt, pl), (OH, OW), mode)
 
 
+def avg_pool2d(x, pool_size, strides, padding):
+    """Channels-last 2-D average pooling (padding excluded from the average) or ``None``."""
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim != 4 or x.numel() == 0:
+        return None
+    N, H, W, C = x.shape
+    if C % (8 if x.dtype == torch.bfloat16 else 4) != 0:
+        return None
+    if padding == "same":
+        OH, OW = -(-H // strides[0]), -(-W // strides[1])
+        pt = max((OH - 1) * strides[0] + pool_size[0] - H, 0) // 2
+        pl = max((OW - 1) * strides[1] + pool_size[1] - W, 0) // 2
+    else:
+        OH = (H - pool_size[0]) // strides[0] + 1
+        OW = (W - pool_size[1]) // strides[1] + 1
+        pt = pl = 0
+    if OH <= 0 or OW <= 0:
+        return None
+    return _ops().FusedAvgPool2D.apply(x, tuple(pool_size), tuple(strides), (pt, pl), (OH, OW))
+
+
+def global_avg_pool(x):
+    """Mean over all axes between the first and the last of a channels-last tensor, ``[N, ..., C] -> [N, C]``, or ``None``."""
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim < 3 or x.numel() == 0:
+        return None
+    if x.shape[-1] % (8 if x.dtype == torch.bfloat16 else 4) != 0:
+        return None
+    return _ops().FusedGlobalAvgPool.apply(x)
+
+
+def softmax(x, mask=None, masked_add=0.0, log=False):
+    """softmax / log-softmax over the last axis in the input's dtype (fp32 arithmetic), or ``None``."""
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim < 1 or x.numel() == 0 or x.shape[-1] > (1 << 24):
+        return None
+    if mask is not None and not (isinstance(mask, torch.Tensor) and mask.is_cuda):
+        return None
+    return _ops().FusedSoftmax.apply(x, mask, float(masked_add), bool(log))
+
+
+def embedding(variable, table, ids, out_dtype):
+    """``table[ids]`` cast to ``out_dtype`` in one gather kernel, with a scatter-add gradient, or ``None``.
+
+    ``variable`` is the ``Variable`` the table was read from (or ``None``)."""
+    if not enabled(table) or not isinstance(ids, torch.Tensor) or not ids.is_cuda or table.ndim != 2 or table.dtype not in _FLOAT_IO:
+        return None
+    if out_dtype not in _FLOAT_IO or table.shape[1] % 8 or ids.dtype not in (torch.int32, torch.int64) or ids.numel() == 0:
+        return None
+    if getattr(variable, "_shard_slices", None) is not None:
+        return None
+    from keras_b200.kernels import gemm
+
+    target = gemm._grad_target(variable, table) if variable is not None else None
+    return _ops().FusedEmbedding.apply(table, ids, out_dtype, target)
+
+
+def resize(x, out_hw, interpolation):
+    """NHWC bilinear / nearest resize without antialiasing, or ``None``."""
+    if not enabled(x) or x.ndim != 4 or x.dtype not in (torch.float32, torch.bfloat16, torch.uint8) or x.numel() == 0:
+        return None
+    if interpolation not in ("bilinear", "nearest") or (torch.is_grad_enabled() and x.requires_grad):
+        return None
+    return _ops().resize_nhwc(x, out_hw, interpolation == "nearest")
+
+
 def softmax_cross_entropy(logits, labels):
     if not enabled(logits) or logits.dtype not in _FLOAT_IO or logits.numel() == 0:
         return None
@@ -279,4 +342,28 @@ def fused_adam(opt, grads, variables, lr):
         plan.adam(opt._alpha(lr), opt.beta_1, opt.beta_2, opt.epsilon, lr=lr, grad_scale=scale, zero_grad=True)
     opt._fused_zeroed_grads = True
     opt._step_scalars_on_device = lr_t is not None
+    return True
+
+
+def fused_rule(opt, grads, variables, lr, name, slot_lists, consts, step_scalars=(), beta1=0.0, beta2=0.0, flags=0, u_product=None,
+               needs_step=False):
+    """RMSprop / Adagrad / Adadelta / Adamax / Nadam / Lion: the whole variable list in one launch.  ``needs_step``: the rule
+    has step-dependent scalars, taken from the device-resident iteration counter when there is one (the launch then
+    stays valid inside a recorded step) and from ``step_scalars`` otherwise."""
+    if opt.gradient_accumulation_steps:
+        return False
+    plan = _plan_for(opt, grads, variables, slot_lists)
+    if plan is None:
+        return False
+    d = _decays(opt, variables)
+    if d is not None:
+        plan.set_decays(d)
+    scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
+    lr_t, step_t = _device_scalars(opt)
+    if u_product is not None and not (u_product.is_cuda and u_product.dtype == torch.float32 and u_product.numel() == 1):
+        step_t = None
+    plan.rule(name, lr, consts, step_scalars, beta1=beta1, beta2=beta2, flags=flags, grad_scale=scale, zero_grad=True, lr_tensor=lr_t,
+              step_tensor=step_t if needs_step else None, u_product=u_product if (needs_step and step_t is not None) else None)
+    opt._fused_zeroed_grads = True
+    opt._step_scalars_on_device = lr_t is not None and (not needs_step or step_t is not None)
     return True

@@ -114,6 +114,147 @@ class FusedMaxPool2D(torch.autograd.Function):
         return dx, None, None, None, None, None
 
 
+class FusedAvgPool2D(torch.autograd.Function):
+    """Channels-last 2-D average pooling; window elements outside the image do not count (as ``padding="same"`` means in
+    keras/src/backend/torch/nn.py:449-533)."""
+
+    @staticmethod
+    def forward(ctx, x, pool, strides, pads, out_hw):
+        lib = _lib()
+        x = x.contiguous()
+        N, H, W, C = x.shape
+        OH, OW = out_hw
+        y = torch.empty((N, OH, OW, C), dtype=x.dtype, device=x.device)
+        _check(lib.kb200_avgpool2d_fwd(_p(x), _p(y), _i(N), _i(H), _i(W), _i(C), _i(OH), _i(OW), _i(pool[0]), _i(pool[1]), _i(strides[0]), _i(strides[1]),
+                                       _i(pads[0]), _i(pads[1]), _i(_dt(x)), _stream()), "avgpool_fwd")
+        ctx.geom = (N, H, W, C, OH, OW, pool, strides, pads)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        N, H, W, C, OH, OW, pool, strides, pads = ctx.geom
+        dy = dy.contiguous()
+        dx = torch.empty((N, H, W, C), dtype=dy.dtype, device=dy.device)
+        _check(lib.kb200_avgpool2d_bwd(_p(dy), _p(dx), _i(N), _i(H), _i(W), _i(C), _i(OH), _i(OW), _i(pool[0]), _i(pool[1]), _i(strides[0]), _i(strides[1]),
+                                       _i(pads[0]), _i(pads[1]), _i(_dt(dy)), _stream()), "avgpool_bwd")
+        return dx, None, None, None, None
+
+
+class FusedGlobalAvgPool(torch.autograd.Function):
+    """Mean over the pixel axes of a channels-last tensor: ``[N, *spatial, C] -> [N, C]``."""
+
+    @staticmethod
+    def forward(ctx, x):
+        lib = _lib()
+        x = x.contiguous()
+        N, C = x.shape[0], x.shape[-1]
+        P = x.numel() // (N * C)
+        y = torch.empty((N, C), dtype=x.dtype, device=x.device)
+        _check(lib.kb200_global_avgpool_fwd(_p(x), _p(y), _i(N), _i(P), _i(C), _i(_dt(x)), _stream()), "global_avgpool_fwd")
+        ctx.shape = tuple(x.shape)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        shape = ctx.shape
+        N, C = shape[0], shape[-1]
+        P = 1
+        for d in shape[1:-1]:
+            P *= d
+        dy = dy.contiguous()
+        dx = torch.empty(shape, dtype=dy.dtype, device=dy.device)
+        _check(lib.kb200_global_avgpool_bwd(_p(dy), _p(dx), _i(N), _i(P), _i(C), _i(_dt(dy)), _stream()), "global_avgpool_bwd")
+        return dx
+
+
+# ------------------------------------------------------------------------------ softmax
+class FusedSoftmax(torch.autograd.Function):
+    """softmax / log-softmax over the last axis of a contiguous tensor; ``mask`` (bool, same shape, or ``None``) marks the
+    elements that take part: the others get ``masked_add`` added before the exponential."""
+
+    @staticmethod
+    def forward(ctx, x, mask, masked_add, log_mode):
+        lib = _lib()
+        x = x.contiguous()
+        C = x.shape[-1]
+        rows = x.numel() // C
+        y = torch.empty_like(x)
+        m8 = None
+        if mask is not None:
+            m8 = mask.expand(x.shape).contiguous().view(torch.uint8) if mask.dtype == torch.bool else (mask != 0).expand(x.shape).contiguous().view(torch.uint8)
+        _check(lib.kb200_softmax_fwd(_p(x), _p(m8), _p(y), _ll(rows), _i(C), _f(masked_add), _i(1 if log_mode else 0), _i(_dt(x)), _stream()), "softmax_fwd")
+        ctx.save_for_backward(y)
+        ctx.log_mode = log_mode
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        (y,) = ctx.saved_tensors
+        C = y.shape[-1]
+        rows = y.numel() // C
+        dy = dy.to(y.dtype).contiguous()
+        dx = torch.empty_like(y)
+        _check(lib.kb200_softmax_bwd(_p(y), _p(dy), _p(dx), _ll(rows), _i(C), _i(1 if ctx.log_mode else 0), _i(_dt(y)), _stream()), "softmax_bwd")
+        return dx, None, None, None
+
+
+# ------------------------------------------------------------------------------ embedding
+class FusedEmbedding(torch.autograd.Function):
+    """``table[ids]`` in ``out_dtype``.  ``table`` is the fp32 parameter or its bf16 shadow read; ``target`` is the fp32
+    parameter when its gradient lives in persistent storage: the scatter-add then goes straight into it."""
+
+    @staticmethod
+    def forward(ctx, table, ids, out_dtype, target):
+        lib = _lib()
+        V, D = table.shape
+        ids64 = ids.reshape(-1).to(torch.int64).contiguous()
+        n = ids64.numel()
+        src = table.detach()
+        if not src.is_contiguous():
+            src = src.contiguous()
+        out = torch.empty((n, D), dtype=out_dtype, device=table.device)
+        _check(lib.kb200_embedding_fwd(_p(src), _p(ids64), _p(out), _ll(n), _i(D), _ll(V), _i(_dt(src)), _i(_dt(out)), _stream()), "embedding_fwd")
+        ctx.save_for_backward(ids64)
+        ctx.table_shape, ctx.table_dtype, ctx.target = (V, D), table.dtype, target
+        ctx.set_materialize_grads(False)
+        return out.reshape(tuple(ids.shape) + (D,))
+
+    @staticmethod
+    def backward(ctx, dout):
+        if dout is None:
+            return None, None, None, None
+        from keras_b200.kernels import shadow
+
+        lib = _lib()
+        (ids64,) = ctx.saved_tensors
+        V, D = ctx.table_shape
+        if dout.dtype not in (torch.float32, torch.bfloat16):
+            dout = dout.float()
+        dout = dout.reshape(-1, D).contiguous()
+        slot = shadow.grad_slot(ctx.target, (V, D))
+        acc = slot.view(V, D) if slot is not None else torch.zeros((V, D), dtype=torch.float32, device=dout.device)
+        _check(lib.kb200_embedding_bwd(_p(dout), _p(ids64), _p(acc), _ll(ids64.numel()), _i(D), _ll(V), _i(_dt(dout)), _stream()), "embedding_bwd")
+        if slot is not None:
+            return None, None, None, None  # already inside the parameter's gradient
+        return acc.to(ctx.table_dtype), None, None, None
+
+
+def resize_nhwc(x, out_hw, nearest, out_dtype=None):
+    """Bilinear (half-pixel centres, no antialiasing) or nearest resize of a contiguous NHWC tensor of uint8, bf16 or fp32."""
+    lib = _lib()
+    codes = {torch.float32: 0, torch.bfloat16: 1, torch.uint8: 2}
+    x = x.contiguous()
+    out_dtype = out_dtype or x.dtype
+    N, H, W, C = x.shape
+    y = torch.empty((N, out_hw[0], out_hw[1], C), dtype=out_dtype, device=x.device)
+    _check(lib.kb200_resize_nhwc(_p(x), _p(y), _i(N), _i(H), _i(W), _i(C), _i(out_hw[0]), _i(out_hw[1]), _i(1 if nearest else 0), _i(codes[x.dtype]),
+                                 _i(codes[out_dtype]), _stream()), "resize_nhwc")
+    return y
+
+
 # ------------------------------------------------------------------------------ batch norm
 class FusedBatchNormAct(torch.autograd.Function):
     """y = relu?(batchnorm_train(x) (+ residual)) for channels-last x, with moving-stat update."""
@@ -377,6 +518,27 @@ class OptimizerPlan:
         lib = _lib()
         _check(lib.kb200_fused_sgd(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _f(lr), _f(momentum), _i(1 if nesterov else 0), _f(grad_scale),
                                    _i(1 if zero_grad else 0), _p(self.found_inf) if check_inf else _vp(0), _p(lr_tensor), _stream()), "fused_sgd")
+
+
+    RULES = {"rmsprop": 0, "adagrad": 1, "adadelta": 2, "adamax": 3, "nadam": 4, "lion": 5}
+
+    def rule(self, name, lr, consts, step_scalars=(), beta1=0.0, beta2=0.0, flags=0, grad_scale=1.0, zero_grad=True, lr_tensor=None, step_tensor=None,
+             u_product=None):
+        """One launch of the rule kernel ``name`` over every tensor of the plan.  ``consts``: up to four rule constants;
+        ``step_scalars``: up to four step-dependent scalars by value, ignored by the rules that derive them from
+        ``step_tensor`` (Adamax, Nadam); ``u_product``: Nadam's device-resident running product, advanced by the kernel
+        when ``step_tensor`` is given."""
+        lib = _lib()
+        c = (ctypes.c_float * 4)(*(list(consts) + [0.0] * (4 - len(consts))))
+        k = (ctypes.c_float * 4)(*(list(step_scalars) + [0.0] * (4 - len(step_scalars))))
+        scratch = None
+        if name == "nadam" and step_tensor is not None:
+            scratch = getattr(self, "_scratch", None)
+            if scratch is None:
+                scratch = self._scratch = torch.zeros(4, dtype=torch.float32, device=self.desc.device)
+        _check(lib.kb200_fused_rule(_p(self.desc), _p(self.chunks), _i(self.n_chunks), _i(self.RULES[name]), _f(lr), c, k, _d(beta1), _d(beta2), _i(flags),
+                                    _f(grad_scale), _i(1 if zero_grad else 0), _vp(0), _p(lr_tensor), _p(step_tensor), _p(u_product), _p(scratch),
+                                    _stream()), "fused_rule")
 
 
 def cast_f32_to_bf16(src, dst):

@@ -142,6 +142,10 @@ class Softmax(Layer):
         self.built = True
 
     def call(self, inputs, mask=None):
+        if mask is not None and isinstance(inputs, torch.Tensor) and inputs.is_cuda and isinstance(mask, torch.Tensor):
+            fused = self._masked_on_device(inputs, mask)
+            if fused is not None:
+                return fused
         if mask is not None:
             # large negative instead of -inf so that fully masked rows do not produce NaN
             big = -3e4 if inputs.dtype == torch.float16 else -1e9
@@ -156,6 +160,23 @@ class Softmax(Layer):
         if mask is not None:
             out = ops.multiply(out, ops.cast(mask, out.dtype))
         return out
+
+    def _masked_on_device(self, inputs, mask):
+        """Mask, softmax over the last axis and the final multiplication by the mask in one kernel plus one multiply."""
+        from keras_b200.kernels import dispatch
+
+        axis = self.axis[0] if isinstance(self.axis, (tuple, list)) and len(self.axis) == 1 else self.axis
+        if not isinstance(axis, int) or axis % inputs.ndim != inputs.ndim - 1:
+            return None
+        keep = mask if mask.dtype == torch.bool else mask != 0
+        try:
+            keep = keep.expand(inputs.shape)
+        except RuntimeError:
+            return None
+        out = dispatch.softmax(inputs, mask=keep, masked_add=-3e4 if inputs.dtype == torch.float16 else -1e9)
+        if out is None:
+            return None
+        return out * keep.to(out.dtype)
 
     def compute_output_shape(self, input_shape):
         return input_shape

@@ -61,8 +61,24 @@ class Embedding(Layer):
     def call(self, inputs):
         if not isinstance(inputs, KerasTensor) and inputs.dtype not in (torch.int32, torch.int64):
             inputs = inputs.to(torch.int32)
+        fused = self._gather_on_device(inputs)
+        if fused is not None:
+            return fused
         out = ops.take(self.embeddings, inputs, axis=0)
         return ops.cast(out, self.compute_dtype)
+
+    def _gather_on_device(self, inputs):
+        """Gather and cast in one kernel; the gradient is scattered straight into the table's fp32 gradient storage."""
+        if not isinstance(inputs, torch.Tensor) or not inputs.is_cuda or self.lora_enabled:
+            return None
+        from keras_b200.core import dtypes
+        from keras_b200.kernels import dispatch
+
+        table = self._embeddings.value
+        if not isinstance(table, torch.Tensor):
+            return None
+        ids = torch.where(inputs < 0, inputs + table.shape[0], inputs)
+        return dispatch.embedding(self._embeddings, table, ids, dtypes.to_torch_dtype(self.compute_dtype))
 
     def compute_mask(self, inputs, mask=None):
         if not self.mask_zero:

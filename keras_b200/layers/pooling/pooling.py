@@ -1,5 +1,7 @@
 """Pooling layers (keras/src/layers/pooling/*.py): max/average 1-3D, global, adaptive."""
 
+import torch
+
 from keras_b200 import ops
 from keras_b200.core import config
 from keras_b200.core.export_registry import keras_export
@@ -119,6 +121,12 @@ def _make_global(name, dims, mode, exports):
         ns = {"__init__": __init__, "call": call, "compute_mask": compute_mask}
     else:
         def call(self, inputs):
+            if self.data_format == "channels_last" and isinstance(inputs, torch.Tensor) and inputs.is_cuda:
+                from keras_b200.kernels import dispatch
+
+                out = dispatch.global_avg_pool(inputs)
+                if out is not None:
+                    return out.reshape((inputs.shape[0],) + (1,) * dims + (inputs.shape[-1],)) if self.keepdims else out
             return ops.mean(inputs, axis=self._axes(), keepdims=self.keepdims)
         ns = {"__init__": __init__, "call": call}
     cls = type(name, (BaseGlobalPooling,), ns)

@@ -125,6 +125,13 @@ def resize(images, size, interpolation="bilinear", antialias=False, crop_to_aspe
     _check_rank(images)
     th, tw = int(size[0]), int(size[1])
     ori = images.dtype
+    if images.is_cuda and data_format == "channels_last" and not (antialias or crop_to_aspect_ratio or pad_to_aspect_ratio):
+        from keras_b200.kernels import dispatch
+
+        batched = images if images.ndim == 4 else images.unsqueeze(0)
+        out = dispatch.resize(batched, (th, tw), interpolation)
+        if out is not None:
+            return out if images.ndim == 4 else out[0]
     x, restore = _to_nchw(images, data_format)
     h, w = x.shape[-2:]
     if crop_to_aspect_ratio:

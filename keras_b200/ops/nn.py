@@ -158,8 +158,34 @@ def threshold(x, threshold, default_value):
     return F.threshold(_floatize(x), threshold=threshold, value=default_value)
 
 
+def _fused_softmax(x, axis, log):
+    """The row kernel on CUDA tensors (fp32 arithmetic on bf16 / fp32 storage, no up-cast copy), or ``None``."""
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16) or x.ndim == 0:
+        return None
+    from keras_b200.kernels import dispatch
+
+    if axis is None:
+        out = dispatch.softmax(x.reshape(-1), log=log)
+        return None if out is None else out.reshape(x.shape)
+    axes = sorted({a % x.ndim for a in (axis if isinstance(axis, (list, tuple)) else (axis,))})
+    keep = [i for i in range(x.ndim) if i not in axes]
+    perm = keep + axes
+    if perm == list(range(x.ndim)):
+        rows = x.reshape(tuple(x.shape[: len(keep)]) + (-1,))
+        out = dispatch.softmax(rows, log=log)
+        return None if out is None else out.reshape(x.shape)
+    y = x.permute(perm)
+    out = dispatch.softmax(y.reshape(tuple(y.shape[: len(keep)]) + (-1,)), log=log)
+    if out is None:
+        return None
+    return out.reshape(y.shape).permute([perm.index(i) for i in range(x.ndim)])
+
+
 def _reduce_axes_softmax(fn, x, axis):
     x = _floatize(x)
+    fused = _fused_softmax(x, axis, fn is torch.log_softmax)
+    if fused is not None:
+        return fused
     ori = x.dtype
     if ori in (torch.float16, torch.bfloat16):
         x = x.to(torch.float32)
@@ -247,6 +273,12 @@ def _pool(x, pool_size, strides, padding, data_format, kind):
         from keras_b200.kernels import dispatch
 
         out = dispatch.max_pool2d(x, pool_size, strides, padding)
+        if out is not None:
+            return out
+    if kind == "avg" and nsp == 2 and data_format == "channels_last" and x.is_cuda:
+        from keras_b200.kernels import dispatch
+
+        out = dispatch.avg_pool2d(x, pool_size, strides, padding)
         if out is not None:
             return out
     xc = _to_cf(x, data_format)

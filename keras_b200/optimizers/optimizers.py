@@ -204,6 +204,18 @@ class RMSprop(Optimizer):
         if self.centered:
             self._average_gradients = self.add_optimizer_variables(var_list, "average_gradient")
 
+    def _fused_apply(self, grads, variables):
+        if self.centered and self.momentum > 0:
+            return False  # three slots per variable: the per-variable path
+        if self.clipnorm or self.global_clipnorm or self.clipvalue or self.use_ema:
+            return False
+        lr = self._lr_float()
+        if lr is None:
+            return False
+        second = self._momentums if self.momentum > 0 else (self._average_gradients if self.centered else None)
+        return dispatch.fused_rule(self, grads, variables, lr, "rmsprop", [self._velocities, second], (self.rho, self.momentum, self.epsilon),
+                                   flags=(1 if self.momentum > 0 else 0) | (2 if self.centered else 0))
+
     def update_step(self, gradient, variable, learning_rate):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
@@ -248,6 +260,14 @@ class Adagrad(Optimizer):
 
         self._accumulators = self.add_optimizer_variables(var_list, "accumulator", initializer=initializers.Constant(self.initial_accumulator_value))
 
+    def _fused_apply(self, grads, variables):
+        if self.clipnorm or self.global_clipnorm or self.clipvalue or self.use_ema:
+            return False
+        lr = self._lr_float()
+        if lr is None:
+            return False
+        return dispatch.fused_rule(self, grads, variables, lr, "adagrad", [self._accumulators], (self.epsilon,))
+
     def update_step(self, gradient, variable, learning_rate):
         p = variable._value
         lr = _lr_for(self, p.dtype, learning_rate)
@@ -276,6 +296,14 @@ class Adadelta(Optimizer):
             return
         super().build(var_list)
         self._accumulated_grads, self._accumulated_delta_vars = self.add_optimizer_variables(var_list, ["accumulated_grad", "accumulated_delta_var"])
+
+    def _fused_apply(self, grads, variables):
+        if self.clipnorm or self.global_clipnorm or self.clipvalue or self.use_ema:
+            return False
+        lr = self._lr_float()
+        if lr is None:
+            return False
+        return dispatch.fused_rule(self, grads, variables, lr, "adadelta", [self._accumulated_grads, self._accumulated_delta_vars], (self.rho, self.epsilon))
 
     def update_step(self, grad, variable, learning_rate):
         p = variable._value
@@ -308,6 +336,16 @@ class Adamax(Optimizer):
             return
         super().build(var_list)
         self._m, self._u = self.add_optimizer_variables(var_list, ["momentum", "norm"])
+
+    def _fused_apply(self, grads, variables):
+        if self.clipnorm or self.global_clipnorm or self.clipvalue or self.use_ema:
+            return False
+        lr = self._lr_float()
+        if lr is None:
+            return False
+        t = self._local_step() + 1
+        return dispatch.fused_rule(self, grads, variables, lr, "adamax", [self._m, self._u], (self.beta_1, self.beta_2, self.epsilon),
+                                   step_scalars=(1 - self.beta_1 ** t,), beta1=self.beta_1, beta2=self.beta_2, needs_step=True)
 
     def update_step(self, gradient, variable, learning_rate):
         p = variable._value
@@ -347,6 +385,21 @@ class Nadam(Optimizer):
         with name_scope(self.name, caller=self):
             self._u_product = Variable(1.0, dtype=dtype, trainable=False, name="u_product")
         self._track_variable(self._u_product)
+
+    def _fused_apply(self, grads, variables):
+        if self.clipnorm or self.global_clipnorm or self.clipvalue or self.use_ema:
+            return False
+        lr = self._lr_float()
+        if lr is None:
+            return False
+        from keras_b200.kernels.dispatch import _device_scalars
+
+        u = self._u_product._value
+        if _device_scalars(self)[1] is None or not (u.is_cuda and u.dtype == torch.float32):
+            return False
+        # the kernel advances the running product and derives the step scalars from the device-resident iteration counter
+        return dispatch.fused_rule(self, grads, variables, lr, "nadam", [self._momentums, self._velocities], (self.beta_1, self.beta_2, self.epsilon),
+                                   beta1=self.beta_1, beta2=self.beta_2, u_product=u, needs_step=True)
 
     def _backend_update_step(self, grads, trainable_variables, learning_rate):
         dtype = self._u_product._value.dtype
@@ -395,6 +448,14 @@ class Lion(Optimizer):
             return
         super().build(var_list)
         self._momentums = self.add_optimizer_variables(var_list, "momentum")
+
+    def _fused_apply(self, grads, variables):
+        if self.clipnorm or self.global_clipnorm or self.clipvalue or self.use_ema:
+            return False
+        lr = self._lr_float()
+        if lr is None:
+            return False
+        return dispatch.fused_rule(self, grads, variables, lr, "lion", [self._momentums], (self.beta_1, self.beta_2))
 
     def update_step(self, gradient, variable, learning_rate):
         p = variable._value

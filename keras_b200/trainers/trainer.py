@@ -711,6 +711,10 @@ class Trainer:
                     "A model is 'built' when its variables have been created and its `self.built` attribute is True. Usually, "
                     "calling the model on a batch of data is the right way to build it.\nException encountered:\n" f"'{e}'"
                 )
+            # variables created while tracing are registered for initialisation and get their values here, on the real device
+            from keras_b200.core.variables import initialize_all_variables
+
+            initialize_all_variables()
             if compile_metrics_unbuilt:
                 self._compile_metrics.build(y, y_pred)
             if compile_loss_unbuilt:

@@ -166,6 +166,44 @@ def test_fused_optimizers_match_eager_rules():
             np.testing.assert_allclose(v.numpy(), r, rtol=2e-4, atol=2e-5)
 
 
+@pytest.mark.parametrize("make", [
+    lambda k: k.optimizers.RMSprop(1e-2, rho=0.9),
+    lambda k: k.optimizers.RMSprop(1e-2, rho=0.9, momentum=0.8),
+    lambda k: k.optimizers.RMSprop(1e-2, centered=True, weight_decay=0.05),
+    lambda k: k.optimizers.Adagrad(0.05),
+    lambda k: k.optimizers.Adadelta(1.0),
+    lambda k: k.optimizers.Adamax(2e-2, weight_decay=0.01),
+    lambda k: k.optimizers.Nadam(2e-2),
+    lambda k: k.optimizers.Lion(1e-3, weight_decay=0.1),
+], ids=["rmsprop", "rmsprop_momentum", "rmsprop_centered_decay", "adagrad", "adadelta", "adamax_decay", "nadam", "lion_decay"])
+def test_rule_kernel_matches_the_per_variable_update(make, monkeypatch):
+    """One launch of the rule kernel over all variables against the same optimizer stepping variable by variable with torch ops."""
+    shapes = [(64, 33), (7,), (3, 3, 16, 32), (1000,), (8193,)]
+    torch.manual_seed(5)
+    init = [torch.randn(s) for s in shapes]
+    steps = [[torch.randn(s, device="cuda") for s in shapes] for _ in range(5)]
+
+    def run(fused):
+        monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "0" if fused else "1")
+        opt = make(keras)
+        vs = [keras.Variable(t.numpy()) for t in init]
+        grads = [torch.zeros(s, device="cuda") for s in shapes]
+        for gs in steps:
+            for dst, src in zip(grads, gs):
+                dst.copy_(src)
+            opt.apply(grads, vs)
+            assert bool(getattr(opt, "_fused_zeroed_grads", False)) == fused
+        return [v.numpy() for v in vs], [v.numpy() for v in opt.variables]
+
+    fused_params, fused_state = run(True)
+    eager_params, eager_state = run(False)
+    monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "0")
+    for a, b in zip(fused_params, eager_params):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+    for a, b in zip(fused_state, eager_state):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-6)
+
+
 def _residual_net(keras, width=64):
     """Stem convolution, one projection block and one identity block (bottlenecks with BatchNorm), classifier."""
     L = keras.layers

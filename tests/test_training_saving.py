@@ -33,6 +33,32 @@ def test_fit_learns_and_history():
     assert ev["loss"] < 0.1
 
 
+def test_fit_builds_models_that_were_never_called():
+    """A Sequential without an Input layer and a subclassed model get their variables on the first fit / evaluate: the
+    variables created while the shapes are traced must end up initialised."""
+    import torch
+
+    y = torch.randint(0, 8, (64,))
+    loss = keras.losses.SparseCategoricalCrossentropy(from_logits=True)
+    seq = keras.Sequential([keras.layers.Embedding(50, 16), keras.layers.GlobalAveragePooling1D(), keras.layers.Dense(8)])
+    seq.compile(optimizer=keras.optimizers.SGD(0.5), loss=loss)
+    hist = seq.fit(torch.randint(0, 50, (64, 12)), y, batch_size=32, epochs=2, verbose=0, shuffle=False)
+    assert hist.history["loss"][1] < hist.history["loss"][0]
+
+    class Sub(keras.Model):
+        def __init__(self):
+            super().__init__()
+            self.dense = keras.layers.Dense(8)
+
+        def call(self, x):
+            return self.dense(x)
+
+    sub = Sub()
+    sub.compile(optimizer="adam", loss=loss)
+    assert np.isfinite(sub.evaluate(torch.randn(64, 20), y, verbose=0))
+    assert all(v._value is not None for v in sub.variables)
+
+
 def test_adam_matches_reference_formula():
     v = keras.Variable(np.array([1.0, -2.0], "float32"))
     opt = keras.optimizers.Adam(0.1, beta_1=0.9, beta_2=0.999, epsilon=1e-7)
