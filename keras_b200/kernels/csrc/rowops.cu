@@ -586,3 +586,89 @@ KB_API int kb200_resize_nhwc(const void* x, void* y, int N, int H, int W, int C,
   KB_CHECK_LAUNCH("resize_nhwc");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ int8 row quantisation
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float round_like(float v);
+template <>
+__device__ __forceinline__ float round_like<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float round_like<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// Dynamic per-row quantisation of activations (keras/src/quantizers/quantizers.py:60-117, abs_max_quantize over the last
+// axis): scale = qmax / (max|x| + eps), q = clip(round(x * scale), -qmax, qmax).  Every intermediate is rounded to the
+// tensor's own type as the chain of library ops would round it, so the codes are the ones that chain produces.
+// Outputs: q int8 [rows, K]; scale [rows] in the tensor's type; inv_scale [rows] fp32 (= 1 / scale, what the GEMM epilogue
+// multiplies by).
+template <typename T, bool BLOCK>
+__global__ void __launch_bounds__(RO_THREADS) int8_quantize_rows_kernel(const T* __restrict__ x, int8_t* __restrict__ q, T* __restrict__ scale_out,
+                                                                        float* __restrict__ inv_out, long long rows, int K, float eps, float qmax, int vec) {
+  __shared__ float red[32];
+  using G = RowGroup<BLOCK>;
+  const long long row = G::row();
+  if (!BLOCK && row >= rows) return;
+  constexpr int VN = RoVec<T>::N;
+  const T* xr = x + row * K;
+  int8_t* qr = q + row * K;
+  const int tid = G::tid(), step = G::size();
+  const int body = vec ? (K / VN) * VN : 0;
+  float m = 0.f;
+  for (int i = tid * VN; i < body; i += step * VN) {
+    float v[VN];
+    ro_load<T>(xr + i, v);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) m = fmaxf(m, fabsf(v[j]));
+  }
+  for (int i = body + tid; i < K; i += step) m = fmaxf(m, fabsf(to_f32<T>(xr[i])));
+  m = G::max(m, red);
+  const float scale = round_like<T>(__fdiv_rn(qmax, round_like<T>(m + eps)));
+  if (tid == 0) {
+    scale_out[row] = from_f32<T>(scale);
+    inv_out[row] = __fdiv_rn(1.f, scale);
+  }
+  for (int i = tid * VN; i < body; i += step * VN) {
+    float v[VN];
+    ro_load<T>(xr + i, v);
+    if constexpr (VN == 8) {
+      int8_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (int8_t)fminf(fmaxf(rintf(round_like<T>(v[j] * scale)), -qmax), qmax);
+      *reinterpret_cast<uint2*>(qr + i) = *reinterpret_cast<const uint2*>(o);
+    } else {
+      int8_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = (int8_t)fminf(fmaxf(rintf(round_like<T>(v[j] * scale)), -qmax), qmax);
+      *reinterpret_cast<uint32_t*>(qr + i) = *reinterpret_cast<const uint32_t*>(o);
+    }
+  }
+  for (int i = body + tid; i < K; i += step) qr[i] = (int8_t)fminf(fmaxf(rintf(round_like<T>(to_f32<T>(xr[i]) * scale)), -qmax), qmax);
+}
+
+template <typename T>
+void launch_int8_rows(const void* x, int8_t* q, void* scale, float* inv, long long rows, int K, float eps, float qmax, cudaStream_t stream) {
+  // vector path: 16-byte loads and 8- or 4-byte stores, so K must keep every row of x and q aligned
+  const int vec = ((((uintptr_t)x) & 15) == 0 && (((uintptr_t)q) & 7) == 0 && ((long long)K * sizeof(T)) % 16 == 0 && K % 8 == 0) ? 1 : 0;
+  if (K <= 1024) {
+    const unsigned grid = (unsigned)((rows + RO_THREADS / 32 - 1) / (RO_THREADS / 32));
+    int8_quantize_rows_kernel<T, false><<<grid, RO_THREADS, 0, stream>>>((const T*)x, q, (T*)scale, inv, rows, K, eps, qmax, vec);
+  } else {
+    int8_quantize_rows_kernel<T, true><<<(unsigned)rows, RO_THREADS, 0, stream>>>((const T*)x, q, (T*)scale, inv, rows, K, eps, qmax, vec);
+  }
+}
+
+}  // namespace
+
+KB_API int kb200_int8_quantize_rows(const void* x, void* q, void* scale, float* inv_scale, long long rows, int K, float eps, float qmax, int dtype,
+                                    cudaStream_t stream) {
+  if (rows <= 0 || K <= 0) return 0;
+  if (rows > 0x7fffffffLL) {
+    kb200_set_error("int8_quantize_rows: too many rows");
+    return -2;
+  }
+  if (dtype == 1) launch_int8_rows<__nv_bfloat16>(x, (int8_t*)q, scale, inv_scale, rows, K, eps, qmax, stream);
+  else launch_int8_rows<float>(x, (int8_t*)q, scale, inv_scale, rows, K, eps, qmax, stream);
+  KB_CHECK_LAUNCH("int8_quantize_rows");
+  return 0;
+}

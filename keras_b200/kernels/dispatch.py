@@ -43,10 +43,31 @@ def dense(x, kernel, bias, activation_name, kernel_shape=None):
 _I8_TRANSPOSED = {}
 
 
-def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bfloat16):
+_I8_COL_SCALE = {}
+
+
+def int8_quantize_rows(x, quantizer):
+    """Dynamic abs-max quantisation of ``x`` over its last axis in one kernel: ``(codes, scale, 1 / scale as fp32)`` with the
+    leading shape of ``x``, or ``None`` when ``quantizer`` is not the plain symmetric int8 one."""
+    from keras_b200 import quantizers
+
+    if not enabled(x) or x.dtype not in _FLOAT_IO or x.ndim < 2 or x.numel() == 0 or type(quantizer) is not quantizers.AbsMaxQuantizer:
+        return None
+    if tuple(quantizer.value_range) != (-127, 127) or quantizer.output_dtype != "int8":
+        return None
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    q, scale, inv = _ops().int8_quantize_rows(x2, float(quantizer.epsilon))
+    lead = tuple(x.shape[:-1])
+    return q.reshape(lead + (x.shape[-1],)), scale.reshape(lead + (1,)), inv
+
+
+def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bfloat16, inv_inputs_scale=None):
     """``(q_inputs @ kernel) / (inputs_scale * kernel_scale)`` on the int8 tensor-core GEMM, or ``None``.
 
-    ``q_inputs``: int8 [..., K] with per-row ``inputs_scale`` [..., 1]; ``kernel``: int8 [K, N] with ``kernel_scale`` [N]."""
+    ``q_inputs``: int8 [..., K] with per-row ``inputs_scale`` [..., 1]; ``kernel``: int8 [K, N] with ``kernel_scale`` [N];
+    ``inv_inputs_scale``: 1 / inputs_scale as fp32 [rows] when the caller already has it."""
     if not (enabled(q_inputs) and enabled(kernel)) or q_inputs.dtype != torch.int8 or kernel.dtype != torch.int8 or kernel.ndim != 2:
         return None
     K, N = kernel.shape
@@ -65,8 +86,15 @@ def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bf
         hit = (kernel._version, kernel.t().contiguous())  # the GEMM wants both operands K-major
         _I8_TRANSPOSED[key] = hit
     bt = hit[1]
-    row_scale = torch.reciprocal(inputs_scale.reshape(-1).float())
-    col_scale = torch.reciprocal(kernel_scale.reshape(-1).float())
+    row_scale = inv_inputs_scale if inv_inputs_scale is not None else torch.reciprocal(inputs_scale.reshape(-1).float())
+    ckey = kernel_scale.data_ptr()
+    chit = _I8_COL_SCALE.get(ckey)
+    if chit is None or chit[0] != kernel_scale._version or chit[1].numel() != N:
+        if len(_I8_COL_SCALE) > 256:
+            _I8_COL_SCALE.clear()
+        chit = (kernel_scale._version, torch.reciprocal(kernel_scale.detach().reshape(-1).float()))
+        _I8_COL_SCALE[ckey] = chit
+    col_scale = chit[1]
     out = torch.empty((M, N), dtype=out_dtype, device=a2.device)
     err = kgemm._err_flag(a2.device)
     code = ops._lib().kb200_gemm_i8(ops._p(a2), ops._p(bt), ops._p(out), None, ops._p(row_scale), ops._p(col_scale), ops._i(M), ops._i(N), ops._i(K),

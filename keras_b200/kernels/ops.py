@@ -242,6 +242,18 @@ class FusedEmbedding(torch.autograd.Function):
         return acc.to(ctx.table_dtype), None, None, None
 
 
+def int8_quantize_rows(x2, eps, qmax=127.0):
+    """Per-row dynamic quantisation of a contiguous 2-D bf16 / fp32 tensor: ``(codes int8, scale [rows, 1] in x's dtype,
+    1 / scale fp32 [rows])`` in one kernel."""
+    lib = _lib()
+    rows, K = x2.shape
+    q = torch.empty((rows, K), dtype=torch.int8, device=x2.device)
+    scale = torch.empty((rows, 1), dtype=x2.dtype, device=x2.device)
+    inv = torch.empty((rows,), dtype=torch.float32, device=x2.device)
+    _check(lib.kb200_int8_quantize_rows(_p(x2), _p(q), _p(scale), _p(inv), _ll(rows), _i(K), _f(eps), _f(qmax), _i(_dt(x2)), _stream()), "int8_quantize_rows")
+    return q, scale, inv
+
+
 def resize_nhwc(x, out_hw, nearest, out_dtype=None):
     """Bilinear (half-pixel centres, no antialiasing) or nearest resize of a contiguous NHWC tensor of uint8, bf16 or fp32."""
     lib = _lib()

@@ -109,6 +109,77 @@ def _gemm_plan(equation):
     return len(k), len(n)
 
 
+def scale_alignment(equation, input_rank):
+    """Where each axis of the layer's output comes from in the kernel: a list over output axes of the kernel axis with the same
+    label, or ``None``.  A quantised kernel's scale is stored with the output's rank (size 1 where the kernel has no such axis)
+    so that it broadcasts against the product; files written by keras/src/layers/core/einsum_dense.py:1449-1491 have that
+    shape."""
+    eq = equation.replace("...", "0")
+    left = right = 0
+    m = re.fullmatch(r"([a-zA-Z]+),([a-zA-Z]+)->([a-zA-Z]+)", eq)
+    if m is None:
+        m = re.fullmatch(r"0([a-zA-Z]+),([a-zA-Z]+)->0([a-zA-Z]+)", eq)
+        if m is not None:
+            left = input_rank - len(m.group(1))
+        else:
+            m = re.fullmatch(r"([a-zA-Z]{2,})0,([a-zA-Z]+)->([a-zA-Z]+)0", eq)
+            if m is None:
+                raise ValueError(f"Invalid einsum equation '{equation}'.")
+            right = input_rank - len(m.group(1))
+    w_spec, out_spec = m.group(2), m.group(3)
+    return [None] * left + [w_spec.index(c) if c in w_spec else None for c in out_spec] + [None] * right
+
+
+def input_alignment(equation, input_rank):
+    """``(contracted input axes, per output axis the input axis with the same label or None, equation of the input
+    gradient)`` with the ellipsis written out."""
+    eq = equation.replace("...", "0")
+    m = re.fullmatch(r"([a-zA-Z]+),([a-zA-Z]+)->([a-zA-Z]+)", eq)
+    in_spec = w_spec = out_spec = None
+    if m is not None:
+        in_spec, w_spec, out_spec = m.groups()
+    else:
+        m = re.fullmatch(r"0([a-zA-Z]+),([a-zA-Z]+)->0([a-zA-Z]+)", eq)
+        side = "left"
+        if m is None:
+            m = re.fullmatch(r"([a-zA-Z]{2,})0,([a-zA-Z]+)->([a-zA-Z]+)0", eq)
+            side = "right"
+        if m is None:
+            raise ValueError(f"Invalid einsum equation '{equation}'.")
+        in_spec, w_spec, out_spec = m.groups()
+        spare = [c for c in "abcdefghijklmnopqrstuvwxyzABCDEFGHIJKLMNOPQRSTUVWXYZ" if c not in in_spec + w_spec + out_spec]
+        extra = "".join(spare[: input_rank - len(in_spec)])
+        in_spec, out_spec = (extra + in_spec, extra + out_spec) if side == "left" else (in_spec + extra, out_spec + extra)
+    contracted = [i for i, c in enumerate(in_spec) if c not in out_spec]
+    from_output = [in_spec.index(c) if c in in_spec else None for c in out_spec]
+    return contracted, from_output, f"{out_spec},{w_spec}->{in_spec}"
+
+
+class _Int8Einsum(torch.autograd.Function):
+    """einsum of activations quantised at call time (abs-max over the contracted axes) with an int8 kernel, de-scaled; the
+    gradient reaches the activations through the de-quantised kernel (keras/src/layers/core/einsum_dense.py:1055-1085)."""
+
+    @staticmethod
+    def forward(ctx, inputs, kernel, scale_for_output, scale_for_kernel, equation, contracted, from_output, grad_equation, quantizer):
+        q, in_scale = quantizer(inputs, axis=tuple(contracted))
+        kept = [a for a in from_output if a is not None]
+        rest = [a for a in range(in_scale.ndim) if a not in kept]
+        aligned = in_scale.permute(kept + rest).reshape([1 if a is None else inputs.shape[a] for a in from_output])
+        if inputs.is_cuda:
+            acc = torch.einsum(equation, q.float(), kernel.float())
+        else:
+            acc = torch.einsum(equation, q.to(torch.int32), kernel.to(torch.int32))
+        ctx.save_for_backward(kernel, scale_for_kernel)
+        ctx.grad_equation, ctx.compute = grad_equation, inputs.dtype
+        return (acc.to(inputs.dtype) / (aligned * scale_for_output.to(inputs.dtype))).to(inputs.dtype)
+
+    @staticmethod
+    def backward(ctx, upstream):
+        kernel, scale_for_kernel = ctx.saved_tensors
+        float_kernel = kernel.to(ctx.compute) / scale_for_kernel.to(ctx.compute)
+        return torch.einsum(ctx.grad_equation, upstream, float_kernel), None, None, None, None, None, None, None, None
+
+
 @keras_export("keras.layers.EinsumDense")
 class EinsumDense(CalibratedKernel, Layer):
     def __init__(self, equation, output_shape, activation=None, bias_axes=None, kernel_initializer="glorot_uniform",
@@ -138,6 +209,7 @@ class EinsumDense(CalibratedKernel, Layer):
         self._kernel_shape = tuple(kshape)
         self.full_output_shape = tuple(full_out)
         self._kernel_in_axes, self._kernel_out_axes = in_axes, out_axes
+        self._scale_from_output = scale_alignment(self.equation, len(input_shape))
         if self.quantization_mode:
             self.quantized_build(self._kernel_shape, mode=self.quantization_mode)
         if self.quantization_mode not in ("int8", "gptq", "awq"):
@@ -267,8 +339,9 @@ class EinsumDense(CalibratedKernel, Layer):
         if self.lora_enabled:
             delta = (self.lora_alpha / self.lora_rank) * torch.matmul(self.lora_kernel_a._value, self.lora_kernel_b._value)
             if mode == "int8":
-                full = self._kernel._value.to(torch.float32) / self.kernel_scale._value + delta
+                full = self._kernel._value.to(torch.float32) / self._scale_for_kernel(self.kernel_scale._value) + delta
                 kernel, scale = quantizers.abs_max_quantize(full, axis=self._kernel_in_axes, to_numpy=False)
+                scale = self._scale_to_storage(scale)
             else:
                 kernel = self._kernel._value + delta.to(self._kernel._value.dtype)
         for i, name in enumerate(self._saved_names()):
@@ -311,11 +384,26 @@ class EinsumDense(CalibratedKernel, Layer):
         return {**super().get_config(), **cfg}
 
     # -- quantization --------------------------------------------------------------------
+    def _scale_storage_shape(self, kernel_shape):
+        return tuple(1 if a is None else kernel_shape[a] for a in self._scale_from_output)
+
+    def _scale_to_storage(self, scale):
+        """Scale shaped like the kernel (1 on the contracted axes) -> output-aligned storage."""
+        kept = [a for a in self._scale_from_output if a is not None]
+        rest = [a for a in range(scale.ndim) if a not in kept]
+        return scale.permute(kept + rest).reshape(self._scale_storage_shape(self._kernel_shape))
+
+    def _scale_for_kernel(self, stored):
+        """Output-aligned storage -> a tensor that broadcasts against the kernel."""
+        kept = [a for a in self._scale_from_output if a is not None]
+        t = stored.reshape([self._kernel_shape[a] for a in kept])
+        t = t.permute([kept.index(a) for a in sorted(kept)])
+        return t.reshape([d if i in kept else 1 for i, d in enumerate(self._kernel_shape)])
+
     def quantized_build(self, kernel_shape, mode, config=None):
         if mode == "int8":
             self._kernel = self.add_weight(name="kernel", shape=kernel_shape, initializer="zeros", dtype="int8", trainable=False)
-            scale_shape = tuple(1 if i in self._kernel_in_axes else d for i, d in enumerate(kernel_shape))
-            self.kernel_scale = self.add_weight(name="kernel_scale", shape=scale_shape, initializer="ones", trainable=False)
+            self.kernel_scale = self.add_weight(name="kernel_scale", shape=self._scale_storage_shape(kernel_shape), initializer="ones", trainable=False)
         elif mode == "float8":
             quantizers.float8_build(self)
         elif mode in ("gptq", "awq"):
@@ -363,9 +451,32 @@ class EinsumDense(CalibratedKernel, Layer):
         return x
 
     def _int8_call(self, inputs, training=None):
-        # Weight-only path: de-quantise the kernel, contract in the compute dtype (the reference's
-        # torch backend does the same, keras/src/layers/core/einsum_dense.py:1086-1098).
-        kernel = self._kernel.value.to(inputs.dtype) / self.kernel_scale.value.to(inputs.dtype)
+        plan = self._gemm
+        kv = self._kernel.value
+        if plan is not None and isinstance(inputs, torch.Tensor) and inputs.dtype in (torch.float32, torch.bfloat16, torch.float16):
+            # The contraction is one GEMM over the flattened input axes: activations are quantised per row over those axes
+            # at run time and the product runs on int8 operands (keras/src/layers/core/einsum_dense.py:1071-1085).
+            nk = plan[0]
+            kdim = 1
+            for d in kv.shape[:nk]:
+                kdim *= d
+            lead = inputs.shape[: inputs.ndim - nk]
+            quantizer = getattr(self, "inputs_quantizer", None)
+            if quantizer is None:
+                quantizer = self.inputs_quantizer = quantizers.AbsMaxQuantizer(axis=-1)
+            out = quantizers.int8_dense_forward(inputs.reshape(tuple(lead) + (kdim,)), kv.reshape(kdim, -1), self.kernel_scale.value.reshape(-1), quantizer)
+            return self._finish(out.reshape(tuple(lead) + tuple(kv.shape[nk:])), inputs)
+        if isinstance(inputs, torch.Tensor) and inputs.dtype in (torch.float32, torch.bfloat16, torch.float16):
+            # any other equation: the same arithmetic through einsum on the integer codes
+            quantizer = getattr(self, "inputs_quantizer", None)
+            if quantizer is None:
+                quantizer = self.inputs_quantizer = quantizers.AbsMaxQuantizer(axis=-1)
+            contracted, from_output, grad_equation = input_alignment(self.equation, inputs.ndim)
+            stored = self.kernel_scale.value
+            out = _Int8Einsum.apply(inputs, kv, stored, self._scale_for_kernel(stored), self.equation, contracted, from_output, grad_equation, quantizer)
+            return self._finish(out, inputs)
+        # symbolic inputs: de-quantise the kernel and contract in the compute dtype
+        kernel = kv.to(inputs.dtype) / self._scale_for_kernel(self.kernel_scale.value).to(inputs.dtype)
         return self._finish(self._contract(inputs, kernel.detach()), inputs)
 
     def _float8_call(self, inputs, training=None):
@@ -405,7 +516,7 @@ class EinsumDense(CalibratedKernel, Layer):
             del self._kernel
             self.quantized_build(kernel_shape, mode)
             self._kernel.assign(q)
-            self.kernel_scale.assign(scale)
+            self.kernel_scale.assign(self._scale_to_storage(scale))
         elif mode == "float8":
             self.quantized_build(kernel_shape, mode)
         elif mode in ("gptq", "awq"):

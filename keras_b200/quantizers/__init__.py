@@ -249,11 +249,19 @@ class _Int8MatmulFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, inputs, kernel, kernel_scale, quantizer, equation):
         compute = inputs.dtype
+        inv_scale = None
         if quantizer is not None:
-            q_in, in_scale = quantizer(inputs, axis=-1 if equation is None else quantizer.axis)
-            out_scale = kernel_scale * in_scale if equation is None else None
+            fused_q = None
+            if equation is None and inputs.is_cuda:
+                from keras_b200.kernels import dispatch
+
+                fused_q = dispatch.int8_quantize_rows(inputs, quantizer)
+            if fused_q is not None:
+                q_in, in_scale, inv_scale = fused_q
+            else:
+                q_in, in_scale = quantizer(inputs, axis=-1 if equation is None else quantizer.axis)
         else:
-            q_in, in_scale, out_scale = inputs, None, kernel_scale
+            q_in, in_scale = inputs, None
         ctx.save_for_backward(kernel, kernel_scale)
         ctx.compute = compute
         ctx.equation = equation
@@ -262,7 +270,7 @@ class _Int8MatmulFn(torch.autograd.Function):
 
             fused = None
             if quantizer is not None and compute in (torch.bfloat16, torch.float32):
-                fused = dispatch.int8_matmul(q_in, kernel, in_scale, kernel_scale, out_dtype=compute)
+                fused = dispatch.int8_matmul(q_in, kernel, in_scale, kernel_scale, out_dtype=compute, inv_inputs_scale=inv_scale)
             if fused is not None:
                 return fused
             lead = q_in.shape[:-1]
@@ -274,6 +282,7 @@ class _Int8MatmulFn(torch.autograd.Function):
             else:
                 acc = torch.matmul(a2.to(torch.int32), kernel.to(torch.int32))
             acc = acc.reshape(tuple(lead) + (kernel.shape[1],))
+            out_scale = kernel_scale * in_scale if in_scale is not None else kernel_scale
             return (acc.to(compute) / out_scale).to(compute)
         raise NotImplementedError
 

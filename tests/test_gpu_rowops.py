@@ -159,3 +159,37 @@ def test_resize_matches_interpolate(interpolation, dtype, size):
         torch.testing.assert_close(y.float(), ref, atol=1.5, rtol=1e-2)
     else:
         torch.testing.assert_close(y, ref, atol=1e-3, rtol=1e-5)
+
+
+@pytest.mark.parametrize("rows,k", [(64, 2048), (1000, 72), (33, 8192), (17, 100)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_int8_row_quantisation_gives_the_codes_of_the_op_chain(rows, k, dtype):
+    from keras_b200 import quantizers
+    from keras_b200.kernels import dispatch
+
+    torch.manual_seed(7)
+    x = (torch.randn(rows, k, device="cuda") * torch.rand(rows, 1, device="cuda") * 5).to(dtype)
+    x[3] = 0  # a row of zeros: the scale is qmax / epsilon
+    quantizer = quantizers.AbsMaxQuantizer(axis=-1)
+    q, scale, inv = dispatch.int8_quantize_rows(x, quantizer)
+    ref_q, ref_scale = quantizer(x, axis=-1)
+    assert q.dtype == torch.int8 and scale.dtype == dtype
+    torch.testing.assert_close(scale.float(), ref_scale.float(), rtol=0, atol=0)
+    assert torch.equal(q, ref_q)
+    torch.testing.assert_close(inv, 1.0 / ref_scale.reshape(-1).float(), rtol=1e-6, atol=0)
+
+
+def test_int8_layers_on_the_kernels_match_the_library_ops(monkeypatch):
+    keras.utils.set_random_seed(8)
+    for make, shape in [(lambda: keras.layers.Dense(96), (4, 33, 64)),
+                        (lambda: keras.layers.EinsumDense("abc,cde->abde", output_shape=(None, 4, 24), bias_axes="de"), (4, 33, 64)),
+                        (lambda: keras.layers.EinsumDense("abcd,cde->abe", output_shape=(None, 64), bias_axes="e"), (4, 33, 4, 16))]:
+        layer = make()
+        x = torch.randn(*shape, device="cuda")
+        layer(x)
+        layer.quantize("int8")
+        monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "1")
+        library = layer(x)
+        monkeypatch.setenv("KERAS_B200_DISABLE_FUSED_KERNELS", "0")
+        fused = layer(x)
+        torch.testing.assert_close(fused, library, rtol=1e-4, atol=1e-4)

@@ -150,3 +150,28 @@ def test_get_weights_order_of_a_model_with_batchnorm():
     ours.set_weights(theirs.get_weights())
     x = _x((3, 6, 6, 3))
     oracle.assert_same(ours.predict(x, verbose=0), theirs.predict(x, verbose=0), "predict", rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("make,shape", [
+    (lambda k: k.layers.Dense(24), (5, 7, 16)),
+    (lambda k: k.layers.EinsumDense("abc,cde->abde", output_shape=(None, 4, 6), bias_axes="de"), (3, 5, 16)),
+    (lambda k: k.layers.EinsumDense("abcd,cde->abe", output_shape=(None, 16), bias_axes="e"), (3, 5, 4, 6)),
+    (lambda k: k.layers.EinsumDense("abc,cd->abd", output_shape=(None, 12)), (3, 5, 16)),
+    (lambda k: k.layers.EinsumDense("abc,dce->abde", output_shape=(None, 4, 6)), (3, 5, 16)),
+    (lambda k: k.layers.EinsumDense("abc,bcd->ad", output_shape=7), (3, 5, 16)),
+], ids=["dense", "attention_projection", "attention_output", "rank3", "kernel_axes_reordered", "two_contracted_axes"])
+def test_int8_quantized_layers_match_reference(make, shape):
+    """quantize("int8"): per-channel int8 kernels and activations quantised per row at call time; codes, scales and the
+    de-scaled product are the reference's."""
+    rk = oracle.ref()
+    x = _x(shape, seed=11)
+    theirs, ours = make(rk), make(keras)
+    theirs(torch.tensor(x))
+    ours(torch.tensor(x))
+    ours.set_weights(theirs.get_weights())
+    theirs.quantize("int8")
+    ours.quantize("int8")
+    assert [w.path.split("/")[-1] for w in ours.weights] == [w.path.split("/")[-1] for w in theirs.weights]
+    for mine, ref_w in zip(ours.get_weights(), theirs.get_weights()):
+        oracle.assert_same(mine, ref_w, "quantised weights", rtol=1e-6, atol=1e-7)
+    oracle.assert_same(ours(torch.tensor(x)), theirs(torch.tensor(x)), "int8 forward", rtol=1e-5, atol=1e-6)
