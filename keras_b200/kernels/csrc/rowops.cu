@@ -623,7 +623,8 @@ __global__ void __launch_bounds__(RO_THREADS) int8_quantize_rows_kernel(const T*
   }
   for (int i = body + tid; i < K; i += step) m = fmaxf(m, fabsf(to_f32<T>(xr[i])));
   m = G::max(m, red);
-  const float scale = round_like<T>(__fdiv_rn(qmax, round_like<T>(m + eps)));
+  // qmax / d is evaluated as (1 / d) * qmax, each step rounded to the tensor's type: that is how the library forms it
+  const float scale = round_like<T>(round_like<T>(__frcp_rn(round_like<T>(m + eps))) * qmax);
   if (tid == 0) {
     scale_out[row] = from_f32<T>(scale);
     inv_out[row] = __fdiv_rn(1.f, scale);
@@ -650,7 +651,7 @@ template <typename T>
 void launch_int8_rows(const void* x, int8_t* q, void* scale, float* inv, long long rows, int K, float eps, float qmax, cudaStream_t stream) {
   // vector path: 16-byte loads and 8- or 4-byte stores, so K must keep every row of x and q aligned
   const int vec = ((((uintptr_t)x) & 15) == 0 && (((uintptr_t)q) & 7) == 0 && ((long long)K * sizeof(T)) % 16 == 0 && K % 8 == 0) ? 1 : 0;
-  if (K <= 1024) {
+  if (K <= 4096) {
     const unsigned grid = (unsigned)((rows + RO_THREADS / 32 - 1) / (RO_THREADS / 32));
     int8_quantize_rows_kernel<T, false><<<grid, RO_THREADS, 0, stream>>>((const T*)x, q, (T*)scale, inv, rows, K, eps, qmax, vec);
   } else {

@@ -63,45 +63,87 @@ def int8_quantize_rows(x, quantizer):
     return q.reshape(lead + (x.shape[-1],)), scale.reshape(lead + (1,)), inv
 
 
-def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bfloat16, inv_inputs_scale=None):
-    """``(q_inputs @ kernel) / (inputs_scale * kernel_scale)`` on the int8 tensor-core GEMM, or ``None``.
+def _i8_operands(kernel, kernel_scale):
+    """Per int8 kernel [K, N], cached: the kernel transposed to [Np, K] (the GEMM wants both operands K-major; N padded to
+    a multiple of 8 with zero rows) and 1 / kernel_scale as fp32 [Np]."""
+    K, N = kernel.shape
+    Np = (N + 7) // 8 * 8
+    key = kernel.data_ptr()
+    hit = _I8_TRANSPOSED.get(key)
+    if hit is None or hit[0] != kernel._version or hit[1].shape != (Np, K):
+        if len(_I8_TRANSPOSED) > 256:
+            _I8_TRANSPOSED.clear()
+        bt = kernel.t().contiguous()
+        if Np != N:
+            bt = torch.nn.functional.pad(bt, (0, 0, 0, Np - N))
+        hit = (kernel._version, bt)
+        _I8_TRANSPOSED[key] = hit
+    ckey = kernel_scale.data_ptr()
+    chit = _I8_COL_SCALE.get(ckey)
+    if chit is None or chit[0] != kernel_scale._version or chit[1].numel() != Np:
+        if len(_I8_COL_SCALE) > 256:
+            _I8_COL_SCALE.clear()
+        col = torch.reciprocal(kernel_scale.detach().reshape(-1).float())
+        if Np != N:
+            col = torch.nn.functional.pad(col, (0, Np - N))
+        chit = (kernel_scale._version, col)
+        _I8_COL_SCALE[ckey] = chit
+    return hit[1], chit[1], Np
+
+
+def int8_matmul(q_inputs, kernel, inputs_scale, kernel_scale, out_dtype=torch.bfloat16, inv_inputs_scale=None, bias=None, act=0):
+    """``act((q_inputs @ kernel) / (inputs_scale * kernel_scale) + bias)`` on the int8 tensor-core GEMM, or ``None``.
 
     ``q_inputs``: int8 [..., K] with per-row ``inputs_scale`` [..., 1]; ``kernel``: int8 [K, N] with ``kernel_scale`` [N];
-    ``inv_inputs_scale``: 1 / inputs_scale as fp32 [rows] when the caller already has it."""
+    ``inv_inputs_scale``: 1 / inputs_scale as fp32 [rows] when the caller already has it; ``bias``: fp32 [N] added in the
+    epilogue; ``act``: activation code of the GEMM epilogue."""
     if not (enabled(q_inputs) and enabled(kernel)) or q_inputs.dtype != torch.int8 or kernel.dtype != torch.int8 or kernel.ndim != 2:
         return None
     K, N = kernel.shape
     a2 = q_inputs.reshape(-1, K)
     M = a2.shape[0]
-    if K % 16 or N % 8 or M < 16 or not a2.is_contiguous() or inputs_scale is None or inputs_scale.numel() != M or kernel_scale.numel() != N:
+    if K % 16 or M < 16 or not a2.is_contiguous() or (inputs_scale is None and inv_inputs_scale is None) or kernel_scale.numel() != N:
+        return None
+    row_scale = inv_inputs_scale if inv_inputs_scale is not None else torch.reciprocal(inputs_scale.reshape(-1).float())
+    if row_scale.numel() != M:
         return None
     from keras_b200.kernels import gemm as kgemm
 
     ops = _ops()
-    key = kernel.data_ptr()
-    hit = _I8_TRANSPOSED.get(key)
-    if hit is None or hit[0] != kernel._version or hit[1].shape != (N, K):
-        if len(_I8_TRANSPOSED) > 256:
-            _I8_TRANSPOSED.clear()
-        hit = (kernel._version, kernel.t().contiguous())  # the GEMM wants both operands K-major
-        _I8_TRANSPOSED[key] = hit
-    bt = hit[1]
-    row_scale = inv_inputs_scale if inv_inputs_scale is not None else torch.reciprocal(inputs_scale.reshape(-1).float())
-    ckey = kernel_scale.data_ptr()
-    chit = _I8_COL_SCALE.get(ckey)
-    if chit is None or chit[0] != kernel_scale._version or chit[1].numel() != N:
-        if len(_I8_COL_SCALE) > 256:
-            _I8_COL_SCALE.clear()
-        chit = (kernel_scale._version, torch.reciprocal(kernel_scale.detach().reshape(-1).float()))
-        _I8_COL_SCALE[ckey] = chit
-    col_scale = chit[1]
-    out = torch.empty((M, N), dtype=out_dtype, device=a2.device)
+    bt, col_scale, Np = _i8_operands(kernel, kernel_scale)
+    if bias is not None:
+        bias = bias.detach().reshape(-1).float()
+        if Np != N:
+            bias = torch.nn.functional.pad(bias, (0, Np - N))
+    out = torch.empty((M, Np), dtype=out_dtype, device=a2.device)
     err = kgemm._err_flag(a2.device)
-    code = ops._lib().kb200_gemm_i8(ops._p(a2), ops._p(bt), ops._p(out), None, ops._p(row_scale), ops._p(col_scale), ops._i(M), ops._i(N), ops._i(K),
-                                    ops._ll(a2.stride(0)), ops._ll(bt.stride(0)), ops._ll(out.stride(0)), ops._i(0),
+    code = ops._lib().kb200_gemm_i8(ops._p(a2), ops._p(bt), ops._p(out), ops._p(bias), ops._p(row_scale), ops._p(col_scale), ops._i(M), ops._i(Np), ops._i(K),
+                                    ops._ll(a2.stride(0)), ops._ll(bt.stride(0)), ops._ll(out.stride(0)), ops._i(act),
                                     ops._i(1 if out_dtype == torch.float32 else 0), ops._p(err), ops._stream())
     ops._check(code, "gemm_i8")
+    if Np != N:
+        out = out[:, :N]
     return out.reshape(tuple(q_inputs.shape[:-1]) + (N,))
+
+
+def int8_dense(inputs, kernel, kernel_scale, quantizer, bias, activation_name):
+    """Inference form of an int8 Dense layer in two launches: per-row quantisation of the activations, then the int8 GEMM
+    whose epilogue de-scales, adds the bias and applies the activation.  Returns ``(output, activation_applied)`` or ``None``
+    (gradients are needed, or the call does not qualify)."""
+    if not enabled(inputs) or (torch.is_grad_enabled() and inputs.requires_grad) or inputs.dtype not in _FLOAT_IO:
+        return None
+    quantised = int8_quantize_rows(inputs, quantizer)
+    if quantised is None:
+        return None
+    from keras_b200.kernels import gemm as kgemm
+
+    q, _, inv = quantised
+    name = {"gelu": "gelu_erf"}.get(activation_name, activation_name)
+    act = kgemm._ACT.get(name)
+    out = int8_matmul(q, kernel, None, kernel_scale, out_dtype=inputs.dtype, inv_inputs_scale=inv, bias=bias, act=act or 0)
+    if out is None:
+        return None
+    return out, act is not None
 
 
 def fp8_matmul(layer, inputs, kernel, equation, training, bias=None):

@@ -249,6 +249,14 @@ class Dense(CalibratedKernel, Layer):
         return out
 
     def _int8_call(self, inputs, training=None):
+        if not self.lora_enabled and isinstance(inputs, torch.Tensor) and inputs.is_cuda:
+            # inference on the device: quantise the rows, then one GEMM whose epilogue de-scales, adds the bias and activates
+            act = self.activation
+            fused = dispatch.int8_dense(inputs, self._kernel.value, self.kernel_scale.value, self.inputs_quantizer,
+                                        self.bias._value if self.bias is not None else None, getattr(act, "__name__", None))
+            if fused is not None:
+                out, act_done = fused
+                return out if act_done or act is None or act is activations.linear else act(out)
         out = quantizers.int8_dense_forward(inputs, self._kernel.value, self.kernel_scale.value, self.inputs_quantizer)
         return self._finish(out, inputs)
 

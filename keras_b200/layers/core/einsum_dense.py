@@ -464,7 +464,19 @@ class EinsumDense(CalibratedKernel, Layer):
             quantizer = getattr(self, "inputs_quantizer", None)
             if quantizer is None:
                 quantizer = self.inputs_quantizer = quantizers.AbsMaxQuantizer(axis=-1)
-            out = quantizers.int8_dense_forward(inputs.reshape(tuple(lead) + (kdim,)), kv.reshape(kdim, -1), self.kernel_scale.value.reshape(-1), quantizer)
+            x2 = inputs.reshape(tuple(lead) + (kdim,))
+            flat_bias = self.bias is None or tuple(self.bias.shape) == tuple(kv.shape[nk:])
+            if inputs.is_cuda and not self.lora_enabled and flat_bias:
+                from keras_b200.kernels import dispatch
+
+                act = self.activation
+                fused = dispatch.int8_dense(x2, kv.reshape(kdim, -1), self.kernel_scale.value.reshape(-1), quantizer,
+                                            self.bias._value if self.bias is not None else None, getattr(act, "__name__", None))
+                if fused is not None:
+                    out, act_done = fused
+                    out = out.reshape(tuple(lead) + tuple(kv.shape[nk:]))
+                    return out if act_done or act is None else act(out)
+            out = quantizers.int8_dense_forward(x2, kv.reshape(kdim, -1), self.kernel_scale.value.reshape(-1), quantizer)
             return self._finish(out.reshape(tuple(lead) + tuple(kv.shape[nk:])), inputs)
         if isinstance(inputs, torch.Tensor) and inputs.dtype in (torch.float32, torch.bfloat16, torch.float16):
             # any other equation: the same arithmetic through einsum on the integer codes
