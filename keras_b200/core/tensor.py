@@ -166,6 +166,9 @@ def convert_to_tensor(x, dtype=None, sparse=None, ragged=None):
     return torch.as_tensor(x, dtype=td, device=get_device())
 
 
+_PINNED_READBACK_BYTES = 1 << 20
+
+
 def convert_to_numpy(x):
     from keras_b200.core.variables import Variable
 
@@ -173,7 +176,15 @@ def convert_to_numpy(x):
         x = x.value
     if isinstance(x, torch.Tensor):
         x = x.detach()
-        if x.device.type != "cpu":
+        if x.device.type == "cuda" and x.numel() * x.element_size() >= _PINNED_READBACK_BYTES:
+            # Large results go through page-locked memory: the copy engine writes it at PCIe speed, where a copy into pageable
+            # memory is staged by the driver in small pieces.  The array keeps the page-locked block alive and the block goes
+            # back to torch's host cache when the array is dropped, so a predict loop allocates it once.
+            host = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+            host.copy_(x, non_blocking=True)
+            torch.cuda.current_stream(x.device).synchronize()
+            x = host
+        elif x.device.type != "cpu":
             x = x.cpu()
         if x.dtype == torch.bfloat16:
             import ml_dtypes
