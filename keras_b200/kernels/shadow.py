@@ -31,6 +31,16 @@ def in_arena_backward():
     return _arena_backward_depth > 0
 
 
+_slot_observer = None
+
+
+def set_slot_observer(fn):
+    """``fn(param)`` is called whenever ``grad_slot`` hands out a parameter's gradient storage, that is, just before a kernel
+    adds a contribution to it (the data-parallel engine counts these to know when a gradient is complete).  ``None`` clears."""
+    global _slot_observer
+    _slot_observer = fn
+
+
 def grad_slot(param, shape=None):
     """``param.grad`` when a kernel may accumulate into it: inside ``arena_backward``, fp32, contiguous, 16-byte aligned."""
     if _arena_backward_depth <= 0 or param is None:
@@ -40,6 +50,8 @@ def grad_slot(param, shape=None):
         return None
     if shape is not None and g.numel() != _numel(shape):
         return None
+    if _slot_observer is not None:
+        _slot_observer(param)
     return g
 
 

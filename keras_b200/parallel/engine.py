@@ -107,6 +107,7 @@ class DataParallelEngine:
             from keras_b200.kernels import shadow
 
             shadow.attach_for_model(model, trainable_weights)
+        reduced = False
         if arena.unused is None:
             # first pass over this set of variables: unbound, to see which variables the loss reaches (see GradArena.adopt)
             arena.unbind()
@@ -115,12 +116,22 @@ class DataParallelEngine:
         else:
             arena.bind()
             if arena.flat.is_cuda:
-                with shadow.arena_backward():
-                    loss.backward()
+                overlap = self._overlap_for(arena, opt)
+                if overlap is not None:
+                    overlap.begin()
+                    shadow.set_slot_observer(overlap.note)
+                try:
+                    with shadow.arena_backward():
+                        loss.backward()
+                finally:
+                    if overlap is not None:
+                        shadow.set_slot_observer(None)
+                if overlap is not None:
+                    reduced = overlap.finish()
             else:
                 loss.backward()
         self._after_backward(trainable_weights)
-        if self.world > 1:
+        if self.world > 1 and not reduced:
             if self._reducer is not None:
                 if first:
                     collectives.barrier()  # absorb start-up skew (lazy initialisation, autotuning) on the host
@@ -134,6 +145,22 @@ class DataParallelEngine:
         if not opt._fused_zeroed_grads:
             arena.zero()
         self._steps += 1
+
+    def _overlap_for(self, arena, opt):
+        """The bucket schedule that reduces gradients during the backward pass, or ``None``: only the plain data-parallel
+        engine with this package's all-reduce, and not while gradients are accumulated over several calls."""
+        from keras_b200.parallel import overlap
+
+        if type(self) is not DataParallelEngine or self.world <= 1 or self._reducer is None or not overlap.enabled():
+            return None
+        if getattr(opt, "gradient_accumulation_steps", None):
+            return None
+        current = getattr(self, "_overlap", None)
+        if current is None or current.arena is not arena or current.reducer is not self._reducer:
+            if current is not None:
+                current.close()
+            current = self._overlap = overlap.GradientOverlap(arena, self._reducer, self.world)
+        return current
 
     def _after_backward(self, trainable_weights):
         """Hook between the backward pass and the replica reduction."""
@@ -201,6 +228,9 @@ class DataParallelEngine:
                 r.check(wait=wait)
 
     def close(self):
+        if getattr(self, "_overlap", None) is not None:
+            self._overlap.close()
+            self._overlap = None
         if self._metric_reducer is not None:
             self._metric_reducer.close()
             self._metric_reducer = None

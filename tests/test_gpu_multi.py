@@ -212,6 +212,55 @@ def test_data_parallel_step_replays_as_cuda_graph():
     np.testing.assert_allclose(out[0]["graphed"], out[1]["graphed"], rtol=1e-6)
 
 
+def _dp_overlap_worker(rank, world):
+    """The same model trained with the gradient reduction after the backward pass and overlapped with it in small buckets."""
+    import keras_b200 as keras
+
+    keras.distribution.initialize()
+    keras.distribution.set_distribution(keras.distribution.DataParallel())
+    out = {}
+    for policy in ("float32", "mixed_bfloat16"):
+        keras.config.set_dtype_policy(policy)
+        for overlap in ("0", "1"):
+            os.environ["KERAS_B200_DP_OVERLAP"] = overlap
+            os.environ["KERAS_B200_DP_BUCKET_BYTES"] = "4096"
+            keras.utils.set_random_seed(31)
+            m = keras.Sequential([keras.layers.Input((32,)), keras.layers.Dense(64, activation="relu"), keras.layers.LayerNormalization(),
+                                  keras.layers.Dense(64, activation="gelu"), keras.layers.Dense(5)])
+            m.compile(optimizer=keras.optimizers.SGD(0.05, momentum=0.9), loss=keras.losses.SparseCategoricalCrossentropy(from_logits=True))
+            rng = np.random.RandomState(7 + rank)
+            xs, ys = rng.randn(4, 32, 32).astype("float32"), rng.randint(0, 5, (4, 32))
+            losses = [float(m.train_on_batch(xs[i % 4], ys[i % 4])) for i in range(9)]
+            engine = m._parallel_engine
+            engine.check(wait=True)
+            schedule = getattr(engine, "_overlap", None)
+            key = f"{policy}_{overlap}"
+            out[key + "_losses"] = np.array(losses)
+            out[key + "_buckets"] = np.array(len(schedule.buckets) if schedule is not None else 0)
+            out[key + "_launched"] = np.array(schedule.launched if schedule is not None else 0)
+            out[key + "_replays"] = np.array(m._graphed_step.replays if m._graphed_step is not None else -1)
+            out[key + "_why"] = np.array(str(m._graphed_step.failure_traceback or m._graphed_step.disabled) if m._graphed_step is not None else "no stepper")
+            for i, w in enumerate(m.get_weights()):
+                out[f"{key}_w{i}"] = w
+            engine.close()
+    keras.config.set_dtype_policy("float32")
+    return out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gradient_reduction_overlapped_with_backward_gives_the_same_weights():
+    codes, out = _spawn("_dp_overlap_worker", 2)
+    assert codes == [0, 0], codes
+    for r in (0, 1):
+        for policy in ("float32", "mixed_bfloat16"):
+            assert int(out[r][f"{policy}_0_buckets"]) == 0
+            assert int(out[r][f"{policy}_1_buckets"]) >= 2 and int(out[r][f"{policy}_1_launched"]) == int(out[r][f"{policy}_1_buckets"])
+            assert int(out[r][f"{policy}_1_replays"]) >= 5, str(out[r][f"{policy}_1_why"])  # the overlapped step is recorded and replayed as well
+            np.testing.assert_array_equal(out[r][f"{policy}_1_losses"], out[r][f"{policy}_0_losses"])
+            for k in [k for k in out[r] if k.startswith(f"{policy}_0_w")]:
+                np.testing.assert_array_equal(out[r][k.replace("_0_w", "_1_w")], out[r][k])
+
+
 def _equivalence_model(keras):
     keras.utils.set_random_seed(23)
     m = keras.Sequential([keras.layers.Input((32,)), keras.layers.Dense(64, activation="relu"), keras.layers.LayerNormalization(),
