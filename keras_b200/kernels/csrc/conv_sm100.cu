@@ -77,6 +77,17 @@ struct ConvParams {
   int items, group;         // accumulators (128 rows of dW each) in total / per work unit
   int pair_taps;            // Cin == 64: one accumulator holds the rows of two taps
   int b_slots;              // depth of the dY ring
+  // wgrad, rows shared between vertical taps: one x box with a halo of image rows per (kernel column s, channel tile) is
+  // the operand of several accumulators.  Cin > 64: accumulator a is tap (a, s), its operand the box entered a image rows
+  // further on; the two 64-channel halves are two boxes `a_half` bytes apart.  Cin == 64: accumulator a holds the taps
+  // (2a, s) and (2a + 1, s); its second 64 rows come from the same box one image row further on, which the descriptor
+  // expresses as a leading-dimension offset of one image row (wt * 128 bytes).
+  int vshare;
+  int n_acc;                // accumulators fed by one stage
+  int a_rows;               // image rows of the box
+  int a_half;               // bytes of one box
+  int acc_step;             // bytes between the operand starts of consecutive accumulators
+  int lbo16;                // leading-dimension byte offset of the A descriptor / 16
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -548,9 +559,14 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             ok = mbar_wait(bar_empty(s, st), ((it / STAGES) & 1) ^ 1, abort_flag);
             if (!ok) break;
             const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
-            mbar_expect_tx(bar_full(s, st), (uint32_t)CV_A_BYTES);
+            mbar_expect_tx(bar_full(s, st), (uint32_t)p.stage_bytes);
             const int item = item0 + i;
-            if (p.pair_taps) {
+            if (p.vshare) {
+              const int sc = item / p.m_tiles, c0 = (item % p.m_tiles) * 128;
+              const int dw = p.dw0 + sc * p.dw_step;
+              tma_load_4d(sa, &map_a, bar_full(s, st), c0, w0 + dw, h0 + p.dh0, n0);
+              if (!p.pair_taps) tma_load_4d(sa + (uint32_t)p.a_half, &map_a, bar_full(s, st), c0 + 64, w0 + dw, h0 + p.dh0, n0);
+            } else if (p.pair_taps) {
               const int ta = 2 * item, tb = 2 * item + 1;
               tma_load_4d(sa, &map_a, bar_full(s, st), 0, w0 + p.dw0 + (ta % p.S) * p.dw_step, h0 + p.dh0 + (ta / p.S) * p.dh_step, n0);
               if (tb < taps) {
@@ -605,11 +621,24 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             ok = mbar_wait(bar_full(s, st), (it / STAGES) & 1, abort_flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t adesc = make_smem_desc(s.ring + (uint32_t)(st * p.stage_bytes), true);
-            const uint32_t tmem_d = tmem_base + (uint32_t)(i * p.bn);
+            const uint32_t sa = s.ring + (uint32_t)(st * p.stage_bytes);
+            if (p.vshare) {
+              for (int a = 0; a < p.n_acc; ++a) {
+                // same descriptor as make_smem_desc(.., true) with the leading-dimension offset of this mode
+                uint64_t adesc = make_smem_desc(sa + (uint32_t)(a * p.acc_step), true);
+                adesc = (adesc & ~(0x3FFFull << 16)) | ((uint64_t)p.lbo16 << 16);
+                const uint32_t tmem_d = tmem_base + (uint32_t)((i * p.n_acc + a) * p.bn);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_bf16(tmem_d, adesc + (uint64_t)(step * kk), bdesc + (uint64_t)(step * kk), idesc, (pb > pb0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 4; ++kk)
+                  umma_bf16(tmem_d, adesc + (uint64_t)(step * kk), bdesc + (uint64_t)(step * kk), idesc, (pb > pb0 || kk > 0) ? 1u : 0u);
+              }
+            } else {
+              const uint64_t adesc = make_smem_desc(sa, true);
+              const uint32_t tmem_d = tmem_base + (uint32_t)(i * p.bn);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                umma_bf16(tmem_d, adesc + (uint64_t)(step * kk), bdesc + (uint64_t)(step * kk), idesc, (pb > pb0 || kk > 0) ? 1u : 0u);
+            }
             umma_commit(bar_empty(s, st));
           }
           if (ok) umma_commit(bar_b_empty(s, bs));
@@ -637,6 +666,19 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       for (int i = 0; i < cnt; ++i) {
         const int item = item0 + i;
+        if (p.vshare) {
+          const int sc = item / p.m_tiles, ctile = item % p.m_tiles;
+          for (int a = 0; a < p.n_acc; ++a) {
+            // rows of dW that this warp's 32 accumulator rows are: tap (r, sc), channels from `ch`
+            const int r = p.pair_taps ? 2 * a + (q >> 1) : a;
+            const int ch = p.pair_taps ? (q & 1) * 32 : ctile * 128 + q * 32;
+            if (r >= p.R) continue;  // the odd tap out of a pair: rows of a tap that does not exist
+            const int row0 = (r * p.S + sc) * p.rows_per_tap + ch;
+            const uint32_t tmem_row = tmem_base + (uint32_t)((i * p.n_acc + a) * p.bn) + ((uint32_t)(q * 32) << 16);
+            store_rows_tma(tmem_row, p.bn, ng0, row0, my_stage, stores, &map_c, gp, lane);
+          }
+          continue;
+        }
         const int row0 = (p.pair_taps ? item * 128 : (item / p.m_tiles) * p.rows_per_tap + (item % p.m_tiles) * 128) + q * 32;
         const uint32_t tmem_row = tmem_base + (uint32_t)(i * p.bn) + ((uint32_t)(q * 32) << 16);
         store_rows_tma(tmem_row, p.bn, ng0, row0, my_stage, stores, &map_c, gp, lane);
@@ -785,6 +827,11 @@ KB_API int kb200_conv_igemm_plan(int N, int Ho, int Wo, int Ca, int Cn, int R, i
   return 0;
 }
 
+// 1 when the most recent kb200_conv_wgrad call of this process shared image rows between vertical taps (for tests; the call
+// comes from autograd's worker thread, so the flag is per process).
+static volatile int g_last_wgrad_shared = 0;
+KB_API int kb200_conv_wgrad_last_shared() { return g_last_wgrad_shared; }
+
 // 1 when kb200_conv_igemm would share image rows between the vertical taps for this problem.
 KB_API int kb200_conv_igemm_shares_rows(int N, int Ho, int Wo, int Ca, int Cn, int R, int S, int dh_step) {
   int lw = 0, lh = 0, hshare = 0;
@@ -920,12 +967,47 @@ KB_API int kb200_conv_wgrad(const void* x, const void* dy, float* dw, int N, int
   p.mode = 1;
   p.lt = 6;
   pick_box(64, Wo, Ho, N, p.lw, p.lh);
+  p.bn = pick_bn(Cout);
+  {
+    // Rows shared between vertical taps (see ConvParams::vshare): the pixel block lies inside one image and is a multiple
+    // of 8 pixels wide; taken when it cuts the x rows the TMA unit fetches by a quarter or more with at most a quarter more
+    // pixel blocks, and the accumulators of one stage fit the 512 tensor-memory columns.
+    static const int allow = [] { const char* e = getenv("KERAS_B200_CONV_WGRAD_SHARE"); return (e != nullptr && e[0] == '0') ? 0 : 1; }();
+    const bool pair = Cin == 64;
+    const int n_acc = pair ? (R + 1) / 2 : R;
+    const bool rank2_call = R == 1 && S == 1;
+    if (allow && !rank2_call && R >= 2 && R <= 8 && dh_step == 1 && Cin >= 64 && n_acc * p.bn <= 512) {
+      const int wt0 = 1 << p.lw, ht0 = 1 << p.lh, nt0 = 1 << (p.lt - p.lw - p.lh);
+      const long long blocks_plain = (long long)((Wo + wt0 - 1) / wt0) * ((Ho + ht0 - 1) / ht0) * ((N + nt0 - 1) / nt0);
+      const long long rows_plain = blocks_plain * R * S * 64;
+      long long best = -1;
+      int best_lw = 0;
+      for (int a = 3; a <= 6; ++a) {
+        const int wt1 = 1 << a, ht1 = 64 >> a;
+        const long long blocks = (long long)((Wo + wt1 - 1) / wt1) * ((Ho + ht1 - 1) / ht1) * N;
+        if (blocks * 4 > blocks_plain * 5) continue;
+        const int box_rows = pair ? ht1 + 2 * n_acc - 1 : ht1 + R - 1;
+        const long long rows = blocks * S * wt1 * box_rows;
+        if (best < 0 || rows < best) { best = rows; best_lw = a; }
+      }
+      if (best > 0 && best * 4 <= rows_plain * 3) {
+        p.vshare = 1;
+        p.lw = best_lw;
+        p.lh = 6 - best_lw;
+        p.n_acc = n_acc;
+        const int wt1 = 1 << p.lw, ht1 = 1 << p.lh;
+        p.a_rows = pair ? ht1 + 2 * n_acc - 1 : ht1 + R - 1;  // a pair reaches one image row past its first tap
+        p.a_half = wt1 * p.a_rows * 128;
+        p.acc_step = (pair ? 2 : 1) * wt1 * 128;
+        p.lbo16 = (pair ? wt1 * 128 : p.a_half) >> 4;
+      }
+    }
+  }
   const int wt = 1 << p.lw, ht = 1 << p.lh, nt = 1 << (p.lt - p.lw - p.lh);
   p.tiles_w = (Wo + wt - 1) / wt;
   p.tiles_h = (Ho + ht - 1) / ht;
   p.tiles_n = (N + nt - 1) / nt;
   p.Wo = Wo; p.Ho = Ho; p.No = N;
-  p.bn = pick_bn(Cout);
   p.n_tiles = (Cout + p.bn - 1) / p.bn;
   p.Ngemm = Cout;
   p.R = R; p.S = S; p.dh0 = dh0; p.dh_step = dh_step; p.dw0 = dw0; p.dw_step = dw_step;
@@ -941,15 +1023,26 @@ KB_API int kb200_conv_wgrad(const void* x, const void* dy, float* dw, int N, int
   p.total_pb = (int)pbs;
   const int taps = R * S;
   p.pair_taps = (Cin == 64 && taps > 1) ? 1 : 0;
-  p.items = p.pair_taps ? (taps + 1) / 2 : taps * p.m_tiles;
-  p.group = 512 / p.bn < p.items ? 512 / p.bn : p.items;
   p.b_slots = p.bn == 256 ? 2 : 3;
   p.res_bytes = p.b_slots * p.bn * 128;
-  p.stage_bytes = CV_A_BYTES;
   p.epi_sets = 1;
   p.oper_bytes = cv_oper_bytes(1);
+  if (p.vshare) {
+    p.items = S * p.m_tiles;                    // stage loads per pixel block; each feeds n_acc accumulators
+    p.group = 512 / (p.bn * p.n_acc);
+    if (p.group > p.items) p.group = p.items;
+    p.stage_bytes = (p.pair_taps ? 1 : 2) * p.a_half;
+  } else {
+    p.items = p.pair_taps ? (taps + 1) / 2 : taps * p.m_tiles;
+    p.group = 512 / p.bn < p.items ? 512 / p.bn : p.items;
+    p.stage_bytes = CV_A_BYTES;
+  }
   p.stages = (p.oper_bytes - p.res_bytes) / p.stage_bytes;
   if (p.stages > CV_MAX_STAGES) p.stages = CV_MAX_STAGES;
+  if (p.stages < 2 || p.group < 1) {
+    kb200_set_error("conv_wgrad: the operand ring does not fit two stages");
+    return -8;
+  }
   const int tiles = ((p.items + p.group - 1) / p.group) * p.n_tiles;
   const int sms = conv_sm_count();
   // slices of the pixel range: one wave of work units, at least 4 pixel blocks each
@@ -961,7 +1054,7 @@ KB_API int kb200_conv_wgrad(const void* x, const void* dy, float* dw, int N, int
   const long long units = (long long)tiles * p.split;
   CUtensorMap map_a, map_b, map_c;
   p.rank2 = (R == 1 && S == 1 && H == 1 && N == 1 && Ho == 1) ? 1 : 0;
-  bool ok = p.rank2 ? make_map(&map_a, x, Cin, W, x_sw, 64, 64) : make_map_4d(&map_a, x, Cin, W, H, N, x_sw, x_sh, x_sn, wt, ht, nt);
+  bool ok = p.rank2 ? make_map(&map_a, x, Cin, W, x_sw, 64, 64) : make_map_4d(&map_a, x, Cin, W, H, N, x_sw, x_sh, x_sn, wt, p.vshare ? p.a_rows : ht, nt);
   ok = ok && (p.rank2 ? make_map(&map_b, dy, Cout, Wo, d_sw, 64, 64) : make_map_4d(&map_b, dy, Cout, Wo, Ho, N, d_sw, d_sh, d_sn, wt, ht, nt));
   ok = ok && make_map(&map_c, dw, Cout, p.Mrows, Cout, 32, 32, true);
   if (!ok) {
@@ -969,6 +1062,7 @@ KB_API int kb200_conv_wgrad(const void* x, const void* dy, float* dw, int N, int
     return -3;
   }
   const unsigned grid = (unsigned)(units < sms ? units : sms);
+  g_last_wgrad_shared = p.vshare;
   conv_wgrad_tcgen05_kernel<<<grid, THREADS, CV_SMEM_BYTES, stream>>>(map_a, map_b, map_c, p);
   KB_CHECK_LAUNCH("conv_wgrad");
   return 0;

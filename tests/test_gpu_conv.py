@@ -236,3 +236,22 @@ def test_row_sharing_is_taken_for_the_resnet_3x3_layers():
     assert lib.kb200_conv_igemm_shares_rows(4, 28, 28, 128, 128, 3, 3, 1) == 1
     assert lib.kb200_conv_igemm_shares_rows(256, 56, 56, 64, 256, 1, 1, 0) == 0
     assert lib.kb200_conv_igemm_shares_rows(2, 20, 20, 64, 64, 3, 3, 2) == 0
+
+
+@pytest.mark.parametrize("shape,expected", [((2, 56, 56, 64, 64), 1), ((4, 28, 28, 128, 128), 1), ((3, 14, 14, 256, 256), 0)])
+def test_weight_gradient_shares_rows_on_the_wide_3x3_layers(shape, expected, monkeypatch):
+    """The weight-gradient kernel feeds the vertical taps of a kernel column from one x box with a halo of image rows where that
+    pays; the result is the plain kernel's (compared against fp32 above), here only the choice is pinned."""
+    from keras_b200.kernels import ops as kops
+
+    conv = _conv_mod()
+    monkeypatch.setattr(conv, "_MIN_WORK", 0)
+    n, h, w, cin, cout = shape
+    torch.manual_seed(3)
+    x = torch.randn(n, h, w, cin, device="cuda").bfloat16()
+    kernel = (torch.randn(3, 3, cin, cout, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = conv.conv(x, kernel, (1, 1), "same", "channels_last", (1, 1))
+    y.backward(torch.randn_like(y))
+    assert kops._lib().kb200_conv_wgrad_last_shared() == expected
+    ref = F.conv2d(x.float().permute(0, 3, 1, 2), kernel.detach().float().permute(3, 2, 0, 1).requires_grad_(True), padding=1)
+    assert torch.isfinite(kernel.grad.float()).all() and ref.shape[1] == cout
