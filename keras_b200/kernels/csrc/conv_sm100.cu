@@ -63,6 +63,7 @@ struct ConvParams {
   int rank2;                // pixels are one flat dimension (1x1 filter, stride 1): 2-D tensor maps, which the TMA unit walks faster
   int oper_bytes, epi_sets; // operand region size; sets of four epilogue warps that share a tile's columns (1 or 2)
   int resident_b;           // igemm: this CTA's column slice of the kernel array stays in shared memory for all tiles
+  int epi_alt;              // igemm, 64-column tiles: the two sets of epilogue warps take alternate tiles (each its own accumulator)
   // igemm, rows shared between vertical taps: one box of (ht + R - 1) image rows per (column offset s, channel block) serves
   // the R taps of that column.  A tap's operand is the same shared-memory tile entered `row offset * wt` pixels further on:
   // with wt a multiple of 8 that is a multiple of 1024 bytes, so the 128-byte swizzle pattern of the tile still applies.
@@ -218,7 +219,7 @@ __device__ __forceinline__ ConvSmem conv_smem(uint8_t* smem_raw, const ConvParam
   s.res = base;
   s.ring = base + (uint32_t)p.res_bytes;
   s.out = base + (uint32_t)p.oper_bytes;
-  s.bar = s.out + (uint32_t)(p.epi_sets * 4 * 8192);
+  s.bar = s.out + (uint32_t)((p.epi_alt ? 2 : p.epi_sets) * 4 * 8192);
   s.bar_ptr = smem_raw + (s.bar - smem_u32(smem_raw));
   return s;
 }
@@ -277,7 +278,7 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const ConvSmem s = conv_smem(smem_raw, p);
   volatile uint32_t* tmem_slot;
   volatile int* abort_flag;
-  conv_prologue(s, p, 8, tmem_slot, abort_flag);
+  conv_prologue(s, p, p.epi_alt ? 4 : 8, tmem_slot, abort_flag);
   const uint32_t tmem_base = *tmem_slot;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -429,9 +430,12 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     // tile's 64-column chunks between them; with epi_sets == 1 the second set only takes part in the barriers.
     const int q = warp & 3;
     const int ew = warp - 2, set = ew >> 2;
-    const bool active = set < p.epi_sets;
+    // With 64-column tiles one set of four warps would do all the work: the sets then take alternate tiles instead, set k
+    // always reading accumulator k.
+    const bool alt = p.epi_alt != 0;
+    const bool active = alt || set < p.epi_sets;
     const int cps = (p.bn >> 6) / p.epi_sets;  // chunks per set
-    const int c_begin = set * cps;
+    const int c_begin = alt ? 0 : set * cps;
     const uint32_t my_stage = s.out + (uint32_t)ew * 8192u;
     uint32_t local = 0, stores = 0;
     bool ok = true;
@@ -440,6 +444,7 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     for (int i = 0; i < 16; ++i) acc_stats[i] = 0.f;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++local) {
       const uint32_t acc = local & 1;
+      if (alt && (int)acc != set) continue;
       ok = mbar_wait(bar_acc_full(s, acc), (local >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -475,8 +480,8 @@ conv_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       for (int col = tid; col < p.bn; col += 256) {
         const uint32_t owner = s.out + (uint32_t)(((col >> 6) / cps) * 4) * 8192u + (uint32_t)col * 4u;
         float sum = 0.f, sq = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        const int contributors = alt ? 8 : 4;  // alternating sets: both sets hold sums of this column
+        for (int w = 0; w < contributors; ++w) {
           float a, b;
           asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a) : "r"(owner + (uint32_t)w * 8192u) : "memory");
           asm volatile("ld.shared.f32 %0, [%1];" : "=f"(b) : "r"(owner + (uint32_t)w * 8192u + 1024u) : "memory");
@@ -767,6 +772,14 @@ bool conv_set_attr() {
 
 int pick_bn(int n) { return n <= 64 ? 64 : (n <= 128 ? 128 : 256); }
 
+// igemm: 64-column tiles let the two sets of epilogue warps take alternate tiles (KERAS_B200_CONV_EPI_ALT=0: one set works)
+bool igemm_epi_alt(int bn) {
+  static const int allow = [] { const char* e = getenv("KERAS_B200_CONV_EPI_ALT"); return (e != nullptr && e[0] == '0') ? 0 : 1; }();
+  return allow && bn == 64;
+}
+// igemm: sets of epilogue warps that need staging buffers
+int igemm_staging_sets(int bn, int steps) { return (igemm_epi_alt(bn) || (bn >= 128 && steps <= 12)) ? 2 : 1; }
+
 bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 }  // namespace
@@ -800,7 +813,7 @@ void igemm_box(int Wo, int Ho, int N, int R, int S, int dh_step, int Ca, int Cn,
   // the operand ring must still hold two stages (four when the kernel slice is resident): same arithmetic as the launcher's
   const int bn = pick_bn(Cn), kc_blocks = (Ca + 63) / 64;
   const int a_bytes = (1 << best_lw) * ((128 >> best_lw) + R - 1) * 128;
-  const int oper = cv_oper_bytes((bn >= 128 && R * S * kc_blocks <= 12) ? 2 : 1);
+  const int oper = cv_oper_bytes(igemm_staging_sets(bn, R * S * kc_blocks));
   const long long bbytes = (long long)R * S * kc_blocks * bn * 128;
   if (bbytes > oper - 4 * a_bytes && 2 * (a_bytes + R * bn * 128) > oper) return;
   hshare = 1;
@@ -911,7 +924,8 @@ KB_API int kb200_conv_igemm(const void* a, const void* wgt, void* out, const flo
   const long long bbytes = (long long)R * S * p.kc_blocks * p.bn * 128;
   const int steps = R * S * p.kc_blocks;
   p.epi_sets = (p.bn >= 128 && steps <= 12) ? 2 : 1;
-  p.oper_bytes = cv_oper_bytes(p.epi_sets);
+  p.epi_alt = igemm_epi_alt(p.bn) ? 1 : 0;
+  p.oper_bytes = cv_oper_bytes(igemm_staging_sets(p.bn, steps));
   const int b_per_stage = (p.hshare ? R : 1) * p.bn * 128;
   if (bbytes <= p.oper_bytes - (p.hshare ? 4 : 6) * p.a_bytes) {
     p.resident_b = 1;
