@@ -33,6 +33,9 @@ CONFIGS = {
     "llama8b": {"kind": "llama", "model": "Llama-style 8B decoder (32 x 4096, 32 query / 8 KV heads, SwiGLU 14336, vocab 128256, RoPE theta 5e5)",
                 "global_batch": 16, "seq": 4096, "vocab": 128256, "layers": 32, "d": 4096, "q_heads": 32, "kv_heads": 8, "ffn": 14336,
                 "rope_theta": 5e5, "model_axis": 4},
+    "llama8b_4layer": {"kind": "llama", "model": "4 layers of the Llama-style 8B decoder (4096 wide, 32 query / 8 KV heads, SwiGLU 14336, vocab 128256)",
+                       "global_batch": 2, "seq": 4096, "vocab": 128256, "layers": 4, "d": 4096, "q_heads": 32, "kv_heads": 8, "ffn": 14336,
+                       "rope_theta": 5e5, "model_axis": 1},
     "llama_small": {"kind": "llama", "model": "Llama-style decoder (smoke size)", "global_batch": 8, "seq": 256, "vocab": 2048, "layers": 2, "d": 512,
                     "q_heads": 8, "kv_heads": 4, "ffn": 1536, "rope_theta": 5e5, "model_axis": 4},
     "gpt_fp8": {"kind": "decoder", "model": "1.3B decoder (24 x 2048, 16 heads, MLP 8192, vocab 50257), float8 policy on Dense/EinsumDense",
