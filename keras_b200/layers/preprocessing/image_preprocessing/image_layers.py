@@ -215,13 +215,26 @@ class RandomCrop(_CropBase):
             left = torch.full((n,), max((w - self.width) // 2, 0), dtype=torch.long)
         return (h, w, top, left)
 
+    # Outside training the layer passes images, masks and boxes through untouched
+    # (keras/src/layers/preprocessing/image_preprocessing/random_crop.py:131-140, 196-280).
+    _ALWAYS = False
+
+    def transform_images(self, images, transformation, training=True):
+        if not training:
+            return convert_to_tensor(images)
+        return self._apply(self._cast(images), transformation)
+
     def _apply(self, images, t):
         return self._crop(images, t[2], t[3])
 
     def transform_segmentation_masks(self, segmentation_masks, transformation, training=True):
+        if not training:
+            return convert_to_tensor(segmentation_masks)
         return self._crop(convert_to_tensor(segmentation_masks), transformation[2], transformation[3])
 
     def transform_bounding_boxes(self, bounding_boxes, transformation, training=True):
+        if not training:
+            return bounding_boxes
         h, w, top, left = transformation
         return self._box_transform(bounding_boxes, h, w, top, left)
 
@@ -961,21 +974,46 @@ def _equalize_planes(planes, bins, clip_limit=None):
 
 @keras_export("keras.layers.Equalization")
 class Equalization(_Base):
+    """Histogram equalisation of every channel.  As in keras/src/layers/preprocessing/image_preprocessing/equalization.py:88-200
+    one histogram is taken per channel over everything else in the tensor (a batch shares it), levels are truncated into bins,
+    the look-up table always spans 0..255, and outside training the input passes through."""
+
     _USE_BASE_FACTOR = False
-    _ALWAYS = True
 
     def __init__(self, value_range=(0, 255), bins=256, data_format=None, **kwargs):
         super().__init__(data_format=data_format, **kwargs)
         self.value_range = _check_value_range(value_range)
         self.bins = bins
 
+    def transform_images(self, images, transformation, training=True):
+        if not training:
+            return convert_to_tensor(images)
+        return self._apply(self._cast(images), transformation)
+
+    def _equalize_channel(self, channel):
+        bins = self.bins
+        lo, hi = float(self.value_range[0]), float(self.value_range[1])
+        scale = 255.0 / (hi - lo)
+        level = channel * scale + (0.0 - lo * scale)
+        flat = (level.to(torch.float32) * (bins - 1) / 255.0).to(torch.int32).clamp(0, bins - 1).reshape(-1)
+        hist = torch.bincount(flat.long(), minlength=bins)
+        if int(torch.count_nonzero(hist)) <= 1:
+            out = level
+        else:
+            cdf = torch.cumsum(hist, dim=0)
+            cdf_min = cdf[torch.nonzero(cdf)[0][0]]
+            denom = cdf[-1] - cdf_min
+            denom = torch.where(denom == 0, torch.ones_like(denom), denom)
+            table = torch.clip(torch.round(((cdf - cdf_min) * 255) / denom), 0, 255)
+            index = torch.clip(level / 255.0 * (bins - 1), 0, bins - 1).to(torch.int32)
+            out = table[index.long()].to(level.dtype)
+        back = (hi - lo) / 255.0
+        return out * back + (lo - 0.0 * back)
+
     def _apply(self, images, t):
-        x = self._to_bchw(self._transform_value_range(images, self.value_range, (0, 255)))
-        B, C, H, W = x.shape
-        levels = (x / 255.0 * (self.bins - 1)).round().clamp(0, self.bins - 1).reshape(B * C, H * W)
-        eq, _ = _equalize_planes(levels, self.bins)
-        out = (eq / (self.bins - 1) * 255.0).reshape(B, C, H, W)
-        return self._transform_value_range(self._from_bchw(out), (0, 255), self.value_range).to(images.dtype)
+        axis = -1 if self.data_format == "channels_last" else -3
+        planes = [self._equalize_channel(images.select(axis, i)) for i in range(images.shape[axis])]
+        return torch.stack(planes, dim=axis).to(images.dtype)
 
     def get_config(self):
         return {**super().get_config(), "bins": self.bins, "value_range": self.value_range}

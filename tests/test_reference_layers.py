@@ -85,7 +85,46 @@ LAYERS = [
     ("Masking", dict(mask_value=0.0), [(2, 4, 3)], {}, None),
     ("ActivityRegularization", dict(l1=0.1), [(2, 4)], {}, None),
     ("MelSpectrogram", dict(fft_length=32, sequence_stride=16, num_mel_bins=8, sampling_rate=800), [(2, 128)], {}, None),
+    ("AdaptiveAveragePooling1D", dict(output_size=3), [(2, 10, 4)], {}, None),
+    ("AdaptiveAveragePooling3D", dict(output_size=(2, 3, 2)), [(2, 6, 7, 5, 3)], {}, None),
+    ("AdaptiveMaxPooling2D", dict(output_size=(3, 2)), [(2, 9, 7, 3)], {}, None),
+    ("AdaptiveMaxPooling3D", dict(output_size=2), [(2, 6, 7, 5, 3)], {}, None),
+    ("AveragePooling3D", dict(pool_size=2, strides=1, padding="same"), [(2, 5, 6, 4, 3)], {}, None),
+    ("MaxPooling1D", dict(pool_size=3, strides=2, padding="same"), [(2, 11, 4)], {}, None),
+    ("ConvLSTM1D", dict(filters=4, kernel_size=3, padding="same", return_sequences=True), [(2, 5, 8, 3)], {}, None),
+    ("ConvLSTM3D", dict(filters=2, kernel_size=2, padding="same"), [(1, 3, 4, 4, 4, 2)], {}, None),
+    ("Cropping1D", dict(cropping=(1, 2)), [(2, 8, 3)], {}, None),
+    ("Cropping3D", dict(cropping=((1, 0), (0, 1), (1, 1))), [(2, 5, 5, 5, 2)], {}, None),
+    ("DepthwiseConv1D", dict(kernel_size=3, depth_multiplier=2, padding="same", strides=2), [(2, 9, 4)], {}, None),
+    ("SeparableConv1D", dict(filters=5, kernel_size=3, padding="same", depth_multiplier=2), [(2, 9, 4)], {}, None),
+    ("GlobalAveragePooling1D", dict(), [(2, 7, 4)], {}, None),
+    ("GlobalAveragePooling3D", dict(keepdims=True), [(2, 3, 4, 5, 6)], {}, None),
+    ("GlobalMaxPooling2D", dict(), [(2, 5, 6, 4)], {}, None),
+    ("GlobalMaxPooling3D", dict(), [(2, 3, 4, 5, 6)], {}, None),
+    ("Identity", dict(), [(2, 3)], {}, None),
+    ("UpSampling1D", dict(size=3), [(2, 4, 3)], {}, None),
+    ("UpSampling3D", dict(size=(2, 1, 2)), [(2, 3, 3, 3, 2)], {}, None),
+    ("ZeroPadding1D", dict(padding=(1, 2)), [(2, 4, 3)], {}, None),
+    ("ZeroPadding3D", dict(padding=((1, 0), (2, 1), (0, 1))), [(2, 3, 3, 3, 2)], {}, None),
+    ("STFTSpectrogram", dict(mode="log", frame_length=32, frame_step=8, fft_length=64), [(2, 200, 1)], {}, None),
+    ("STFTSpectrogram", dict(mode="stft", frame_length=32, frame_step=16, expand_dims=True, padding="same", window="hamming"), [(2, 200, 1)], {}, None),
+    ("ReversibleEmbedding", dict(input_dim=20, output_dim=6), [(2, 5)], {}, 20),
+    ("Activation", dict(activation="hard_silu"), [(3, 5)], {}, None),
+    ("RandomCrop", dict(height=4, width=5), [(2, 8, 8, 3)], dict(training=False), None),
 ]
+
+
+def test_equalization_follows_the_reference_per_channel_over_the_batch():
+    rk = oracle.ref()
+    images = (np.random.default_rng(4).random((2, 16, 16, 3)) * 255).astype("float32")
+    for kwargs in (dict(value_range=(0, 255)), dict(value_range=(0, 255), bins=64)):
+        expected = rk.layers.Equalization(**kwargs)(torch.tensor(images))
+        oracle.assert_same(keras.layers.Equalization(**kwargs)(torch.tensor(images)), expected, "Equalization", rtol=1e-5, atol=1e-4)
+    unit = images / 255.0
+    expected = rk.layers.Equalization(value_range=(0, 1))(torch.tensor(unit))
+    oracle.assert_same(keras.layers.Equalization(value_range=(0, 1))(torch.tensor(unit)), expected, "Equalization 0..1", rtol=1e-5, atol=1e-5)
+    same = keras.layers.Equalization()(torch.tensor(images), training=False)
+    np.testing.assert_array_equal(same.numpy(), images)
 
 
 def _make(k, name, kwargs):
