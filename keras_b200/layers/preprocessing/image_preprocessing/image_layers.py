@@ -953,25 +953,6 @@ class AutoContrast(_Base):
         return {**super().get_config(), "value_range": self.value_range}
 
 
-def _equalize_planes(planes, bins, clip_limit=None):
-    """Histogram-equalise ``planes [P, N]`` of integer levels in ``[0, bins)``; returns float levels in [0, bins-1]."""
-    P, N = planes.shape
-    hist = torch.zeros((P, bins), dtype=torch.float32, device=planes.device)
-    hist.scatter_add_(1, planes.long(), torch.ones_like(planes, dtype=torch.float32))
-    if clip_limit is not None:
-        limit = max(clip_limit * N / bins, 1.0)
-        excess = (hist - limit).clamp(min=0).sum(dim=1, keepdim=True)
-        hist = hist.clamp(max=limit) + excess / bins
-    cdf = hist.cumsum(dim=1)
-    nz = torch.where(hist > 0, cdf, torch.full_like(cdf, float("inf"))).amin(dim=1, keepdim=True)
-    cdf_min = torch.where(torch.isfinite(nz), nz, torch.zeros_like(nz))
-    denom = (cdf[:, -1:] - cdf_min).clamp(min=1.0)
-    lut = ((cdf - cdf_min) / denom * (bins - 1)).clamp(0, bins - 1)
-    flat = lut.gather(1, planes.long())
-    constant = (cdf[:, -1:] - cdf_min) <= 0
-    return torch.where(constant, planes.to(torch.float32), flat), lut
-
-
 @keras_export("keras.layers.Equalization")
 class Equalization(_Base):
     """Histogram equalisation of every channel.  As in keras/src/layers/preprocessing/image_preprocessing/equalization.py:88-200
@@ -1021,7 +1002,10 @@ class Equalization(_Base):
 
 @keras_export("keras.layers.ContrastLimitedAdaptiveHistogramEqualization")
 class ContrastLimitedAdaptiveHistogramEqualization(_Base):
-    """CLAHE: per-tile clipped histogram equalisation with bilinear blending of the tile look-up tables."""
+    """CLAHE with the arithmetic of keras/src/layers/preprocessing/image_preprocessing/clahe.py:116-312: symmetric padding to
+    whole tiles, histograms of truncated levels, clipping at ``clip_limit * tile pixels / 256`` with the excess spread
+    evenly, a look-up table per tile from its cumulative histogram, and bilinear blending of the four neighbouring tables
+    around tile centres.  Applied in training and inference alike."""
 
     _USE_BASE_FACTOR = False
     _ALWAYS = True
@@ -1032,36 +1016,72 @@ class ContrastLimitedAdaptiveHistogramEqualization(_Base):
         self.clip_limit = clip_limit
         self.tile_grid_size = tuple(tile_grid_size)
 
+    def transform_images(self, images, transformation, training=True):
+        images = convert_to_tensor(images)
+        return self._apply(images, transformation)
+
+    @staticmethod
+    def _mirror(n, pad, device):
+        """Indices of ``n + pad`` positions that read ``n`` real ones, the tail mirrored about the edge (edge repeated)."""
+        idx = torch.arange(n + pad, device=device)
+        return torch.where(idx >= n, 2 * n - 1 - idx, idx).clamp(0, n - 1)
+
     def _apply(self, images, t):
-        x = self._to_bchw(self._transform_value_range(images, self.value_range, (0, 255)))
-        B, C, H, W = x.shape
+        original = images.dtype
+        batched = images.ndim == 4
+        x = images if batched else images.unsqueeze(0)
+        if self.data_format == "channels_first":
+            x = x.permute(0, 2, 3, 1)
+        x = self._transform_value_range(x.to(torch.float32), self.value_range, (0, 255))
+        B, H, W, C = x.shape
         gh, gw = self.tile_grid_size
         th, tw = -(-H // gh), -(-W // gw)
         ph, pw = th * gh - H, tw * gw - W
-        xp = F.pad(x, (0, pw, 0, ph), mode="reflect") if (ph or pw) and ph < H and pw < W else F.pad(x, (0, pw, 0, ph), mode="replicate")
-        lv = xp.round().clamp(0, 255)
-        tiles = lv.reshape(B, C, gh, th, gw, tw).permute(0, 1, 2, 4, 3, 5).reshape(B * C * gh * gw, th * tw)
-        _, lut = _equalize_planes(tiles, 256, clip_limit=self.clip_limit)
-        lut = lut.reshape(B, C, gh, gw, 256)
-        # bilinear blend of the four neighbouring tile LUTs at every pixel
-        ys = (torch.arange(H, device=x.device, dtype=torch.float32) + 0.5) / th - 0.5
-        xs = (torch.arange(W, device=x.device, dtype=torch.float32) + 0.5) / tw - 0.5
-        y0 = ys.floor().clamp(0, gh - 1).long()
-        y1 = (ys.floor() + 1).clamp(0, gh - 1).long()
-        x0 = xs.floor().clamp(0, gw - 1).long()
-        x1 = (xs.floor() + 1).clamp(0, gw - 1).long()
-        wy = (ys - ys.floor()).clamp(0, 1).reshape(1, 1, H, 1)
-        wx = (xs - xs.floor()).clamp(0, 1).reshape(1, 1, 1, W)
-        wy = torch.where((ys < 0).reshape(1, 1, H, 1), torch.zeros_like(wy), wy)
-        wx = torch.where((xs < 0).reshape(1, 1, 1, W), torch.zeros_like(wx), wx)
-        pix = lv[:, :, :H, :W].long()
+        if ph or pw:
+            x = x[:, self._mirror(H, ph, x.device)][:, :, self._mirror(W, pw, x.device)]
+        Hp, Wp = H + ph, W + pw
+        levels = x.to(torch.int32).clamp(0, 255)
+        tiles = levels.reshape(B, gh, th, gw, tw, C).permute(0, 1, 3, 5, 2, 4).reshape(B, gh, gw, C, th * tw)
+        hist = torch.zeros((B, gh, gw, C, 256), dtype=torch.float32, device=x.device)
+        hist.scatter_add_(-1, tiles.long(), torch.ones_like(tiles, dtype=torch.float32))
+        if self.clip_limit > 0:
+            # the histograms the limit is compared with are integer counts and the limit takes their type: a limit below one
+            # clips every bin to zero (keras/src/layers/preprocessing/image_preprocessing/clahe.py:176-190 over
+            # keras/src/backend/torch/nn.py:872-886, whose one_hot stays int64)
+            limit = float(int(self.clip_limit * (th * tw) / 256.0))
+            clipped = hist.clamp(0, limit)
+            hist = clipped + (hist - clipped).sum(dim=-1, keepdim=True) / 256.0
+        cdf = hist.cumsum(dim=-1)
+        lowest = cdf.amin(dim=-1, keepdim=True)
+        span = float(th * tw) - lowest
+        span = torch.where(span == 0, torch.ones_like(span), span)
+        table = ((cdf - lowest) * 255.0 / span).clamp(0, 255)
+        # one ring of repeated border tiles, then every pixel blends the tables of the four tile centres around it
+        table = torch.cat([table[:, :1], table, table[:, -1:]], dim=1)
+        table = torch.cat([table[:, :, :1], table, table[:, :, -1:]], dim=2)
+        ys = (torch.arange(Hp, dtype=torch.float32, device=x.device) - th / 2.0) / th + 1.0
+        xs = (torch.arange(Wp, dtype=torch.float32, device=x.device) - tw / 2.0) / tw + 1.0
+        y0f, x0f = ys.floor(), xs.floor()
+        wy, wx = (ys - y0f).reshape(1, Hp, 1, 1), (xs - x0f).reshape(1, 1, Wp, 1)
+        y0, y1 = y0f.clamp(0, gh + 1).long(), (y0f + 1).clamp(0, gh + 1).long()
+        x0, x1 = x0f.clamp(0, gw + 1).long(), (x0f + 1).clamp(0, gw + 1).long()
+        step_c, step_x = 256, 256 * C
+        step_y = step_x * (gw + 2)
+        step_b = step_y * (gh + 2)
+        flat = table.reshape(-1)
+        base = (torch.arange(B, device=x.device).reshape(B, 1, 1, 1) * step_b + torch.arange(C, device=x.device).reshape(1, 1, 1, C) * step_c
+                + levels.long())
 
         def look(yi, xi):
-            table = lut[:, :, yi][:, :, :, xi]  # [B, C, H, W, 256]
-            return table.gather(-1, pix.unsqueeze(-1)).squeeze(-1)
+            return flat[base + yi.reshape(1, Hp, 1, 1) * step_y + xi.reshape(1, 1, Wp, 1) * step_x]
 
-        out = (1 - wy) * ((1 - wx) * look(y0, x0) + wx * look(y0, x1)) + wy * ((1 - wx) * look(y1, x0) + wx * look(y1, x1))
-        return self._transform_value_range(self._from_bchw(out), (0, 255), self.value_range).to(images.dtype)
+        upper = look(y0, x0) * (1.0 - wx) + look(y0, x1) * wx
+        lower = look(y1, x0) * (1.0 - wx) + look(y1, x1) * wx
+        out = (upper * (1.0 - wy) + lower * wy)[:, :H, :W]
+        out = self._transform_value_range(out, (0, 255), self.value_range).to(original)
+        if self.data_format == "channels_first":
+            out = out.permute(0, 3, 1, 2)
+        return out if batched else out[0]
 
     def get_config(self):
         return {**super().get_config(), "value_range": self.value_range, "clip_limit": self.clip_limit, "tile_grid_size": self.tile_grid_size}

@@ -214,3 +214,16 @@ def test_int8_quantized_layers_match_reference(make, shape):
     for mine, ref_w in zip(ours.get_weights(), theirs.get_weights()):
         oracle.assert_same(mine, ref_w, "quantised weights", rtol=1e-6, atol=1e-7)
     oracle.assert_same(ours(torch.tensor(x)), theirs(torch.tensor(x)), "int8 forward", rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("shape,grid", [((2, 16, 16, 3), (8, 8)), ((1, 30, 45, 2), (4, 4)), ((1, 64, 64, 1), (8, 8))])
+def test_clahe_matches_reference(shape, grid):
+    rk = oracle.ref()
+    images = (np.random.default_rng(5).random(shape) * 255).astype("float32")
+    expected = rk.layers.ContrastLimitedAdaptiveHistogramEqualization(tile_grid_size=grid)(torch.tensor(images))
+    got = keras.layers.ContrastLimitedAdaptiveHistogramEqualization(tile_grid_size=grid)(torch.tensor(images))
+    oracle.assert_same(got, expected, "CLAHE", rtol=1e-5, atol=1e-3)
+    unit = images / 255.0
+    expected = rk.layers.ContrastLimitedAdaptiveHistogramEqualization(value_range=(0, 1), clip_limit=2.0, tile_grid_size=grid)(torch.tensor(unit))
+    got = keras.layers.ContrastLimitedAdaptiveHistogramEqualization(value_range=(0, 1), clip_limit=2.0, tile_grid_size=grid)(torch.tensor(unit))
+    oracle.assert_same(got, expected, "CLAHE 0..1", rtol=1e-5, atol=1e-5)
