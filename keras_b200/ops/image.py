@@ -143,7 +143,9 @@ def resize(images, size, interpolation="bilinear", antialias=False, crop_to_aspe
         ph = max(int(w * th / tw), h)
         pw = max(int(h * tw / th), w)
         top, left = int((ph - h) / 2), int((pw - w) / 2)
-        x = F.pad(x, (left, pw - w - left, top, ph - h - top), value=fill_value)
+        # the same margin on both sides, so an odd difference pads one line less than the target aspect asks for
+        # (keras/src/backend/torch/image.py:268-321)
+        x = F.pad(x, (left, left, top, top), value=fill_value)
     xf = x if x.dtype in (torch.float32, torch.float64) else x.float()
     if interpolation in ("lanczos3", "lanczos5"):
         radius = 3 if interpolation == "lanczos3" else 5

@@ -201,6 +201,9 @@ def _cases():
         "ctc_loss": lambda o: o.ctc_loss(np.array([[1, 2, 0], [2, 1, 1]], "int32"), seq[:, :, :4], np.array([2, 3], "int32"), np.array([9, 7], "int32")),
         "image_resize_bilinear": lambda o: o.image.resize(img, (5, 11), interpolation="bilinear"),
         "image_resize_nearest": lambda o: o.image.resize(img, (16, 4), interpolation="nearest"),
+        "image_resize_pad_to_aspect": lambda o: o.image.resize(img, (10, 7), pad_to_aspect_ratio=True, fill_value=3.0),
+        "image_resize_pad_to_aspect_wide": lambda o: o.image.resize(img, (5, 13), pad_to_aspect_ratio=True),
+        "image_resize_crop_to_aspect": lambda o: o.image.resize(img, (10, 7), crop_to_aspect_ratio=True),
         "image_resize_bicubic_antialias": lambda o: o.image.resize(img, (4, 4), interpolation="bicubic", antialias=True),
         # data_format is named: the reference's eager path forwards an unset data_format to its backend, which then blurs
         # the wrong axes of a channels-last image
