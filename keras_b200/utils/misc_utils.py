@@ -28,7 +28,13 @@ def get_random_seed():
 @keras_export("keras.utils.to_categorical")
 def to_categorical(x, num_classes=None):
     if isinstance(x, torch.Tensor):
-        x = x.cpu().numpy()
+        # a tensor stays a tensor (the torch one-hot without a dtype is int64: keras/src/backend/torch/nn.py:872-886);
+        # anything else gives a float64 NumPy array (keras/src/utils/numerical_utils.py:77-103)
+        from keras_b200 import ops
+
+        if x.ndim > 1 and x.shape[-1] == 1:
+            x = x.reshape(tuple(x.shape[:-1]))
+        return ops.one_hot(x, num_classes, dtype="int64")
     x = np.array(x, dtype="int64")
     input_shape = x.shape
     if input_shape and input_shape[-1] == 1 and len(input_shape) > 1:
@@ -36,7 +42,7 @@ def to_categorical(x, num_classes=None):
     x = x.reshape(-1)
     if not num_classes:
         num_classes = np.max(x) + 1
-    out = np.zeros((x.shape[0], num_classes), dtype="float32")
+    out = np.zeros((x.shape[0], num_classes))
     out[np.arange(x.shape[0]), x] = 1
     return out.reshape(input_shape + (num_classes,))
 

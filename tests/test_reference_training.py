@@ -236,3 +236,16 @@ def test_multi_optimizer_routing_matches_reference():
         np.testing.assert_allclose(a, b, rtol=2e-5, atol=2e-6)
     with pytest.raises(ValueError):
         keras.optimizers.OptimizerMap(keras.optimizers.SGD(0.1), {"a.*": keras.optimizers.SGD(0.1), "ab.*": keras.optimizers.SGD(0.2)})["abc"]
+
+
+def test_to_categorical_types_follow_the_reference():
+    rk = oracle.ref()
+    import torch
+
+    for labels in ([0, 2, 1, 3], np.array([[0], [2], [1]]), np.array([[0, 2], [1, 3]])):
+        theirs, ours = rk.utils.to_categorical(labels, num_classes=5), keras.utils.to_categorical(labels, num_classes=5)
+        assert type(ours) is type(theirs) and ours.dtype == theirs.dtype and ours.shape == theirs.shape
+        np.testing.assert_array_equal(ours, theirs)
+    theirs, ours = rk.utils.to_categorical(torch.tensor([[1], [3]]), 4), keras.utils.to_categorical(torch.tensor([[1], [3]]), 4)
+    assert isinstance(ours, torch.Tensor) and ours.dtype == theirs.dtype and tuple(ours.shape) == tuple(theirs.shape)
+    np.testing.assert_array_equal(ours.numpy(), theirs.numpy())
