@@ -61,8 +61,10 @@ class LazyLogs(dict):
 
 
 def pythonify_logs(logs):
+    """Plain Python values, nested dicts flattened, keys in sorted order (keras/src/utils/python_utils.py:165-194: histories
+    and ``evaluate(return_dict=True)`` list ``accuracy`` before ``loss``)."""
     out = {}
-    for k, v in (logs or {}).items():
+    for k, v in sorted((logs or {}).items()):
         if isinstance(v, dict):
             out.update(pythonify_logs(v))
         else:

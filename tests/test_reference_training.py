@@ -249,3 +249,42 @@ def test_to_categorical_types_follow_the_reference():
     theirs, ours = rk.utils.to_categorical(torch.tensor([[1], [3]]), 4), keras.utils.to_categorical(torch.tensor([[1], [3]]), 4)
     assert isinstance(ours, torch.Tensor) and ours.dtype == theirs.dtype and tuple(ours.shape) == tuple(theirs.shape)
     np.testing.assert_array_equal(ours.numpy(), theirs.numpy())
+
+
+def test_multi_output_fit_evaluate_match_reference_keys_and_values():
+    """Two inputs, two outputs, per-output losses, loss weights, metrics and sample weights: histories, evaluate dicts and
+    train_on_batch dicts carry the reference's keys in the reference's order with the reference's numbers."""
+    rk = oracle.ref()
+    rng = np.random.default_rng(0)
+    xa, xb = rng.normal(size=(64, 8)).astype("float32"), rng.normal(size=(64, 5)).astype("float32")
+    y1, y2 = rng.integers(0, 3, (64,)), rng.normal(size=(64, 1)).astype("float32")
+
+    def build(k):
+        a, b = k.Input((8,), name="a"), k.Input((5,), name="b")
+        h = k.layers.Concatenate()([k.layers.Dense(16, activation="relu", name="da")(a), k.layers.Dense(16, activation="tanh", name="db")(b)])
+        return k.Model({"a": a, "b": b}, {"cls": k.layers.Dense(3, name="cls")(h), "reg": k.layers.Dense(1, name="reg")(h)})
+
+    rk.utils.set_random_seed(1)
+    start = build(rk).get_weights()
+
+    def run(k):
+        m = build(k)
+        m.set_weights(start)
+        m.compile(optimizer=k.optimizers.Adam(1e-2), loss={"cls": k.losses.SparseCategoricalCrossentropy(from_logits=True), "reg": "mse"},
+                  loss_weights={"cls": 1.0, "reg": 0.5},
+                  metrics={"cls": ["accuracy", k.metrics.SparseTopKCategoricalAccuracy(2, name="top2")], "reg": [k.metrics.MeanAbsoluteError()]})
+        hist = m.fit({"a": xa, "b": xb}, {"cls": y1, "reg": y2}, batch_size=16, epochs=2, verbose=0, shuffle=False, validation_split=0.25,
+                     sample_weight={"cls": np.linspace(0.5, 1.5, 64).astype("float32"), "reg": np.ones(64, "float32")}).history
+        ev = m.evaluate({"a": xa, "b": xb}, {"cls": y1, "reg": y2}, batch_size=32, verbose=0, return_dict=True)
+        flat = m.evaluate({"a": xa, "b": xb}, {"cls": y1, "reg": y2}, batch_size=32, verbose=0)
+        step = m.train_on_batch({"a": xa[:8], "b": xb[:8]}, {"cls": y1[:8], "reg": y2[:8]}, return_dict=True)
+        return hist, ev, flat, step
+
+    theirs, ours = run(rk), run(keras)
+    for a, b in zip(ours, theirs):
+        if isinstance(b, dict):
+            assert list(a) == list(b)
+            for key in b:
+                np.testing.assert_allclose(a[key], b[key], rtol=3e-4, atol=3e-5, err_msg=key)
+        else:
+            np.testing.assert_allclose(a, b, rtol=3e-4, atol=3e-5)
