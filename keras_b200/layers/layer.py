@@ -10,6 +10,7 @@ plan* (argument names, whether ``training`` / ``mask`` are accepted) so the hot 
 
 import collections
 import inspect
+import os
 import warnings
 
 import torch
@@ -28,6 +29,10 @@ from keras_b200.ops.node import Node
 from keras_b200.ops.operation import Operation
 
 _TENSOR_TYPES = (torch.Tensor, KerasTensor)
+
+
+# KERAS_B200_NVTX=1: every eager layer call opens an NVTX range named by the layer's path (for profiler timelines).
+_NVTX_RANGES = os.environ.get("KERAS_B200_NVTX", "0") == "1" and torch.cuda.is_available()
 
 
 class _TrackedList(list):
@@ -797,6 +802,13 @@ class Layer(Operation):
                         # a graph node remembers only what the caller chose: an implicit `training` stays open so that the
                         # model's own call can set it later
                         outputs = self._symbolic_call(*args, _implicit=implicit, **kwargs) if implicit else self._symbolic_call(*args, **kwargs)
+                    elif _NVTX_RANGES:
+                        # one profiler range per layer call, named by the layer's path: a timeline then reads in model terms
+                        torch.cuda.nvtx.range_push(getattr(self, "path", None) or self.name)
+                        try:
+                            outputs = self._eager_call(*args, **kwargs)
+                        finally:
+                            torch.cuda.nvtx.range_pop()
                     else:
                         outputs = self._eager_call(*args, **kwargs)
                 finally:

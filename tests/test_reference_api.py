@@ -31,3 +31,16 @@ def test_public_namespace_covers_the_reference():
 
     walk(rk, keras, "keras", 0)
     assert not missing, missing
+
+
+def test_exported_paths_match_the_pinned_listing():
+    """Adding or removing a public symbol has to come with an update of tests/golden_api.txt
+    (``python -m keras_b200.api_listing > tests/golden_api.txt``)."""
+    import os
+
+    from keras_b200 import api_listing
+
+    with open(os.path.join(os.path.dirname(__file__), "golden_api.txt")) as f:
+        pinned = [line.strip() for line in f if line.strip()]
+    current = api_listing.public_paths()
+    assert current == pinned, {"added": sorted(set(current) - set(pinned)), "removed": sorted(set(pinned) - set(current))}
