@@ -224,6 +224,11 @@ def run_bn(layer, x, training, residual=None, relu=False, pre_bias=None, stats=N
     bias_value = pre_bias._value if pre_bias is not None else None
     out = dispatch.batch_norm(layer, x, train, residual=residual, relu=relu, pre_bias=bias_value, conv_stats=stats)
     if out is not None:
+        if pre_bias is not None and train:
+            # A bias in front of a batch normalization in training mode is removed with the batch mean: its gradient is exactly
+            # zero.  The fused kernel never materialises it, so the variable is marked: gradient storage reports a zero
+            # gradient for it (the optimizer then treats it as the reference does, weight decay included) instead of none.
+            pre_bias._gradient_is_zero_when_absent = True
         return out
     if pre_bias is not None:
         x = x + pre_bias.value.to(x.dtype)

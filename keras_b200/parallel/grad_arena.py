@@ -67,6 +67,8 @@ class GradArena:
             for idx, (v, view) in enumerate(zip(self.variables, self.views)):
                 g = v._value.grad
                 if g is None:
+                    if getattr(v, "_gradient_is_zero_when_absent", False) and view is not None:
+                        continue  # known to be zero (a bias folded into a batch normalization): its zeroed slot is its gradient
                     self.unused.add(idx)
                 elif view is not None:
                     view.copy_(g)
