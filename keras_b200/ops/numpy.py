@@ -63,6 +63,41 @@ def _pair(x1, x2):
     return convert_to_tensor(x1, d), convert_to_tensor(x2, d)
 
 
+def _pair_native(x1, x2):
+    """Both operands as tensors, promoted by torch's own rule (0-dim operands count as scalars).  The reference hands the
+    operands of add, subtract, multiply, power, where, append, kron, outer, mod, gcd, lcm and the bitwise ops to torch
+    unpromoted (keras/src/backend/torch/numpy.py:68-71 and the like), so 64-bit operands keep 64 bits there although
+    ``result_type`` would narrow them."""
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
+    if type(x1) is _T and type(x2) is _T and x1.dtype == x2.dtype:
+        return x1, x2
+    a, b = convert_to_tensor(x1), convert_to_tensor(x2)
+    if a.dtype == b.dtype:
+        return a, b
+    d = torch.result_type(a, b)
+    return a.to(d), b.to(d)
+
+
+def _pair_strict(x1, x2):
+    """Both operands cast to ``result_type`` of their dtypes even when the dtypes are equal: ops that resolve their dtype that
+    way in the reference (maximum, minimum, floor_divide, the products) turn int64 into int32 and float64 into float32."""
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
+    d = to_torch_dtype(result_type(_dt(x1), _dt(x2)))
+    return convert_to_tensor(x1, d), convert_to_tensor(x2, d)
+
+
+def _narrow64(x):
+    """``result_type`` of a single dtype: 64-bit types become their 32-bit counterparts."""
+    d = to_torch_dtype(result_type(_dt(x)))
+    return x if x.dtype == d else x.to(d)
+
+
 def _floatize(x):
     """ints/bools → floatx; floats unchanged."""
     x = _t(x)
@@ -111,14 +146,30 @@ for _n, _f in {
     "expm1": torch.expm1, "log": torch.log, "log10": torch.log10, "log1p": torch.log1p,
     "log2": torch.log2, "sin": torch.sin, "sinh": torch.sinh, "sqrt": torch.sqrt,
     "tan": torch.tan, "tanh": torch.tanh, "sinc": torch.sinc, "i0": torch.i0,
-    "deg2rad": torch.deg2rad, "rad2deg": torch.rad2deg, "reciprocal": torch.reciprocal,
+    "reciprocal": torch.reciprocal,
 }.items():
     _reg_unary_float(_n, _f)
 
 
+def _reg_angle(name, torch_fn):
+    def f(x):
+        x = _t(x)
+        # int64 degrees / radians come back as float64 (keras/src/backend/torch/numpy.py deg2rad, rad2deg)
+        return torch_fn(x.to(torch.float64)) if x.dtype == torch.int64 else torch_fn(_floatize(x))
+
+    f.__name__ = name
+    f.__qualname__ = name
+    globals()[name] = op("numpy")(f)
+
+
+_reg_angle("deg2rad", torch.deg2rad)
+_reg_angle("rad2deg", torch.rad2deg)
+
+
 @op("numpy")
 def cbrt(x):
-    x = _floatize(x)
+    x = _t(x)
+    x = x.to(torch.float64) if x.dtype == torch.int64 else _floatize(x)
     return torch.sign(x) * torch.pow(torch.abs(x), 1.0 / 3.0)
 
 
@@ -126,13 +177,13 @@ def cbrt(x):
 
 @op("numpy")
 def add(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.add(x1, x2) if x1.dtype != torch.bool else torch.logical_or(x1, x2)
 
 
 @op("numpy")
 def subtract(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     if x1.dtype == torch.bool:
         x1, x2 = x1.to(torch.int32), x2.to(torch.int32)
     return torch.subtract(x1, x2)
@@ -140,13 +191,24 @@ def subtract(x1, x2):
 
 @op("numpy")
 def multiply(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.multiply(x1, x2) if x1.dtype != torch.bool else torch.logical_and(x1, x2)
 
 
 @op("numpy", also=("keras.ops.true_divide", "keras.ops.numpy.true_divide"))
 def divide(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    # torch's true division of the operands as they are: float64 stays float64, integer by integer gives floatx
+    # (keras/src/backend/torch/numpy.py divide)
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
+    if not isinstance(x1, (int, float)):
+        x1 = convert_to_tensor(x1)
+    if not isinstance(x2, (int, float)):
+        x2 = convert_to_tensor(x2)
+    if not isinstance(x1, _T) and not isinstance(x2, _T):
+        x1 = convert_to_tensor(x1)
     return torch.divide(x1, x2)
 
 
@@ -161,13 +223,13 @@ def divide_no_nan(x1, x2):
 
 @op("numpy")
 def floor_divide(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_strict(x1, x2)
     return torch.floor_divide(x1, x2)
 
 
 @op("numpy")
 def mod(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     if x1.dtype == torch.bool:
         x1, x2 = x1.to(torch.int32), x2.to(torch.int32)
     return torch.remainder(x1, x2)
@@ -181,19 +243,19 @@ def fmod(x1, x2):
 
 @op("numpy")
 def power(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.pow(x1, x2)
 
 
 @op("numpy")
 def maximum(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_strict(x1, x2)
     return torch.maximum(x1, x2)
 
 
 @op("numpy")
 def minimum(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_strict(x1, x2)
     return torch.minimum(x1, x2)
 
 
@@ -241,7 +303,12 @@ def nextafter(x1, x2):
 
 @op("numpy")
 def heaviside(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    x1, x2 = _pair_strict(x1, x2)
+    if x1.dtype == torch.int64:
+        x1, x2 = x1.to(torch.float64), x2.to(torch.float64)
+    elif x1.dtype in (torch.int8, torch.int16, torch.int32, torch.uint8):
+        f = to_torch_dtype(config.floatx())
+        x1, x2 = x1.to(f), x2.to(f)
     return torch.heaviside(x1, x2)
 
 
@@ -256,13 +323,13 @@ def ldexp(x1, x2):
 
 @op("numpy")
 def gcd(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.gcd(x1, x2)
 
 
 @op("numpy")
 def lcm(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.lcm(x1, x2)
 
 
@@ -308,7 +375,7 @@ def logical_not(x):
 
 def _bitwise(name, fn):
     def f(x, y):
-        a, b = _pair(x, y)
+        a, b = _pair_native(x, y)
         return fn(a, b)
 
     f.__name__ = name
@@ -372,12 +439,12 @@ def signbit(x):
 
 @op("numpy")
 def ceil(x):
-    return torch.ceil(_floatize(x))
+    return torch.ceil(_narrow64(_floatize(x)))
 
 
 @op("numpy")
 def floor(x):
-    return torch.floor(_floatize(x))
+    return torch.floor(_narrow64(_floatize(x)))
 
 
 @op("numpy")
@@ -476,7 +543,7 @@ def _promote_sum_dtype(x):
     if x.dtype in (torch.int8, torch.int16):
         return x.to(torch.int32)
     if x.dtype == torch.uint8:
-        return x.to(torch.int64)  # stands for uint32
+        return x.to(torch.int32)  # the reference's torch backend has no uint32 and uses int32
     return x
 
 
@@ -496,6 +563,8 @@ def prod(x, axis=None, keepdims=False, dtype=None):
     x = _promote_sum_dtype(_t(x))
     if dtype is not None:
         x = x.to(to_torch_dtype(dtype))
+    else:
+        x = _narrow64(x)  # result_type of the input's dtype (keras/src/backend/torch/numpy.py prod)
     if axis is None:
         r = torch.prod(x, dtype=x.dtype)
         return r.reshape((1,) * x.ndim) if keepdims else r
@@ -614,7 +683,8 @@ def _var_like(fn, x, axis, keepdims):
 
 @op("numpy")
 def var(x, axis=None, keepdims=False):
-    return _var_like(torch.var, x, axis, keepdims)
+    x = _t(x)
+    return _var_like(torch.var, x.to(torch.float32) if x.dtype == torch.float64 else x, axis, keepdims)
 
 
 @op("numpy")
@@ -651,7 +721,8 @@ def cumsum(x, axis=None, dtype=None):
     x = _t(x)
     if axis is None:
         x, axis = x.flatten(), 0
-    d = to_torch_dtype(dtype) if dtype is not None else (torch.int32 if x.dtype == torch.bool else x.dtype)
+    d = to_torch_dtype(result_type(dtype if dtype is not None else _dt(x)))  # 64-bit narrows, as result_type says
+    d = torch.int32 if d == torch.bool else d
     return torch.cumsum(x, dim=axis, dtype=d)
 
 
@@ -660,7 +731,8 @@ def cumprod(x, axis=None, dtype=None):
     x = _t(x)
     if axis is None:
         x, axis = x.flatten(), 0
-    d = to_torch_dtype(dtype) if dtype is not None else (torch.int32 if x.dtype == torch.bool else x.dtype)
+    d = to_torch_dtype(result_type(dtype if dtype is not None else _dt(x)))
+    d = torch.int32 if d == torch.bool else d
     return torch.cumprod(x, dim=axis, dtype=d)
 
 
@@ -693,7 +765,7 @@ def median(x, axis=None, keepdims=False):
 @op("numpy")
 def quantile(x, q, axis=None, method="linear", keepdims=False):
     x = _t(x)
-    ori = x.dtype if x.dtype in _FLOATS else to_torch_dtype(config.floatx())
+    ori = to_torch_dtype(result_type(_dt(x), float))  # float64 narrows to float32 here, as in the reference
     compute = torch.float32 if ori in (torch.float16, torch.bfloat16) else ori
     xq = x.to(compute)
     qt = _t(q).to(compute)
@@ -869,11 +941,13 @@ def matmul(x1, x2):
         if x1.is_cuda:
             return torch.matmul(x1.to(torch.float32), x2.to(torch.float32)).to(torch.int32)
         return torch.matmul(x1.to(torch.int32), x2.to(torch.int32))
-    if x1.dtype != x2.dtype:
-        d = to_torch_dtype(result_type(x1.dtype, x2.dtype))
+    if x1.dtype != x2.dtype or x1.dtype in (torch.int64, torch.float64):
+        d = to_torch_dtype(result_type(x1.dtype, x2.dtype))  # also narrows a pair of 64-bit operands, as the reference does
         x1, x2 = x1.to(d), x2.to(d)
     if x1.dtype == torch.bool:
-        return torch.matmul(x1.to(torch.int32), x2.to(torch.int32))
+        # computed in floatx and cast back to bool (keras/src/backend/torch/numpy.py matmul)
+        f = to_torch_dtype(config.floatx())
+        return torch.matmul(x1.to(f), x2.to(f)).to(torch.bool)
     from keras_b200.kernels import dispatch
 
     out = dispatch.matmul(x1, x2)
@@ -883,30 +957,43 @@ def matmul(x1, x2):
 
 
 @op("numpy")
+def _float_product(x1, x2, body):
+    """dot / inner / vdot: operands promoted by ``result_type``, the product formed in a float type and cast back to that
+    dtype (keras/src/backend/torch/numpy.py dot, inner, vdot: integer and bool operands give integer and bool results)."""
+    x1, x2 = _pair_strict(x1, x2)
+    out = x1.dtype
+    compute = to_torch_dtype(result_type(_dt(x1), float))
+    if compute == torch.float16 and not x1.is_cuda:
+        compute = torch.float32
+    r = body(x1.to(compute), x2.to(compute))
+    return r if r.dtype == out else r.to(out)
+
+
+@op("numpy")
 def dot(x1, x2):
-    x1, x2 = _pair(x1, x2)
-    if x1.ndim == 0 or x2.ndim == 0:
-        return x1 * x2
-    if x2.ndim <= 2:
-        return torch.matmul(x1, x2)
-    return torch.tensordot(x1, x2, dims=([-1], [-2]))
+    def body(a, b):
+        if a.ndim == 0 or b.ndim == 0:
+            return a * b
+        if b.ndim <= 2:
+            return torch.matmul(a, b)
+        return torch.tensordot(a, b, dims=([-1], [-2]))
+
+    return _float_product(x1, x2, body)
 
 
 @op("numpy")
 def vdot(x1, x2):
-    x1, x2 = _pair(x1, x2)
-    return torch.vdot(x1.flatten(), x2.flatten())
+    return _float_product(x1, x2, lambda a, b: torch.vdot(a.flatten(), b.flatten()))
 
 
 @op("numpy")
 def inner(x1, x2):
-    x1, x2 = _pair(x1, x2)
-    return torch.inner(x1, x2)
+    return _float_product(x1, x2, torch.inner)
 
 
 @op("numpy")
 def outer(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.outer(x1.flatten(), x2.flatten())
 
 
@@ -937,13 +1024,13 @@ def einsum(subscripts, *operands, **kwargs):
 
 @op("numpy")
 def kron(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.kron(x1, x2)
 
 
 @op("numpy")
 def cross(x1, x2, axisa=-1, axisb=-1, axisc=-1, axis=None):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_strict(x1, x2)
     if axis is not None:
         axisa = axisb = axisc = axis
     a = torch.movedim(x1, axisa, -1)
@@ -1350,7 +1437,7 @@ def column_stack(xs):
 
 @op("numpy")
 def append(x1, x2, axis=None):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     if axis is None:
         return torch.cat([x1.flatten(), x2.flatten()])
     return torch.cat([x1, x2], dim=axis)
@@ -1538,7 +1625,7 @@ def where(condition, x1=None, x2=None):
         return torch.where(condition)
     if x1 is None or x2 is None:
         raise ValueError("`x1` and `x2` either both should be `None` or both should have non-None value.")
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
     return torch.where(condition, x1, x2)
 
 

@@ -246,3 +246,66 @@ def test_op_case_matches_reference(name):
         pytest.skip("op absent from this reference version")
     tol = TOLERANCE.get(name, 2e-5)
     oracle.assert_same(fn(keras.ops), expected, name, rtol=tol, atol=tol)
+
+
+_SWEEP_DTYPES = ["bool", "int8", "uint8", "int32", "int64", "float16", "bfloat16", "float32", "float64"]
+_SWEEP_UNARY = ["abs", "arccos", "arcsinh", "arctan", "ceil", "cos", "exp", "expm1", "floor", "log", "log1p", "negative", "sign", "sin", "sqrt", "square", "tanh", "mean", "sum", "prod",
+                "max", "min", "std", "var", "cumsum", "cumprod", "argmax", "sort", "argsort", "flip", "transpose", "round", "trunc", "isfinite", "logical_not", "count_nonzero", "median",
+                "diag", "trace", "tril", "reciprocal", "real", "ones_like", "any", "all", "average", "exp2", "cbrt", "rsqrt", "erf", "logsumexp", "relu", "sigmoid", "deg2rad", "rad2deg",
+                "bitwise_not", "signbit", "amax", "ptp"]
+_SWEEP_BINARY = ["add", "subtract", "multiply", "divide", "floor_divide", "mod", "power", "maximum", "minimum", "equal", "greater", "logical_and", "arctan2", "hypot", "matmul", "dot",
+                 "outer", "inner", "kron", "cross", "where", "append", "logaddexp", "bitwise_and", "bitwise_xor", "left_shift", "isclose", "heaviside", "gcd", "lcm", "copysign",
+                 "tensordot", "vdot"]
+
+
+def test_output_dtypes_follow_the_reference_for_every_input_dtype():
+    """Result dtype of unary and binary ops over all input dtype (pairs), 64-bit ones included: wherever the reference gives a
+    result, this framework gives the same dtype (the reference's torch backend promotes some ops by torch's rule and others
+    by ``result_type``)."""
+    rk = oracle.ref()
+
+    def operand(k, dtype, shape):
+        base = (np.arange(1, 1 + int(np.prod(shape))).reshape(shape) % 5 + 1).astype("float32")
+        return k.ops.cast(k.ops.convert_to_tensor(base), dtype)
+
+    def dtype_of(k, fn):
+        try:
+            out = fn()
+        except Exception:
+            return None
+        if isinstance(out, (list, tuple)):
+            out = out[0]
+        return k.backend.standardize_dtype(out.dtype)
+
+    wrong = []
+    for name in _SWEEP_UNARY:
+        shape = (3, 3) if name in ("diag", "trace", "tril") else (3, 4)
+        for dtype in _SWEEP_DTYPES:
+            expected = dtype_of(rk, lambda: getattr(rk.ops, name)(operand(rk, dtype, shape)))
+            if expected is None:
+                continue
+            got = dtype_of(keras, lambda: getattr(keras.ops, name)(operand(keras, dtype, shape)))
+            if got != expected:
+                wrong.append((name, dtype, expected, got))
+    for name in _SWEEP_BINARY:
+        for d1 in _SWEEP_DTYPES:
+            for d2 in _SWEEP_DTYPES:
+                def call(k):
+                    x, y = operand(k, d1, (3, 4)), operand(k, d2, (3, 4))
+                    if name in ("matmul", "dot", "tensordot"):
+                        y = k.ops.transpose(y)
+                    if name == "cross":
+                        x, y = x[:, :3], y[:, :3]
+                    if name == "where":
+                        return k.ops.where(k.ops.cast(x, "float32") > 2, x, y)
+                    if name in ("outer", "inner", "kron", "vdot"):
+                        x, y = x[0], y[0]
+                    return getattr(k.ops, name)(x, y)
+
+                expected = dtype_of(rk, lambda: call(rk))
+                if expected is None:
+                    continue
+                got = dtype_of(keras, lambda: call(keras))
+                if got != expected:
+                    wrong.append((name, d1, d2, expected, got))
+    assert not wrong, wrong[:40]
