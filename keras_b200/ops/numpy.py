@@ -956,7 +956,6 @@ def matmul(x1, x2):
     return torch.matmul(x1, x2)
 
 
-@op("numpy")
 def _float_product(x1, x2, body):
     """dot / inner / vdot: operands promoted by ``result_type``, the product formed in a float type and cast back to that
     dtype (keras/src/backend/torch/numpy.py dot, inner, vdot: integer and bool operands give integer and bool results)."""
