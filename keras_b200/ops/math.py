@@ -216,9 +216,13 @@ def erfinv(x):
 
 @op()
 def gammainc(a, x):
-    a, x = _floatize(a), _floatize(x)
-    d = to_torch_dtype(result_type(a.dtype, x.dtype))
-    return torch.special.gammainc(a.to(d), x.to(d))
+    from keras_b200.ops.numpy import _pair_converted
+
+    a, x = _pair_converted(a, x, floating=True)
+    out = a.dtype
+    if out in (torch.float16, torch.bfloat16):
+        a, x = a.float(), x.float()
+    return torch.special.gammainc(a, x).to(out)
 
 
 @op()

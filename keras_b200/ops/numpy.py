@@ -38,6 +38,8 @@ def _dt(x):
         return x.value.dtype
     if isinstance(x, _T):
         return x.dtype
+    if isinstance(x, np.generic):
+        return x.dtype  # np.float64 subclasses float, but it carries a dtype: not a weak Python scalar
     if isinstance(x, bool):
         return "bool"
     if isinstance(x, int):
@@ -81,6 +83,18 @@ def _pair_native(x1, x2):
     return a.to(d), b.to(d)
 
 
+def _dt_converted(x):
+    """dtype an operand has once the reference has passed it through ``convert_to_tensor``: a Python int is int32 and a Python
+    float is floatx from then on, no longer a weakly typed scalar."""
+    if isinstance(x, bool):
+        return "bool"
+    if isinstance(x, int) and not isinstance(x, np.generic):
+        return "int32" if -(2 ** 31) <= x < 2 ** 31 else "int64"
+    if isinstance(x, float) and not isinstance(x, np.generic):
+        return config.floatx()
+    return _dt(x)
+
+
 def _pair_strict(x1, x2):
     """Both operands cast to ``result_type`` of their dtypes even when the dtypes are equal: ops that resolve their dtype that
     way in the reference (maximum, minimum, floor_divide, the products) turn int64 into int32 and float64 into float32."""
@@ -90,6 +104,32 @@ def _pair_strict(x1, x2):
         x2 = x2.value
     d = to_torch_dtype(result_type(_dt(x1), _dt(x2)))
     return convert_to_tensor(x1, d), convert_to_tensor(x2, d)
+
+
+def _pair_converted(x1, x2, floating=False):
+    """``result_type`` of the operands' dtypes after conversion to tensors (Python scalars typed, see ``_dt_converted``),
+    optionally lifted to a float type: arctan2, hypot, logaddexp, nextafter, the dot products, cross, tensordot."""
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
+    kinds = (_dt_converted(x1), _dt_converted(x2)) + ((float,) if floating else ())
+    d = to_torch_dtype(result_type(*kinds))
+    return convert_to_tensor(x1, d), convert_to_tensor(x2, d)
+
+
+def _pair_full(x1, x2):
+    """torch's promotion without the scalar rule (0-dim operands count like any other): what concatenation and the outer /
+    Kronecker products apply."""
+    if isinstance(x1, Variable):
+        x1 = x1.value
+    if isinstance(x2, Variable):
+        x2 = x2.value
+    a, b = convert_to_tensor(x1), convert_to_tensor(x2)
+    if a.dtype == b.dtype:
+        return a, b
+    d = torch.promote_types(a.dtype, b.dtype)
+    return a.to(d), b.to(d)
 
 
 def _narrow64(x):
@@ -237,7 +277,9 @@ def mod(x1, x2):
 
 @op("numpy")
 def fmod(x1, x2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_native(x1, x2)
+    if x1.dtype == torch.bool:
+        x1, x2 = x1.to(torch.int32), x2.to(torch.int32)
     return torch.fmod(x1, x2)
 
 
@@ -273,37 +315,37 @@ def fmin(x1, x2):
 
 @op("numpy")
 def arctan2(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    x1, x2 = _pair_converted(x1, x2, floating=True)
     return torch.arctan2(x1, x2)
 
 
 @op("numpy")
 def hypot(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    x1, x2 = _pair_converted(x1, x2, floating=True)
     return torch.hypot(x1, x2)
 
 
 @op("numpy")
 def logaddexp(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    x1, x2 = _pair_converted(x1, x2, floating=True)
     return torch.logaddexp(x1, x2)
 
 
 @op("numpy")
 def logaddexp2(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    x1, x2 = _pair_converted(x1, x2, floating=True)
     return torch.logaddexp2(x1, x2)
 
 
 @op("numpy")
 def nextafter(x1, x2):
-    x1, x2 = _pair_float(x1, x2)
+    x1, x2 = _pair_converted(x1, x2, floating=True)
     return torch.nextafter(x1, x2)
 
 
 @op("numpy")
 def heaviside(x1, x2):
-    x1, x2 = _pair_strict(x1, x2)
+    x1, x2 = _pair_converted(x1, x2)
     if x1.dtype == torch.int64:
         x1, x2 = x1.to(torch.float64), x2.to(torch.float64)
     elif x1.dtype in (torch.int8, torch.int16, torch.int32, torch.uint8):
@@ -374,7 +416,11 @@ def logical_not(x):
 
 
 def _bitwise(name, fn):
+    shift = "shift" in name
+
     def f(x, y):
+        if shift and isinstance(y, int) and not isinstance(y, bool):
+            return fn(_t(x), y)  # the count stays a Python int, as in keras/src/backend/torch/numpy.py bitwise_left_shift
         a, b = _pair_native(x, y)
         return fn(a, b)
 
@@ -959,7 +1005,7 @@ def matmul(x1, x2):
 def _float_product(x1, x2, body):
     """dot / inner / vdot: operands promoted by ``result_type``, the product formed in a float type and cast back to that
     dtype (keras/src/backend/torch/numpy.py dot, inner, vdot: integer and bool operands give integer and bool results)."""
-    x1, x2 = _pair_strict(x1, x2)
+    x1, x2 = _pair_converted(x1, x2)
     out = x1.dtype
     compute = to_torch_dtype(result_type(_dt(x1), float))
     if compute == torch.float16 and not x1.is_cuda:
@@ -992,13 +1038,13 @@ def inner(x1, x2):
 
 @op("numpy")
 def outer(x1, x2):
-    x1, x2 = _pair_native(x1, x2)
+    x1, x2 = _pair_full(x1, x2)
     return torch.outer(x1.flatten(), x2.flatten())
 
 
 @op("numpy")
 def tensordot(x1, x2, axes=2):
-    x1, x2 = _pair(x1, x2)
+    x1, x2 = _pair_converted(x1, x2)
     if isinstance(axes, (list, tuple)):
         a, b = axes
         a = [a] if isinstance(a, int) else list(a)
@@ -1023,13 +1069,13 @@ def einsum(subscripts, *operands, **kwargs):
 
 @op("numpy")
 def kron(x1, x2):
-    x1, x2 = _pair_native(x1, x2)
+    x1, x2 = _pair_full(x1, x2)
     return torch.kron(x1, x2)
 
 
 @op("numpy")
 def cross(x1, x2, axisa=-1, axisb=-1, axisc=-1, axis=None):
-    x1, x2 = _pair_strict(x1, x2)
+    x1, x2 = _pair_converted(x1, x2)
     if axis is not None:
         axisa = axisb = axisc = axis
     a = torch.movedim(x1, axisa, -1)
@@ -1436,7 +1482,7 @@ def column_stack(xs):
 
 @op("numpy")
 def append(x1, x2, axis=None):
-    x1, x2 = _pair_native(x1, x2)
+    x1, x2 = _pair_full(x1, x2)
     if axis is None:
         return torch.cat([x1.flatten(), x2.flatten()])
     return torch.cat([x1, x2], dim=axis)

@@ -309,3 +309,50 @@ def test_output_dtypes_follow_the_reference_for_every_input_dtype():
                 if got != expected:
                     wrong.append((name, d1, d2, expected, got))
     assert not wrong, wrong[:40]
+
+
+def test_scalar_operands_give_the_reference_dtypes_and_values():
+    """Every two-operand op with a Python or NumPy scalar on either side of tensors of several dtypes: some ops of the reference
+    keep a Python scalar weakly typed, others convert it to an int32 / float32 tensor first; results must agree in dtype and
+    value wherever the reference gives one."""
+    import inspect
+
+    rk = oracle.ref()
+    names = []
+    for n in sorted(dir(rk.ops)):
+        f = getattr(rk.ops, n)
+        if n.startswith("_") or not callable(f) or inspect.isclass(f):
+            continue
+        try:
+            ps = list(inspect.signature(f).parameters)
+        except (TypeError, ValueError):
+            continue
+        if len(ps) >= 2 and ps[0] in ("x1", "x", "a") and ps[1] in ("x2", "y"):
+            names.append(n)
+    assert len(names) > 40
+    pairs = [("bfloat16", 2.5), ("float16", 2), ("int8", 3), ("int8", 2.5), ("uint8", 3), ("int32", 2.5), ("float32", 2), ("bool", 2), ("bfloat16", np.float32(2.5)),
+             ("int8", np.int64(3)), ("float16", np.float64(2.5)), ("int64", 2), ("float64", 2.5), ("int32", True)]
+    wrong = []
+    for n in names:
+        for dtype, scalar in pairs:
+            for tensor_first in (True, False):
+                def result(k):
+                    x = k.ops.cast(k.ops.convert_to_tensor(np.array([[1, 2, 3], [2, 3, 1], [1, 1, 2]], "float32")), dtype)
+                    try:
+                        out = getattr(k.ops, n)(x, scalar) if tensor_first else getattr(k.ops, n)(scalar, x)
+                        if isinstance(out, (list, tuple)):
+                            out = out[0]
+                        return k.backend.standardize_dtype(out.dtype), np.asarray(k.ops.convert_to_numpy(k.ops.cast(out, "float64")))
+                    except Exception:
+                        return None
+
+                expected = result(rk)
+                if expected is None:
+                    continue
+                got = result(keras)
+                tag = (n, dtype, repr(scalar), tensor_first)
+                if got is None or got[0] != expected[0]:
+                    wrong.append(tag + (expected[0], None if got is None else got[0]))
+                elif got[1].shape != expected[1].shape or not np.allclose(got[1], expected[1], rtol=3e-2, atol=3e-2, equal_nan=True):
+                    wrong.append(tag + ("value",))
+    assert not wrong, wrong[:40]
