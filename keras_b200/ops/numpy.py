@@ -515,8 +515,14 @@ def clip(x, x_min, x_max):
     x = _t(x)
     if x.dtype == torch.bool:
         x = x.to(torch.int32)
-    lo = x_min.to(x.dtype) if isinstance(x_min, _T) else x_min
-    hi = x_max.to(x.dtype) if isinstance(x_max, _T) else x_max
+    def scalar(b):
+        return b is None or (isinstance(b, (int, float)) and not isinstance(b, np.generic))
+
+    if scalar(x_min) and scalar(x_max):
+        return torch.clip(x, x_min, x_max)
+    # a bound that is an array or a tensor: torch wants both bounds as tensors then
+    lo = None if x_min is None else _t(x_min).to(x.dtype)
+    hi = None if x_max is None else _t(x_max).to(x.dtype)
     return torch.clip(x, lo, hi)
 
 
@@ -1194,7 +1200,7 @@ def full(shape, fill_value, dtype=None):
     shape = (shape,) if isinstance(shape, int) else tuple(shape)
     if isinstance(fill_value, (_T, np.ndarray, Variable)):
         fv = _t(fill_value)
-        d = to_torch_dtype(dtype) if dtype is not None else fv.dtype
+        d = to_torch_dtype(dtype if dtype is not None else config.floatx())  # no dtype: floatx here too, not the array's type
         return torch.broadcast_to(fv.to(d), shape).clone()
     d = to_torch_dtype(dtype if dtype is not None else config.floatx())  # no dtype: floatx, whatever the scalar's type
     return torch.full(shape, fill_value, dtype=d, device=get_device())
