@@ -366,6 +366,13 @@ def _decays(opt, variables):
     return [float(wd) if opt._use_weight_decay(v) else 0.0 for v in variables]
 
 
+def _consumes_gradients(opt):
+    """True while the caller of ``apply`` is this package's training step, whose gradients live in its own persistent storage:
+    the update kernel then zeroes them as it reads them.  Gradients handed to ``optimizer.apply`` by user code are left as they
+    are (a custom loop may log or reuse them afterwards)."""
+    return bool(getattr(opt, "_gradients_are_step_storage", False))
+
+
 def _device_scalars(opt):
     """(learning-rate tensor, iteration tensor) when both live on the device in the types the kernels read: the update
     then takes its step scalars from device memory and a captured replay of it stays correct as they change."""
@@ -389,8 +396,8 @@ def fused_sgd(opt, grads, variables, lr):
         plan.set_decays(d)
     scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
     lr_t, _ = _device_scalars(opt)
-    plan.sgd(lr, opt.momentum, opt.nesterov, grad_scale=scale, zero_grad=True, lr_tensor=lr_t)
-    opt._fused_zeroed_grads = True
+    plan.sgd(lr, opt.momentum, opt.nesterov, grad_scale=scale, zero_grad=_consumes_gradients(opt), lr_tensor=lr_t)
+    opt._fused_zeroed_grads = _consumes_gradients(opt)
     opt._step_scalars_on_device = lr_t is not None
     return True
 
@@ -407,10 +414,10 @@ def fused_adam(opt, grads, variables, lr):
     scale = 1.0 / opt.loss_scale_factor if opt.loss_scale_factor else 1.0
     lr_t, step_t = _device_scalars(opt)
     if lr_t is not None:
-        plan.adam(0.0, opt.beta_1, opt.beta_2, opt.epsilon, grad_scale=scale, zero_grad=True, lr_tensor=lr_t, step_tensor=step_t)
+        plan.adam(0.0, opt.beta_1, opt.beta_2, opt.epsilon, grad_scale=scale, zero_grad=_consumes_gradients(opt), lr_tensor=lr_t, step_tensor=step_t)
     else:
-        plan.adam(opt._alpha(lr), opt.beta_1, opt.beta_2, opt.epsilon, lr=lr, grad_scale=scale, zero_grad=True)
-    opt._fused_zeroed_grads = True
+        plan.adam(opt._alpha(lr), opt.beta_1, opt.beta_2, opt.epsilon, lr=lr, grad_scale=scale, zero_grad=_consumes_gradients(opt))
+    opt._fused_zeroed_grads = _consumes_gradients(opt)
     opt._step_scalars_on_device = lr_t is not None
     return True
 
@@ -432,8 +439,8 @@ def fused_rule(opt, grads, variables, lr, name, slot_lists, consts, step_scalars
     lr_t, step_t = _device_scalars(opt)
     if u_product is not None and not (u_product.is_cuda and u_product.dtype == torch.float32 and u_product.numel() == 1):
         step_t = None
-    plan.rule(name, lr, consts, step_scalars, beta1=beta1, beta2=beta2, flags=flags, grad_scale=scale, zero_grad=True, lr_tensor=lr_t,
+    plan.rule(name, lr, consts, step_scalars, beta1=beta1, beta2=beta2, flags=flags, grad_scale=scale, zero_grad=_consumes_gradients(opt), lr_tensor=lr_t,
               step_tensor=step_t if needs_step else None, u_product=u_product if (needs_step and step_t is not None) else None)
-    opt._fused_zeroed_grads = True
+    opt._fused_zeroed_grads = _consumes_gradients(opt)
     opt._step_scalars_on_device = lr_t is not None and (not needs_step or step_t is not None)
     return True

@@ -141,7 +141,11 @@ class DataParallelEngine:
                 arena.flat.div_(self.world)
         grads = arena.gradients()
         opt._fused_zeroed_grads = False
-        opt.apply(grads, trainable_weights)
+        opt._gradients_are_step_storage = True  # the arena is this engine's: the update may zero what it consumes
+        try:
+            opt.apply(grads, trainable_weights)
+        finally:
+            opt._gradients_are_step_storage = False
         if not opt._fused_zeroed_grads:
             arena.zero()
         self._steps += 1

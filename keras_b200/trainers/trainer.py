@@ -299,7 +299,11 @@ class Trainer:
                     grads = arena.gradients()
                 opt = self.optimizer
                 opt._fused_zeroed_grads = False
-                opt.apply(grads, trainable_weights)
+                opt._gradients_are_step_storage = arena is not None  # the update may zero what it consumes
+                try:
+                    opt.apply(grads, trainable_weights)
+                finally:
+                    opt._gradients_are_step_storage = False
                 if arena is None:
                     for p in params:
                         p.grad = None
