@@ -33,3 +33,26 @@ def test_namespaces_and_preprocessing():
     assert keras.applications.mobilenet_v3.preprocess_input(x) is x
     with pytest.raises(ValueError):
         keras.applications.VGG16(weights="imagenet")
+
+
+@pytest.mark.parametrize("name,size,kwargs", [("MobileNetV2", 64, dict(alpha=0.35)), ("EfficientNetB0", 64, {}), ("ConvNeXtTiny", 64, {}), ("DenseNet121", 64, {}),
+                                              ("Xception", 96, {}), ("NASNetMobile", 64, {})])
+def test_application_outputs_match_reference_with_transferred_weights(name, size, kwargs):
+    """Same constructor, the reference's (perturbed) weights through get_weights / set_weights, same input: the predictions agree,
+    which exercises every layer type of the family in place (depthwise convolutions, squeeze-excite, layer scale, ...)."""
+    import torch
+
+    from tests import oracle
+
+    rk = oracle.ref()
+    rng = np.random.default_rng(0)
+    theirs = getattr(rk.applications, name)(weights=None, input_shape=(size, size, 3), classes=10, **kwargs)
+    ours = getattr(keras.applications, name)(weights=None, input_shape=(size, size, 3), classes=10, **kwargs)
+    weights = [w + rng.normal(size=w.shape).astype(w.dtype) * 0.02 if w.dtype.kind == "f" else w for w in theirs.get_weights()]
+    weights = [np.abs(w) + 0.5 if "variance" in v.path else w for w, v in zip(weights, theirs.weights)]
+    theirs.set_weights(weights)
+    ours.set_weights(weights)
+    x = torch.tensor(rng.random((2, size, size, 3)).astype("float32") * 255)
+    expected = theirs(x, training=False).detach().numpy()
+    got = ours(x, training=False).detach().numpy()
+    np.testing.assert_allclose(got, expected, rtol=1e-4, atol=2e-6)
