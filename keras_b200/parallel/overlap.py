@@ -23,6 +23,26 @@ def enabled():
     return os.environ.get("KERAS_B200_DP_OVERLAP", "1") != "0"
 
 
+def plan_buckets(offsets, total, target_bytes, max_buckets):
+    """Cut a flat fp32 arena of ``total`` elements into contiguous buckets at variable boundaries.
+
+    ``offsets``: variable index -> first element of that variable in the arena.  Returns ``(buckets, bucket_of)``: the
+    ``(offset, numel)`` ranges in arena order (which is the order in which backward completes them) and, per variable, the
+    index of its bucket.  About ``target_bytes`` each, at most ``max_buckets``; a variable is never split."""
+    order = sorted(offsets, key=lambda i: offsets[i])
+    n = max(1, min(max_buckets, (total * 4 + target_bytes - 1) // target_bytes))
+    per = (total + n - 1) // n
+    buckets, bucket_of = [], {}
+    start = 0
+    for pos, i in enumerate(order):
+        end = offsets[order[pos + 1]] if pos + 1 < len(order) else total
+        bucket_of[i] = len(buckets)
+        if end - start >= per or pos + 1 == len(order):
+            buckets.append((start, end - start))
+            start = end
+    return buckets, [bucket_of[i] for i in range(len(order))]
+
+
 class GradientOverlap:
     def __init__(self, arena, reducer, world, target_bytes=None, max_buckets=8):
         if target_bytes is None:
@@ -48,21 +68,7 @@ class GradientOverlap:
         self._hooks = []
 
     def _make_buckets(self, target_bytes, max_buckets):
-        """Contiguous arena ranges [(offset, numel)] cut at variable boundaries, and the bucket of every variable."""
-        arena = self.arena
-        order = sorted(range(len(arena.variables)), key=lambda i: arena.offsets[i])  # arena order = backward order
-        total = arena.total
-        n = max(1, min(max_buckets, (total * 4 + target_bytes - 1) // target_bytes))
-        per = (total + n - 1) // n
-        buckets, bucket_of = [], [0] * len(order)
-        start = 0
-        for pos, i in enumerate(order):
-            end = arena.offsets[order[pos + 1]] if pos + 1 < len(order) else total
-            bucket_of[i] = len(buckets)
-            if end - start >= per or pos + 1 == len(order):
-                buckets.append((start, end - start))
-                start = end
-        return buckets, bucket_of
+        return plan_buckets(self.arena.offsets, self.arena.total, target_bytes, max_buckets)
 
     # -- events ---------------------------------------------------------------------------------------------------------
     def _accumulated(self, param):

@@ -454,3 +454,23 @@ def test_failure_detection_aborts_fit_and_backup_restores_the_epoch():
         assert codes == [0, 0], codes
         assert str(out[0]["outcome"]) == "finished"
         assert list(out[0]["epochs"])[0] >= 2 and list(out[0]["epochs"])[-1] == 3, out[0]["epochs"]
+
+
+def test_gradient_buckets_cover_the_arena_in_backward_order():
+    """Buckets of the overlapped data-parallel reduction: contiguous, at variable boundaries, in arena order, nothing left out."""
+    from keras_b200.parallel.overlap import plan_buckets
+
+    sizes = [32, 320, 64, 4096, 64, 64, 64, 2048]          # arena order (last layer first)
+    offsets, at = {}, 0
+    for position, size in enumerate(sizes):
+        offsets[len(sizes) - 1 - position] = at            # variable indices run in creation order: the reverse
+        at += size
+    buckets, bucket_of = plan_buckets(offsets, at, target_bytes=4096, max_buckets=8)
+    assert buckets[0][0] == 0 and sum(n for _, n in buckets) == at
+    assert all(buckets[i][0] + buckets[i][1] == buckets[i + 1][0] for i in range(len(buckets) - 1))
+    starts = {start for start, _ in buckets}
+    assert starts <= set(offsets.values())                 # cut at variable boundaries only
+    assert bucket_of == sorted(bucket_of, reverse=True)    # later variables (earlier in backward) sit in earlier buckets
+    assert 2 <= len(buckets) <= 8
+    one, _ = plan_buckets(offsets, at, target_bytes=1 << 30, max_buckets=8)
+    assert one == [(0, at)]
