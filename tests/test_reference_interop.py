@@ -122,3 +122,62 @@ def test_unknown_modules_are_never_imported(tmp_path):
             keras.saving.deserialize_keras_object({"module": "keras_b200.saving.hdf5", "class_name": "File", "config": {}, "registered_name": "File"})
     finally:
         sys.path.remove(str(tmp_path))
+
+
+CHILD_SAVE = textwrap.dedent(
+    """
+    import os, sys, json
+    import numpy as np
+    sys.path.insert(0, {repo!r})
+    from keras_b200.saving import h5py_compat
+    h5py_compat.install()
+    sys.path.append({ref!r})
+    import keras
+    assert keras.__file__.startswith({ref!r}), keras.__file__
+    keras.utils.set_random_seed(5)
+    rng = np.random.default_rng(0)
+    if {kind!r} == "sequence":
+        i = keras.Input((12, 6)); h = keras.layers.Bidirectional(keras.layers.LSTM(5, return_sequences=True))(i)
+        h = keras.layers.MultiHeadAttention(2, 4)(h, h); h = keras.layers.LayerNormalization()(h)
+        model = keras.Model(i, keras.layers.Dense(3, activation="softmax")(keras.layers.GlobalAveragePooling1D()(h)))
+        x, y = rng.normal(size=(8, 12, 6)).astype("float32"), rng.integers(0, 3, (8,))
+        model.compile(optimizer=keras.optimizers.Adam(1e-2), loss="sparse_categorical_crossentropy")
+    else:
+        i = keras.Input((16, 16, 3)); h = keras.layers.Conv2D(8, 3, padding="same")(i); h = keras.layers.BatchNormalization()(h); h = keras.layers.ReLU()(h)
+        h = keras.layers.DepthwiseConv2D(3)(h); h = keras.layers.SeparableConv2D(6, 3)(h); h = keras.layers.GroupNormalization(2)(h)
+        h = keras.layers.Conv2DTranspose(4, 3, strides=2, padding="same")(h); h = keras.layers.PReLU()(h)
+        model = keras.Model(i, keras.layers.Dense(2)(keras.layers.Flatten()(keras.layers.MaxPooling2D()(h))))
+        x, y = rng.normal(size=(8, 16, 16, 3)).astype("float32"), rng.normal(size=(8, 2)).astype("float32")
+        model.compile(optimizer=keras.optimizers.SGD(1e-2, momentum=0.9), loss="mse")
+    model.fit(x, y, batch_size=4, epochs=1, verbose=0)
+    model.save({path!r})
+    model.save_weights({wpath!r})
+    np.save({x!r}, x)
+    np.save({y!r}, model.predict(x, verbose=0))
+    print("RESULT " + json.dumps({{"weights": len(model.weights), "iterations": int(model.optimizer.iterations.numpy())}}))
+    """
+)
+
+
+@pytest.mark.parametrize("kind", ["sequence", "vision"])
+def test_archives_written_by_the_reference_load_here(kind, tmp_path):
+    """The reverse direction: the reference's own saver decides the layout of the archive (its ``h5py`` calls are served by this
+    package's HDF5 writer, since no h5py is installed); this framework loads the ``.keras`` file and the ``.weights.h5`` file and
+    predicts the same."""
+    oracle.ref()
+    path, wpath = str(tmp_path / f"{kind}.keras"), str(tmp_path / f"{kind}.weights.h5")
+    script = CHILD_SAVE.format(repo=REPO, ref=oracle.reference_path(), kind=kind, path=path, wpath=wpath, x=str(tmp_path / "x.npy"), y=str(tmp_path / "y.npy"))
+    env = dict(os.environ, KERAS_BACKEND="torch", KERAS_HOME=str(tmp_path / "home"), KERAS_TORCH_DEVICE="cpu", PYTHONPATH="")
+    proc = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    result = json.loads([l for l in proc.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    x, want = np.load(tmp_path / "x.npy"), np.load(tmp_path / "y.npy")
+    model = keras.saving.load_model(path)
+    np.testing.assert_allclose(model.predict(x, verbose=0), want, rtol=1e-4, atol=1e-5)
+    assert len(model.weights) == result["weights"]
+    assert int(model.optimizer.iterations) == result["iterations"] == 2
+    # weights only, into a freshly initialised copy of the architecture
+    fresh = keras.Model.from_config(model.get_config())
+    assert not np.allclose(fresh.predict(x, verbose=0), want, atol=1e-3)
+    fresh.load_weights(wpath)
+    np.testing.assert_allclose(fresh.predict(x, verbose=0), want, rtol=1e-4, atol=1e-5)
