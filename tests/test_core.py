@@ -78,3 +78,30 @@ def test_kernel_front_ends_import_without_gpu():
 
     for name in ("gemm", "ops", "dispatch", "conv", "attention", "microbench", "build", "loader"):
         importlib.import_module(f"keras_b200.kernels.{name}")
+
+
+def test_convolution_tiling_choices_without_a_gpu():
+    """The host-side planning of the tcgen05 convolution (which pixel tile, whether vertical taps share one TMA box) is plain
+    C++ and can be asked without a device: the ResNet-50 3x3 layers with 64 and 128 channels share rows, the others do not."""
+    import ctypes
+    import os
+
+    import keras_b200
+
+    path = os.path.join(os.path.dirname(keras_b200.__file__), "kernels", "libkb200.so")
+    if not os.path.exists(path):
+        pytest.skip("kernel library not built")
+    lib = ctypes.CDLL(path)
+    shares = lib.kb200_conv_igemm_shares_rows
+    assert shares(256, 56, 56, 64, 64, 3, 3, 1) == 1 and shares(256, 56, 56, 64, 64, 3, 3, -1) == 1
+    assert shares(256, 28, 28, 128, 128, 3, 3, 1) == 1
+    assert shares(256, 14, 14, 256, 256, 3, 3, 1) == 0      # would need a quarter more tiles
+    assert shares(256, 7, 7, 512, 512, 3, 3, 1) == 0
+    assert shares(256, 56, 56, 64, 256, 1, 1, 0) == 0       # nothing to share in a 1x1 filter
+    assert shares(2, 20, 20, 64, 64, 3, 3, 2) == 0          # dilated rows are not adjacent
+    plan = (ctypes.c_int * 3)()
+    assert lib.kb200_conv_igemm_plan(256, 56, 56, 64, 64, 3, 3, 1, plan) == 0
+    grid, n_tiles, bn = plan[0], plan[1], plan[2]
+    assert bn == 64 and n_tiles == 1 and 0 < grid <= 148
+    assert lib.kb200_conv_igemm_plan(256, 14, 14, 256, 1024, 1, 1, 0, plan) == 0
+    assert plan[2] == 256 and plan[1] == 4 and plan[0] % 4 == 0
