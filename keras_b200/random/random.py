@@ -121,10 +121,14 @@ def dropout(inputs, rate, noise_shape=None, seed=None):
 
 @keras_export("keras.random.shuffle")
 def shuffle(x, axis=0, seed=None):
+    # Ranks of uniform draws, as keras/src/backend/torch/random.py:177-203 does it: the same seed gives the same order, and
+    # for axis > 0 every leading index gets its own permutation.
     x = convert_to_tensor(x)
+    axis = axis % x.ndim
     g = _generator(seed, x.device)
-    perm = torch.randperm(x.shape[axis], generator=g, device=x.device)
-    return torch.index_select(x, axis, perm)
+    order = torch.rand(tuple(x.shape[: axis + 1]), generator=g, device=x.device).argsort(axis)
+    order = order.reshape(tuple(order.shape) + (1,) * (x.ndim - axis - 1)).expand(x.shape)
+    return torch.gather(x, axis, order)
 
 
 @keras_export("keras.random.gamma")

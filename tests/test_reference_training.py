@@ -288,3 +288,11 @@ def test_multi_output_fit_evaluate_match_reference_keys_and_values():
                 np.testing.assert_allclose(a[key], b[key], rtol=3e-4, atol=3e-5, err_msg=key)
         else:
             np.testing.assert_allclose(a, b, rtol=3e-4, atol=3e-5)
+
+
+def test_random_shuffle_orders_like_the_reference():
+    rk = oracle.ref()
+    x = np.arange(24).reshape(4, 3, 2)
+    for seed in (0, 7):
+        for axis in (0, 1, -1):
+            np.testing.assert_array_equal(keras.random.shuffle(x, axis=axis, seed=seed).numpy(), rk.random.shuffle(x, axis=axis, seed=seed).numpy())
