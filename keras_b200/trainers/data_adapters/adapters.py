@@ -116,29 +116,29 @@ class ArrayDataAdapter(DataAdapter):
             self._shard_id = dist.data_shard_id if hasattr(dist, "data_shard_id") else 0
 
     def _batch_indices(self):
+        """Index sets of one pass.  The order is a function of the epoch number alone, drawn as the reference draws it
+        (keras/src/trainers/data_adapters/array_data_adapter.py:308-343: a ``torch.Generator`` seeded with the epoch, one
+        ``randperm`` over the samples, or one per batch for ``shuffle="batch"``), so every process of a data-parallel job
+        sees the same order without talking and a run can be repeated."""
         n, bs = self._num_samples, self._batch_size
+        if not self._shuffle:
+            return [slice(i, min(i + bs, n)) for i in range(0, n, bs)]
+        gen = torch.Generator()
+        gen.manual_seed(int(self._epoch))
         if self._shuffle == "batch":
-            rng = np.random.default_rng(self._epoch_seed())
-            batches = [np.arange(i, min(i + bs, n)) for i in range(0, n, bs)]
-            out = []
-            for b in batches:
-                rng.shuffle(b)
-                out.append(b)
-            return out
-        if self._shuffle:
-            perm = np.random.default_rng(self._epoch_seed()).permutation(n)
-            return [np.sort(perm[i:i + bs]) if False else perm[i:i + bs] for i in range(0, n, bs)]
-        return [slice(i, min(i + bs, n)) for i in range(0, n, bs)]
+            # a shard keeps every num_shards-th batch first and draws only for those, one draw after the other
+            starts = list(range(0, n, bs))[self._shard_id::self._num_shards]
+            return [i + torch.randperm(min(bs, n - i), generator=gen).numpy() for i in starts]
+        perm = torch.randperm(n, generator=gen).numpy()
+        return [perm[i:i + bs] for i in range(0, n, bs)]
 
-    def _epoch_seed(self):
-        if not hasattr(self, "_base_seed"):
-            self._base_seed = random.randint(0, 2**31 - 1)
-        return self._base_seed + self._epoch
+    def on_epoch_end(self):
+        self._epoch += 1
 
     def get_numpy_iterator(self):
         flat = tree.flatten(self._inputs)
         batches = self._batch_indices()
-        if self._num_shards > 1:
+        if self._num_shards > 1 and self._shuffle != "batch":
             batches = batches[self._shard_id::self._num_shards]
 
         def take(a, idx):
@@ -152,7 +152,6 @@ class ArrayDataAdapter(DataAdapter):
 
         for idx in batches:
             yield tree.pack_sequence_as(self._inputs, [take(a, idx) for a in flat])
-        self._epoch += 1
 
     @property
     def num_batches(self):

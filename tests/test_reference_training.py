@@ -171,7 +171,8 @@ def _small_convnet(k):
         k.layers.GlobalAveragePooling2D(), k.layers.Dropout(0.25, seed=3), k.layers.Dense(5, activation="softmax")])
 
 
-@pytest.mark.parametrize("options", [dict(), dict(steps_per_execution=2), dict(gradient_accumulation_steps=2)], ids=["plain", "steps_per_execution", "accumulation"])
+@pytest.mark.parametrize("options", [dict(), dict(steps_per_execution=2), dict(gradient_accumulation_steps=2), dict(shuffle=True), dict(shuffle="batch")],
+                         ids=["plain", "steps_per_execution", "accumulation", "shuffled", "shuffled_in_batches"])
 def test_fit_history_matches_reference(options):
     rk = oracle.ref()
     rng = np.random.default_rng(4)
@@ -185,7 +186,7 @@ def test_fit_history_matches_reference(options):
     for k, model in ((rk, theirs), (keras, ours)):
         opt = k.optimizers.Adam(1e-2, gradient_accumulation_steps=accumulation) if accumulation else k.optimizers.Adam(1e-2)
         model.compile(optimizer=opt, loss="sparse_categorical_crossentropy", metrics=["accuracy"], steps_per_execution=spe)
-        h = model.fit(x, y, batch_size=16, epochs=2, shuffle=False, verbose=0, validation_split=0.25)
+        h = model.fit(x, y, batch_size=16, epochs=3 if options.get("shuffle") else 2, shuffle=options.get("shuffle", False), verbose=0, validation_split=0.25)
         histories.append(h.history)
     for key in histories[0]:
         np.testing.assert_allclose(histories[1][key], histories[0][key], rtol=2e-3, atol=2e-4, err_msg=key)
