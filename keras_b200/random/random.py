@@ -41,12 +41,11 @@ def normal(shape, mean=0.0, stddev=1.0, dtype=None, seed=None):
     td = to_torch_dtype(dtype or config.floatx())
     dev = get_device()
     g = _generator(seed, dev)
-    out = torch.randn(_shape(shape), generator=g, dtype=td if td != torch.bfloat16 or dev.type != "cpu" else td, device=dev)
-    if stddev != 1.0:
-        out = out * stddev
-    if mean != 0.0:
-        out = out + mean
-    return out
+    if isinstance(mean, (int, float)) and isinstance(stddev, (int, float)):
+        # one kernel that scales and shifts before it rounds to the output type (keras/src/backend/torch/random.py:31-47)
+        return torch.normal(float(mean), float(stddev), size=_shape(shape), generator=g, dtype=td, device=dev)
+    out = torch.randn(_shape(shape), generator=g, dtype=td, device=dev)
+    return out * stddev + mean
 
 
 @keras_export("keras.random.uniform")

@@ -297,3 +297,59 @@ def test_random_shuffle_orders_like_the_reference():
     for seed in (0, 7):
         for axis in (0, 1, -1):
             np.testing.assert_array_equal(keras.random.shuffle(x, axis=axis, seed=seed).numpy(), rk.random.shuffle(x, axis=axis, seed=seed).numpy())
+
+
+INITIALIZERS = ["GlorotUniform", "GlorotNormal", "HeUniform", "HeNormal", "LecunUniform", "LecunNormal", "RandomNormal", "RandomUniform", "TruncatedNormal", "Orthogonal",
+                "VarianceScaling"]
+
+
+@pytest.mark.parametrize("name", INITIALIZERS)
+def test_seeded_initializers_draw_the_reference_values(name):
+    rk = oracle.ref()
+    for shape in [(6, 6), (3, 3, 4, 8)]:
+        for dtype in ("float32", "float16"):
+            if name == "Orthogonal" and dtype == "float16":
+                continue  # no half-precision QR on the CPU
+            theirs = getattr(rk.initializers, name)(seed=7)(shape, dtype=dtype)
+            ours = getattr(keras.initializers, name)(seed=7)(shape, dtype=dtype)
+            oracle.assert_same(ours, theirs, f"{name} {shape} {dtype}")
+    again = getattr(keras.initializers, name)(seed=7)
+    oracle.assert_same(again((4, 4)), again((4, 4)), "an integer seed gives the same values at every call")
+
+
+def test_fixed_initializers_regularizers_and_constraints_match_reference():
+    rk = oracle.ref()
+    w = np.random.default_rng(0).normal(size=(4, 5, 3)).astype("float32")
+    for make in (lambda k: k.initializers.Identity(gain=2.0)((5, 5)), lambda k: k.initializers.Constant(2.5)((3, 2)),
+                 lambda k: k.initializers.STFT(side="real", window="hann")((16, 1, 9)),
+                 lambda k: k.initializers.VarianceScaling(2.0, "fan_out", "untruncated_normal", seed=3)((5, 7)),
+                 lambda k: k.initializers.Orthogonal(gain=2.0, seed=1)((4, 10)),
+                 lambda k: k.regularizers.L1L2(l1=0.1, l2=0.2)(torch.tensor(w)),
+                 lambda k: k.regularizers.OrthogonalRegularizer(factor=0.1, mode="rows")(torch.tensor(w[0])),
+                 lambda k: k.regularizers.OrthogonalRegularizer(factor=0.1, mode="columns")(torch.tensor(w[0])),
+                 lambda k: k.constraints.MaxNorm(max_value=1.0, axis=0)(torch.tensor(w)),
+                 lambda k: k.constraints.MinMaxNorm(min_value=0.5, max_value=1.0, rate=0.7, axis=[0, 1])(torch.tensor(w)),
+                 lambda k: k.constraints.NonNeg()(torch.tensor(w)), lambda k: k.constraints.UnitNorm(axis=1)(torch.tensor(w))):
+        oracle.assert_same(make(keras), make(rk), "fixed initializer, regularizer or constraint", rtol=1e-5, atol=1e-6)
+
+
+SCHEDULES = [
+    ("ExponentialDecay", dict(initial_learning_rate=0.1, decay_steps=10, decay_rate=0.5)),
+    ("ExponentialDecay", dict(initial_learning_rate=0.1, decay_steps=10, decay_rate=0.5, staircase=True)),
+    ("PiecewiseConstantDecay", dict(boundaries=[5, 10], values=[1.0, 0.5, 0.1])),
+    ("PolynomialDecay", dict(initial_learning_rate=0.1, decay_steps=20, end_learning_rate=0.01, power=2.0)),
+    ("PolynomialDecay", dict(initial_learning_rate=0.1, decay_steps=7, end_learning_rate=0.01, power=0.5, cycle=True)),
+    ("InverseTimeDecay", dict(initial_learning_rate=0.1, decay_steps=5, decay_rate=0.5, staircase=True)),
+    ("CosineDecay", dict(initial_learning_rate=0.0, decay_steps=20, alpha=0.1, warmup_target=0.2, warmup_steps=5)),
+    ("CosineDecayRestarts", dict(initial_learning_rate=0.1, first_decay_steps=5, t_mul=2.0, m_mul=0.9, alpha=0.05)),
+]
+
+
+@pytest.mark.parametrize("spec", SCHEDULES, ids=[f"{n}_{i}" for i, (n, _) in enumerate(SCHEDULES)])
+def test_learning_rate_schedules_match_reference(spec):
+    rk = oracle.ref()
+    name, kwargs = spec
+    theirs, ours = getattr(rk.optimizers.schedules, name)(**kwargs), getattr(keras.optimizers.schedules, name)(**kwargs)
+    assert sorted(ours.get_config()) == sorted(theirs.get_config())
+    for step in range(30):
+        np.testing.assert_allclose(float(oracle.to_np(ours(step))), float(oracle.to_np(theirs(step))), rtol=1e-6, err_msg=f"{name} at step {step}")
