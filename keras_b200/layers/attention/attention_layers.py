@@ -206,6 +206,21 @@ class MultiHeadAttention(Layer):
              training=None, use_causal_mask=False):
         if key is None:
             key = value
+        # The masks are handled here, at the level of the layer: the projections below see plain tensors
+        # (keras/src/layers/attention/multi_head_attention.py:626-631).  Unlike there, an explicit ``query_mask`` is
+        # honoured and the inputs get their masks back afterwards, so another consumer of the same tensor still sees them.
+        carried = [(t, t._keras_mask) for t in {id(t): t for t in (query, value, key)}.values() if getattr(t, "_keras_mask", None) is not None]
+        if query_mask is None:
+            query_mask = getattr(query, "_keras_mask", None)
+        for t, _ in carried:
+            t._keras_mask = None
+        try:
+            return self._attend(query, value, key, query_mask, value_mask, key_mask, attention_mask, return_attention_scores, training, use_causal_mask)
+        finally:
+            for t, m in carried:
+                t._keras_mask = m
+
+    def _attend(self, query, value, key, query_mask, value_mask, key_mask, attention_mask, return_attention_scores, training, use_causal_mask):
         causal_only = (use_causal_mask and query_mask is None and value_mask is None and key_mask is None and attention_mask is None
                        and self._sliding_window is None and type(self)._compute_attention is MultiHeadAttention._compute_attention)
         if causal_only:

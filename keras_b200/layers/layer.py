@@ -98,7 +98,7 @@ class _CallPlan:
 
     _tree_rebuild_as_dict = True
 
-    __slots__ = ("arg_names", "has_training", "has_mask", "has_var_kw", "build_names", "build_by_name", "signature", "context_args", "n_positional")
+    __slots__ = ("arg_names", "has_training", "has_mask", "has_var_kw", "build_names", "build_by_name", "signature", "context_args", "n_positional", "mask_pairs")
 
     def __init__(self, cls):
         sig = inspect.signature(cls.call)
@@ -109,6 +109,7 @@ class _CallPlan:
         self.has_var_kw = any(p.kind == p.VAR_KEYWORD for p in params)
         self.has_training = "training" in self.arg_names
         self.has_mask = "mask" in self.arg_names
+        self.mask_pairs = [(n, f"{n}_mask") for n in self.arg_names if f"{n}_mask" in self.arg_names]
         try:
             bparams = list(inspect.signature(cls.build).parameters.values())[1:]
         except (TypeError, ValueError):
@@ -771,17 +772,15 @@ class Layer(Operation):
                     m = _get_mask(first_arg)
                     if m is not None:
                         kwargs["mask"] = m
-            if len(plan.arg_names) > 1:
-                bound = None
-                for nm in plan.arg_names[1:]:
-                    mk = f"{nm}_mask"
-                    if mk in plan.arg_names and kwargs.get(mk) is None:
-                        if bound is None:
-                            bound = dict(zip(plan.arg_names, args))
-                            bound.update(kwargs)
-                        src = bound.get(nm)
-                        if src is not None:
-                            m = _get_mask(src)
+            if plan.mask_pairs:
+                # an argument ``x`` with a companion ``x_mask`` gets the mask attached to its value, once the call has more
+                # than one tensor argument (with a single one only ``mask`` is filled, above)
+                bound = dict(zip(plan.arg_names, args))
+                bound.update(kwargs)
+                if sum(1 for v in bound.values() if isinstance(v, (torch.Tensor, KerasTensor))) > 1:
+                    for nm, mk in plan.mask_pairs:
+                        if bound.get(mk) is None and bound.get(nm) is not None:
+                            m = _get_mask(bound[nm])
                             if m is not None:
                                 kwargs[mk] = m
 
@@ -833,8 +832,9 @@ class Layer(Operation):
                 if prev is not None or not _is_default(type(self), "compute_mask"):
                     mask_arg = kwargs.get("mask", prev) if plan.has_mask else prev
                     self._set_output_mask(first_arg, outputs, mask_arg)
-            elif first_arg is not None and _any_mask(first_arg) and not symbolic:
-                pass  # mask consumed: outputs carry none
+            elif first_arg is not None and _any_mask(first_arg):
+                warnings.warn(f"Layer '{self.name}' (of type {self.__class__.__name__}) was passed an input with a mask attached to it. However, this layer "
+                              "does not support masking and will therefore destroy the mask information. Downstream layers will not see the mask.")
             return outputs
         finally:
             ctx.training = prev_training if not entered else None

@@ -18,8 +18,9 @@ from keras_b200.saving import serialization_lib
 
 
 class DropoutRNNCell:
-    """Mixin giving a cell one input-dropout and one recurrent-dropout mask per sequence
-    (keras/src/layers/rnn/dropout_rnn_cell.py)."""
+    """Mixin giving a cell its input-dropout and recurrent-dropout masks, drawn once per sequence and reused at every step
+    (keras/src/layers/rnn/dropout_rnn_cell.py).  A cell that sets ``dropout_mask_count`` gets that many independent masks, one per
+    gate, drawn one after the other from the cell's seed generator."""
 
     def _mask(self, attr, rate, like):
         if rate == 0:
@@ -28,7 +29,12 @@ class DropoutRNNCell:
         if m is None:
             from keras_b200 import random
 
-            m = random.dropout(ops.ones_like(like), rate=rate, seed=self.seed_generator)
+            count = getattr(self, "dropout_mask_count", None)
+            ones = ops.ones_like(like)
+            if count is None:
+                m = random.dropout(ones, rate=rate, seed=self.seed_generator)
+            else:
+                m = [random.dropout(ones, rate=rate, seed=self.seed_generator) for _ in range(count)]
             object.__setattr__(self, attr, m)
         return m
 
@@ -43,6 +49,22 @@ class DropoutRNNCell:
 
     def reset_recurrent_dropout_mask(self):
         object.__setattr__(self, "_recurrent_dropout_mask", None)
+
+
+def _gate_matmul(x, masks, weight, gates):
+    """``x @ weight`` where gate ``g`` (a block of columns of ``weight``) sees ``x * masks[g]``."""
+    if masks is None:
+        return ops.matmul(x, weight)
+    w = weight.value if hasattr(weight, "value") else weight
+    u = w.shape[1] // gates
+    return ops.concatenate([ops.matmul(x * masks[g], w[:, g * u:(g + 1) * u]) for g in range(gates)], axis=-1)
+
+
+def _use_gate_masks(cell, implementation):
+    """Recurrent dropout forces the per-gate formulation, which draws one mask per gate (keras/src/layers/rnn/lstm.py:136-139)."""
+    cell.implementation = 1 if cell.recurrent_dropout != 0.0 else implementation
+    if cell.implementation == 1:
+        cell.dropout_mask_count = cell.GATES
 
 
 class _BaseCell(Layer, DropoutRNNCell):
@@ -149,7 +171,7 @@ class LSTMCell(_BaseCell):
                          recurrent_dropout, seed, **kwargs)
         self.recurrent_activation = activations.get(recurrent_activation)
         self.unit_forget_bias = unit_forget_bias
-        self.implementation = implementation
+        _use_gate_masks(self, implementation)
         self.state_size = [units, units]
 
     def _bias_init(self):
@@ -173,11 +195,14 @@ class LSTMCell(_BaseCell):
 
     def call(self, sequence, states, training=False):
         h_prev, c_prev = states[0], states[1]
-        if training and self.dropout > 0.0:
-            sequence = sequence * self.get_dropout_mask(sequence)
-        if training and self.recurrent_dropout > 0.0:
-            h_prev = h_prev * self.get_recurrent_dropout_mask(h_prev)
-        z = ops.matmul(sequence, self.kernel) + ops.matmul(h_prev, self.recurrent_kernel)
+        dp = self.get_dropout_mask(sequence) if training and 0.0 < self.dropout < 1.0 else None
+        if self.implementation == 1:
+            rdp = self.get_recurrent_dropout_mask(h_prev) if training and 0.0 < self.recurrent_dropout < 1.0 else None
+            z = _gate_matmul(sequence, dp, self.kernel, 4) + _gate_matmul(h_prev, rdp, self.recurrent_kernel, 4)
+        else:
+            if dp is not None:
+                sequence = sequence * dp
+            z = ops.matmul(sequence, self.kernel) + ops.matmul(h_prev, self.recurrent_kernel)
         if self.bias is not None:
             z = ops.add(z, self.bias)
         h, c = self.gates(z, c_prev)
@@ -206,7 +231,7 @@ class GRUCell(_BaseCell):
                          recurrent_dropout, seed, **kwargs)
         self.recurrent_activation = activations.get(recurrent_activation)
         self.reset_after = reset_after
-        self.implementation = implementation
+        _use_gate_masks(self, implementation)
 
     def _bias_shape(self):
         return (2, 3 * self.units) if self.reset_after else (3 * self.units,)
@@ -230,6 +255,28 @@ class GRUCell(_BaseCell):
             hh = self.activation(xz[:, 2 * u:] + ops.matmul(r * h_prev, rk[:, 2 * u:]))
         return z * h_prev + (1 - z) * hh
 
+    def _step_with_gate_masks(self, xz, h_prev, recurrent_bias, masks):
+        """The per-gate formulation: each gate sees the previous state under its own recurrent-dropout mask; the state carried
+        over by the update gate is the unmasked one (keras/src/layers/rnn/gru.py:196-254)."""
+        u = self.units
+        rk = self.recurrent_kernel
+        rk = rk.value if hasattr(rk, "value") else rk
+        hz, hr, hh_in = (h_prev * m for m in masks) if masks is not None else (h_prev, h_prev, h_prev)
+        rz, rr = ops.matmul(hz, rk[:, :u]), ops.matmul(hr, rk[:, u:2 * u])
+        if recurrent_bias is not None:
+            rz, rr = rz + recurrent_bias[:u], rr + recurrent_bias[u:2 * u]
+        z = self.recurrent_activation(xz[:, :u] + rz)
+        r = self.recurrent_activation(xz[:, u:2 * u] + rr)
+        if self.reset_after:
+            rh = ops.matmul(hh_in, rk[:, 2 * u:])
+            if recurrent_bias is not None:
+                rh = rh + recurrent_bias[2 * u:]
+            rh = r * rh
+        else:
+            rh = ops.matmul(r * hh_in, rk[:, 2 * u:])
+        hh = self.activation(xz[:, 2 * u:] + rh)
+        return z * h_prev + (1 - z) * hh
+
     def _split_bias(self):
         if self.bias is None:
             return None, None
@@ -240,15 +287,19 @@ class GRUCell(_BaseCell):
 
     def call(self, sequence, states, training=False):
         h_prev = states[0] if isinstance(states, (list, tuple)) else states
-        if training and self.dropout > 0.0:
-            sequence = sequence * self.get_dropout_mask(sequence)
-        if training and self.recurrent_dropout > 0.0:
-            h_prev = h_prev * self.get_recurrent_dropout_mask(h_prev)
+        dp = self.get_dropout_mask(sequence) if training and 0.0 < self.dropout < 1.0 else None
         ib, rb = self._split_bias()
-        xz = ops.matmul(sequence, self.kernel)
-        if ib is not None:
-            xz = xz + ib
-        h = self.step_from_projection(xz, h_prev, rb)
+        if self.implementation == 1:
+            rdp = self.get_recurrent_dropout_mask(h_prev) if training and 0.0 < self.recurrent_dropout < 1.0 else None
+            xz = _gate_matmul(sequence, dp, self.kernel, 3)
+            if ib is not None:
+                xz = xz + ib
+            h = self._step_with_gate_masks(xz, h_prev, rb, rdp)
+        else:
+            xz = ops.matmul(sequence * dp if dp is not None else sequence, self.kernel)
+            if ib is not None:
+                xz = xz + ib
+            h = self.step_from_projection(xz, h_prev, rb)
         new_state = [h] if isinstance(states, (list, tuple)) else h
         return h, new_state
 
@@ -345,7 +396,9 @@ class RNN(Layer):
         self.cell = cell
         self.return_sequences, self.return_state, self.go_backwards = return_sequences, return_state, go_backwards
         self.stateful, self.unroll = stateful, unroll
-        self.supports_masking = True
+        # the mask steers the recurrence (through the ``mask`` argument) but is not attached to the output
+        # (keras/src/layers/rnn/rnn.py:212)
+        self.supports_masking = False
         self.input_spec = None
         self.states = None
         self._expected_batch_size = None
@@ -704,7 +757,9 @@ class Bidirectional(Layer):
         self.stateful = layer.stateful
         self.return_sequences = layer.return_sequences
         self.return_state = layer.return_state
-        self.supports_masking = True
+        # The mask reaches both directions through the ``mask`` argument, but the merged output carries none
+        # (keras/src/layers/rnn/bidirectional.py:153).
+        self.supports_masking = False
         self.input_spec = layer.input_spec
 
     def _verify_layer_config(self):
@@ -831,7 +886,7 @@ class TimeDistributed(Layer):
             raise ValueError(f"Please initialize `TimeDistributed` layer with a `keras.layers.Layer` instance. Received: {layer}")
         super().__init__(**kwargs)
         self.layer = layer
-        self.supports_masking = True
+        self.supports_masking = False  # keras/src/layers/rnn/time_distributed.py:54: the output carries no mask
 
     def _child_shape(self, input_shape):
         if not isinstance(input_shape, (tuple, list)) or len(input_shape) < 3:
@@ -907,6 +962,7 @@ class ConvLSTMCell(Layer, DropoutRNNCell):
         self.kernel_constraint = constraints.get(kernel_constraint)
         self.recurrent_constraint = constraints.get(recurrent_constraint)
         self.bias_constraint = constraints.get(bias_constraint)
+        self.dropout_mask_count = 4
         self.dropout = min(1.0, max(0.0, dropout))
         self.recurrent_dropout = min(1.0, max(0.0, recurrent_dropout))
         self.input_spec = InputSpec(ndim=rank + 2)
@@ -946,18 +1002,25 @@ class ConvLSTMCell(Layer, DropoutRNNCell):
 
     def call(self, inputs, states, training=False):
         h_prev, c_prev = states[0], states[1]
-        if training and self.dropout > 0.0:
-            inputs = inputs * self.get_dropout_mask(inputs)
-        if training and self.recurrent_dropout > 0.0:
-            h_prev = h_prev * self.get_recurrent_dropout_mask(h_prev)
-        x = ops.conv(inputs, self.kernel, self.strides, padding=self.padding, data_format=self.data_format, dilation_rate=self.dilation_rate)
+        dp = self.get_dropout_mask(inputs) if training and 0.0 < self.dropout < 1.0 else None
+        rdp = self.get_recurrent_dropout_mask(h_prev) if training and 0.0 < self.recurrent_dropout < 1.0 else None
+        caxis = -1 if self.data_format == "channels_last" else 1
+
+        def gate_conv(x, masks, kernel, **kw):
+            # one mask per gate (keras/src/layers/rnn/conv_lstm.py:244-266): gate g convolves x * masks[g] with its block of filters
+            if masks is None:
+                return ops.conv(x, kernel, **kw)
+            k = kernel.value if hasattr(kernel, "value") else kernel
+            f = self.filters
+            return ops.concatenate([ops.conv(x * masks[g], k[..., g * f:(g + 1) * f], **kw) for g in range(4)], axis=caxis)
+
+        x = gate_conv(inputs, dp, self.kernel, strides=self.strides, padding=self.padding, data_format=self.data_format, dilation_rate=self.dilation_rate)
         if self.bias is not None:
             shape = (1,) * (self.rank + 1) + (self.filters * 4,) if self.data_format == "channels_last" else (1, self.filters * 4) + (1,) * self.rank
             x = x + ops.reshape(self.bias, shape)
-        hc = ops.conv(h_prev, self.recurrent_kernel, 1, padding="same", data_format=self.data_format)
+        hc = gate_conv(h_prev, rdp, self.recurrent_kernel, strides=1, padding="same", data_format=self.data_format)
         z = x + hc
-        axis = -1 if self.data_format == "channels_last" else 1
-        zi, zf, zc, zo = ops.split(z, 4, axis=axis)
+        zi, zf, zc, zo = ops.split(z, 4, axis=caxis)
         i = self.recurrent_activation(zi)
         f = self.recurrent_activation(zf)
         c = f * c_prev + i * self.activation(zc)

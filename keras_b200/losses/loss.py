@@ -131,9 +131,10 @@ def apply_mask(sample_weight, mask, dtype, reduction):
         return sample_weight
     mask = mask.to(dtype)
     if reduction in ("mean", "sum_over_batch_size"):
-        total = float(mask.numel())
+        # valid entries weigh total/valid, so that the mean over all entries is the mean over the valid ones; no valid entry: 0
         valid = torch.sum(mask)
-        mask = mask * (total / (valid + config.epsilon()))
+        weight = torch.where(valid == 0, torch.zeros_like(valid), float(mask.numel()) / valid)
+        mask = torch.where(mask.to(torch.bool), weight, torch.zeros_like(weight))
     if sample_weight is not None:
         sample_weight = sample_weight.to(dtype)
         mask, sample_weight = squeeze_or_expand_to_same_rank(mask, sample_weight)

@@ -97,8 +97,10 @@ class MeanMetricWrapper(Mean):
     def update_state(self, y_true, y_pred, sample_weight=None):
         mask = getattr(y_pred, "_keras_mask", None)
         values = self._fn(y_true, y_pred, **self._fn_kwargs)
-        if sample_weight is not None and mask is not None:
-            sample_weight = losses.loss.apply_mask(convert_to_tensor(sample_weight), mask, dtype=to_torch_dtype(self.dtype), reduction="sum")
+        if mask is not None:
+            # masked entries weigh nothing, with or without sample weights (keras/src/metrics/reduction_metrics.py:201-206)
+            weights = convert_to_tensor(sample_weight) if sample_weight is not None else None
+            sample_weight = losses.loss.apply_mask(weights, convert_to_tensor(mask), dtype=to_torch_dtype(self.dtype), reduction="sum")
         return super().update_state(values, sample_weight=sample_weight)
 
     def get_config(self):

@@ -711,6 +711,10 @@ def dot_product_attention(query, key, value, bias=None, mask=None, scale=None, i
     if bias is not None:
         b = _t(bias).to(d)
         attn_mask = b if attn_mask is None else b + _attention_mask_bias(attn_mask, d)
+    elif attn_mask is not None:
+        # a large finite negative instead of -inf: a row with every position masked attends uniformly instead of producing
+        # zeros or NaN (keras/src/backend/torch/nn.py:1539)
+        attn_mask = _attention_mask_bias(attn_mask, d)
     out = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=attn_mask, is_causal=is_causal and attn_mask is None, scale=scale, enable_gqa=(K != N))
     return out.transpose(1, 2)
 
