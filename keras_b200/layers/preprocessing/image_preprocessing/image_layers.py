@@ -207,9 +207,11 @@ class RandomCrop(_CropBase):
 
     def get_random_transformation(self, data, training=True, seed=None):
         n, h, w = self._batch_hw(self._images_of(data))
-        if training and h >= self.height and w >= self.width:
-            top = (self._uniform((n,), seed=seed) * (h - self.height + 1)).floor().long().clamp(max=h - self.height)
-            left = (self._uniform((n,), seed=seed) * (w - self.width + 1)).floor().long().clamp(max=w - self.width)
+        if training and h > self.height and w > self.width:
+            # one window for the whole batch, its corner drawn as two scalars
+            # (keras/src/layers/preprocessing/image_preprocessing/random_crop.py:97-116)
+            top = self._uniform((), 0.0, float(h - self.height + 1), seed=seed).to(torch.int32).long().clamp(max=h - self.height).cpu().expand(n)
+            left = self._uniform((), 0.0, float(w - self.width + 1), seed=seed).to(torch.int32).long().clamp(max=w - self.width).cpu().expand(n)
         else:
             top = torch.full((n,), max((h - self.height) // 2, 0), dtype=torch.long)
             left = torch.full((n,), max((w - self.width) // 2, 0), dtype=torch.long)
@@ -263,7 +265,7 @@ class RandomFlip(_Base):
         images = self._images_of(data)
         n, h, w = self._batch_hw(images)
         flips = self._uniform((n,), seed=seed) <= 0.5
-        flips_v = self._uniform((n,), seed=seed) <= 0.5 if self.mode == HORIZONTAL_AND_VERTICAL else flips
+        flips_v = flips  # one draw decides both directions (keras/src/layers/preprocessing/image_preprocessing/random_flip.py:79-82)
         return {"flips": flips, "flips_v": flips_v, "input_shape": (h, w)}
 
     def _flip(self, x, t):
@@ -439,19 +441,29 @@ class RandomShear(_AffineBase):
             if len(f) != 2:
                 raise ValueError(f"`{name}` must be a pair of numbers. Received: {f}")
             lo, hi = sorted(f)
+            if lo < 0 or hi > 1:
+                raise ValueError(f"`{name}` must be in the range [0, 1]. Received: {f}")
         else:
-            lo, hi = 0.0, abs(f)
-        if lo < 0 or hi > 1:
-            raise ValueError(f"`{name}` must be in the range [0, 1]. Received: {f}")
+            if f < 0 or f > 1:
+                raise ValueError(f"`{name}` must be in the range [0, 1]. Received: {f}")
+            lo, hi = -abs(f), abs(f)  # a single number draws from (-f, f)
         return lo, hi
 
-    def _params(self, n, h, w, seed):
-        def draw(lo, hi):
-            mag = self._uniform((n,), lo, hi, seed=seed).cpu()
-            sign = torch.where(self._uniform((n,), seed=seed).cpu() > 0.5, 1.0, -1.0)
-            return torch.rad2deg(torch.atan(mag * sign))
-
-        return {"shx": draw(*self.x_factor), "shy": draw(*self.y_factor)}
+    def get_random_transformation(self, data, training=True, seed=None):
+        """Output pixel (x, y) reads input pixel (x + sx*y, sy*x + y): a shear about the top-left corner, with one random sign for
+        both factors of an image (keras/src/layers/preprocessing/image_preprocessing/random_shear.py:141-225)."""
+        if not training:
+            return None
+        n, h, w = self._batch_hw(self._images_of(data))
+        sign = torch.where(self._uniform((n, 1), seed=seed).cpu() > 0.5, -1.0, 1.0)
+        shy = self._uniform((n, 1), self.y_factor[0], self.y_factor[1], seed=seed).cpu()
+        shx = self._uniform((n, 1), self.x_factor[0], self.x_factor[1], seed=seed).cpu()
+        factor = torch.cat([shx, shy], dim=1) * sign
+        sx, sy = factor[:, 0], factor[:, 1]
+        det = 1.0 - sx * sy
+        z = torch.zeros(n)
+        forward = (1.0 / det, -sx / det, z, -sy / det, 1.0 / det, z)  # the inverse of the read map
+        return {"forward": forward, "input_shape": (h, w), "shear_factor": factor}
 
     def get_config(self):
         return {**super().get_config(), "x_factor": self.x_factor, "y_factor": self.y_factor, **self._sampling_config()}
@@ -538,16 +550,19 @@ class RandomElasticTransform(_Base):
         if not training:
             return None
         n, _, _ = self._batch_hw(self._images_of(data))
-        apply = self._uniform((1,), seed=seed).cpu() < self._uniform((1,), self.factor[0], self.factor[1], seed=seed).cpu()
-        alpha = self._uniform((1,), self.scale[0], self.scale[1], seed=seed).cpu() * 20.0
-        return {"apply": bool(apply), "alpha": float(alpha)}
+        # per image: a probability, then a threshold; one distortion factor for the batch
+        # (keras/src/layers/preprocessing/image_preprocessing/random_elastic_transform.py:170-260)
+        probability = self._uniform((n,), self.factor[0], self.factor[1], seed=seed)
+        apply = self._uniform((n,), seed=seed) < probability
+        distortion = float(self._uniform((), self.scale[0], self.scale[1], seed=seed))
+        return {"apply_transform": apply, "distortion_factor": distortion, "seed": seed if seed is not None else self._get_seed_generator()}
 
     def _apply(self, images, t):
-        if not t["apply"]:
-            return images
-        out = image_ops.elastic_transform(images, alpha=t["alpha"], sigma=5.0, interpolation=self.interpolation, fill_mode=self.fill_mode,
-                                          fill_value=self.fill_value, seed=self._get_seed_generator(), data_format=self.data_format)
-        return self._clip(out)
+        _, h, w = self._batch_hw(images)
+        alpha, sigma = max(h, w) * 0.1 * t["distortion_factor"], min(h, w) * 0.05 * t["distortion_factor"]
+        out = image_ops.elastic_transform(images, alpha=alpha, sigma=sigma, interpolation=self.interpolation, fill_mode=self.fill_mode,
+                                          fill_value=self.fill_value, seed=t["seed"], data_format=self.data_format)
+        return self._clip(torch.where(self._per_sample(t["apply_transform"].to(images.device), images.ndim), out, images))
 
     def get_config(self):
         return {**super().get_config(), "factor": self.factor, "scale": self.scale, "interpolation": self.interpolation,
@@ -589,14 +604,9 @@ class RandomContrast(_Base):
         self._seeded(seed)
 
     def _set_factor(self, factor):
-        if isinstance(factor, (tuple, list)):
-            lo, hi = factor
-        else:
-            lo = hi = factor
-        if lo < 0.0 or hi < 0.0 or lo > 1.0:
-            raise ValueError(f"`factor` argument cannot have negative values or values greater than 1.Received: factor={factor}")
-        self.factor = (lo, hi)
-        self.lower, self.upper = lo, hi
+        # the shared rule: a single number f means the range (max(-f, 0), f) = (0, f), so the contrast is only ever raised
+        super()._set_factor(factor)
+        self.lower, self.upper = self.factor
 
     def get_random_transformation(self, data, training=True, seed=None):
         if not training:
@@ -632,6 +642,12 @@ class _HSVBase(_Base):
 
 @keras_export("keras.layers.RandomSaturation")
 class RandomSaturation(_HSVBase):
+    """The saturation channel of the images, as they come (no rescaling to 0..1), is multiplied by ``f / (1 - f)`` and clipped to
+    ``value_range``; a single number ``f`` draws from ``(-f, f)``
+    (keras/src/layers/preprocessing/image_preprocessing/random_saturation.py)."""
+
+    _FACTOR_BOUNDS = (-1, 1)
+
     def __init__(self, factor, value_range=(0, 255), data_format=None, seed=None, **kwargs):
         super().__init__(factor=factor, data_format=data_format, **kwargs)
         self.value_range = _check_value_range(value_range)
@@ -646,9 +662,9 @@ class RandomSaturation(_HSVBase):
         return {"factor": f / (1 - f + 1e-7)}
 
     def _apply(self, images, t):
-        (h, s, v), ax = self._channels(self._hsv(images))
-        s = (s * self._per_sample(t["factor"].to(images.device).to(s.dtype))).clamp(0, 1)
-        return self._rgb(torch.cat([h, s, v], dim=ax), images.dtype)
+        (h, s, v), ax = self._channels(image_ops.rgb_to_hsv(images, data_format=self.data_format))
+        s = (s * self._per_sample(t["factor"].to(images.device).to(s.dtype))).clamp(self.value_range[0], self.value_range[1])
+        return image_ops.hsv_to_rgb(torch.cat([h, s, v], dim=ax), data_format=self.data_format).to(images.dtype)
 
     def get_config(self):
         return {**super().get_config(), "factor": self.factor, "value_range": self.value_range, "seed": self.seed}
@@ -667,11 +683,14 @@ class RandomHue(_HSVBase):
         images = self._images_of(data)
         n = images.shape[0] if len(images.shape) == 4 else 1
         sign = torch.where(self._uniform((n,), seed=seed) > 0.5, -1.0, 1.0)
-        return {"factor": self._uniform((n,), self.factor[0], self.factor[1], seed=seed) * sign}
+        # a factor of 1 turns the hue by half the circle, either way (random_hue.py: ``invert * factor * 0.5``)
+        return {"factor": self._uniform((n,), self.factor[0], self.factor[1], seed=seed) * sign * 0.5}
 
     def _apply(self, images, t):
         (h, s, v), ax = self._channels(self._hsv(images))
-        h = torch.remainder(h + self._per_sample(t["factor"].to(images.device).to(h.dtype)), 1.0)
+        h = h + self._per_sample(t["factor"].to(images.device).to(h.dtype))
+        h = torch.where(h > 1.0, h - 1.0, h)
+        h = torch.where(h < 0.0, h + 1.0, h)
         return self._rgb(torch.cat([h, s, v], dim=ax), images.dtype)
 
     def get_config(self):
@@ -680,7 +699,7 @@ class RandomHue(_HSVBase):
 
 @keras_export("keras.layers.RandomColorDegeneration")
 class RandomColorDegeneration(_Base):
-    _FACTOR_BOUNDS = (0, 1)
+    _FACTOR_BOUNDS = (-1, 1)  # the shared rule: a single number f draws from (-f, f)
 
     def __init__(self, factor, value_range=(0, 255), data_format=None, seed=None, **kwargs):
         super().__init__(factor=factor, data_format=data_format, **kwargs)
@@ -749,7 +768,8 @@ class RandomInvert(_Base):
             return None
         images = self._images_of(data)
         n = images.shape[0] if len(images.shape) == 4 else 1
-        return self._uniform((n,), seed=seed) < self._uniform((n,), self.factor[0], self.factor[1], seed=seed)
+        probability = self._uniform((n,), self.factor[0], self.factor[1], seed=seed)  # drawn first, then the threshold
+        return self._uniform((n,), seed=seed) < probability
 
     def _apply(self, images, t):
         inv = self.value_range[1] + self.value_range[0] - images
@@ -761,24 +781,35 @@ class RandomInvert(_Base):
 
 @keras_export("keras.layers.RandomPosterization")
 class RandomPosterization(_Base):
+    """Keeps the top ``factor`` bits of every 8-bit channel value.  ``factor`` is a number or a pair in 1..8; a single number f
+    means the range (1, f), and a range draws one integer per image, upper bound excluded
+    (keras/src/layers/preprocessing/image_preprocessing/random_posterization.py)."""
+
     _USE_BASE_FACTOR = False
+    _FACTOR_BOUNDS = (1, 8)
     _MAX_FACTOR = 8
 
     def __init__(self, factor, value_range=(0, 255), data_format=None, seed=None, **kwargs):
         super().__init__(data_format=data_format, **kwargs)
-        if not isinstance(factor, int) or not 1 <= factor <= self._MAX_FACTOR:
-            raise ValueError(f"`factor` must be an integer in the range [1, {self._MAX_FACTOR}]. Received: factor={factor}")
-        self.factor = factor
-        self.value_range = _check_value_range(value_range)
+        self._set_factor(factor)
+        self.value_range = tuple(sorted(_check_value_range(value_range)))
         self._seeded(seed)
 
     def get_random_transformation(self, data, training=True, seed=None):
-        return None
+        images = self._images_of(data)
+        n = images.shape[0] if len(images.shape) == 4 else 1
+        if self.factor[0] != self.factor[1]:
+            from keras_b200 import random
+
+            bits = random.randint((n,), minval=self.factor[0], maxval=self.factor[1], seed=seed if seed is not None else self._get_seed_generator(), dtype="uint8")
+        else:
+            bits = torch.full((n,), self.factor[0], dtype=torch.uint8)
+        return {"shift_factor": self._MAX_FACTOR - bits}
 
     def _apply(self, images, t):
-        x = self._transform_value_range(images, self.value_range, (0, 255)).round().clamp(0, 255).to(torch.int32)
-        shift = self._MAX_FACTOR - self.factor
-        x = (x >> shift) << shift
+        x = self._transform_value_range(images, self.value_range, (0, 255)).to(torch.uint8)
+        shift = self._per_sample(t["shift_factor"].to(images.device))
+        x = torch.bitwise_left_shift(torch.bitwise_right_shift(x, shift), shift)
         return self._transform_value_range(x.to(images.dtype), (0, 255), self.value_range).to(images.dtype)
 
     def get_config(self):
@@ -819,11 +850,13 @@ class Solarization(_Base):
                 "threshold_factor": self.threshold_factor, "seed": self.seed}
 
 
-def _depthwise_filter(x_bchw, kernel2d):
+def _depthwise_filter(x_bchw, kernel2d, mode="replicate"):
     c = x_bchw.shape[1]
     k = kernel2d.to(x_bchw.dtype).to(x_bchw.device).expand(c, 1, *kernel2d.shape[-2:])
     ph, pw = kernel2d.shape[-2] // 2, kernel2d.shape[-1] // 2
-    return F.conv2d(F.pad(x_bchw, (pw, pw, ph, ph), mode="replicate"), k, groups=c)
+    if mode == "zeros":
+        return F.conv2d(x_bchw, k, padding=(ph, pw), groups=c)
+    return F.conv2d(F.pad(x_bchw, (pw, pw, ph, ph), mode=mode), k, groups=c)
 
 
 @keras_export("keras.layers.RandomSharpness")
@@ -845,7 +878,7 @@ class RandomSharpness(_Base):
     def _apply(self, images, t):
         x = self._to_bchw(images)
         kernel = torch.tensor([[1.0, 1.0, 1.0], [1.0, 5.0, 1.0], [1.0, 1.0, 1.0]]) / 13.0
-        blurred = _depthwise_filter(x, kernel)
+        blurred = _depthwise_filter(x, kernel, mode="zeros")  # "same" padding with zeros, as the reference's depthwise convolution
         a = t.to(x.device).to(x.dtype).reshape(-1, 1, 1, 1)
         return self._clip(self._from_bchw(blurred + a * (x - blurred)))
 
@@ -872,8 +905,9 @@ class RandomGaussianBlur(_Base):
             return None
         images = self._images_of(data)
         n = images.shape[0] if len(images.shape) == 4 else 1
-        apply = self._uniform((n,), seed=seed) < self._uniform((n,), self.factor[0], self.factor[1], seed=seed)
-        sigma = self._uniform((2,), self.sigma[0], self.sigma[1], seed=seed).clamp(min=1e-3)
+        probability = self._uniform((n,), self.factor[0], self.factor[1], seed=seed)  # drawn first, then the threshold
+        apply = self._uniform((n,), seed=seed) < probability
+        sigma = self._uniform((2,), self.sigma[0], self.sigma[1], seed=seed) + 1e-6
         return {"apply": apply, "sigma": (float(sigma[0]), float(sigma[1]))}
 
     def _apply(self, images, t):

@@ -227,3 +227,35 @@ def test_clahe_matches_reference(shape, grid):
     expected = rk.layers.ContrastLimitedAdaptiveHistogramEqualization(value_range=(0, 1), clip_limit=2.0, tile_grid_size=grid)(torch.tensor(unit))
     got = keras.layers.ContrastLimitedAdaptiveHistogramEqualization(value_range=(0, 1), clip_limit=2.0, tile_grid_size=grid)(torch.tensor(unit))
     oracle.assert_same(got, expected, "CLAHE 0..1", rtol=1e-5, atol=1e-5)
+
+
+AUGMENTATIONS = [
+    ("RandomFlip", dict(seed=1)), ("RandomFlip", dict(mode="vertical", seed=2)),
+    ("RandomRotation", dict(factor=0.2, seed=1)), ("RandomRotation", dict(factor=(-0.1, 0.3), fill_mode="constant", interpolation="nearest", seed=3)),
+    ("RandomZoom", dict(height_factor=0.3, seed=1)), ("RandomZoom", dict(height_factor=(-0.2, 0.3), width_factor=0.2, fill_mode="nearest", seed=1)),
+    ("RandomTranslation", dict(height_factor=0.2, width_factor=0.3, seed=1)),
+    ("RandomBrightness", dict(factor=0.3, seed=1)), ("RandomContrast", dict(factor=0.4, seed=1)), ("RandomCrop", dict(height=6, width=5, seed=1)),
+    ("RandomHue", dict(factor=0.5, value_range=(0, 255), seed=1)), ("RandomSaturation", dict(factor=0.5, value_range=(0, 255), seed=1)),
+    ("RandomGrayscale", dict(factor=0.7, seed=1)), ("RandomSharpness", dict(factor=0.5, value_range=(0, 255), seed=1)),
+    ("RandomShear", dict(x_factor=0.3, y_factor=0.2, seed=1)), ("RandomPosterization", dict(factor=3, value_range=(0, 255), seed=1)),
+    ("RandomColorDegeneration", dict(factor=0.6, value_range=(0, 255), seed=1)),
+    ("RandomGaussianBlur", dict(factor=1.0, kernel_size=3, sigma=1.0, value_range=(0, 255), seed=1)),
+    ("RandomInvert", dict(factor=0.7, value_range=(0, 255), seed=1)),  # RandomElasticTransform: the reference's displacement field ignores the seed
+    ("Solarization", dict(addition_factor=0.3, threshold_factor=0.4, value_range=(0, 255), seed=1)), ("AutoContrast", dict(value_range=(0, 255))),
+    ("MixUp", dict(alpha=0.3, seed=1)), ("GaussianNoise", dict(stddev=0.3, seed=1)), ("GaussianDropout", dict(rate=0.3, seed=1)),
+    ("AlphaDropout", dict(rate=0.3, seed=1)), ("SpatialDropout2D", dict(rate=0.4, seed=1)), ("Dropout", dict(rate=0.4, noise_shape=(2, 1, 1, 3), seed=1)),
+]
+
+
+@pytest.mark.parametrize("spec", AUGMENTATIONS, ids=[f"{n}_{i}" for i, (n, _) in enumerate(AUGMENTATIONS)])
+def test_seeded_augmentation_in_training_matches_reference(spec):
+    """Same seed, same picture: the draws come in the reference's order and mean what they mean there."""
+    rk = oracle.ref()
+    name, kwargs = spec
+    if not hasattr(rk.layers, name):
+        pytest.skip("layer absent from this reference version")
+    images = (np.random.default_rng(0).random((2, 12, 10, 3)) * 255).astype("float32")
+    theirs, ours = getattr(rk.layers, name)(**kwargs), getattr(keras.layers, name)(**kwargs)
+    for call in range(2):
+        expected = theirs(torch.tensor(images), training=True)
+        oracle.assert_same(ours(torch.tensor(images), training=True), expected, f"{name}, call {call}", rtol=1e-3, atol=1e-2)
