@@ -1185,23 +1185,29 @@ class CutMix(_Base):
             return None
         from keras_b200 import random
 
-        n, h, w = self._batch_hw(self._images_of(data))
+        images = self._images_of(data)
+        if len(images.shape) == 3:
+            return None
+        n, h, w = self._batch_hw(images)
         gen = seed if seed is not None else self._get_seed_generator()
-        perm = random.shuffle(torch.arange(n), seed=gen).cpu()
-        mix = self._uniform((n,), self.factor[0], self.factor[1], seed=seed)
+        # The draws, in the reference's order (keras/src/layers/preprocessing/image_preprocessing/cut_mix.py:60-183): a shared
+        # Beta parameter, one Beta(alpha, alpha) weight per image, the window's left edge, its top edge, then the partner order.
+        alpha = self._uniform((), self.factor[0], self.factor[1], seed=gen) + 1e-6
+        mix = random.beta((n,), alpha, alpha, seed=gen).cpu()
         ratio = torch.sqrt(1.0 - mix)
-        cy, cx = self._uniform((n,), 0, h, seed=seed), self._uniform((n,), 0, w, seed=seed)
-        bh, bw = ratio * h, ratio * w
-        y1, y2 = (cy - bh / 2).clamp(0, h).floor(), (cy + bh / 2).clamp(0, h).floor()
-        x1, x2 = (cx - bw / 2).clamp(0, w).floor(), (cx + bw / 2).clamp(0, w).floor()
+        bw, bh = ratio * w, ratio * h
+        x1 = self._uniform((n,), seed=gen).cpu() * (w - bw)
+        y1 = self._uniform((n,), seed=gen).cpu() * (h - bh)
+        x2, y2 = x1 + bw, y1 + bh
+        perm = random.shuffle(torch.arange(n, dtype=torch.int32), seed=gen).cpu().long()
         area = ((y2 - y1) * (x2 - x1)) / float(h * w)
         return {"permutation_order": perm, "box": (y1, y2, x1, x2), "mix_weight": 1.0 - area, "input_shape": (h, w)}
 
     def _mask(self, t, dev):
         h, w = t["input_shape"]
         y1, y2, x1, x2 = [v.to(dev).reshape(-1, 1, 1) for v in t["box"]]
-        ys = torch.arange(h, device=dev).reshape(1, h, 1)
-        xs = torch.arange(w, device=dev).reshape(1, 1, w)
+        ys = torch.arange(h, device=dev, dtype=torch.float32).reshape(1, h, 1)
+        xs = torch.arange(w, device=dev, dtype=torch.float32).reshape(1, 1, w)
         return ((ys >= y1) & (ys < y2) & (xs >= x1) & (xs < x2)).unsqueeze(self._channel_axis())
 
     def _apply(self, images, t):
@@ -1250,7 +1256,8 @@ class RandomColorJitter(_Base):
         if training:
             for lyr in (self.random_brightness, self.random_contrast, self.random_saturation, self.random_hue):
                 if lyr is not None:
-                    t = lyr.get_random_transformation(images, training=True)
+                    # all four adjustments draw from this layer's generator, one after the other
+                    t = lyr.get_random_transformation(images, training=True, seed=self._get_seed_generator())
                     images = lyr.transform_images(images, t, training=True)
         return images
 

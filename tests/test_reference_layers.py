@@ -242,7 +242,8 @@ AUGMENTATIONS = [
     ("RandomGaussianBlur", dict(factor=1.0, kernel_size=3, sigma=1.0, value_range=(0, 255), seed=1)),
     ("RandomInvert", dict(factor=0.7, value_range=(0, 255), seed=1)),  # RandomElasticTransform: the reference's displacement field ignores the seed
     ("Solarization", dict(addition_factor=0.3, threshold_factor=0.4, value_range=(0, 255), seed=1)), ("AutoContrast", dict(value_range=(0, 255))),
-    ("MixUp", dict(alpha=0.3, seed=1)), ("GaussianNoise", dict(stddev=0.3, seed=1)), ("GaussianDropout", dict(rate=0.3, seed=1)),
+    ("MixUp", dict(alpha=0.3, seed=1)), ("CutMix", dict(factor=0.8, seed=1)),
+    ("RandomColorJitter", dict(value_range=(0, 255), brightness_factor=0.2, contrast_factor=0.3, saturation_factor=0.4, hue_factor=0.1, seed=1)), ("GaussianNoise", dict(stddev=0.3, seed=1)), ("GaussianDropout", dict(rate=0.3, seed=1)),
     ("AlphaDropout", dict(rate=0.3, seed=1)), ("SpatialDropout2D", dict(rate=0.4, seed=1)), ("Dropout", dict(rate=0.4, noise_shape=(2, 1, 1, 3), seed=1)),
 ]
 
